@@ -1,0 +1,574 @@
+/*
+ * CPU oracle for the attention hot path.  TEST INFRASTRUCTURE ONLY.
+ *
+ * This file is a plain-C restatement of the reference's CPU algorithms for the
+ * attention path.  It exists to check the CUDA kernels and to serve as the timed
+ * CPU baseline of the benchmark; the shipped library never links, loads or calls
+ * it.  Only the test-suite, the smoke check and the benchmark's cpu-baseline /
+ * reference arm may use it.
+ *
+ * What is restated (paths are relative to the reference project root):
+ *   crates/rustorch-attention/src/cpu_forward.rs:142-169   validate()
+ *   crates/rustorch-attention/src/cpu_forward.rs:193-242   flash_forward_masked(): one task per (b,h)
+ *   crates/rustorch-attention/src/cpu_forward.rs:268-425   flash_forward_bh_blas(): tile loop
+ *   crates/rustorch-attention/src/cpu_forward.rs:702-763   naive_forward_masked()
+ *   crates/rustorch-attention/src/mask.rs:40-65            Mask::is_masked / validate
+ *   crates/rustorch-attention/src/online_softmax.rs:44-151 OnlineSoftmaxState, combine_tiles
+ *   crates/rustorch-nn/src/gqa.rs:94-270                   gqa_forward_f32 + decode_attn_row
+ *   crates/rustorch-nn/src/kv_cache.rs:77-112              KVLayerCache::append indexing
+ *   crates/rustorch-amp/src/dtypes.rs:10-24                bf16 conversion = round-to-nearest-even
+ *
+ * Third-party arithmetic: the reference's per-tile GEMMs are calls into the `gemm`
+ * crate 0.18.2 (cpu_forward.rs:487-507 and :564-584), whose source is not part of
+ * the reference tree.  They are plain f32 GEMMs (S = scale*Q*K^T, O += P*V); only
+ * the summation order is unspecified.  They are restated here as plain loop nests.
+ * The reference's own tests tie its tiled path to its in-tree scalar naive path at
+ * 1e-4, which is the gate this oracle is pinned with.
+ *
+ * Extensions beyond the reference (needed by the bf16 / varlen / decode workloads):
+ *   (1) log-sum-exp output per row, LSE = m + ln(l) in natural-log units of the scaled scores;
+ *   (2) causal AND padding masks at the same time, per-batch key-keep vectors, per-batch kv_len;
+ *   (3) `fix_leading_masked_tile`: a row whose first visited KV tile is fully masked turns
+ *       NaN in the reference's tiled path (exp(-inf - -inf)), while its naive path gives the
+ *       finite answer.  With the flag set the tiled path follows the naive semantics;
+ *   (4) decode over a [B, Hkv, max_seq, D] cache with per-sequence lengths, a KV range and LSE;
+ *   (5) merge of (O, LSE) partials (the algebra of combine_tiles applied to normalised partials).
+ *
+ * Parity status: pinned by the reference's known-answer tests and flash-vs-naive
+ * equivalence matrix (see tests/test_oracle_pins.py).  The reference is Rust and
+ * no Rust toolchain exists on the build or GPU machines, so the reference itself
+ * was never executed here.  Decode has no numeric golden vectors in the reference
+ * (only range / finiteness checks); its parity is pinned by the algorithm text.
+ */
+#include <math.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+#define ORC_OK 0
+#define ORC_ERR_ZERO_DIM -1
+#define ORC_ERR_MASK_LEN -4
+#define ORC_ERR_HEADS -5
+#define ORC_ERR_ALLOC -100
+
+static int g_threads = 0; /* 0 = OpenMP default (all cores) */
+
+void orc_set_threads(int n) { g_threads = n; }
+
+int orc_get_threads(void) {
+#ifdef _OPENMP
+    return g_threads > 0 ? g_threads : omp_get_max_threads();
+#else
+    return 1;
+#endif
+}
+
+/* ---------------------------------------------------------------- masks */
+
+/* mask.rs:26-46 extended: causal, per-key keep flags and kv_len may be combined. */
+typedef struct {
+    int causal;
+    const uint8_t* keep; /* NULL or `keep_len` flags, 0 = masked */
+    int64_t keep_len;
+    int64_t kv_len; /* < 0: unused; keys j >= kv_len are masked */
+} orc_mask;
+
+static inline int is_masked(const orc_mask* m, int64_t qi, int64_t kj) {
+    if (m->causal && kj > qi) return 1;                           /* mask.rs:43 */
+    if (m->keep && kj < m->keep_len && !m->keep[kj]) return 1;    /* mask.rs:44 */
+    if (m->kv_len >= 0 && kj >= m->kv_len) return 1;              /* extension (2) */
+    return 0;
+}
+
+static inline int mask_is_none(const orc_mask* m) {
+    return !m->causal && !m->keep && m->kv_len < 0;
+}
+
+/* ---------------------------------------------------------------- tile GEMMs */
+
+/* cpu_forward.rs:468-509: S[m x n] = alpha * Q[m x k] * K[n x k]^T, row-major, beta = 0. */
+static void sgemm_score_tile(int m, int n, int kd, float alpha, const float* q, int ldq,
+                             const float* k, int ldk, float* s, int lds) {
+    for (int r = 0; r < m; ++r) {
+        const float* qr = q + (size_t)r * ldq;
+        for (int c = 0; c < n; ++c) {
+            const float* kr = k + (size_t)c * ldk;
+            float acc = 0.0f;
+#pragma omp simd reduction(+ : acc)
+            for (int d = 0; d < kd; ++d) acc += qr[d] * kr[d];
+            s[(size_t)r * lds + c] = alpha * acc;
+        }
+    }
+}
+
+/* cpu_forward.rs:548-586: O[m x n] += P[m x k] * V[k x n], row-major, beta = 1. */
+static void sgemm_value_accumulate(int m, int n, int kd, const float* p, int ldp, const float* v,
+                                   int ldv, float* o, int ldo) {
+    for (int r = 0; r < m; ++r) {
+        float* orow = o + (size_t)r * ldo;
+        for (int j = 0; j < kd; ++j) {
+            const float w = p[(size_t)r * ldp + j];
+            const float* vr = v + (size_t)j * ldv;
+#pragma omp simd
+            for (int d = 0; d < n; ++d) orow[d] += w * vr[d];
+        }
+    }
+}
+
+/* ---------------------------------------------------------------- tiled forward */
+
+/* cpu_forward.rs:268-425 for one (b,h) slab.  Every KV tile is visited, masked or
+ * not, exactly like the reference.  `lse` may be NULL. */
+static int flash_forward_bh(const float* q, const float* k, const float* v, float* out, float* lse,
+                            int64_t seq, int dim, int br, int bc, float scale, const orc_mask* mask,
+                            int fix_leading_masked_tile) {
+    float* s_buf = (float*)malloc(sizeof(float) * (size_t)br * bc);
+    float* p_buf = (float*)malloc(sizeof(float) * (size_t)br * bc);
+    float* o_buf = (float*)malloc(sizeof(float) * (size_t)br * dim);
+    float* m_buf = (float*)malloc(sizeof(float) * (size_t)br);
+    float* l_buf = (float*)malloc(sizeof(float) * (size_t)br);
+    if (!s_buf || !p_buf || !o_buf || !m_buf || !l_buf) {
+        free(s_buf); free(p_buf); free(o_buf); free(m_buf); free(l_buf);
+        return ORC_ERR_ALLOC;
+    }
+    const int none = mask_is_none(mask);
+    for (int64_t qi = 0; qi < seq; qi += br) {
+        const int br_used = (int)((qi + br < seq ? qi + br : seq) - qi);
+        for (int r = 0; r < br_used; ++r) { /* :303-309 */
+            m_buf[r] = -INFINITY;
+            l_buf[r] = 0.0f;
+            for (int d = 0; d < dim; ++d) o_buf[(size_t)r * dim + d] = 0.0f;
+        }
+        for (int64_t kj = 0; kj < seq; kj += bc) { /* :312-403 */
+            const int bc_used = (int)((kj + bc < seq ? kj + bc : seq) - kj);
+            sgemm_score_tile(br_used, bc_used, dim, scale, q + (size_t)qi * dim, dim,
+                             k + (size_t)kj * dim, dim, s_buf, bc_used);
+            if (!none) { /* :342-352 */
+                for (int r = 0; r < br_used; ++r)
+                    for (int c = 0; c < bc_used; ++c)
+                        if (is_masked(mask, qi + r, kj + c)) s_buf[(size_t)r * bc_used + c] = -INFINITY;
+            }
+            for (int r = 0; r < br_used; ++r) { /* :355-386 */
+                const float* s_row = s_buf + (size_t)r * bc_used;
+                float m_tile = -INFINITY;
+                for (int c = 0; c < bc_used; ++c)
+                    if (s_row[c] > m_tile) m_tile = s_row[c];
+                const float m_prev = m_buf[r];
+                const float m_new = m_tile > m_prev ? m_tile : m_prev;
+                const float alpha = (m_prev == -INFINITY) ? 0.0f : expf(m_prev - m_new);
+                if (alpha != 1.0f) {
+                    l_buf[r] *= alpha;
+                    for (int d = 0; d < dim; ++d) o_buf[(size_t)r * dim + d] *= alpha;
+                }
+                float* p_row = p_buf + (size_t)r * bc_used;
+                float tile_l = 0.0f;
+                if (fix_leading_masked_tile && m_new == -INFINITY) {
+                    for (int c = 0; c < bc_used; ++c) p_row[c] = 0.0f;
+                } else {
+                    for (int c = 0; c < bc_used; ++c) {
+                        const float p = expf(s_row[c] - m_new);
+                        p_row[c] = p;
+                        tile_l += p;
+                    }
+                }
+                l_buf[r] += tile_l;
+                m_buf[r] = m_new;
+            }
+            sgemm_value_accumulate(br_used, dim, bc_used, p_buf, bc_used, v + (size_t)kj * dim, dim,
+                                   o_buf, dim);
+        }
+        for (int r = 0; r < br_used; ++r) { /* :406-421 */
+            float* dst = out + (size_t)(qi + r) * dim;
+            const float l = l_buf[r];
+            if (l > 0.0f && isfinite(l)) {
+                const float inv_l = 1.0f / l;
+                for (int d = 0; d < dim; ++d) dst[d] = o_buf[(size_t)r * dim + d] * inv_l;
+            } else {
+                for (int d = 0; d < dim; ++d) dst[d] = NAN;
+            }
+            if (lse) lse[qi + r] = (l > 0.0f) ? m_buf[r] + logf(l) : (l == 0.0f ? -INFINITY : NAN);
+        }
+    }
+    free(s_buf); free(p_buf); free(o_buf); free(m_buf); free(l_buf);
+    return ORC_OK;
+}
+
+/*
+ * Extended tiled forward over [B,H,N,D] buffers (cpu_forward.rs:193-242 plus the
+ * extensions listed in the header).
+ *   keep            NULL, or key-keep flags; batch b uses keep + b*keep_batch_stride
+ *                   (stride 0 = one vector shared by the whole batch, as in the reference)
+ *   kv_lens         NULL, or per-batch valid key counts
+ *   lse             NULL, or [B,H,N]
+ *   scale           <= 0 selects the reference's 1/sqrt(dim)
+ */
+int orc_flash_forward_ext(int64_t batch, int64_t heads, int64_t seq, int dim, int br, int bc,
+                          const float* q, const float* k, const float* v, int causal,
+                          const uint8_t* keep, int64_t keep_len, int64_t keep_batch_stride,
+                          const int32_t* kv_lens, float scale, int fix_leading_masked_tile,
+                          float* out, float* lse) {
+    if (dim == 0) return ORC_ERR_ZERO_DIM;              /* :148-150 */
+    if (keep && keep_len != seq) return ORC_ERR_MASK_LEN; /* mask.rs:54-62 */
+    if (seq == 0) return ORC_OK;                        /* :203-206 */
+    if (scale <= 0.0f) scale = 1.0f / sqrtf((float)dim); /* :208 */
+    const int64_t s_h = seq * dim;
+    const int64_t n_bh = batch * heads;
+    int rc = ORC_OK;
+#pragma omp parallel for schedule(dynamic, 1) num_threads(orc_get_threads())
+    for (int64_t bh = 0; bh < n_bh; ++bh) { /* :219-240, one task per (b,h) */
+        const int64_t b = bh / heads;
+        orc_mask m;
+        m.causal = causal;
+        m.keep = keep ? keep + b * keep_batch_stride : NULL;
+        m.keep_len = keep_len;
+        m.kv_len = kv_lens ? kv_lens[b] : -1;
+        int r = flash_forward_bh(q + bh * s_h, k + bh * s_h, v + bh * s_h, out + bh * s_h,
+                                 lse ? lse + bh * seq : NULL, seq, dim, br, bc, scale, &m,
+                                 fix_leading_masked_tile);
+        if (r != ORC_OK) {
+#pragma omp critical
+            rc = r;
+        }
+    }
+    return rc;
+}
+
+/* The reference API exactly: flash_forward_masked(shape, q, k, v, mask, out).
+ * mask_kind: 0 None, 1 Causal, 2 Padding(keep[keep_len]). */
+int orc_flash_forward_masked(int64_t batch, int64_t heads, int64_t seq, int dim, int br, int bc,
+                             const float* q, const float* k, const float* v, int mask_kind,
+                             const uint8_t* keep, int64_t keep_len, float* out) {
+    return orc_flash_forward_ext(batch, heads, seq, dim, br, bc, q, k, v, mask_kind == 1,
+                                 mask_kind == 2 ? keep : NULL, keep_len, 0, NULL, -1.0f, 0, out,
+                                 NULL);
+}
+
+/* cpu_forward.rs:702-763 with the same mask extensions and an optional LSE. Serial. */
+int orc_naive_forward_ext(int64_t batch, int64_t heads, int64_t seq, int dim, const float* q,
+                          const float* k, const float* v, int causal, const uint8_t* keep,
+                          int64_t keep_len, int64_t keep_batch_stride, const int32_t* kv_lens,
+                          float scale, float* out, float* lse) {
+    if (dim == 0) return ORC_ERR_ZERO_DIM;
+    if (keep && keep_len != seq) return ORC_ERR_MASK_LEN;
+    if (seq == 0) return ORC_OK;
+    if (scale <= 0.0f) scale = 1.0f / sqrtf((float)dim);
+    const int64_t s_h = seq * dim;
+    float* scores = (float*)malloc(sizeof(float) * (size_t)seq * seq);
+    if (!scores) return ORC_ERR_ALLOC;
+    for (int64_t b = 0; b < batch; ++b) {
+        orc_mask m;
+        m.causal = causal;
+        m.keep = keep ? keep + b * keep_batch_stride : NULL;
+        m.keep_len = keep_len;
+        m.kv_len = kv_lens ? kv_lens[b] : -1;
+        for (int64_t h = 0; h < heads; ++h) {
+            const int64_t base = (b * heads + h) * s_h;
+            for (int64_t i = 0; i < seq; ++i)
+                for (int64_t j = 0; j < seq; ++j) {
+                    if (is_masked(&m, i, j)) {
+                        scores[i * seq + j] = -INFINITY;
+                        continue;
+                    }
+                    float s = 0.0f;
+                    for (int d = 0; d < dim; ++d) s += q[base + i * dim + d] * k[base + j * dim + d];
+                    scores[i * seq + j] = s * scale;
+                }
+            for (int64_t i = 0; i < seq; ++i) {
+                float* row = scores + i * seq;
+                float mx = -INFINITY;
+                for (int64_t j = 0; j < seq; ++j) mx = fmaxf(mx, row[j]); /* f32::max ignores NaN */
+                float sum = 0.0f;
+                for (int64_t j = 0; j < seq; ++j) {
+                    row[j] = expf(row[j] - mx);
+                    sum += row[j];
+                }
+                float* dst = out + base + i * dim;
+                if (sum > 0.0f && isfinite(sum)) {
+                    for (int64_t j = 0; j < seq; ++j) row[j] /= sum;
+                    for (int d = 0; d < dim; ++d) {
+                        float o = 0.0f;
+                        for (int64_t j = 0; j < seq; ++j) o += row[j] * v[base + j * dim + d];
+                        dst[d] = o;
+                    }
+                } else {
+                    for (int d = 0; d < dim; ++d) dst[d] = NAN;
+                }
+                if (lse)
+                    lse[(b * heads + h) * seq + i] =
+                        (sum > 0.0f) ? mx + logf(sum) : (mx == -INFINITY ? -INFINITY : NAN);
+            }
+        }
+    }
+    free(scores);
+    return ORC_OK;
+}
+
+int orc_naive_forward_masked(int64_t batch, int64_t heads, int64_t seq, int dim, const float* q,
+                             const float* k, const float* v, int mask_kind, const uint8_t* keep,
+                             int64_t keep_len, float* out) {
+    return orc_naive_forward_ext(batch, heads, seq, dim, q, k, v, mask_kind == 1,
+                                 mask_kind == 2 ? keep : NULL, keep_len, 0, NULL, -1.0f, out, NULL);
+}
+
+/* ---------------------------------------------------------------- online softmax */
+
+/* online_softmax.rs:44-102: state is (m, l); EMPTY = (-inf, 0). */
+void orc_online_softmax_full(const float* xs, int64_t n, float* m_out, float* l_out) {
+    float m = -INFINITY, l = 0.0f;
+    for (int64_t i = 0; i < n; ++i) { /* absorb(), :70-79 */
+        const float x = xs[i];
+        if (x > m) {
+            l = l * expf(m - x) + 1.0f;
+            m = x;
+        } else {
+            l += expf(x - m);
+        }
+    }
+    *m_out = m;
+    *l_out = l;
+}
+
+/* online_softmax.rs:105-131. */
+void orc_combine_tiles(float am, float al, float bm, float bl, float* m_out, float* l_out) {
+    const int a_empty = (am == -INFINITY && al == 0.0f);
+    const int b_empty = (bm == -INFINITY && bl == 0.0f);
+    if (a_empty) { *m_out = bm; *l_out = bl; return; }
+    if (b_empty) { *m_out = am; *l_out = al; return; }
+    const float m_new = am > bm ? am : bm;
+    if (am == m_new && bm == m_new) { *m_out = m_new; *l_out = al + bl; }
+    else if (am == m_new) { *m_out = m_new; *l_out = al + bl * expf(bm - m_new); }
+    else { *m_out = m_new; *l_out = al * expf(am - m_new) + bl; }
+}
+
+/* ---------------------------------------------------------------- GQA */
+
+/* gqa.rs:216-270 for one (b, h): scores -> max -> exp/sum -> normalise -> sum w*V.
+ * k_block / v_block point at the first key of the KV head; consecutive keys are
+ * `kv_stride` floats apart (= head_dim for the reference's trimmed tensors). */
+static void decode_attn_row(const float* q_row, const float* k_block, const float* v_block,
+                            int64_t kv_stride, int64_t seq_kv, int head_dim, float scale,
+                            float* out_row, float* lse_out, float* scores) {
+    for (int64_t t = 0; t < seq_kv; ++t) {
+        const float* k_row = k_block + t * kv_stride;
+        float acc = 0.0f;
+        for (int d = 0; d < head_dim; ++d) acc += q_row[d] * k_row[d];
+        scores[t] = acc * scale;
+    }
+    float max_s = -INFINITY;
+    for (int64_t t = 0; t < seq_kv; ++t) max_s = fmaxf(max_s, scores[t]);
+    float sum_exp = 0.0f;
+    for (int64_t t = 0; t < seq_kv; ++t) {
+        scores[t] = expf(scores[t] - max_s);
+        sum_exp += scores[t];
+    }
+    const float inv_sum = 1.0f / sum_exp;
+    for (int64_t t = 0; t < seq_kv; ++t) scores[t] *= inv_sum;
+    for (int d = 0; d < head_dim; ++d) out_row[d] = 0.0f;
+    for (int64_t t = 0; t < seq_kv; ++t) {
+        const float* v_row = v_block + t * kv_stride;
+        const float w = scores[t];
+        for (int d = 0; d < head_dim; ++d) out_row[d] += w * v_row[d];
+    }
+    if (lse_out) *lse_out = (seq_kv > 0) ? max_s + logf(sum_exp) : -INFINITY;
+}
+
+/* gqa.rs:94-210: the reference API.  seq_q == seq_kv replicates the KV heads and runs the
+ * unmasked tiled forward; anything else is the row kernel (serial when seq_q == 1,
+ * one task per (b,h) otherwise). */
+int orc_gqa_forward_f32(const float* q, const float* k, const float* v, float* out, int64_t batch,
+                        int64_t n_heads, int64_t n_kv_heads, int64_t seq_q, int64_t seq_kv,
+                        int head_dim) {
+    if (n_kv_heads == 0 || n_heads % n_kv_heads != 0) return ORC_ERR_HEADS; /* :106-111 */
+    const int64_t group = n_heads / n_kv_heads;
+    if (seq_q == seq_kv) { /* :151-177 */
+        const int64_t kv_h_size = seq_kv * head_dim;
+        const size_t block = (size_t)(batch * n_heads * kv_h_size);
+        float* k_rep = (float*)malloc(sizeof(float) * (block ? block : 1));
+        float* v_rep = (float*)malloc(sizeof(float) * (block ? block : 1));
+        if (!k_rep || !v_rep) { free(k_rep); free(v_rep); return ORC_ERR_ALLOC; }
+        for (int64_t b = 0; b < batch; ++b)
+            for (int64_t h = 0; h < n_heads; ++h) {
+                const int64_t src = (b * n_kv_heads + h / group) * kv_h_size;
+                const int64_t dst = (b * n_heads + h) * kv_h_size;
+                memcpy(k_rep + dst, k + src, sizeof(float) * (size_t)kv_h_size);
+                memcpy(v_rep + dst, v + src, sizeof(float) * (size_t)kv_h_size);
+            }
+        int rc = orc_flash_forward_masked(batch, n_heads, seq_q, head_dim, 64, 64, q, k_rep, v_rep,
+                                          0, NULL, 0, out);
+        free(k_rep); free(v_rep);
+        return rc;
+    }
+    const float scale = 1.0f / sqrtf((float)head_dim);
+    const int64_t n_bh = batch * n_heads;
+    const int threads = (seq_q == 1) ? 1 : orc_get_threads(); /* :190-198 serial decode */
+#pragma omp parallel for schedule(dynamic, 1) num_threads(threads)
+    for (int64_t bh = 0; bh < n_bh; ++bh) {
+        const int64_t b = bh / n_heads, h = bh % n_heads, kv_h = h / group;
+        const float* k_block = k + (b * n_kv_heads + kv_h) * seq_kv * head_dim;
+        const float* v_block = v + (b * n_kv_heads + kv_h) * seq_kv * head_dim;
+        float* scores = (float*)malloc(sizeof(float) * (size_t)(seq_kv ? seq_kv : 1));
+        for (int64_t qp = 0; qp < seq_q; ++qp)
+            decode_attn_row(q + (bh * seq_q + qp) * head_dim, k_block, v_block, head_dim, seq_kv,
+                            head_dim, scale, out + (bh * seq_q + qp) * head_dim, NULL, scores);
+        free(scores);
+    }
+    return ORC_OK;
+}
+
+/*
+ * Decode over a KV cache [B, Hkv, max_seq, D] (kv_cache.rs:49-60 layout) for one query
+ * token per sequence: sequence b attends to cache positions [kv_begin, min(kv_end, kv_lens[b])).
+ * This is what the reference's model does per token (trim copy + gqa_forward_f32 with
+ * batch = 1, seq_q = 1) without materialising the trimmed copy.
+ *   q, out  [B, Hq, D];  lse  NULL or [B, Hq];  kv_end < 0 = no upper bound.
+ * An empty range yields out = 0 and lse = -inf (the reference's row kernel also returns
+ * zeros for seq_kv = 0).  `parallel` != 0 runs one task per (b, h).
+ */
+int orc_gqa_decode_cache(const float* q, const float* k_cache, const float* v_cache,
+                         const int32_t* kv_lens, int64_t batch, int64_t n_heads, int64_t n_kv_heads,
+                         int head_dim, int64_t max_seq, int64_t kv_begin, int64_t kv_end,
+                         float scale, int parallel, float* out, float* lse) {
+    if (n_kv_heads == 0 || n_heads % n_kv_heads != 0) return ORC_ERR_HEADS;
+    if (head_dim == 0) return ORC_ERR_ZERO_DIM;
+    if (scale <= 0.0f) scale = 1.0f / sqrtf((float)head_dim);
+    const int64_t group = n_heads / n_kv_heads;
+    const int64_t n_bh = batch * n_heads;
+    const int threads = parallel ? orc_get_threads() : 1;
+#pragma omp parallel for schedule(dynamic, 1) num_threads(threads)
+    for (int64_t bh = 0; bh < n_bh; ++bh) {
+        const int64_t b = bh / n_heads, h = bh % n_heads, kv_h = h / group; /* gqa.rs:231-233 */
+        int64_t hi = kv_lens[b];
+        if (kv_end >= 0 && kv_end < hi) hi = kv_end;
+        int64_t n = hi - kv_begin;
+        if (n < 0) n = 0;
+        const int64_t off = ((b * n_kv_heads + kv_h) * max_seq + kv_begin) * head_dim;
+        float* scores = (float*)malloc(sizeof(float) * (size_t)(n ? n : 1));
+        decode_attn_row(q + bh * head_dim, k_cache + off, v_cache + off, head_dim, n, head_dim,
+                        scale, out + bh * head_dim, lse ? lse + bh : NULL, scores);
+        free(scores);
+    }
+    return ORC_OK;
+}
+
+/*
+ * Merge R normalised partial results (O_r, LSE_r) of the same rows:
+ *   LSE = logsumexp_r LSE_r,  O = sum_r exp(LSE_r - LSE) * O_r.
+ * It is combine_tiles (online_softmax.rs:105-131) applied to states (m = LSE_r, l = 1)
+ * carrying a value vector; an empty partial (LSE_r = -inf) is the identity.  All partials
+ * empty -> O = 0, LSE = -inf.
+ *   o_parts [R, rows, D], lse_parts [R, rows]  ->  out [rows, D], lse NULL or [rows].
+ */
+void orc_merge_partials(const float* o_parts, const float* lse_parts, int64_t n_parts, int64_t rows,
+                        int dim, float* out, float* lse) {
+    for (int64_t r = 0; r < rows; ++r) {
+        float m = -INFINITY;
+        for (int64_t p = 0; p < n_parts; ++p) m = fmaxf(m, lse_parts[p * rows + r]);
+        float* dst = out + r * dim;
+        for (int d = 0; d < dim; ++d) dst[d] = 0.0f;
+        if (m == -INFINITY) {
+            if (lse) lse[r] = -INFINITY;
+            continue;
+        }
+        float l = 0.0f;
+        for (int64_t p = 0; p < n_parts; ++p) {
+            const float w = expf(lse_parts[p * rows + r] - m);
+            l += w;
+            const float* src = o_parts + (p * rows + r) * dim;
+            if (w != 0.0f)
+                for (int d = 0; d < dim; ++d) dst[d] += w * src[d];
+        }
+        const float inv = 1.0f / l;
+        for (int d = 0; d < dim; ++d) dst[d] *= inv;
+        if (lse) lse[r] = m + logf(l);
+    }
+}
+
+/* kv_cache.rs:77-112: append `n_new` tokens of K and V, given as [B, Hkv, n_new, D], into
+ * caches [B, Hkv, max_seq, D] at position `cur_len`.  Returns the new length or -1 on overflow. */
+int64_t orc_kv_cache_append(float* k_cache, float* v_cache, const float* k_new, const float* v_new,
+                            int64_t batch, int64_t n_kv_heads, int64_t max_seq, int head_dim,
+                            int64_t cur_len, int64_t n_new) {
+    if (cur_len + n_new > max_seq) return -1; /* :88-93 */
+    for (int64_t b = 0; b < batch; ++b)
+        for (int64_t h = 0; h < n_kv_heads; ++h) {
+            const int64_t src = ((b * n_kv_heads + h) * n_new) * head_dim;
+            const int64_t dst = ((b * n_kv_heads + h) * max_seq + cur_len) * head_dim;
+            memcpy(k_cache + dst, k_new + src, sizeof(float) * (size_t)(n_new * head_dim));
+            memcpy(v_cache + dst, v_new + src, sizeof(float) * (size_t)(n_new * head_dim));
+        }
+    return cur_len + n_new;
+}
+
+/* ---------------------------------------------------------------- inputs */
+
+/* f32 -> bf16 with round-to-nearest-even, the rule of the `half` crate the reference
+ * uses (rustorch-amp/src/dtypes.rs:10-24).  NaN stays a quiet NaN. */
+static inline uint16_t f32_to_bf16_rne(float f) {
+    uint32_t u;
+    memcpy(&u, &f, 4);
+    if ((u & 0x7fffffffu) > 0x7f800000u) return (uint16_t)((u >> 16) | 0x0040u);
+    const uint32_t lsb = (u >> 16) & 1u;
+    u += 0x7fffu + lsb;
+    return (uint16_t)(u >> 16);
+}
+
+void orc_f32_to_bf16(const float* src, uint16_t* dst, int64_t n) {
+    for (int64_t i = 0; i < n; ++i) dst[i] = f32_to_bf16_rne(src[i]);
+}
+
+void orc_bf16_to_f32(const uint16_t* src, float* dst, int64_t n) {
+    for (int64_t i = 0; i < n; ++i) {
+        const uint32_t u = (uint32_t)src[i] << 16;
+        memcpy(dst + i, &u, 4);
+    }
+}
+
+/* Round every element to the nearest bf16 value, keeping f32 storage. */
+void orc_round_to_bf16(float* buf, int64_t n) {
+    for (int64_t i = 0; i < n; ++i) {
+        const uint32_t u = (uint32_t)f32_to_bf16_rne(buf[i]) << 16;
+        memcpy(buf + i, &u, 4);
+    }
+}
+
+static inline uint64_t splitmix64(uint64_t x) {
+    x += 0x9e3779b97f4a7c15ull;
+    x = (x ^ (x >> 30)) * 0xbf58476d1ce4e5b9ull;
+    x = (x ^ (x >> 27)) * 0x94d049bb133111ebull;
+    return x ^ (x >> 31);
+}
+
+/* Counter-based N(0,1): element i is a pure function of (seed, first_index + i), so
+ * any shard of a tensor can be produced independently.  Box-Muller on two 32-bit
+ * halves of one splitmix64 draw. */
+void orc_fill_normal(float* dst, int64_t n, uint64_t seed, uint64_t first_index) {
+    const uint64_t key = splitmix64(seed);
+#pragma omp parallel for schedule(static) num_threads(orc_get_threads())
+    for (int64_t i = 0; i < n; ++i) {
+        const uint64_t r = splitmix64(key ^ ((first_index + (uint64_t)i) * 0xd1342543de82ef95ull));
+        const double u1 = ((double)(uint32_t)(r >> 32) + 1.0) * (1.0 / 4294967296.0); /* (0,1] */
+        const double u2 = (double)(uint32_t)r * (1.0 / 4294967296.0);                 /* [0,1) */
+        dst[i] = (float)(sqrt(-2.0 * log(u1)) * cos(6.283185307179586 * u2));
+    }
+}
+
+/* Uniform integers in [lo, hi] from the same counter-based stream. */
+void orc_fill_uniform_int(int32_t* dst, int64_t n, uint64_t seed, int32_t lo, int32_t hi) {
+    const uint64_t key = splitmix64(seed ^ 0x5eedull);
+    const uint64_t span = (uint64_t)(hi - lo) + 1u;
+    for (int64_t i = 0; i < n; ++i)
+        dst[i] = lo + (int32_t)(splitmix64(key ^ ((uint64_t)i * 0xd1342543de82ef95ull)) % span);
+}
+
+/* The reference tests' LCG fixture (cpu_forward.rs:769-780, tests/equivalence.rs:23-31):
+ * s = seed*2654435761; s = s*1664525 + 1013904223; value = (s/u32::MAX - 0.5) * width. */
+void orc_fill_lcg(float* dst, int64_t n, uint32_t seed, float width) {
+    uint32_t s = seed * 2654435761u;
+    for (int64_t i = 0; i < n; ++i) {
+        s = s * 1664525u + 1013904223u;
+        dst[i] = ((float)s / (float)UINT32_MAX - 0.5f) * width;
+    }
+}
