@@ -1,0 +1,375 @@
+#!/usr/bin/env python
+"""Benchmark of the attention hot path on B200.
+
+    python bench.py --gpus N --steps K --warmup W            (N>1: launched under torch.distributed.run)
+    python bench.py --impl reference --gpus N --steps K --warmup W
+
+Headline workload (one "step" = one pass of the hot path over one batch of synthetic input):
+causal prefill, bf16, B=4 H=32 N=4096 D=128 per GPU, Q,K,V ~ N(0,1) from a seed, scale 1/sqrt(128),
+output bf16 + f32 LSE.  `value` is attention TFLOP/s with inputs resident in HBM, counting only the
+unmasked (query,key) pairs: FLOPs = 4*D*B*H*N(N+1)/2.  `e2e` is the same metric through the C-ABI
+host entry (pinned host buffers, H2D and D2H inside the timed region).  The same JSON line carries
+the HBM-bound half of the metric under "decode" (batched GQA decode, B=64 Hq=32 Hkv=8 D=128, cache of
+8192 positions, lengths ~ U[1024,8192]: KV-read GB/s = 4096 B * sum(len) / time) and, on N>1 GPUs,
+"decode_splitkv" (KV range sharded over the ranks, (O,LSE) partials all-gathered with NCCL and merged).
+
+Multi-GPU: (b,h) units are independent, so every rank runs the workload on its own shard with no
+data-path collective (weak scaling: per-GPU work fixed); only the split-KV decode exchanges data.
+
+`--impl reference` times the CPU restatement of the reference's rayon flash-attention path (the
+reference is Rust and cannot be built on this machine) on all host cores, on a bounded sample of the
+same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+CFG2 = dict(B=4, H=32, N=4096, D=128)
+CFG4 = dict(B=64, Hq=32, Hkv=8, D=128, S=8192, lo=1024, hi=8192)
+CFG5_TOKENS_PER_GPU = 131072  # 1,048,576 / 8
+
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            d = json.load(f)
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
+                "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "source": "measured"}
+    except Exception:
+        return dict(FALLBACK_PEAKS, bf16_tflops_sustained=1400.0, source="fallback")
+
+
+def load_traffic():
+    """DRAM bytes per launch of the dominant kernels, taken from the committed ncu summaries."""
+    try:
+        with open(os.path.join(ROOT, "profiles", "dram_traffic.json")) as f:
+            return json.load(f)
+    except Exception:
+        return {}
+
+
+def prefill_flops(B, H, N, D):
+    return 4.0 * D * B * H * (N * (N + 1) / 2.0)
+
+
+# ------------------------------------------------------------------------------------------ clocks
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML while a timed region runs."""
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self._nv = None
+
+    def _loop(self):
+        nv = self._nv
+        names = {
+            getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8): "hw_slowdown",
+            getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+            getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+            getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4): "sw_power_cap",
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(int(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM)))
+                try:
+                    r = nv.nvmlDeviceGetCurrentClocksEventReasons(self._h)
+                except Exception:
+                    r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h)
+                for bit, name in names.items():
+                    if r & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.002)
+
+    def __enter__(self):
+        if self._nv:
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread:
+            self._thread.join()
+
+    def summary(self):
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(s)}
+
+
+# ------------------------------------------------------------------------------------------ CPU arm
+def cpu_flash_sample(steps: int, warmup: int, target_seconds: float | None):
+    """Times the oracle's tiled flash forward (one task per (b,h), all host threads) on `slabs`
+    (b,h) slabs of the headline workload.  Returns (TFLOP/s algorithmic, cores, slabs, s/step)."""
+    import numpy as np
+    from oracle import oracle as orc
+
+    cores = orc.get_threads()
+    N, D = CFG2["N"], CFG2["D"]
+    slabs = min(CFG2["B"] * CFG2["H"], max(8, cores))
+    q, k, v = (orc.round_to_bf16(orc.fill_normal((1, slabs, N, D), s)) for s in (0xC0FFEE, 0xBADBEEF, 0xCAFE00))
+    for _ in range(max(0, warmup)):
+        orc.flash_forward_ext(q, k, v, causal=True)
+    times = []
+    t_begin = time.perf_counter()
+    for i in range(max(1, steps)):
+        t0 = time.perf_counter()
+        rc, _, _ = orc.flash_forward_ext(q, k, v, causal=True)
+        times.append(time.perf_counter() - t0)
+        assert rc == 0
+        if target_seconds is not None and time.perf_counter() - t_begin > target_seconds:
+            break
+    per_step = float(np.mean(times))
+    return prefill_flops(1, slabs, N, D) / per_step / 1e12, cores, slabs, per_step, len(times)
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    tf, cores, slabs, per_step, done = cpu_flash_sample(args.steps, args.warmup, None)
+    sample = (f"{slabs} of {CFG2['B'] * CFG2['H']} (b,h) slabs of the workload per step (N={CFG2['N']} D={CFG2['D']} "
+              f"causal, f32 math on bf16-rounded inputs), C restatement of the reference's rayon path, {cores} threads")
+    line = {
+        "impl": "reference", "metric": "attn_prefill_tflops", "value": tf, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": done, "warmup": args.warmup, "ms_per_step": per_step * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "causal prefill B=4 H=32 N=4096 D=128 (BASELINE config 2), bounded sample",
+                   "sample_slabs": slabs},
+        "cpu_baseline": {"value": tf, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": tf, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+    return 0
+
+
+# ------------------------------------------------------------------------------------------ GPU arm
+def timed(fn, steps, warmup, dist_mod, torch):
+    """W untimed + K timed calls bracketed by barrier + synchronize; CUDA events on the launch stream;
+    returns the max over ranks of the average ms per step."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    if dist_mod is not None:
+        dist_mod.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    if dist_mod is not None:
+        dist_mod.barrier()
+    ms = e0.elapsed_time(e1) / steps
+    if dist_mod is not None:
+        t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+        dist_mod.all_reduce(t, op=dist_mod.ReduceOp.MAX)
+        ms = float(t.item())
+    return ms
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--skip-cpu", action="store_true", help="skip the cpu_baseline leg (profiling runs)")
+    ap.add_argument("--only", default="", help="comma list of legs: prefill,e2e,decode,splitkv (default all)")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    if args.impl == "reference":
+        return run_reference_arm(args)
+
+    import torch
+    import rustorch_b200 as rt
+    from rustorch_b200 import _lib
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist_mod.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        dist = dist_mod
+    n_gpus = world
+    legs = set(args.only.split(",")) if args.only else {"prefill", "e2e", "decode", "splitkv"}
+    peaks = load_peaks()
+    traffic = load_traffic()
+    lib = _lib.lib()
+    out_line = {}
+
+    # ---------------------------------------------------------------- prefill (headline)
+    B, H, N, D = CFG2["B"], CFG2["H"], CFG2["N"], CFG2["D"]
+    g = torch.Generator(device="cuda").manual_seed(0xC0FFEE + rank)
+    q, k, v = (torch.randn((B, H, N, D), device="cuda", generator=g).to(torch.bfloat16) for _ in range(3))
+    o = torch.empty_like(q)
+    lse = torch.empty((B, H, N), dtype=torch.float32, device="cuda")
+    flops = prefill_flops(B, H, N, D)
+
+    def step_prefill():
+        rt.prefill_bf16(q, k, v, causal=True, out=o, lse=lse)
+
+    with ClockSampler(local_rank) as clk:
+        ms = timed(step_prefill, args.steps, args.warmup, dist, torch)
+    status = _lib.device_status()
+    if status != 0:
+        raise RuntimeError(f"device status word {status}: a bounded wait expired inside the prefill kernel")
+    per_gpu_tflops = flops / (ms * 1e-3) / 1e12
+    value = per_gpu_tflops * n_gpus
+    clocks = clk.summary()
+
+    # ---------------------------------------------------------------- e2e through the C-ABI host entry
+    e2e = None
+    if "e2e" in legs:
+        hq, hk, hv = (t.cpu().pin_memory() for t in (q, k, v))
+        ho = torch.empty_like(hq).pin_memory()
+        hl = torch.empty((B, H, N), dtype=torch.float32).pin_memory()
+
+        def step_e2e():
+            rc = lib.rt_attn_prefill_bf16_host(hq.data_ptr(), hk.data_ptr(), hv.data_ptr(), ho.data_ptr(),
+                                               hl.data_ptr(), B, H, N, D, _lib.RT_MASK_CAUSAL, None, -1.0)
+            _lib.check(rc, "rt_attn_prefill_bf16_host")
+
+        e2e_steps = max(3, min(args.steps, 10))
+        for _ in range(2):
+            step_e2e()
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            step_e2e()  # blocks until the result is back in host memory
+        torch.cuda.synchronize()
+        e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
+        if dist is not None:
+            t = torch.tensor([e2e_ms], dtype=torch.float64, device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            e2e_ms = float(t.item())
+        e2e = {"value": n_gpus * flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
+               "h2d_bytes_per_step": int(3 * q.numel() * 2), "d2h_bytes_per_step": int(o.numel() * 2 + lse.numel() * 4),
+               "steps": e2e_steps, "api": "rt_attn_prefill_bf16_host (pinned host buffers, copies inside the timed region)"}
+        assert torch.equal(ho.cuda(), o), "host entry and device entry disagree"
+        del hq, hk, hv, ho, hl
+    del q, k, v, o, lse
+    torch.cuda.empty_cache()
+
+    # ---------------------------------------------------------------- decode (HBM-bound half of the metric)
+    decode = None
+    if "decode" in legs:
+        c = CFG4
+        g = torch.Generator(device="cuda").manual_seed(0x5EED + rank)
+        qd = torch.randn((c["B"], c["Hq"], c["D"]), device="cuda", generator=g).to(torch.bfloat16)
+        kc = torch.randn((c["B"], c["Hkv"], c["S"], c["D"]), device="cuda", generator=g).to(torch.bfloat16)
+        vc = torch.randn((c["B"], c["Hkv"], c["S"], c["D"]), device="cuda", generator=g).to(torch.bfloat16)
+        lens = torch.randint(c["lo"], c["hi"] + 1, (c["B"],), device="cuda", generator=g, dtype=torch.int32)
+        kv_bytes = 2.0 * c["Hkv"] * c["D"] * 2 * float(lens.sum().item())
+
+        def step_decode():
+            rt.gqa_decode(qd, kc, vc, kv_lens=lens)
+
+        with ClockSampler(local_rank) as dclk:
+            dms = timed(step_decode, args.steps, args.warmup, dist, torch)
+        gbs = kv_bytes / (dms * 1e-3) / 1e9
+        decode = {"metric": "kv_read_gbs", "value": gbs * n_gpus, "unit": "GB/s", "ms_per_step": dms,
+                  "config": {"workload": "batched GQA decode B=64 Hq=32 Hkv=8 D=128 max_seq=8192 lens~U[1024,8192] per GPU "
+                                         "(BASELINE config 4)", "kv_bytes_per_step": kv_bytes,
+                             "l2": "1.2 GB of KV streamed per step, far larger than L2"},
+                  "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                               "frac": gbs / peaks["hbm_gbs"], "peak_source": peaks["source"],
+                               "traffic": traffic.get("gqa_decode_splitkv_kernel")},
+                  "gpu_launches": 2 * args.steps, "clocks": dclk.summary()}
+        del qd, kc, vc
+        torch.cuda.empty_cache()
+
+    # ---------------------------------------------------------------- long-context split-KV decode (N>1 only)
+    splitkv = None
+    if "splitkv" in legs and dist is not None:
+        Hq, Hkv, Dd, T = 32, 8, 128, CFG5_TOKENS_PER_GPU
+        g = torch.Generator(device="cuda").manual_seed(0xBEEF)  # the same q on every rank
+        q1 = torch.randn((1, Hq, Dd), device="cuda", generator=g).to(torch.bfloat16)
+        g = torch.Generator(device="cuda").manual_seed(0xF00D + rank)
+        k1 = torch.randn((1, Hkv, T, Dd), device="cuda", generator=g).to(torch.bfloat16)
+        v1 = torch.randn((1, Hkv, T, Dd), device="cuda", generator=g).to(torch.bfloat16)
+        rec = torch.empty((Hq, Dd + 1), dtype=torch.float32, device="cuda")       # packed [O | LSE] of this rank
+        allrec = torch.empty((world, Hq, Dd + 1), dtype=torch.float32, device="cuda")
+        ws = torch.empty(rt.decode_workspace_bytes(1, Hq, Hkv, Dd, T), dtype=torch.uint8, device="cuda")
+
+        def step_splitkv():
+            o32, l32 = rt.gqa_decode(q1, k1, v1, kv_len=T, out_dtype=torch.float32, workspace=ws)
+            rec[:, :Dd].copy_(o32[0])
+            rec[:, Dd].copy_(l32[0])
+            dist.all_gather_into_tensor(allrec, rec)
+            return rt.merge_partials(allrec[:, :, :Dd].contiguous(), allrec[:, :, Dd].contiguous())
+
+        sms = timed(step_splitkv, args.steps, args.warmup, dist, torch)
+        total_bytes = 2.0 * Hkv * Dd * 2 * T * world
+        splitkv = {"metric": "kv_read_gbs", "value": total_bytes / (sms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": sms,
+                   "config": {"workload": f"split-KV decode B=1 Hq=32 Hkv=8 D=128, {T} KV positions per GPU "
+                                          f"(BASELINE config 5 sharding), NCCL all-gather of (O,LSE) + merge",
+                              "kv_len_total": T * world},
+                   "per_gpu_gbs": total_bytes / world / (sms * 1e-3) / 1e9}
+        del k1, v1
+        torch.cuda.empty_cache()
+
+    # ---------------------------------------------------------------- CPU baseline (rank 0, N = 1 only)
+    cpu = None
+    if rank == 0 and n_gpus == 1 and not args.skip_cpu:
+        tf, cores, slabs, per_step, reps = cpu_flash_sample(8, 1, 12.0)
+        cpu = {"value": tf, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+               "sample": f"{slabs} of {B * H} (b,h) slabs of the workload, {reps} repetitions, {per_step:.2f} s each; "
+                         f"C restatement of the reference's rayon tiled path (visits every KV tile), all host threads"}
+
+    if rank == 0:
+        out_line = {
+            "metric": "attn_prefill_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": n_gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "causal prefill bf16 B=4 H=32 N=4096 D=128 per GPU (BASELINE config 2), out bf16 + f32 LSE",
+                       "flops_per_step_per_gpu": flops, "flop_convention": "4*D*unmasked (q,k) pairs",
+                       "sharding": "independent (b,h) units per rank, no collective",
+                       "l2": "Q,K,V,O = 512 MiB per step, larger than the 126 MB L2"},
+            "roofline": {"bound": "tensor", "achieved": per_gpu_tflops, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                         "frac": per_gpu_tflops / peaks["bf16_tflops"], "peak_source": peaks["source"],
+                         "frac_of_sustained": per_gpu_tflops / peaks["bf16_tflops_sustained"],
+                         "traffic": traffic.get("prefill_tc_kernel")},
+            "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": args.steps, "clocks": clocks,
+            "decode": decode, "decode_splitkv": splitkv,
+        }
+        print(json.dumps(out_line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,253 @@
+/*
+ * rustorch_attn.h — C ABI of the B200 (sm_100a) attention library.
+ *
+ * Every entry point is `extern "C"`, takes plain pointers and sizes, and returns an
+ * `int` status: 0 = success, > 0 = a `cudaError_t` value (maps to the reference's
+ * `CudaError::Driver{code, location}`, crates/rustorch-cuda/src/error.rs:8-62),
+ * < 0 = a validation error (RT_ERR_* below) raised BEFORE any device work is queued.
+ *
+ * Conventions
+ *   - "device" pointers are CUDA device addresses (the reference passes them as `u64`
+ *     obtained from `CudaSlice::device_ptr`, crates/rustorch-llm/src/cuda_backend.rs:969-972).
+ *   - bf16 buffers are raw 16-bit words (`__nv_bfloat16`), produced with round-to-nearest-even
+ *     (crates/rustorch-amp/src/dtypes.rs:10-24).
+ *   - `stream` is a `cudaStream_t` passed as `void*`; NULL = the legacy default stream.
+ *     Device entry points only enqueue work and return; the caller synchronises, like
+ *     `LlamaModelCuda::decode_step` does (crates/rustorch-llm/src/cuda_backend.rs:1088-1091).
+ *     `*_host` entry points take host memory, copy both ways and block until done.
+ *   - Tensors are dense row-major: prefill `[B,H,N,D]` (crates/rustorch-attention/src/cpu_forward.rs:22-27),
+ *     KV cache `[B,Hkv,max_seq,D]` (crates/rustorch-nn/src/kv_cache.rs:49-60; the CUDA model's
+ *     `[Hkv,max_seq,D]` of crates/rustorch-cuda/src/llm_kernels.rs:349-352 is the B = 1 case),
+ *     decode q/out `[B,Hq,D]`.
+ *   - LSE is the natural-log log-sum-exp of the scaled scores of a row (`m + ln l` of
+ *     `OnlineSoftmaxState`, crates/rustorch-attention/src/online_softmax.rs:44-56);
+ *     a row with no visible key has LSE = -inf.
+ *   - There is no CPU fallback: without a CUDA device every compute entry point fails.
+ */
+#ifndef RUSTORCH_ATTN_H
+#define RUSTORCH_ATTN_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ------------------------------------------------------------------ */
+#define RT_OK 0
+/* AttentionError::ZeroDim (cpu_forward.rs:108) */
+#define RT_ERR_ZERO_DIM (-1)
+/* AttentionError::BufferShapeMismatch{which,expected,got} (cpu_forward.rs:94-102) */
+#define RT_ERR_BUFFER_SHAPE (-2)
+/* AttentionError::OutputShapeMismatch (cpu_forward.rs:103-108) */
+#define RT_ERR_OUTPUT_SHAPE (-3)
+/* AttentionError::Mask(MaskError::PaddingLengthMismatch) (mask.rs:70-78) */
+#define RT_ERR_MASK_LEN (-4)
+/* GQAError::HeadCountMismatch (gqa.rs:37-44) */
+#define RT_ERR_HEAD_COUNT (-5)
+/* GQAError::WrongInputLen (gqa.rs:45-54) */
+#define RT_ERR_WRONG_INPUT_LEN (-6)
+/* CudaError::Unsupported{msg} (error.rs): shape outside what the kernels implement */
+#define RT_ERR_UNSUPPORTED (-7)
+#define RT_ERR_NULL_POINTER (-8)
+/* kv_len > max_seq, negative sizes */
+#define RT_ERR_BAD_LENGTH (-9)
+/* caller workspace too small or missing */
+#define RT_ERR_WORKSPACE (-10)
+/* a device pointer is not 16-byte aligned */
+#define RT_ERR_ALIGNMENT (-11)
+/* a bounded device-side wait ran out; see rt_attn_device_status() */
+#define RT_ERR_DEVICE_TIMEOUT (-12)
+
+/* ---- mask flags for the prefill entry points ---------------------------------------- */
+#define RT_MASK_NONE 0
+/* Mask::Causal: key j > query i is masked (mask.rs:43) */
+#define RT_MASK_CAUSAL 1
+
+/* Mask kinds of the reference enum, for the host entry that mirrors it (mask.rs:26-34) */
+#define RT_MASKKIND_NONE 0
+#define RT_MASKKIND_CAUSAL 1
+#define RT_MASKKIND_PADDING 2
+
+/* precision selector of the f32 host entry points */
+#define RT_PRECISION_F32 0  /* f32 CUDA-core kernel, parity with the f32 reference at 1e-4 */
+#define RT_PRECISION_BF16 1 /* inputs rounded to bf16 (RNE), tcgen05 tensor-core kernel */
+
+/* Library version: major*10000 + minor*100 + patch. */
+int rt_attn_version(void);
+
+/* Static description of a status code (never NULL). */
+const char* rt_attn_error_string(int status);
+
+/*
+ * Reads (and clears) the device-side status word of the current device: 0 = clean,
+ * otherwise a code identifying which bounded wait inside a kernel gave up.  Synchronises
+ * the device.  Returns RT_OK, a cudaError_t, or RT_ERR_DEVICE_TIMEOUT when *status != 0.
+ */
+int rt_attn_device_status(int* status);
+
+/* ===================================================================================== *
+ * Prefill — replaces rustorch_attention::flash_forward / flash_forward_masked
+ * (crates/rustorch-attention/src/cpu_forward.rs:175-242) on device memory.
+ * ===================================================================================== */
+
+/*
+ * Tiled flash-attention forward on bf16 device tensors, tcgen05/TMEM tensor-core kernel.
+ *   q, k, v, out : bf16 [B,H,N,D], 16-byte aligned.  D must be 64 or 128.
+ *   lse          : NULL or f32 [B,H,N].
+ *   mask_flags   : RT_MASK_NONE or RT_MASK_CAUSAL.
+ *   kv_lens      : NULL or device int32 [B]; keys j >= kv_lens[b] are masked for batch b
+ *                  (the padding mask of a right-padded batch; combines with causal).
+ *   key_keep     : NULL or device u8 keep flags (0 = masked), the reference's
+ *                  Mask::Padding (mask.rs:31-33); batch b reads key_keep + b*keep_batch_stride,
+ *                  stride 0 shares one vector of length N across the batch as the reference does.
+ *   scale        : softmax scale; <= 0 selects the reference's 1/sqrt(D) (cpu_forward.rs:208).
+ * Semantics follow the reference with two documented choices: a row whose visible keys
+ * begin after a fully masked stretch gets the finite (naive_forward_masked) answer, and a
+ * row with no visible key is NaN with LSE = -inf (cpu_forward.rs:411-420).  Padded QUERY
+ * rows are computed like any other row (mask.rs:44 masks keys only).
+ * N = 0 is a no-op (cpu_forward.rs:203-206).
+ */
+int rt_attn_prefill_bf16(const void* q, const void* k, const void* v, void* out, float* lse,
+                         int64_t batch, int64_t heads, int64_t seq, int dim, int mask_flags,
+                         const int32_t* kv_lens, const uint8_t* key_keep, int64_t keep_batch_stride,
+                         float scale, void* stream);
+
+/*
+ * The same operator on f32 device tensors with f32 arithmetic on CUDA cores (any D in
+ * [1,256]); grouped KV heads and seq_q != seq_kv are allowed so that it also serves
+ * gqa_forward_f32's prefill and cross-attention branches (gqa.rs:151-210).
+ *   q, out : f32 [B,Hq,Nq,D];  k, v : f32 [B,Hkv,Nkv,D];  lse : NULL or f32 [B,Hq,Nq].
+ *   Causal masking compares key j with query i directly (j > i masked), as mask.rs:43 does.
+ */
+int rt_attn_prefill_f32(const float* q, const float* k, const float* v, float* out, float* lse,
+                        int64_t batch, int64_t heads_q, int64_t heads_kv, int64_t seq_q,
+                        int64_t seq_kv, int dim, int mask_flags, const int32_t* kv_lens,
+                        const uint8_t* key_keep, int64_t keep_batch_stride, float scale,
+                        void* stream);
+
+/*
+ * Host-slice mirror of
+ *   flash_forward_masked(shape:&AttentionShape, q:&[f32], k:&[f32], v:&[f32], mask:&Mask, out:&mut [f32])
+ * (cpu_forward.rs:193-200; flash_forward at :175-183 is mask_kind = RT_MASKKIND_NONE).
+ * `*_len` are the slice lengths in elements and are validated exactly like validate()
+ * (cpu_forward.rs:142-169) and Mask::validate (mask.rs:51-65).  `br`/`bc` of AttentionShape
+ * only change summation order in the reference and are not part of this ABI.
+ * Copies to the device, runs the selected kernel, copies back, blocks.
+ */
+int rt_flash_forward_f32_host(const float* q, size_t q_len, const float* k, size_t k_len,
+                              const float* v, size_t v_len, float* out, size_t out_len,
+                              int64_t batch, int64_t heads, int64_t seq, int64_t dim, int mask_kind,
+                              const uint8_t* keep, size_t keep_len, int precision);
+
+/*
+ * Host entry for bf16 tensors: the end-to-end call a host-resident caller makes.
+ * q,k,v,out are host bf16 [B,H,N,D] (pinned memory recommended), lse NULL or host f32 [B,H,N],
+ * kv_lens NULL or host int32 [B].  Copies in, runs rt_attn_prefill_bf16, copies out, blocks.
+ */
+int rt_attn_prefill_bf16_host(const void* q, const void* k, const void* v, void* out, float* lse,
+                              int64_t batch, int64_t heads, int64_t seq, int dim, int mask_flags,
+                              const int32_t* kv_lens, float scale);
+
+/* ===================================================================================== *
+ * Decode — replaces LlmKernels::gqa_decode_online_bf16 / gqa_decode_naive_bf16
+ * (crates/rustorch-cuda/src/llm_kernels.rs:376-536, wrappers :915-958, :1000-1042) and the
+ * seq_q == 1 branch of rustorch_nn::gqa::gqa_forward_f32 (crates/rustorch-nn/src/gqa.rs:190-270).
+ * ===================================================================================== */
+
+/*
+ * Bytes of device scratch the split-KV decode needs for this problem size (partial
+ * (O, m, l) records of every KV chunk).  Returns 0 when no scratch is needed.
+ */
+size_t rt_gqa_decode_workspace_bytes(int64_t batch, int64_t n_heads, int64_t n_kv_heads, int head_dim,
+                                     int64_t max_seq);
+
+/*
+ * Batched single-token GQA decode over a bf16 KV cache with per-sequence lengths.
+ *   q [B,Hq,D] bf16;  k_cache, v_cache [B,Hkv,max_seq,D] bf16;  16-byte aligned.
+ *   out_bf16 : NULL or bf16 [B,Hq,D];  out_f32 : NULL or f32 [B,Hq,D] (at least one of them);
+ *   lse      : NULL or f32 [B,Hq].
+ *   kv_lens  : device int32 [B], or NULL to use `kv_len_uniform` for every sequence.
+ *   kv_begin / kv_end : sequence b attends to positions [kv_begin, min(kv_end, len_b));
+ *              kv_end < 0 = unbounded.  A non-trivial range yields the partial result of a
+ *              KV shard; merge shards with rt_attn_merge_partials.
+ *   Query head h reads KV head h / (Hq/Hkv) (gqa.rs:233; llm_kernels.rs:410 is the same map).
+ *   head_dim must be 64, 128 or 256 and Hq/Hkv one of 1,2,4,8.
+ *   An empty range gives out = 0 and lse = -inf (the reference kernels return zeros too:
+ *   gqa.rs:262-269 with seq_kv = 0, llm_kernels.rs:456).
+ *   workspace : device scratch of at least rt_gqa_decode_workspace_bytes(...) bytes.
+ */
+int rt_gqa_decode_bf16(const void* q, const void* k_cache, const void* v_cache, void* out_bf16,
+                       float* out_f32, float* lse, int64_t batch, int64_t n_heads, int64_t n_kv_heads,
+                       int head_dim, int64_t max_seq, const int32_t* kv_lens, int64_t kv_len_uniform,
+                       int64_t kv_begin, int64_t kv_end, float scale, void* workspace,
+                       size_t workspace_bytes, void* stream);
+
+/*
+ * Drop-in for
+ *   LlmKernels::gqa_decode_online_bf16(stream, q, k_cache, v_cache, out, n_heads, n_kv, kv_len, head_dim, max_seq)
+ * (llm_kernels.rs:915-927): one sequence, caches [n_kv,max_seq,head_dim], scale = 1/sqrt(head_dim)
+ * (llm_kernels.rs:933), plus the caller-owned scratch this library needs instead of
+ * allocating.  gqa_decode_naive_bf16 (llm_kernels.rs:1000-1012) has the same signature and
+ * the same result; bind both names to this symbol.
+ */
+int rt_gqa_decode_online_bf16(const void* q, const void* k_cache, const void* v_cache, void* out,
+                              int n_heads, int n_kv, int kv_len, int head_dim, int max_seq,
+                              void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Merge R partial results of the same rows (split-KV across GPUs or across calls):
+ *   LSE = logsumexp_r LSE_r,   O = sum_r exp(LSE_r - LSE) * O_r
+ * — combine_tiles (online_softmax.rs:105-131) with a value vector attached; a partial with
+ * LSE = -inf is the identity element.
+ *   o_parts f32 [R,rows,D], lse_parts f32 [R,rows]  (device)
+ *   out_bf16 NULL or bf16 [rows,D]; out_f32 NULL or f32 [rows,D]; lse NULL or f32 [rows].
+ */
+int rt_attn_merge_partials(const float* o_parts, const float* lse_parts, int64_t n_parts, int64_t rows,
+                           int dim, void* out_bf16, float* out_f32, float* lse, void* stream);
+
+/*
+ * Host-slice mirror of
+ *   gqa_forward_f32(q,k,v,out, batch,n_heads,n_kv_heads,seq_q,seq_kv,head_dim) -> Result<(),GQAError>
+ * (gqa.rs:94-105), f32 arithmetic.  seq_q == seq_kv runs the unmasked prefill without
+ * materialising the repeated KV heads (the reference copies them, gqa.rs:154-168);
+ * other shapes run the same f32 kernel with seq_q != seq_kv.  Blocks.
+ */
+int rt_gqa_forward_f32_host(const float* q, size_t q_len, const float* k, size_t k_len, const float* v,
+                            size_t v_len, float* out, size_t out_len, int64_t batch, int64_t n_heads,
+                            int64_t n_kv_heads, int64_t seq_q, int64_t seq_kv, int64_t head_dim);
+
+/*
+ * Drop-in for LlmKernels::kv_append_bf16(stream, k_cache, v_cache, k_in, v_in, pos, n_kv, head_dim, max_seq)
+ * (llm_kernels.rs:345-373, wrapper :872-911), batched: k_in, v_in are bf16 [B,Hkv,D] and are
+ * written at position pos (or positions[b] when `positions` is a device int32 [B]) of the
+ * [B,Hkv,max_seq,D] caches.
+ */
+int rt_kv_append_bf16(void* k_cache, void* v_cache, const void* k_in, const void* v_in, int64_t batch,
+                      int n_kv, int head_dim, int64_t max_seq, int64_t pos, const int32_t* positions,
+                      void* stream);
+
+/* f32 <-> bf16 (RNE) conversion of n elements on the device; helpers of the host entries. */
+int rt_convert_f32_to_bf16(const float* src, void* dst, int64_t n, void* stream);
+int rt_convert_bf16_to_f32(const void* src, float* dst, int64_t n, void* stream);
+
+/* ===================================================================================== *
+ * Diagnostics (no counterpart in the reference).
+ * ===================================================================================== */
+
+/*
+ * Runs the two tensor-core MMA shapes of the prefill kernel on one 128-row tile and returns
+ * the raw f32 accumulators, so that the TMA / shared-memory / instruction descriptor
+ * encodings can be checked against a plain matrix product:
+ *   s_out [128,128] = A * B^T                 (A, B: bf16 [128,dim], the Q and K roles)
+ *   o_out [128,dim] = bf16(s_out / 16) * V    (V: bf16 [128,dim])
+ * dim must be 64 or 128; all pointers are device pointers.
+ */
+int rt_debug_tc_selftest(const void* a, const void* b, const void* v, float* s_out, float* o_out, int dim,
+                         void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RUSTORCH_ATTN_H */

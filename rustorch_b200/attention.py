@@ -1,0 +1,218 @@
+"""Host-side mirror of the ``rustorch-attention`` public API on top of the C ABI.
+
+Same names, argument meaning and error behaviour as the reference
+(crates/rustorch-attention/src/lib.rs:27-33):
+
+    AttentionShape, Mask, flash_forward, flash_forward_masked,
+    AttentionError{BufferShapeMismatch, OutputShapeMismatch, ZeroDim, Mask(PaddingLengthMismatch)}
+
+``flash_forward*`` take host f32 arrays exactly like the Rust functions take ``&[f32]`` slices
+and run on the GPU through ``rt_flash_forward_f32_host``.  ``prefill_bf16`` is the device-resident
+entry (torch CUDA tensors in, no host copies) that the benchmark measures.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import POINTER, c_float, c_uint8
+from dataclasses import dataclass
+from typing import Optional
+
+import numpy as np
+
+from . import _lib
+
+
+# ---------------------------------------------------------------- errors (cpu_forward.rs:93-114, mask.rs:70-78)
+class AttentionError(Exception):
+    pass
+
+
+class BufferShapeMismatch(AttentionError):
+    def __init__(self, which: str, expected: int, got: int):
+        self.which, self.expected, self.got = which, expected, got
+        super().__init__(f"{which} buffer has {got} elements, expected {expected}")
+
+
+class OutputShapeMismatch(AttentionError):
+    def __init__(self, expected: int, got: int):
+        self.expected, self.got = expected, got
+        super().__init__(f"output buffer has {got} elements, expected {expected}")
+
+
+class ZeroDim(AttentionError):
+    def __init__(self):
+        super().__init__("dim must be > 0")
+
+
+class MaskError(AttentionError):
+    pass
+
+
+class PaddingLengthMismatch(MaskError):
+    def __init__(self, expected: int, got: int):
+        self.expected, self.got = expected, got
+        super().__init__(f"mask error: padding mask len {got}, expected {expected}")
+
+
+# ---------------------------------------------------------------- shape and mask
+@dataclass
+class AttentionShape:
+    """cpu_forward.rs:49-89.  ``br``/``bc`` are kept for signature parity; they only change the
+    summation order of the CPU reference and are ignored by the GPU kernels."""
+    batch: int
+    heads: int
+    seq: int
+    dim: int
+    br: int = 64
+    bc: int = 64
+
+    @classmethod
+    def new(cls, batch: int, heads: int, seq: int, dim: int) -> "AttentionShape":
+        return cls(batch, heads, seq, dim)
+
+    def buffer_len(self) -> int:
+        return self.batch * self.heads * self.seq * self.dim
+
+
+class Mask:
+    """mask.rs:26-66: ``Mask.none()``, ``Mask.causal()``, ``Mask.padding(keep)``."""
+    NONE, CAUSAL, PADDING = 0, 1, 2
+
+    def __init__(self, kind: int, keep=None):
+        self.kind = kind
+        self.keep = None if keep is None else np.ascontiguousarray(keep, dtype=np.bool_)
+
+    @classmethod
+    def none(cls) -> "Mask":
+        return cls(cls.NONE)
+
+    @classmethod
+    def causal(cls) -> "Mask":
+        return cls(cls.CAUSAL)
+
+    @classmethod
+    def padding(cls, keep) -> "Mask":
+        return cls(cls.PADDING, keep)
+
+    def is_masked(self, qi: int, kj: int) -> bool:
+        if self.kind == Mask.CAUSAL:
+            return kj > qi
+        if self.kind == Mask.PADDING:
+            return kj < len(self.keep) and not bool(self.keep[kj])
+        return False
+
+    def validate(self, seq: int) -> None:
+        if self.kind == Mask.PADDING and len(self.keep) != seq:
+            raise PaddingLengthMismatch(seq, len(self.keep))
+
+
+def _validate(shape: AttentionShape, q, k, v, out) -> None:  # cpu_forward.rs:142-169
+    if shape.dim == 0:
+        raise ZeroDim()
+    expected = shape.buffer_len()
+    for which, buf in (("q", q), ("k", k), ("v", v)):
+        if buf.size != expected:
+            raise BufferShapeMismatch(which, expected, buf.size)
+    if out.size != expected:
+        raise OutputShapeMismatch(expected, out.size)
+
+
+def _f32(a, name):
+    if not isinstance(a, np.ndarray) or a.dtype != np.float32 or not a.flags["C_CONTIGUOUS"]:
+        raise TypeError(f"{name} must be a C-contiguous float32 numpy array")
+    return a.ctypes.data_as(POINTER(c_float))
+
+
+def flash_forward(shape: AttentionShape, q, k, v, out, precision: str = "f32") -> None:
+    """cpu_forward.rs:175-183."""
+    flash_forward_masked(shape, q, k, v, Mask.none(), out, precision)
+
+
+def flash_forward_masked(shape: AttentionShape, q, k, v, mask: Mask, out, precision: str = "f32") -> None:
+    """cpu_forward.rs:193-242 on the GPU.  ``precision``: "f32" = f32 CUDA-core kernel (parity with
+    the f32 reference at 1e-4), "bf16" = inputs rounded to bf16, tcgen05 kernel (D in {64,128})."""
+    _validate(shape, q, k, v, out)
+    mask.validate(shape.seq)
+    if shape.seq == 0:
+        return
+    keep_ptr, keep_len = None, 0
+    if mask.kind == Mask.PADDING:
+        keep_u8 = mask.keep.astype(np.uint8)
+        keep_ptr, keep_len = keep_u8.ctypes.data_as(POINTER(c_uint8)), keep_u8.size
+    prec = {"f32": _lib.RT_PRECISION_F32, "bf16": _lib.RT_PRECISION_BF16}[precision]
+    rc = _lib.lib().rt_flash_forward_f32_host(_f32(q, "q"), q.size, _f32(k, "k"), k.size, _f32(v, "v"), v.size,
+                                              _f32(out, "out"), out.size, shape.batch, shape.heads, shape.seq,
+                                              shape.dim, mask.kind, keep_ptr, keep_len, prec)
+    if rc == _lib.RT_ERR_ZERO_DIM:
+        raise ZeroDim()
+    if rc == _lib.RT_ERR_MASK_LEN:
+        raise PaddingLengthMismatch(shape.seq, keep_len)
+    _lib.check(rc, "rt_flash_forward_f32_host")
+
+
+# ---------------------------------------------------------------- device-resident entry (torch tensors)
+def _stream_ptr():
+    import torch
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def prefill_bf16(q, k, v, causal: bool = False, kv_lens=None, key_keep=None, scale: Optional[float] = None,
+                 out=None, lse=None, return_lse: bool = True):
+    """Flash-attention forward on bf16 CUDA tensors [B,H,N,D] (D in {64,128}) via ``rt_attn_prefill_bf16``.
+
+    kv_lens: optional int32 CUDA tensor [B]; key_keep: optional uint8/bool CUDA tensor [N] or [B,N].
+    Returns (out bf16 [B,H,N,D], lse f32 [B,H,N] or None).  Enqueues on the current stream.
+    """
+    import torch
+    for name, t in (("q", q), ("k", k), ("v", v)):
+        if not (t.is_cuda and t.dtype == torch.bfloat16 and t.is_contiguous() and t.dim() == 4):
+            raise TypeError(f"{name} must be a contiguous 4-D bfloat16 CUDA tensor")
+    B, H, N, D = q.shape
+    if k.shape != q.shape or v.shape != q.shape:
+        raise BufferShapeMismatch("k/v", q.numel(), k.numel())
+    if out is None:
+        out = torch.empty_like(q)
+    if lse is None and return_lse:
+        lse = torch.empty((B, H, N), dtype=torch.float32, device=q.device)
+    keep_ptr, keep_stride = None, 0
+    if key_keep is not None:
+        key_keep = key_keep.to(torch.uint8).contiguous()
+        if key_keep.shape[-1] != N:
+            raise PaddingLengthMismatch(N, key_keep.shape[-1])
+        keep_stride = N if key_keep.dim() == 2 else 0
+        keep_ptr = key_keep.data_ptr()
+    lens_ptr = None
+    if kv_lens is not None:
+        if not (kv_lens.is_cuda and kv_lens.dtype == torch.int32 and kv_lens.numel() == B):
+            raise TypeError("kv_lens must be an int32 CUDA tensor of B elements")
+        lens_ptr = kv_lens.data_ptr()
+    rc = _lib.lib().rt_attn_prefill_bf16(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
+                                         lse.data_ptr() if lse is not None else None, B, H, N, D,
+                                         _lib.RT_MASK_CAUSAL if causal else _lib.RT_MASK_NONE, lens_ptr, keep_ptr,
+                                         keep_stride, -1.0 if scale is None else float(scale), _stream_ptr())
+    if rc == _lib.RT_ERR_ZERO_DIM:
+        raise ZeroDim()
+    _lib.check(rc, "rt_attn_prefill_bf16")
+    return out, lse
+
+
+def prefill_f32(q, k, v, causal: bool = False, kv_lens=None, key_keep=None, scale: Optional[float] = None):
+    """f32 CUDA-core forward on f32 CUDA tensors q [B,Hq,Nq,D], k/v [B,Hkv,Nkv,D] via ``rt_attn_prefill_f32``."""
+    import torch
+    B, Hq, Nq, D = q.shape
+    _, Hkv, Nkv, _ = k.shape
+    out = torch.empty_like(q)
+    lse = torch.empty((B, Hq, Nq), dtype=torch.float32, device=q.device)
+    keep_ptr, keep_stride = None, 0
+    if key_keep is not None:
+        key_keep = key_keep.to(torch.uint8).contiguous()
+        keep_stride = Nkv if key_keep.dim() == 2 else 0
+        keep_ptr = key_keep.data_ptr()
+    rc = _lib.lib().rt_attn_prefill_f32(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(), B,
+                                        Hq, Hkv, Nq, Nkv, D, _lib.RT_MASK_CAUSAL if causal else _lib.RT_MASK_NONE,
+                                        kv_lens.data_ptr() if kv_lens is not None else None, keep_ptr, keep_stride,
+                                        -1.0 if scale is None else float(scale), _stream_ptr())
+    if rc == _lib.RT_ERR_ZERO_DIM:
+        raise ZeroDim()
+    _lib.check(rc, "rt_attn_prefill_f32")
+    return out, lse

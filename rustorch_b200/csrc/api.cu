@@ -1,0 +1,329 @@
+// extern "C" boundary of the attention library: argument validation (mirroring the reference's
+// validate() / Mask::validate / gqa_forward_f32 checks) and dispatch to the sm_100a kernels.
+// Nothing here computes attention on the host: without a CUDA device every compute entry fails.
+#include <cmath>
+#include <cstdlib>
+
+#include "../../include/rustorch_attn.h"
+#include "common.cuh"
+#include "kernels.h"
+
+namespace rt {
+__device__ int g_device_status = 0;
+
+int* device_status_ptr() {
+    static int* cache[64] = {nullptr};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (!cache[dev]) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_device_status) != cudaSuccess) return nullptr;
+        cache[dev] = static_cast<int*>(p);
+    }
+    return cache[dev];
+}
+}  // namespace rt
+
+namespace {
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+inline cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
+inline float default_scale(float scale, int dim) { return scale > 0.f ? scale : 1.0f / std::sqrt((float)dim); }
+
+// RAII device buffer for the blocking host entry points.
+struct DevBuf {
+    void* p = nullptr;
+    cudaError_t alloc(size_t bytes) { return cudaMalloc(&p, bytes ? bytes : 1); }
+    ~DevBuf() {
+        if (p) cudaFree(p);
+    }
+    template <class T>
+    T* as() const { return static_cast<T*>(p); }
+};
+
+#define RT_CUDA(expr)                         \
+    do {                                      \
+        cudaError_t _e = (expr);              \
+        if (_e != cudaSuccess) return (int)_e; \
+    } while (0)
+
+}  // namespace
+
+extern "C" {
+
+int rt_attn_version(void) { return 100; }
+
+const char* rt_attn_error_string(int status) {
+    switch (status) {
+        case RT_OK: return "ok";
+        case RT_ERR_ZERO_DIM: return "dim must be > 0";
+        case RT_ERR_BUFFER_SHAPE: return "q/k/v buffer length does not match the shape";
+        case RT_ERR_OUTPUT_SHAPE: return "output buffer length does not match the shape";
+        case RT_ERR_MASK_LEN: return "padding mask length does not match seq";
+        case RT_ERR_HEAD_COUNT: return "n_heads not divisible by n_kv_heads";
+        case RT_ERR_WRONG_INPUT_LEN: return "gqa buffer length does not match the shape";
+        case RT_ERR_UNSUPPORTED: return "shape not supported by the sm_100a kernels";
+        case RT_ERR_NULL_POINTER: return "required pointer is NULL";
+        case RT_ERR_BAD_LENGTH: return "negative size or kv_len > max_seq";
+        case RT_ERR_WORKSPACE: return "workspace missing or too small";
+        case RT_ERR_ALIGNMENT: return "device pointer not 16-byte aligned";
+        case RT_ERR_DEVICE_TIMEOUT: return "a bounded device-side wait expired";
+        default: return status > 0 ? cudaGetErrorString((cudaError_t)status) : "unknown status";
+    }
+}
+
+int rt_attn_device_status(int* status) {
+    if (!status) return RT_ERR_NULL_POINTER;
+    RT_CUDA(cudaDeviceSynchronize());
+    int v = 0;
+    RT_CUDA(cudaMemcpyFromSymbol(&v, rt::g_device_status, sizeof(int)));
+    if (v != 0) {
+        const int zero = 0;
+        RT_CUDA(cudaMemcpyToSymbol(rt::g_device_status, &zero, sizeof(int)));
+    }
+    *status = v;
+    return v ? RT_ERR_DEVICE_TIMEOUT : RT_OK;
+}
+
+// ------------------------------------------------------------------------------ prefill
+
+int rt_attn_prefill_bf16(const void* q, const void* k, const void* v, void* out, float* lse, int64_t batch,
+                         int64_t heads, int64_t seq, int dim, int mask_flags, const int32_t* kv_lens,
+                         const uint8_t* key_keep, int64_t keep_batch_stride, float scale, void* stream) {
+    if (dim == 0) return RT_ERR_ZERO_DIM;
+    if (batch < 0 || heads < 0 || seq < 0 || dim < 0 || keep_batch_stride < 0) return RT_ERR_BAD_LENGTH;
+    if (batch == 0 || heads == 0 || seq == 0) return RT_OK;  // cpu_forward.rs:203-206
+    if (!q || !k || !v || !out) return RT_ERR_NULL_POINTER;
+    if (dim != 64 && dim != 128) return RT_ERR_UNSUPPORTED;
+    if (seq > (1 << 30) || batch * heads > (1 << 30)) return RT_ERR_UNSUPPORTED;
+    if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(out)) return RT_ERR_ALIGNMENT;
+    if (mask_flags & ~RT_MASK_CAUSAL) return RT_ERR_UNSUPPORTED;
+    RT_CUDA(rt::launch_prefill_tc(q, k, v, out, lse, batch, heads, seq, dim, mask_flags & RT_MASK_CAUSAL, kv_lens,
+                                  key_keep, keep_batch_stride, default_scale(scale, dim), as_stream(stream)));
+    return RT_OK;
+}
+
+int rt_attn_prefill_f32(const float* q, const float* k, const float* v, float* out, float* lse, int64_t batch,
+                        int64_t heads_q, int64_t heads_kv, int64_t seq_q, int64_t seq_kv, int dim, int mask_flags,
+                        const int32_t* kv_lens, const uint8_t* key_keep, int64_t keep_batch_stride, float scale,
+                        void* stream) {
+    if (dim == 0) return RT_ERR_ZERO_DIM;
+    if (batch < 0 || heads_q < 0 || heads_kv < 0 || seq_q < 0 || seq_kv < 0 || dim < 0) return RT_ERR_BAD_LENGTH;
+    if (heads_kv == 0 || heads_q % heads_kv != 0) return heads_q == 0 ? RT_OK : RT_ERR_HEAD_COUNT;
+    if (batch == 0 || heads_q == 0 || seq_q == 0) return RT_OK;
+    if (!q || !out || (seq_kv > 0 && (!k || !v))) return RT_ERR_NULL_POINTER;
+    if (dim > 256) return RT_ERR_UNSUPPORTED;
+    if (mask_flags & ~RT_MASK_CAUSAL) return RT_ERR_UNSUPPORTED;
+    RT_CUDA(rt::launch_prefill_f32(q, k, v, out, lse, batch, heads_q, heads_kv, seq_q, seq_kv, dim,
+                                   mask_flags & RT_MASK_CAUSAL, kv_lens, key_keep, keep_batch_stride,
+                                   default_scale(scale, dim), as_stream(stream)));
+    return RT_OK;
+}
+
+int rt_flash_forward_f32_host(const float* q, size_t q_len, const float* k, size_t k_len, const float* v,
+                              size_t v_len, float* out, size_t out_len, int64_t batch, int64_t heads, int64_t seq,
+                              int64_t dim, int mask_kind, const uint8_t* keep, size_t keep_len, int precision) {
+    // validate(): cpu_forward.rs:142-169
+    if (dim == 0) return RT_ERR_ZERO_DIM;
+    if (batch < 0 || heads < 0 || seq < 0 || dim < 0) return RT_ERR_BAD_LENGTH;
+    const size_t expected = (size_t)batch * (size_t)heads * (size_t)seq * (size_t)dim;
+    if (q_len != expected || k_len != expected || v_len != expected) return RT_ERR_BUFFER_SHAPE;
+    if (out_len != expected) return RT_ERR_OUTPUT_SHAPE;
+    // Mask::validate: mask.rs:51-65
+    if (mask_kind < RT_MASKKIND_NONE || mask_kind > RT_MASKKIND_PADDING) return RT_ERR_UNSUPPORTED;
+    if (mask_kind == RT_MASKKIND_PADDING && keep_len != (size_t)seq) return RT_ERR_MASK_LEN;
+    if (seq == 0 || expected == 0) return RT_OK;
+    if (!q || !k || !v || !out) return RT_ERR_NULL_POINTER;
+    if (mask_kind == RT_MASKKIND_PADDING && !keep) return RT_ERR_NULL_POINTER;
+    if (precision != RT_PRECISION_F32 && precision != RT_PRECISION_BF16) return RT_ERR_UNSUPPORTED;
+    if (precision == RT_PRECISION_BF16 && dim != 64 && dim != 128) return RT_ERR_UNSUPPORTED;
+    if (precision == RT_PRECISION_F32 && dim > 256) return RT_ERR_UNSUPPORTED;
+
+    const size_t bytes = expected * sizeof(float);
+    DevBuf dq, dk, dv, dout, dkeep;
+    RT_CUDA(dq.alloc(bytes));
+    RT_CUDA(dk.alloc(bytes));
+    RT_CUDA(dv.alloc(bytes));
+    RT_CUDA(dout.alloc(bytes));
+    RT_CUDA(cudaMemcpy(dq.p, q, bytes, cudaMemcpyHostToDevice));
+    RT_CUDA(cudaMemcpy(dk.p, k, bytes, cudaMemcpyHostToDevice));
+    RT_CUDA(cudaMemcpy(dv.p, v, bytes, cudaMemcpyHostToDevice));
+    const uint8_t* keep_dev = nullptr;
+    if (mask_kind == RT_MASKKIND_PADDING) {
+        RT_CUDA(dkeep.alloc(keep_len));
+        RT_CUDA(cudaMemcpy(dkeep.p, keep, keep_len, cudaMemcpyHostToDevice));
+        keep_dev = dkeep.as<uint8_t>();
+    }
+    const int flags = (mask_kind == RT_MASKKIND_CAUSAL) ? RT_MASK_CAUSAL : RT_MASK_NONE;
+    if (precision == RT_PRECISION_F32) {
+        int rc = rt_attn_prefill_f32(dq.as<float>(), dk.as<float>(), dv.as<float>(), dout.as<float>(), nullptr,
+                                     batch, heads, heads, seq, seq, (int)dim, flags, nullptr, keep_dev, 0, -1.f,
+                                     nullptr);
+        if (rc != RT_OK) return rc;
+    } else {
+        DevBuf bq, bk, bv, bo;
+        RT_CUDA(bq.alloc(expected * 2));
+        RT_CUDA(bk.alloc(expected * 2));
+        RT_CUDA(bv.alloc(expected * 2));
+        RT_CUDA(bo.alloc(expected * 2));
+        RT_CUDA(rt::launch_f32_to_bf16(dq.as<float>(), bq.p, (int64_t)expected, nullptr));
+        RT_CUDA(rt::launch_f32_to_bf16(dk.as<float>(), bk.p, (int64_t)expected, nullptr));
+        RT_CUDA(rt::launch_f32_to_bf16(dv.as<float>(), bv.p, (int64_t)expected, nullptr));
+        int rc = rt_attn_prefill_bf16(bq.p, bk.p, bv.p, bo.p, nullptr, batch, heads, seq, (int)dim, flags, nullptr,
+                                      keep_dev, 0, -1.f, nullptr);
+        if (rc != RT_OK) return rc;
+        RT_CUDA(rt::launch_bf16_to_f32(bo.p, dout.as<float>(), (int64_t)expected, nullptr));
+        RT_CUDA(cudaDeviceSynchronize());
+    }
+    RT_CUDA(cudaMemcpy(out, dout.p, bytes, cudaMemcpyDeviceToHost));
+    return RT_OK;
+}
+
+int rt_attn_prefill_bf16_host(const void* q, const void* k, const void* v, void* out, float* lse, int64_t batch,
+                              int64_t heads, int64_t seq, int dim, int mask_flags, const int32_t* kv_lens,
+                              float scale) {
+    if (dim == 0) return RT_ERR_ZERO_DIM;
+    if (batch < 0 || heads < 0 || seq < 0 || dim < 0) return RT_ERR_BAD_LENGTH;
+    const size_t n = (size_t)batch * heads * seq * dim;
+    if (n == 0) return RT_OK;
+    if (!q || !k || !v || !out) return RT_ERR_NULL_POINTER;
+    DevBuf dq, dk, dv, dout, dlse, dlens;
+    RT_CUDA(dq.alloc(n * 2));
+    RT_CUDA(dk.alloc(n * 2));
+    RT_CUDA(dv.alloc(n * 2));
+    RT_CUDA(dout.alloc(n * 2));
+    cudaStream_t s = nullptr;
+    RT_CUDA(cudaMemcpyAsync(dq.p, q, n * 2, cudaMemcpyHostToDevice, s));
+    RT_CUDA(cudaMemcpyAsync(dk.p, k, n * 2, cudaMemcpyHostToDevice, s));
+    RT_CUDA(cudaMemcpyAsync(dv.p, v, n * 2, cudaMemcpyHostToDevice, s));
+    const size_t rows = (size_t)batch * heads * seq;
+    if (lse) RT_CUDA(dlse.alloc(rows * 4));
+    if (kv_lens) {
+        RT_CUDA(dlens.alloc((size_t)batch * 4));
+        RT_CUDA(cudaMemcpyAsync(dlens.p, kv_lens, (size_t)batch * 4, cudaMemcpyHostToDevice, s));
+    }
+    int rc = rt_attn_prefill_bf16(dq.p, dk.p, dv.p, dout.p, lse ? dlse.as<float>() : nullptr, batch, heads, seq, dim,
+                                  mask_flags, kv_lens ? dlens.as<int32_t>() : nullptr, nullptr, 0, scale, s);
+    if (rc != RT_OK) return rc;
+    RT_CUDA(cudaMemcpyAsync(out, dout.p, n * 2, cudaMemcpyDeviceToHost, s));
+    if (lse) RT_CUDA(cudaMemcpyAsync(lse, dlse.p, rows * 4, cudaMemcpyDeviceToHost, s));
+    RT_CUDA(cudaStreamSynchronize(s));
+    return RT_OK;
+}
+
+// ------------------------------------------------------------------------------ decode
+
+size_t rt_gqa_decode_workspace_bytes(int64_t batch, int64_t n_heads, int64_t n_kv_heads, int head_dim,
+                                     int64_t max_seq) {
+    (void)n_kv_heads;
+    if (batch <= 0 || n_heads <= 0 || head_dim <= 0 || max_seq <= 0) return 0;
+    const size_t chunks = (size_t)rt::decode_num_chunks(max_seq);
+    if (chunks <= 1) return 0;
+    return chunks * (size_t)batch * (size_t)n_heads * ((size_t)head_dim + 1) * sizeof(float);
+}
+
+int rt_gqa_decode_bf16(const void* q, const void* k_cache, const void* v_cache, void* out_bf16, float* out_f32,
+                       float* lse, int64_t batch, int64_t n_heads, int64_t n_kv_heads, int head_dim, int64_t max_seq,
+                       const int32_t* kv_lens, int64_t kv_len_uniform, int64_t kv_begin, int64_t kv_end, float scale,
+                       void* workspace, size_t workspace_bytes, void* stream) {
+    if (n_kv_heads <= 0 || n_heads <= 0 || n_heads % n_kv_heads != 0) return RT_ERR_HEAD_COUNT;  // gqa.rs:106-111
+    if (head_dim == 0) return RT_ERR_ZERO_DIM;
+    if (batch < 0 || max_seq <= 0 || kv_begin < 0 || head_dim < 0) return RT_ERR_BAD_LENGTH;
+    if (!kv_lens && (kv_len_uniform < 0 || kv_len_uniform > max_seq)) return RT_ERR_BAD_LENGTH;
+    if (batch == 0) return RT_OK;
+    if (!q || !k_cache || !v_cache || (!out_bf16 && !out_f32)) return RT_ERR_NULL_POINTER;
+    const int64_t group = n_heads / n_kv_heads;
+    if (head_dim != 64 && head_dim != 128 && head_dim != 256) return RT_ERR_UNSUPPORTED;
+    if (group != 1 && group != 2 && group != 4 && group != 8) return RT_ERR_UNSUPPORTED;
+    if (batch > 65535 || n_kv_heads > 65535) return RT_ERR_UNSUPPORTED;
+    if (!aligned16(q) || !aligned16(k_cache) || !aligned16(v_cache)) return RT_ERR_ALIGNMENT;
+    const size_t need = rt_gqa_decode_workspace_bytes(batch, n_heads, n_kv_heads, head_dim, max_seq);
+    if (need > 0 && (!workspace || workspace_bytes < need)) return RT_ERR_WORKSPACE;
+    RT_CUDA(rt::launch_gqa_decode(q, k_cache, v_cache, out_bf16, out_f32, lse, batch, (int)n_heads, (int)n_kv_heads,
+                                  head_dim, max_seq, kv_lens, kv_len_uniform, kv_begin, kv_end,
+                                  default_scale(scale, head_dim), need ? workspace : nullptr, as_stream(stream)));
+    return RT_OK;
+}
+
+int rt_gqa_decode_online_bf16(const void* q, const void* k_cache, const void* v_cache, void* out, int n_heads,
+                              int n_kv, int kv_len, int head_dim, int max_seq, void* workspace,
+                              size_t workspace_bytes, void* stream) {
+    return rt_gqa_decode_bf16(q, k_cache, v_cache, out, nullptr, nullptr, 1, n_heads, n_kv, head_dim, max_seq, nullptr,
+                              kv_len, 0, -1, -1.f, workspace, workspace_bytes, stream);
+}
+
+int rt_attn_merge_partials(const float* o_parts, const float* lse_parts, int64_t n_parts, int64_t rows, int dim,
+                           void* out_bf16, float* out_f32, float* lse, void* stream) {
+    if (dim == 0) return RT_ERR_ZERO_DIM;
+    if (n_parts < 0 || rows < 0 || dim < 0 || n_parts > 0x7fffffff) return RT_ERR_BAD_LENGTH;
+    if (rows == 0) return RT_OK;
+    if ((n_parts > 0 && (!o_parts || !lse_parts)) || (!out_bf16 && !out_f32)) return RT_ERR_NULL_POINTER;
+    RT_CUDA(rt::launch_merge_partials(o_parts, lse_parts, n_parts, rows, dim, out_bf16, out_f32, lse,
+                                      as_stream(stream)));
+    return RT_OK;
+}
+
+int rt_gqa_forward_f32_host(const float* q, size_t q_len, const float* k, size_t k_len, const float* v, size_t v_len,
+                            float* out, size_t out_len, int64_t batch, int64_t n_heads, int64_t n_kv_heads,
+                            int64_t seq_q, int64_t seq_kv, int64_t head_dim) {
+    // gqa.rs:106-141
+    if (n_kv_heads <= 0 || n_heads < 0 || n_heads % n_kv_heads != 0) return RT_ERR_HEAD_COUNT;
+    if (batch < 0 || seq_q < 0 || seq_kv < 0 || head_dim < 0) return RT_ERR_BAD_LENGTH;
+    const size_t qn = (size_t)batch * n_heads * seq_q * head_dim;
+    const size_t kn = (size_t)batch * n_kv_heads * seq_kv * head_dim;
+    if (q_len != qn || k_len != kn || v_len != kn || out_len != qn) return RT_ERR_WRONG_INPUT_LEN;
+    if (qn == 0) return RT_OK;
+    if (head_dim > 256) return RT_ERR_UNSUPPORTED;
+    if (!q || !out || (kn > 0 && (!k || !v))) return RT_ERR_NULL_POINTER;
+    DevBuf dq, dk, dv, dout;
+    RT_CUDA(dq.alloc(qn * 4));
+    RT_CUDA(dk.alloc(kn * 4));
+    RT_CUDA(dv.alloc(kn * 4));
+    RT_CUDA(dout.alloc(qn * 4));
+    RT_CUDA(cudaMemcpy(dq.p, q, qn * 4, cudaMemcpyHostToDevice));
+    if (kn) {
+        RT_CUDA(cudaMemcpy(dk.p, k, kn * 4, cudaMemcpyHostToDevice));
+        RT_CUDA(cudaMemcpy(dv.p, v, kn * 4, cudaMemcpyHostToDevice));
+    }
+    if (seq_kv == 0) {
+        // The reference's row kernel returns zeros when there is nothing to attend to (gqa.rs:262-269).
+        RT_CUDA(cudaMemset(dout.p, 0, qn * 4));
+    } else {
+        int rc = rt_attn_prefill_f32(dq.as<float>(), dk.as<float>(), dv.as<float>(), dout.as<float>(), nullptr, batch,
+                                     n_heads, n_kv_heads, seq_q, seq_kv, (int)head_dim, RT_MASK_NONE, nullptr,
+                                     nullptr, 0, -1.f, nullptr);
+        if (rc != RT_OK) return rc;
+    }
+    RT_CUDA(cudaMemcpy(out, dout.p, qn * 4, cudaMemcpyDeviceToHost));
+    return RT_OK;
+}
+
+int rt_kv_append_bf16(void* k_cache, void* v_cache, const void* k_in, const void* v_in, int64_t batch, int n_kv,
+                      int head_dim, int64_t max_seq, int64_t pos, const int32_t* positions, void* stream) {
+    if (batch < 0 || n_kv < 0 || head_dim < 0 || max_seq < 0) return RT_ERR_BAD_LENGTH;
+    if (!positions && (pos < 0 || pos >= max_seq)) return RT_ERR_BAD_LENGTH;  // kv_cache.rs:88-93 overflow
+    if (batch == 0 || n_kv == 0 || head_dim == 0) return RT_OK;
+    if (!k_cache || !v_cache || !k_in || !v_in) return RT_ERR_NULL_POINTER;
+    if (batch > 65535) return RT_ERR_UNSUPPORTED;
+    RT_CUDA(rt::launch_kv_append(k_cache, v_cache, k_in, v_in, batch, n_kv, head_dim, max_seq, pos, positions,
+                                 as_stream(stream)));
+    return RT_OK;
+}
+
+int rt_convert_f32_to_bf16(const float* src, void* dst, int64_t n, void* stream) {
+    if (n < 0) return RT_ERR_BAD_LENGTH;
+    if (n == 0) return RT_OK;
+    if (!src || !dst) return RT_ERR_NULL_POINTER;
+    RT_CUDA(rt::launch_f32_to_bf16(src, dst, n, as_stream(stream)));
+    return RT_OK;
+}
+
+int rt_convert_bf16_to_f32(const void* src, float* dst, int64_t n, void* stream) {
+    if (n < 0) return RT_ERR_BAD_LENGTH;
+    if (n == 0) return RT_OK;
+    if (!src || !dst) return RT_ERR_NULL_POINTER;
+    RT_CUDA(rt::launch_bf16_to_f32(src, dst, n, as_stream(stream)));
+    return RT_OK;
+}
+
+}  // extern "C"

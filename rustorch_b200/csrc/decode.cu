@@ -1,0 +1,444 @@
+// Split-KV GQA decode for a bf16 KV cache, plus the (O, LSE) merge kernel.
+//
+// Replaces the reference's one-CTA-per-query-head decode kernels
+// (crates/rustorch-cuda/src/llm_kernels.rs:376-536) and the seq_q == 1 branch of
+// gqa_forward_f32 (crates/rustorch-nn/src/gqa.rs:190-270).
+//
+// The path is HBM-bound (4 FLOP per KV byte at Hq/Hkv = 4), so the design is about
+// streaming the cache once, fully coalesced, with many bytes in flight:
+//   * one CTA per (sequence, KV head, KV chunk); the G = Hq/Hkv query heads of a group are
+//     processed together so every K/V element is fetched once (the reference re-reads the
+//     cache once per query head);
+//   * a token row (D bf16) is spread over D/8 lanes, 16 bytes per lane, so one warp load
+//     instruction covers 512 contiguous bytes; the next block of K and V rows is prefetched
+//     into registers while the current one is consumed;
+//   * the q.k partial sums of G heads x T tokens are reduced across the D/8 lanes with a
+//     recursive-halving exchange (V-1 shuffles instead of V*log2(D/8)), which also leaves
+//     exactly one (head, token) score per lane, so each exponential is evaluated once;
+//   * per lane-group online softmax in the log2 domain with a warp-uniform lazy rescale;
+//   * chunk results are written as normalised (O f32, LSE) partials and merged by
+//     merge_partials_kernel, the same kernel that merges per-GPU partials.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace rt {
+
+template <int D, int G>
+struct DecodeCfg {
+    static constexpr int LPT = D / 8;                 // lanes per token row
+    static constexpr int TPI = 32 / LPT;              // token rows per warp load instruction
+    static constexpr int T = (LPT / G >= 4) ? 4 : ((LPT / G >= 1) ? LPT / G : 1);  // rows per lane-group per step
+    static constexpr int V = G * T;                   // scores reduced per step
+    static constexpr int R = LPT / V;                 // replication of a score after the reduce
+    static constexpr int TOK = TPI * T;               // token rows per warp step
+    static constexpr int NW = 4;                      // warps per CTA
+    static constexpr int NG = NW * TPI;               // lane-groups per CTA
+    static_assert(V <= LPT, "scores per step must not exceed lanes per token");
+};
+
+struct DecodeParams {
+    const __nv_bfloat16* q;
+    const __nv_bfloat16* k;
+    const __nv_bfloat16* v;
+    __nv_bfloat16* out_bf16;
+    float* out_f32;
+    float* lse;
+    float* part_o;    // [n_chunks, rows, D]
+    float* part_lse;  // [n_chunks, rows]
+    const int32_t* kv_lens;
+    int64_t kv_len_uniform;
+    int64_t kv_begin, kv_end;
+    int64_t max_seq;
+    int n_heads, n_kv;
+    int chunk, n_chunks;
+    int64_t rows;  // B * Hq
+    float scale_log2;
+};
+
+template <int D, int G>
+__global__ void __launch_bounds__(128) gqa_decode_splitkv_kernel(const DecodeParams p) {
+    using C = DecodeCfg<D, G>;
+    constexpr int LPT = C::LPT, TPI = C::TPI, T = C::T, V = C::V, R = C::R, TOK = C::TOK, NW = C::NW,
+                  NG = C::NG;
+
+    __shared__ float sm_m[NG][G];
+    __shared__ float sm_l[NG][G];
+    __shared__ __align__(16) float sm_o[NG][G][D];
+
+    const int chunk_idx = blockIdx.x;
+    const int kvh = blockIdx.y;
+    const int b = blockIdx.z;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int gi = lane / LPT;   // lane-group within the warp
+    const int lig = lane % LPT;  // lane within the group: owns dims [lig*8, lig*8+8)
+    const int64_t row0 = (int64_t)b * p.n_heads + (int64_t)kvh * G;  // first output row of the group
+    const bool direct = (p.n_chunks == 1);
+
+    int64_t len = p.kv_lens ? (int64_t)p.kv_lens[b] : p.kv_len_uniform;
+    if (len > p.max_seq) len = p.max_seq;
+    int64_t hi = (p.kv_end >= 0 && p.kv_end < len) ? p.kv_end : len;
+    const int64_t c0 = p.kv_begin + (int64_t)chunk_idx * p.chunk;
+    int64_t c1 = c0 + p.chunk;
+    if (c1 > hi) c1 = hi;
+
+    if (c0 >= c1) {  // nothing visible in this chunk: identity partial
+        if (direct) {
+            for (int i = tid; i < G * D; i += 128) {
+                const int64_t o = (row0 + i / D) * D + i % D;
+                if (p.out_bf16) p.out_bf16[o] = __float2bfloat16(0.f);
+                if (p.out_f32) p.out_f32[o] = 0.f;
+            }
+            if (tid < G && p.lse) p.lse[row0 + tid] = -INFINITY;
+        } else if (tid < G) {
+            p.part_lse[(int64_t)chunk_idx * p.rows + row0 + tid] = -INFINITY;
+        }
+        return;
+    }
+
+    // q of the G heads, my 8 dims, pre-multiplied by scale*log2(e).
+    float2 q2[G][4];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        const uint4 w = *reinterpret_cast<const uint4*>(p.q + (row0 + g) * D + lig * 8);
+        const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f = bf16x2_to_float2(ww[i]);
+            q2[g][i] = make_float2(f.x * p.scale_log2, f.y * p.scale_log2);
+        }
+    }
+
+    const __nv_bfloat16* kbase = p.k + ((int64_t)b * p.n_kv + kvh) * p.max_seq * D + lig * 8;
+    const __nv_bfloat16* vbase = p.v + ((int64_t)b * p.n_kv + kvh) * p.max_seq * D + lig * 8;
+
+    // Online-softmax state of this lane-group.  A lane tracks the head g_own of the one
+    // score it receives from the reduce; O accumulators cover all G heads for my 8 dims.
+    const int idx_own = lig / R;      // which of the V scores lands here
+    const int g_own = idx_own / T;
+    float m_run = -INFINITY;          // running max (log2 domain) of head g_own
+    float l_part = 0.f;               // my share of the running sum of head g_own
+    float2 o2[G][4];
+#pragma unroll
+    for (int g = 0; g < G; ++g)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) o2[g][i] = make_float2(0.f, 0.f);
+
+    uint4 kreg[T], vreg[T], knext[T], vnext[T];
+    auto load_block = [&](int64_t tb, uint4(&kk)[T], uint4(&vv)[T]) {
+#pragma unroll
+        for (int j = 0; j < T; ++j) {
+            const int64_t t = tb + j * TPI + gi;
+            if (t < c1) {
+                kk[j] = ld_stream_16B(kbase + t * D);
+                vv[j] = ld_stream_16B(vbase + t * D);
+            } else {
+                kk[j] = make_uint4(0, 0, 0, 0);
+                vv[j] = make_uint4(0, 0, 0, 0);
+            }
+        }
+    };
+
+    int64_t tb = c0 + (int64_t)warp * TOK;
+    if (tb < c1) load_block(tb, knext, vnext);
+    for (; tb < c1; tb += NW * TOK) {
+#pragma unroll
+        for (int j = 0; j < T; ++j) {
+            kreg[j] = knext[j];
+            vreg[j] = vnext[j];
+        }
+        if (tb + NW * TOK < c1) load_block(tb + NW * TOK, knext, vnext);
+
+        // ---- scores: partial dot products over my 8 dims, then reduce across the group
+        float s[V];
+#pragma unroll
+        for (int j = 0; j < T; ++j) {
+            const uint32_t kw[4] = {kreg[j].x, kreg[j].y, kreg[j].z, kreg[j].w};
+            float2 k2[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) k2[i] = bf16x2_to_float2(kw[i]);
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                float2 acc = __fmul2_rn(q2[g][0], k2[0]);
+#pragma unroll
+                for (int i = 1; i < 4; ++i) acc = __ffma2_rn(q2[g][i], k2[i], acc);
+                s[g * T + j] = acc.x + acc.y;
+            }
+        }
+        {
+            int n = V;
+#pragma unroll
+            for (int off = LPT / 2; off >= 1; off >>= 1) {
+                if (n > 1) {
+                    const bool up = (lig & off) != 0;
+#pragma unroll
+                    for (int i = 0; i < n / 2; ++i) {
+                        const float send = up ? s[i] : s[i + n / 2];
+                        const float keep = up ? s[i + n / 2] : s[i];
+                        s[i] = keep + __shfl_xor_sync(kFullMask, send, off);
+                    }
+                    n /= 2;
+                } else {
+                    s[0] += __shfl_xor_sync(kFullMask, s[0], off);
+                }
+            }
+        }
+        // s[0] is now the full score of (head g_own, token slot j_own).
+        const int j_own = idx_own % T;
+        const int64_t t_own = tb + j_own * TPI + gi;
+        float sc = (t_own < c1) ? s[0] : -INFINITY;
+
+        // ---- online softmax for head g_own over the T tokens of this step
+        float m_step = sc;
+#pragma unroll
+        for (int off = R; off < R * T; off <<= 1) m_step = fmaxf(m_step, __shfl_xor_sync(kFullMask, m_step, off));
+        const float m_new = fmaxf(m_run, m_step);
+        const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+        const float pexp = fast_exp2(sc - m_use);
+        const bool changed = (m_new != m_run);
+        if (__any_sync(kFullMask, changed)) {  // warp-uniform lazy rescale
+            const float alpha = fast_exp2(m_run - m_use);  // m_run = -inf -> 0, O is 0 then anyway
+            l_part *= alpha;
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                const float a = __shfl_sync(kFullMask, alpha, (g * T) * R, LPT);
+                const float2 a2 = make_float2(a, a);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) o2[g][i] = __fmul2_rn(o2[g][i], a2);
+            }
+            m_run = m_new;
+        }
+        l_part += pexp;
+
+        // ---- O += P V
+#pragma unroll
+        for (int j = 0; j < T; ++j) {
+            const uint32_t vw[4] = {vreg[j].x, vreg[j].y, vreg[j].z, vreg[j].w};
+            float2 v2[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) v2[i] = bf16x2_to_float2(vw[i]);
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                const float pj = __shfl_sync(kFullMask, pexp, (g * T + j) * R, LPT);
+                const float2 p2 = make_float2(pj, pj);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) o2[g][i] = __ffma2_rn(p2, v2[i], o2[g][i]);
+            }
+        }
+    }
+
+    // ---- merge the NG lane-group states of the CTA
+#pragma unroll
+    for (int off = R; off < R * T; off <<= 1) l_part += __shfl_xor_sync(kFullMask, l_part, off);
+    const int grp = warp * TPI + gi;
+    if (lig == (g_own * T) * R) {
+        sm_m[grp][g_own] = m_run;
+        sm_l[grp][g_own] = l_part;
+    }
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        float4* dst = reinterpret_cast<float4*>(&sm_o[grp][g][lig * 8]);
+        dst[0] = make_float4(o2[g][0].x, o2[g][0].y, o2[g][1].x, o2[g][1].y);
+        dst[1] = make_float4(o2[g][2].x, o2[g][2].y, o2[g][3].x, o2[g][3].y);
+    }
+    __syncthreads();
+
+    for (int i = tid; i < G * D; i += 128) {
+        const int g = i / D, d = i % D;
+        float m = -INFINITY;
+#pragma unroll
+        for (int x = 0; x < NG; ++x) m = fmaxf(m, sm_m[x][g]);
+        float l = 0.f, o = 0.f;
+        if (m != -INFINITY) {
+#pragma unroll
+            for (int x = 0; x < NG; ++x) {
+                const float w = fast_exp2(sm_m[x][g] - m);  // -inf -> 0
+                l += w * sm_l[x][g];
+                o += w * sm_o[x][g][d];
+            }
+        }
+        const float outv = (l > 0.f) ? o / l : 0.f;
+        const float lse = (l > 0.f) ? (m + fast_log2(l)) * kLn2 : -INFINITY;
+        const int64_t row = row0 + g;
+        if (direct) {
+            if (p.out_bf16) p.out_bf16[row * D + d] = __float2bfloat16(outv);
+            if (p.out_f32) p.out_f32[row * D + d] = outv;
+            if (d == 0 && p.lse) p.lse[row] = lse;
+        } else {
+            p.part_o[((int64_t)chunk_idx * p.rows + row) * D + d] = outv;
+            if (d == 0) p.part_lse[(int64_t)chunk_idx * p.rows + row] = lse;
+        }
+    }
+}
+
+// O = sum_r exp(LSE_r - LSE) O_r, LSE = logsumexp_r LSE_r; one CTA per output row.
+// A partial with LSE_r = -inf is skipped without reading its O (it may be uninitialised).
+__global__ void __launch_bounds__(128) merge_partials_kernel(const float* __restrict__ o_parts,
+                                                             const float* __restrict__ lse_parts,
+                                                             int n_parts, int64_t rows, int dim,
+                                                             __nv_bfloat16* out_bf16, float* out_f32,
+                                                             float* lse_out) {
+    const int64_t row = blockIdx.x;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    __shared__ float red[4];
+    __shared__ float s_m, s_l;
+
+    float m = -INFINITY;
+    for (int r = tid; r < n_parts; r += 128) m = fmaxf(m, lse_parts[(int64_t)r * rows + row]);
+#pragma unroll
+    for (int off = 16; off; off >>= 1) m = fmaxf(m, __shfl_xor_sync(kFullMask, m, off));
+    if (lane == 0) red[warp] = m;
+    __syncthreads();
+    if (tid == 0) s_m = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+    __syncthreads();
+    m = s_m;
+
+    if (m == -INFINITY) {  // every partial empty
+        for (int d = tid; d < dim; d += 128) {
+            if (out_bf16) out_bf16[row * dim + d] = __float2bfloat16(0.f);
+            if (out_f32) out_f32[row * dim + d] = 0.f;
+        }
+        if (tid == 0 && lse_out) lse_out[row] = -INFINITY;
+        return;
+    }
+
+    float l = 0.f;
+    for (int r = tid; r < n_parts; r += 128) l += expf(lse_parts[(int64_t)r * rows + row] - m);
+#pragma unroll
+    for (int off = 16; off; off >>= 1) l += __shfl_xor_sync(kFullMask, l, off);
+    __syncthreads();
+    if (lane == 0) red[warp] = l;
+    __syncthreads();
+    if (tid == 0) s_l = red[0] + red[1] + red[2] + red[3];
+    __syncthreads();
+    l = s_l;
+    const float inv = 1.f / l;
+
+    for (int d = tid; d < dim; d += 128) {
+        float acc = 0.f;
+        for (int r = 0; r < n_parts; ++r) {
+            const float lr = lse_parts[(int64_t)r * rows + row];
+            if (lr == -INFINITY) continue;
+            acc += expf(lr - m) * o_parts[((int64_t)r * rows + row) * dim + d];
+        }
+        const float o = acc * inv;
+        if (out_bf16) out_bf16[row * dim + d] = __float2bfloat16(o);
+        if (out_f32) out_f32[row * dim + d] = o;
+    }
+    if (tid == 0 && lse_out) lse_out[row] = m + logf(l);
+}
+
+// Writes one token's K and V rows into the caches (llm_kernels.rs:345-373, batched).
+__global__ void kv_append_kernel(__nv_bfloat16* k_cache, __nv_bfloat16* v_cache,
+                                 const __nv_bfloat16* k_in, const __nv_bfloat16* v_in, int n_kv,
+                                 int head_dim, int64_t max_seq, int64_t pos, const int32_t* positions) {
+    const int kvh = blockIdx.x, b = blockIdx.y;
+    const int64_t at = positions ? (int64_t)positions[b] : pos;
+    if (at < 0 || at >= max_seq) return;
+    const int64_t src = ((int64_t)b * n_kv + kvh) * head_dim;
+    const int64_t dst = (((int64_t)b * n_kv + kvh) * max_seq + at) * head_dim;
+    for (int i = threadIdx.x; i < head_dim; i += blockDim.x) {
+        k_cache[dst + i] = k_in[src + i];
+        v_cache[dst + i] = v_in[src + i];
+    }
+}
+
+int decode_chunk_tokens() {
+    static int chunk = [] {
+        const char* e = getenv("RT_ATTN_DECODE_CHUNK");
+        int c = e ? atoi(e) : 0;
+        return (c >= 64 && c % 64 == 0) ? c : 512;
+    }();
+    return chunk;
+}
+
+int decode_num_chunks(int64_t max_seq) {
+    const int chunk = decode_chunk_tokens();
+    int64_t n = (max_seq + chunk - 1) / chunk;
+    return (int)(n < 1 ? 1 : n);
+}
+
+template <int D, int G>
+static cudaError_t launch_decode_dg(const DecodeParams& p, int64_t batch, cudaStream_t stream) {
+    dim3 grid(p.n_chunks, p.n_kv, (unsigned)batch);
+    gqa_decode_splitkv_kernel<D, G><<<grid, 128, 0, stream>>>(p);
+    return cudaGetLastError();
+}
+
+template <int D>
+static cudaError_t launch_decode_d(const DecodeParams& p, int group, int64_t batch, cudaStream_t stream) {
+    switch (group) {
+        case 1: return launch_decode_dg<D, 1>(p, batch, stream);
+        case 2: return launch_decode_dg<D, 2>(p, batch, stream);
+        case 4: return launch_decode_dg<D, 4>(p, batch, stream);
+        case 8: return launch_decode_dg<D, 8>(p, batch, stream);
+    }
+    return cudaErrorInvalidValue;
+}
+
+cudaError_t launch_gqa_decode(const void* q, const void* k, const void* v, void* out_bf16, float* out_f32,
+                              float* lse, int64_t batch, int n_heads, int n_kv, int head_dim,
+                              int64_t max_seq, const int32_t* kv_lens, int64_t kv_len_uniform,
+                              int64_t kv_begin, int64_t kv_end, float scale, void* workspace,
+                              cudaStream_t stream) {
+    DecodeParams p;
+    p.q = (const __nv_bfloat16*)q;
+    p.k = (const __nv_bfloat16*)k;
+    p.v = (const __nv_bfloat16*)v;
+    p.out_bf16 = (__nv_bfloat16*)out_bf16;
+    p.out_f32 = out_f32;
+    p.lse = lse;
+    p.kv_lens = kv_lens;
+    p.kv_len_uniform = kv_len_uniform;
+    p.kv_begin = kv_begin;
+    p.kv_end = kv_end;
+    p.max_seq = max_seq;
+    p.n_heads = n_heads;
+    p.n_kv = n_kv;
+    p.chunk = decode_chunk_tokens();
+    // The visible range can be no longer than this; chunks past it would all be empty.
+    int64_t span = max_seq - kv_begin;
+    if (!kv_lens && kv_len_uniform - kv_begin < span) span = kv_len_uniform - kv_begin;
+    if (kv_end >= 0 && kv_end - kv_begin < span) span = kv_end - kv_begin;
+    if (span < 1) span = 1;
+    p.n_chunks = (int)((span + p.chunk - 1) / p.chunk);
+    p.rows = batch * n_heads;
+    p.scale_log2 = scale * kLog2e;
+    p.part_o = (float*)workspace;
+    p.part_lse = p.part_o ? p.part_o + (int64_t)decode_num_chunks(max_seq) * p.rows * head_dim : nullptr;
+    const int group = n_heads / n_kv;
+    cudaError_t e;
+    switch (head_dim) {
+        case 64: e = launch_decode_d<64>(p, group, batch, stream); break;
+        case 128: e = launch_decode_d<128>(p, group, batch, stream); break;
+        case 256: e = launch_decode_d<256>(p, group, batch, stream); break;
+        default: return cudaErrorInvalidValue;
+    }
+    if (e != cudaSuccess) return e;
+    if (p.n_chunks > 1) {
+        merge_partials_kernel<<<(unsigned)p.rows, 128, 0, stream>>>(p.part_o, p.part_lse, p.n_chunks, p.rows,
+                                                                    head_dim, p.out_bf16, p.out_f32, lse);
+        e = cudaGetLastError();
+    }
+    return e;
+}
+
+cudaError_t launch_merge_partials(const float* o_parts, const float* lse_parts, int64_t n_parts, int64_t rows,
+                                  int dim, void* out_bf16, float* out_f32, float* lse, cudaStream_t stream) {
+    if (rows == 0) return cudaSuccess;
+    merge_partials_kernel<<<(unsigned)rows, 128, 0, stream>>>(o_parts, lse_parts, (int)n_parts, rows, dim,
+                                                              (__nv_bfloat16*)out_bf16, out_f32, lse);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_kv_append(void* k_cache, void* v_cache, const void* k_in, const void* v_in, int64_t batch,
+                             int n_kv, int head_dim, int64_t max_seq, int64_t pos, const int32_t* positions,
+                             cudaStream_t stream) {
+    if (batch == 0 || n_kv == 0) return cudaSuccess;
+    dim3 grid(n_kv, (unsigned)batch);
+    kv_append_kernel<<<grid, 64, 0, stream>>>((__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache,
+                                              (const __nv_bfloat16*)k_in, (const __nv_bfloat16*)v_in, n_kv,
+                                              head_dim, max_seq, pos, positions);
+    return cudaGetLastError();
+}
+
+}  // namespace rt

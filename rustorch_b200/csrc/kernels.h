@@ -1,0 +1,40 @@
+// Internal launch interface between the C ABI (api.cu) and the kernel translation units.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace rt {
+
+// ---- api.cu: device address of the status word of the current device (NULL on failure)
+int* device_status_ptr();
+
+// ---- decode.cu
+int decode_chunk_tokens();
+int decode_num_chunks(int64_t max_seq);
+cudaError_t launch_gqa_decode(const void* q, const void* k, const void* v, void* out_bf16, float* out_f32,
+                              float* lse, int64_t batch, int n_heads, int n_kv, int head_dim,
+                              int64_t max_seq, const int32_t* kv_lens, int64_t kv_len_uniform,
+                              int64_t kv_begin, int64_t kv_end, float scale, void* workspace,
+                              cudaStream_t stream);
+cudaError_t launch_merge_partials(const float* o_parts, const float* lse_parts, int64_t n_parts, int64_t rows,
+                                  int dim, void* out_bf16, float* out_f32, float* lse, cudaStream_t stream);
+cudaError_t launch_kv_append(void* k_cache, void* v_cache, const void* k_in, const void* v_in, int64_t batch,
+                             int n_kv, int head_dim, int64_t max_seq, int64_t pos, const int32_t* positions,
+                             cudaStream_t stream);
+
+// ---- prefill_simt.cu
+cudaError_t launch_prefill_f32(const float* q, const float* k, const float* v, float* out, float* lse,
+                               int64_t batch, int64_t heads_q, int64_t heads_kv, int64_t seq_q,
+                               int64_t seq_kv, int dim, int causal, const int32_t* kv_lens,
+                               const uint8_t* key_keep, int64_t keep_batch_stride, float scale,
+                               cudaStream_t stream);
+cudaError_t launch_f32_to_bf16(const float* src, void* dst, int64_t n, cudaStream_t stream);
+cudaError_t launch_bf16_to_f32(const void* src, float* dst, int64_t n, cudaStream_t stream);
+
+// ---- prefill_tc.cu (tcgen05 / TMEM / TMA)
+cudaError_t launch_prefill_tc(const void* q, const void* k, const void* v, void* out, float* lse,
+                              int64_t batch, int64_t heads, int64_t seq, int dim, int causal,
+                              const int32_t* kv_lens, const uint8_t* key_keep, int64_t keep_batch_stride,
+                              float scale, cudaStream_t stream);
+
+}  // namespace rt

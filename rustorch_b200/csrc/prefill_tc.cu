@@ -1,0 +1,491 @@
+// Flash-attention forward on the Blackwell tensor cores (tcgen05 + TMEM + TMA), bf16.
+//
+// Replaces rustorch_attention::flash_forward_masked (crates/rustorch-attention/src/cpu_forward.rs:193-425)
+// for bf16 device tensors of head dim 64 or 128.  The recurrence is the reference's online
+// softmax (cpu_forward.rs:355-386) evaluated in the log2 domain; unlike the reference, KV tiles
+// that a causal mask or a per-batch kv_len hides completely are never visited.
+//
+// CTA = 256 query rows of one (batch, head) = two 128-row Q tiles that ping-pong on the tensor
+// pipe, so the softmax of one tile overlaps the MMAs of the other.  320 threads:
+//   warps 0-3 : softmax + lazy O rescale + epilogue of Q tile 0 (one thread per query row)
+//   warps 4-7 : the same for Q tile 1
+//   warp  8   : TMA producer (Q once, then K_j / V_j through 2..4-stage rings)
+//   warp  9   : TMEM allocation and the single thread that issues every tcgen05.mma
+// TMEM (512 columns x 128 lanes, f32): S0 [0,128) S1 [128,256) O0 [256,256+D) O1 [256+D,256+2D).
+// P (bf16) overwrites the first 64 columns of its S tile and feeds the PV MMA from TMEM.
+// S = Q K^T is an SS MMA with both operands K-major in 128-byte-swizzled shared memory; O += P V
+// is a TS MMA whose B operand (V) is MN-major, i.e. V is used exactly as TMA lands it.
+// Every mbarrier wait is bounded; on expiry the kernel records a code in the device status
+// word, drains its own copies and MMAs, frees TMEM and returns.
+#include <cuda.h>
+#include <mutex>
+
+#include "kernels.h"
+#include "tc_ptx.cuh"
+
+namespace rt {
+
+using namespace ptx;
+
+template <int D>
+struct TcCfg {
+    static constexpr int BM = 128;                      // query rows per tile
+    static constexpr int BN = 128;                      // keys per KV tile
+    static constexpr int STAGES = (D == 128) ? 2 : 4;   // ring depth of K and of V
+    static constexpr int TILE_BYTES = 128 * D * 2;
+    static constexpr int SUB_BYTES = 128 * 64 * 2;      // one 64-column (128-byte) swizzled sub-tile
+    static constexpr int NSUB = D / 64;
+    static constexpr int NBARS = 2 + 4 * STAGES + 6 + 1;
+    static constexpr int SMEM_BYTES = (2 + 2 * STAGES) * TILE_BYTES + NBARS * 8 + 16 + 1024;
+    static constexpr uint32_t TMEM_COLS = 512;
+    static constexpr uint32_t COL_S = 0, COL_O = 256;
+};
+
+struct TcParams {
+    __nv_bfloat16* out;
+    float* lse;
+    const int32_t* kv_lens;
+    const uint8_t* key_keep;
+    int64_t keep_batch_stride;
+    int seq, heads;
+    float scale_log2;  // scale * log2(e)
+    int* status;       // device status word (bounded-wait expiry codes)
+};
+
+// Timeout codes written to the device status word (100 + site).
+enum { kToQ = 101, kToKFull, kToKEmpty, kToVFull, kToVEmpty, kToSFull, kToPFull, kToOFull, kToDone, kToDrain };
+
+template <int D, bool kCausal, bool kKeep>
+__global__ void __launch_bounds__(320, 1)
+prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                  const __grid_constant__ CUtensorMap tm_v, const TcParams p) {
+    using C = TcCfg<D>;
+    constexpr int STAGES = C::STAGES, TILE = C::TILE_BYTES, SUB = C::SUB_BYTES;
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* sQ = smem;
+    uint8_t* sK = sQ + 2 * TILE;
+    uint8_t* sV = sK + STAGES * TILE;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sV + STAGES * TILE);
+    uint64_t* q_full = bars;                  // [2]
+    uint64_t* k_full = q_full + 2;            // [STAGES]
+    uint64_t* k_empty = k_full + STAGES;      // [STAGES]
+    uint64_t* v_full = k_empty + STAGES;      // [STAGES]
+    uint64_t* v_empty = v_full + STAGES;      // [STAGES]
+    uint64_t* s_full = v_empty + STAGES;      // [2]
+    uint64_t* p_full = s_full + 2;            // [2]
+    uint64_t* o_full = p_full + 2;            // [2]
+    uint64_t* done_bar = o_full + 2;          // [1]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done_bar + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int N = p.seq;
+    const int n_qb = (N + 255) / 256;
+    const int bh = blockIdx.x / n_qb;
+    const int qb = n_qb - 1 - (int)(blockIdx.x % n_qb);  // heaviest causal block of a head first
+    const int b = bh / p.heads;
+    const int q0 = qb * 256;
+
+    int kv_hi = N;
+    if (p.kv_lens) {
+        const int l = p.kv_lens[b];
+        kv_hi = l < 0 ? 0 : (l < N ? l : N);
+    }
+    const int n_kv_tiles = (kv_hi + 127) / 128;
+    int nj[2];
+    nj[0] = kCausal ? min(n_kv_tiles, 2 * qb + 1) : n_kv_tiles;
+    nj[1] = kCausal ? min(n_kv_tiles, 2 * qb + 2) : n_kv_tiles;
+    const int nj_max = nj[1];
+
+    if (nj_max == 0) {  // no visible key at all: NaN rows, LSE = -inf (cpu_forward.rs:411-420)
+        if (warp < 8) {
+            const int row = q0 + warp * 32 + lane;  // (warp/4)*128 + (warp%4)*32 + lane
+            if (row < N) {
+                uint4 nan4 = make_uint4(0x7fc07fc0u, 0x7fc07fc0u, 0x7fc07fc0u, 0x7fc07fc0u);
+                uint4* dst = reinterpret_cast<uint4*>(p.out + ((int64_t)bh * N + row) * D);
+#pragma unroll
+                for (int i = 0; i < D / 8; ++i) dst[i] = nan4;
+                if (p.lse) p.lse[(int64_t)bh * N + row] = -INFINITY;
+            }
+        }
+        return;
+    }
+
+    // ------------------------------------------------------------------ setup
+    if (warp == 8 && lane == 0) {
+        prefetch_tensormap(&tm_q);
+        prefetch_tensormap(&tm_k);
+        prefetch_tensormap(&tm_v);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&q_full[i], 1);
+            mbar_init(&s_full[i], 1);
+            mbar_init(&p_full[i], 128);
+            mbar_init(&o_full[i], 1);
+        }
+        for (int i = 0; i < STAGES; ++i) {
+            mbar_init(&k_full[i], 1);
+            mbar_init(&k_empty[i], 1);
+            mbar_init(&v_full[i], 1);
+            mbar_init(&v_empty[i], 1);
+        }
+        mbar_init(done_bar, 1);
+        fence_barrier_init();
+        fence_proxy_async();
+    }
+    if (warp == 9) {
+        tmem_alloc(tmem_slot, C::TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 8) {
+        // ============================================================== TMA producer
+        if (lane == 0) {
+            bool ok = true;
+            for (int w = 0; w < 2; ++w) {
+                mbar_arrive_expect_tx(&q_full[w], TILE);
+#pragma unroll
+                for (int s = 0; s < C::NSUB; ++s)
+                    tma_load_3d(sQ + w * TILE + s * SUB, &tm_q, &q_full[w], s * 64, q0 + w * 128, bh);
+            }
+            int issued = 0;
+            for (int j = 0; j < nj_max && ok; ++j) {
+                const int st = j % STAGES;
+                const uint32_t ph = (uint32_t)(j / STAGES) & 1u;
+                if (!mbar_wait(&k_empty[st], ph ^ 1u, p.status, kToKEmpty)) { ok = false; break; }
+                mbar_arrive_expect_tx(&k_full[st], TILE);
+#pragma unroll
+                for (int s = 0; s < C::NSUB; ++s)
+                    tma_load_3d(sK + st * TILE + s * SUB, &tm_k, &k_full[st], s * 64, j * 128, bh);
+                if (!mbar_wait(&v_empty[st], ph ^ 1u, p.status, kToVEmpty)) {
+                    // K_j was issued but V_j was not: drain K below with `issued` excluding j.
+                    ok = false;
+                    mbar_wait(&k_full[st], ph, p.status, kToDrain);
+                    break;
+                }
+                mbar_arrive_expect_tx(&v_full[st], TILE);
+#pragma unroll
+                for (int s = 0; s < C::NSUB; ++s)
+                    tma_load_3d(sV + st * TILE + s * SUB, &tm_v, &v_full[st], s * 64, j * 128, bh);
+                issued = j + 1;
+            }
+            // Drain: every copy this thread issued must have landed before the CTA may exit.
+            mbar_wait(&q_full[0], 0, p.status, kToDrain);
+            mbar_wait(&q_full[1], 0, p.status, kToDrain);
+            for (int j = max(0, issued - STAGES); j < issued; ++j) {
+                const int st = j % STAGES;
+                const uint32_t ph = (uint32_t)(j / STAGES) & 1u;
+                mbar_wait(&k_full[st], ph, p.status, kToDrain);
+                mbar_wait(&v_full[st], ph, p.status, kToDrain);
+            }
+        }
+    } else if (warp == 9) {
+        // ============================================================== MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);
+            constexpr uint32_t idesc_o = make_idesc_bf16(128, D, 0, 1);
+            const uint32_t sQ_a = smem_u32(sQ), sK_a = smem_u32(sK), sV_a = smem_u32(sV);
+            auto issue_S = [&](int w, int st) {
+#pragma unroll
+                for (int kk = 0; kk < D / 16; ++kk) {
+                    const uint32_t off = (kk / 4) * SUB + (kk % 4) * 32;
+                    mma_ss(tmem_base + C::COL_S + w * 128, make_smem_desc_sw128(sQ_a + w * TILE + off, 16, 1024),
+                           make_smem_desc_sw128(sK_a + st * TILE + off, 16, 1024), idesc_s, kk > 0);
+                }
+            };
+            auto issue_PV = [&](int w, int st, bool acc) {
+#pragma unroll
+                for (int kk = 0; kk < 8; ++kk) {
+                    mma_ts(tmem_base + C::COL_O + w * D, tmem_base + C::COL_S + w * 128 + kk * 8,
+                           make_smem_desc_sw128(sV_a + st * TILE + kk * 2048, SUB, 1024), idesc_o,
+                           (acc || kk > 0) ? 1u : 0u);
+                }
+            };
+            bool ok = true;
+            // prologue: S_0(0), S_1(0)
+            ok = mbar_wait(&q_full[0], 0, p.status, kToQ) && mbar_wait(&k_full[0], 0, p.status, kToKFull);
+            if (ok) {
+                tc_fence_after();
+                issue_S(0, 0);
+                mma_commit(&s_full[0]);
+                ok = mbar_wait(&q_full[1], 0, p.status, kToQ);
+            }
+            if (ok) {
+                tc_fence_after();
+                issue_S(1, 0);
+                mma_commit(&s_full[1]);
+                mma_commit(&k_empty[0]);
+            }
+            for (int j = 0; j < nj_max && ok; ++j) {
+                const int st = j % STAGES;
+                const uint32_t ph = (uint32_t)(j / STAGES) & 1u;
+                const int st1 = (j + 1) % STAGES;
+                const uint32_t ph1 = (uint32_t)((j + 1) / STAGES) & 1u;
+                if (!mbar_wait(&v_full[st], ph, p.status, kToVFull)) { ok = false; break; }
+                bool k_next_ready = false;
+                if (j < nj[0]) {
+                    if (!mbar_wait(&p_full[0], (uint32_t)j & 1u, p.status, kToPFull)) { ok = false; break; }
+                    tc_fence_after();
+                    issue_PV(0, st, j > 0);
+                    mma_commit(&o_full[0]);
+                    if (j + 1 < nj[0]) {
+                        if (!mbar_wait(&k_full[st1], ph1, p.status, kToKFull)) { ok = false; break; }
+                        k_next_ready = true;
+                        tc_fence_after();
+                        issue_S(0, st1);
+                        mma_commit(&s_full[0]);
+                    }
+                }
+                if (!mbar_wait(&p_full[1], (uint32_t)j & 1u, p.status, kToPFull)) { ok = false; break; }
+                tc_fence_after();
+                issue_PV(1, st, j > 0);
+                mma_commit(&o_full[1]);
+                mma_commit(&v_empty[st]);
+                if (j + 1 < nj[1]) {
+                    if (!k_next_ready && !mbar_wait(&k_full[st1], ph1, p.status, kToKFull)) { ok = false; break; }
+                    tc_fence_after();
+                    issue_S(1, st1);
+                    mma_commit(&s_full[1]);
+                    mma_commit(&k_empty[st1]);
+                }
+            }
+            // All MMAs issued by this thread must retire before TMEM is freed.
+            mma_commit(done_bar);
+            mbar_wait(done_bar, 0, p.status, kToDone);
+        }
+    } else {
+        // ============================================================== softmax / epilogue warps
+        const int w = warp >> 2;                       // Q tile
+        const int row_in_tile = (warp & 3) * 32 + lane;
+        const int row = q0 + w * 128 + row_in_tile;    // query index within the sequence
+        const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
+        const uint32_t tS = tmem_base + lane_sel + C::COL_S + w * 128;
+        const uint32_t tO = tmem_base + lane_sel + C::COL_O + w * D;
+        const float c = p.scale_log2;
+        const uint8_t* keep = kKeep ? p.key_keep + (int64_t)b * p.keep_batch_stride : nullptr;
+
+        float m_ref = -INFINITY;  // reference max (raw score units) the running sums are relative to
+        float l = 0.f;
+        bool ok = true;
+        const int n_iter = nj[w];
+
+        for (int j = 0; j < n_iter; ++j) {
+            if (!__all_sync(kFullMask, mbar_wait(&s_full[w], (uint32_t)j & 1u, p.status, kToSFull))) { ok = false; break; }
+            tc_fence_after();
+
+            uint32_t s[128];
+            {
+                uint32_t(&s0)[32] = *reinterpret_cast<uint32_t(*)[32]>(&s[0]);
+                uint32_t(&s1)[32] = *reinterpret_cast<uint32_t(*)[32]>(&s[32]);
+                uint32_t(&s2)[32] = *reinterpret_cast<uint32_t(*)[32]>(&s[64]);
+                uint32_t(&s3)[32] = *reinterpret_cast<uint32_t(*)[32]>(&s[96]);
+                tmem_ld32(tS + 0, s0);
+                tmem_ld32(tS + 32, s1);
+                tmem_ld32(tS + 64, s2);
+                tmem_ld32(tS + 96, s3);
+                tc_wait_ld();
+            }
+
+            // ---- masks: keys beyond kv_hi, causal diagonal, keep flags
+            const int col0 = j * 128;
+            int lim = kv_hi - 1 - col0;                       // last visible column in this tile
+            if (kCausal) lim = min(lim, row - col0);
+            if (lim < 127) {
+#pragma unroll
+                for (int i = 0; i < 128; ++i)
+                    if (i > lim) s[i] = 0xff800000u;  // -inf
+            }
+            if (kKeep) {  // Mask::Padding keep flags (mask.rs:44); every thread reads the same bytes
+#pragma unroll
+                for (int i = 0; i < 128; ++i)
+                    if (col0 + i < N && __ldg(keep + col0 + i) == 0) s[i] = 0xff800000u;
+            }
+
+            // ---- row max
+            float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < 128; i += 4) {
+                mx0 = fmaxf(mx0, __uint_as_float(s[i]));
+                mx1 = fmaxf(mx1, __uint_as_float(s[i + 1]));
+                mx2 = fmaxf(mx2, __uint_as_float(s[i + 2]));
+                mx3 = fmaxf(mx3, __uint_as_float(s[i + 3]));
+            }
+            const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+
+            // ---- lazy rescale: move the reference max only when it would grow by > 2^8
+            if (j == 0) {
+                m_ref = mx;
+            } else {
+                const bool need = (mx > m_ref) && ((mx - m_ref) * c > 8.0f || m_ref == -INFINITY);
+                if (__any_sync(kFullMask, need)) {
+                    if (!__all_sync(kFullMask, mbar_wait(&o_full[w], (uint32_t)(j - 1) & 1u, p.status, kToOFull))) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const float m_new = fmaxf(m_ref, mx);
+                    const float alpha = (m_new == -INFINITY) ? 1.f : fast_exp2((m_ref - m_new) * c);
+                    l *= alpha;
+                    m_ref = m_new;
+#pragma unroll
+                    for (int ch = 0; ch < D / 32; ++ch) {
+                        uint32_t o[32];
+                        tmem_ld32(tO + ch * 32, o);
+                        tc_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                        tmem_st32(tO + ch * 32, o);
+                    }
+                    tc_wait_st();
+                }
+            }
+
+            // ---- P = exp2(s*c - m*c), row sum, bf16 pack, store to TMEM over S
+            const float mc = (m_ref == -INFINITY) ? 0.f : m_ref * c;
+            float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+            for (int ch = 0; ch < 4; ++ch) {
+                uint32_t pk[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const float p0 = fast_exp2(fmaf(__uint_as_float(s[ch * 32 + 2 * i]), c, -mc));
+                    const float p1 = fast_exp2(fmaf(__uint_as_float(s[ch * 32 + 2 * i + 1]), c, -mc));
+                    sum0 += p0;
+                    sum1 += p1;
+                    pk[i] = float2_to_bf16x2(p0, p1);
+                }
+                tmem_st16(tS + ch * 16, pk);
+            }
+            l += sum0 + sum1;
+            tc_wait_st();
+            tc_fence_before();
+            mbar_arrive(&p_full[w]);
+        }
+
+        // ---- epilogue: O / l -> bf16, LSE
+        if (ok && __all_sync(kFullMask, mbar_wait(&o_full[w], (uint32_t)(n_iter - 1) & 1u, p.status, kToOFull))) {
+            tc_fence_after();
+            const bool valid = (l > 0.f);
+            const float inv = valid ? 1.f / l : 0.f;
+            __nv_bfloat16* dst = p.out + ((int64_t)bh * N + row) * D;
+#pragma unroll
+            for (int ch = 0; ch < D / 32; ++ch) {
+                uint32_t o[32];
+                tmem_ld32(tO + ch * 32, o);
+                tc_wait_ld();
+                if (row < N) {
+#pragma unroll
+                    for (int v4 = 0; v4 < 4; ++v4) {
+                        uint4 pack;
+                        uint32_t* pw = reinterpret_cast<uint32_t*>(&pack);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const float a = __uint_as_float(o[v4 * 8 + 2 * i]) * inv;
+                            const float bb = __uint_as_float(o[v4 * 8 + 2 * i + 1]) * inv;
+                            pw[i] = valid ? float2_to_bf16x2(a, bb) : 0x7fc07fc0u;
+                        }
+                        *reinterpret_cast<uint4*>(dst + ch * 32 + v4 * 8) = pack;
+                    }
+                }
+            }
+            if (p.lse && row < N)
+                p.lse[(int64_t)bh * N + row] =
+                    valid ? (m_ref * c + fast_log2(l)) * kLn2 : (l == 0.f ? -INFINITY : NAN);
+        }
+    }
+
+    // ------------------------------------------------------------------ teardown
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 9) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, C::TMEM_COLS);
+    }
+}
+
+// ---------------------------------------------------------------------- host side
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+    });
+    return fn;
+}
+
+// View of a [B*H, N, D] bf16 tensor as a 3-D TMA tensor; box = 64 columns x 128 rows of one
+// (b,h), 128-byte swizzle.  Rows past N are zero-filled, so tiles never read a neighbour head.
+bool make_tensor_map_bf16_3d(CUtensorMap* map, const void* base, int64_t bh, int64_t seq, int dim) {
+    EncodeTiledFn enc = get_encode_fn();
+    if (!enc) return false;
+    cuuint64_t dims[3] = {(cuuint64_t)dim, (cuuint64_t)seq, (cuuint64_t)bh};
+    cuuint64_t strides[2] = {(cuuint64_t)dim * 2, (cuuint64_t)seq * dim * 2};
+    cuuint32_t box[3] = {64, 128, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int D, bool kCausal, bool kKeep>
+static cudaError_t launch_tc(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const TcParams& p,
+                             int64_t n_ctas, cudaStream_t stream) {
+    auto kern = prefill_tc_kernel<D, kCausal, kKeep>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TcCfg<D>::SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    kern<<<(unsigned)n_ctas, 320, TcCfg<D>::SMEM_BYTES, stream>>>(mq, mk, mv, p);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_prefill_tc(const void* q, const void* k, const void* v, void* out, float* lse, int64_t batch,
+                              int64_t heads, int64_t seq, int dim, int causal, const int32_t* kv_lens,
+                              const uint8_t* key_keep, int64_t keep_batch_stride, float scale,
+                              cudaStream_t stream) {
+    const int64_t bh = batch * heads;
+    if (bh == 0 || seq == 0) return cudaSuccess;
+    CUtensorMap mq, mk, mv;
+    if (!make_tensor_map_bf16_3d(&mq, q, bh, seq, dim) || !make_tensor_map_bf16_3d(&mk, k, bh, seq, dim) ||
+        !make_tensor_map_bf16_3d(&mv, v, bh, seq, dim))
+        return cudaErrorInvalidValue;
+    TcParams p;
+    p.out = (__nv_bfloat16*)out;
+    p.lse = lse;
+    p.kv_lens = kv_lens;
+    p.key_keep = key_keep;
+    p.keep_batch_stride = keep_batch_stride;
+    p.seq = (int)seq;
+    p.heads = (int)heads;
+    p.scale_log2 = scale * kLog2e;
+    p.status = device_status_ptr();
+    if (!p.status) return cudaErrorInvalidSymbol;
+    const int64_t n_ctas = bh * ((seq + 255) / 256);
+    if (n_ctas > 0x7fffffff) return cudaErrorInvalidValue;
+    const bool keep = key_keep != nullptr;
+#define RT_TC_DISPATCH(DD)                                                                         \
+    if (causal) {                                                                                  \
+        return keep ? launch_tc<DD, true, true>(mq, mk, mv, p, n_ctas, stream)                     \
+                    : launch_tc<DD, true, false>(mq, mk, mv, p, n_ctas, stream);                   \
+    } else {                                                                                       \
+        return keep ? launch_tc<DD, false, true>(mq, mk, mv, p, n_ctas, stream)                    \
+                    : launch_tc<DD, false, false>(mq, mk, mv, p, n_ctas, stream);                  \
+    }
+    if (dim == 128) { RT_TC_DISPATCH(128) }
+    if (dim == 64) { RT_TC_DISPATCH(64) }
+#undef RT_TC_DISPATCH
+    return cudaErrorInvalidValue;
+}
+
+}  // namespace rt

@@ -1,0 +1,168 @@
+"""Host-side mirror of the reference's GQA / KV-cache decode API on top of the C ABI.
+
+* ``gqa_forward_f32``   — rustorch_nn::gqa::gqa_forward_f32 (crates/rustorch-nn/src/gqa.rs:94-105),
+                          host f32 buffers, ``GQAError`` variants.
+* ``LlmKernels``        — the attention part of rustorch_cuda::llm_kernels::LlmKernels
+                          (crates/rustorch-cuda/src/llm_kernels.rs:872-958, 1000-1042): raw device
+                          pointers as integers, one sequence, bf16.
+* ``gqa_decode``        — batched split-KV decode over a [B,Hkv,max_seq,D] cache with per-sequence
+                          lengths (what a batched server needs; the reference has batch 1 only).
+* ``merge_partials``    — (O, LSE) merge of KV shards (combine_tiles, online_softmax.rs:105-131).
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import POINTER, c_float
+from typing import Optional
+
+import numpy as np
+
+from . import _lib
+
+
+# ---------------------------------------------------------------- errors (gqa.rs:37-78)
+class GQAError(Exception):
+    pass
+
+
+class HeadCountMismatch(GQAError):
+    def __init__(self, n_heads: int, n_kv_heads: int):
+        self.n_heads, self.n_kv_heads = n_heads, n_kv_heads
+        super().__init__(f"gqa: n_heads {n_heads} not divisible by n_kv_heads {n_kv_heads}")
+
+
+class WrongInputLen(GQAError):
+    def __init__(self, which: str, expected: int, got: int):
+        self.which, self.expected, self.got = which, expected, got
+        super().__init__(f"gqa: {which} expected {expected} f32, got {got}")
+
+
+def _f32(a, name):
+    if not isinstance(a, np.ndarray) or a.dtype != np.float32 or not a.flags["C_CONTIGUOUS"]:
+        raise TypeError(f"{name} must be a C-contiguous float32 numpy array")
+    return a.ctypes.data_as(POINTER(c_float))
+
+
+def gqa_forward_f32(q, k, v, out, batch: int, n_heads: int, n_kv_heads: int, seq_q: int, seq_kv: int,
+                    head_dim: int) -> None:
+    """gqa.rs:94-210 on the GPU (f32 arithmetic).  Buffers are flat host f32 arrays."""
+    if n_kv_heads == 0 or n_heads % n_kv_heads != 0:
+        raise HeadCountMismatch(n_heads, n_kv_heads)
+    q_len = batch * n_heads * seq_q * head_dim
+    kv_len = batch * n_kv_heads * seq_kv * head_dim
+    for which, buf, exp in (("q", q, q_len), ("k", k, kv_len), ("v", v, kv_len), ("out", out, q_len)):
+        if buf.size != exp:
+            raise WrongInputLen(which, exp, buf.size)
+    rc = _lib.lib().rt_gqa_forward_f32_host(_f32(q, "q"), q.size, _f32(k, "k"), k.size, _f32(v, "v"), v.size,
+                                            _f32(out, "out"), out.size, batch, n_heads, n_kv_heads, seq_q, seq_kv,
+                                            head_dim)
+    if rc == _lib.RT_ERR_HEAD_COUNT:
+        raise HeadCountMismatch(n_heads, n_kv_heads)
+    if rc == _lib.RT_ERR_WRONG_INPUT_LEN:
+        raise WrongInputLen("buffer", 0, 0)
+    _lib.check(rc, "rt_gqa_forward_f32_host")
+
+
+def _stream_ptr(stream=None):
+    import torch
+    s = stream if stream is not None else torch.cuda.current_stream()
+    return ctypes.c_void_p(s.cuda_stream)
+
+
+def decode_workspace_bytes(batch: int, n_heads: int, n_kv_heads: int, head_dim: int, max_seq: int) -> int:
+    return int(_lib.lib().rt_gqa_decode_workspace_bytes(batch, n_heads, n_kv_heads, head_dim, max_seq))
+
+
+class LlmKernels:
+    """Attention subset of the reference's ``LlmKernels`` (llm_kernels.rs:540-641 holds compiled
+    modules; this holds the split-KV scratch instead).  Pointers are device addresses as ints,
+    like the reference's ``u64`` arguments."""
+
+    def __init__(self):
+        self._ws = None
+
+    def _workspace(self, nbytes: int):
+        import torch
+        if nbytes == 0:
+            return None, 0
+        if self._ws is None or self._ws.numel() < nbytes:
+            self._ws = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+        return self._ws.data_ptr(), self._ws.numel()
+
+    def gqa_decode_online_bf16(self, stream, q: int, k_cache: int, v_cache: int, out: int, n_heads: int, n_kv: int,
+                               kv_len: int, head_dim: int, max_seq: int) -> None:
+        """llm_kernels.rs:915-958."""
+        ws, ws_bytes = self._workspace(decode_workspace_bytes(1, n_heads, max(n_kv, 1), head_dim, max_seq))
+        rc = _lib.lib().rt_gqa_decode_online_bf16(q, k_cache, v_cache, out, n_heads, n_kv, kv_len, head_dim, max_seq,
+                                                  ws, ws_bytes, _stream_ptr(stream))
+        _lib.check(rc, "gqa_decode_online_bf16::launch")
+
+    # llm_kernels.rs:1000-1042: same contract, same result.
+    gqa_decode_naive_bf16 = gqa_decode_online_bf16
+
+    def kv_append_bf16(self, stream, k_cache: int, v_cache: int, k_in: int, v_in: int, pos: int, n_kv: int,
+                       head_dim: int, max_seq: int) -> None:
+        """llm_kernels.rs:872-911."""
+        rc = _lib.lib().rt_kv_append_bf16(k_cache, v_cache, k_in, v_in, 1, n_kv, head_dim, max_seq, pos, None,
+                                          _stream_ptr(stream))
+        _lib.check(rc, "kv_append_bf16::launch")
+
+
+_default_ws = {}
+
+
+def gqa_decode(q, k_cache, v_cache, kv_lens=None, kv_len: Optional[int] = None, kv_begin: int = 0, kv_end: int = -1,
+               scale: Optional[float] = None, out_dtype=None, return_lse: bool = True, workspace=None):
+    """Batched single-token GQA decode via ``rt_gqa_decode_bf16``.
+
+    q [B,Hq,D] bf16, caches [B,Hkv,max_seq,D] bf16 (CUDA, contiguous); kv_lens int32 CUDA [B] or a
+    uniform ``kv_len``.  Returns (out [B,Hq,D] in ``out_dtype`` (bf16 default, or float32), lse or None).
+    """
+    import torch
+    B, Hq, D = q.shape
+    _, Hkv, max_seq, _ = k_cache.shape
+    out_dtype = out_dtype or torch.bfloat16
+    out = torch.empty((B, Hq, D), dtype=out_dtype, device=q.device)
+    lse = torch.empty((B, Hq), dtype=torch.float32, device=q.device) if return_lse else None
+    need = decode_workspace_bytes(B, Hq, Hkv, D, max_seq)
+    if workspace is None and need:
+        key = (q.device.index, need)
+        workspace = _default_ws.get(key)
+        if workspace is None:
+            workspace = _default_ws[key] = torch.empty(need, dtype=torch.uint8, device=q.device)
+    rc = _lib.lib().rt_gqa_decode_bf16(
+        q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+        out.data_ptr() if out_dtype == torch.bfloat16 else None,
+        out.data_ptr() if out_dtype == torch.float32 else None,
+        lse.data_ptr() if lse is not None else None, B, Hq, Hkv, D, max_seq,
+        kv_lens.data_ptr() if kv_lens is not None else None, 0 if kv_len is None else int(kv_len), kv_begin, kv_end,
+        -1.0 if scale is None else float(scale), workspace.data_ptr() if workspace is not None else None,
+        workspace.numel() if workspace is not None else 0, _stream_ptr())
+    if rc == _lib.RT_ERR_HEAD_COUNT:
+        raise HeadCountMismatch(Hq, Hkv)
+    _lib.check(rc, "rt_gqa_decode_bf16")
+    return out, lse
+
+
+def merge_partials(o_parts, lse_parts, out_dtype=None):
+    """o_parts f32 [R,rows,D], lse_parts f32 [R,rows] (CUDA) -> (out [rows,D], lse [rows])."""
+    import torch
+    R, rows, D = o_parts.shape
+    out_dtype = out_dtype or torch.bfloat16
+    out = torch.empty((rows, D), dtype=out_dtype, device=o_parts.device)
+    lse = torch.empty((rows,), dtype=torch.float32, device=o_parts.device)
+    rc = _lib.lib().rt_attn_merge_partials(o_parts.data_ptr(), lse_parts.data_ptr(), R, rows, D,
+                                           out.data_ptr() if out_dtype == torch.bfloat16 else None,
+                                           out.data_ptr() if out_dtype == torch.float32 else None, lse.data_ptr(),
+                                           _stream_ptr())
+    _lib.check(rc, "rt_attn_merge_partials")
+    return out, lse
+
+
+def kv_append(k_cache, v_cache, k_in, v_in, pos=None, positions=None) -> None:
+    """Batched kv_append via ``rt_kv_append_bf16``: k_in/v_in [B,Hkv,D] -> caches [B,Hkv,max_seq,D]."""
+    B, Hkv, max_seq, D = k_cache.shape
+    rc = _lib.lib().rt_kv_append_bf16(k_cache.data_ptr(), v_cache.data_ptr(), k_in.data_ptr(), v_in.data_ptr(), B, Hkv,
+                                      D, max_seq, 0 if pos is None else int(pos),
+                                      positions.data_ptr() if positions is not None else None, _stream_ptr())
+    _lib.check(rc, "rt_kv_append_bf16")

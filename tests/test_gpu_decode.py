@@ -1,0 +1,190 @@
+"""GPU parity of the split-KV GQA decode and the (O, LSE) merge against the CPU oracle."""
+import numpy as np
+import pytest
+
+from tests import util
+
+pytestmark = pytest.mark.gpu
+
+
+def _problem(orc, B, Hq, Hkv, D, max_seq, lens):
+    q = util.normal_bf16(orc, (B, Hq, D), util.SEED_Q)
+    k = util.normal_bf16(orc, (B, Hkv, max_seq, D), util.SEED_K)
+    v = util.normal_bf16(orc, (B, Hkv, max_seq, D), util.SEED_V)
+    return q, k, v, np.asarray(lens, dtype=np.int32)
+
+
+def _run(q, k, v, lens, **kw):
+    import torch
+    import rustorch_b200 as rt
+    out, lse = rt.gqa_decode(util.to_cuda_bf16(q), util.to_cuda_bf16(k), util.to_cuda_bf16(v),
+                             kv_lens=util.to_cuda(lens), **kw)
+    torch.cuda.synchronize()
+    return util.to_np(out), util.to_np(lse)
+
+
+@pytest.mark.parametrize("D,Hq,Hkv", [(128, 8, 2), (128, 4, 4), (128, 4, 2), (128, 16, 2), (64, 8, 2), (64, 8, 8),
+                                       (64, 8, 4), (64, 8, 1), (256, 8, 2), (256, 2, 2)])
+def test_decode_small_matches_oracle(oracle, D, Hq, Hkv):
+    q, k, v, lens = _problem(oracle, 3, Hq, Hkv, D, 1024, [1, 63, 1000])
+    out, lse = _run(q, k, v, lens)
+    rc, ref, ref_lse = oracle.gqa_decode_cache(q, k, v, lens)
+    assert rc == 0
+    util.check_output(out, ref, label=f"decode D{D} Hq{Hq} Hkv{Hkv}")
+    util.check_lse(lse, ref_lse)
+
+
+def test_decode_ragged_lengths_and_f32_out(oracle):
+    import torch
+    B, Hq, Hkv, D, S = 8, 32, 8, 128, 2048
+    lens = oracle.fill_uniform_int(B, util.SEED_LEN, 1, S)
+    lens[0], lens[1], lens[2] = S, 1, 513
+    q, k, v, lens = _problem(oracle, B, Hq, Hkv, D, S, lens)
+    out, lse = _run(q, k, v, lens, out_dtype=torch.float32)
+    _, ref, ref_lse = oracle.gqa_decode_cache(q, k, v, lens)
+    util.check_output(out, ref, bf16_out=False, label="ragged f32")
+    util.check_lse(lse, ref_lse)
+
+
+def test_decode_empty_sequence_gives_zeros(oracle):
+    q, k, v, lens = _problem(oracle, 2, 8, 2, 128, 1024, [0, 700])
+    out, lse = _run(q, k, v, lens)
+    assert np.all(out[0] == 0) and np.all(np.isneginf(lse[0]))
+    _, ref, ref_lse = oracle.gqa_decode_cache(q, k, v, lens)
+    util.check_output(out, ref)
+    util.check_lse(lse, ref_lse)
+
+
+def test_kv_range_partials_merge_to_full(oracle):
+    """Split the KV range in 4 shards (as 4 GPUs would), merge the (O, LSE) partials, compare with
+    the un-split result and the oracle.  One shard is empty for the short sequence (identity)."""
+    import torch
+    import rustorch_b200 as rt
+    B, Hq, Hkv, D, S = 2, 32, 8, 128, 4096
+    q, k, v, lens = _problem(oracle, B, Hq, Hkv, D, S, [4096, 1500])
+    dq, dk, dv, dl = util.to_cuda_bf16(q), util.to_cuda_bf16(k), util.to_cuda_bf16(v), util.to_cuda(lens)
+    parts_o, parts_l = [], []
+    for r in range(4):
+        o, l = rt.gqa_decode(dq, dk, dv, kv_lens=dl, kv_begin=r * 1024, kv_end=(r + 1) * 1024,
+                             out_dtype=torch.float32)
+        parts_o.append(o.reshape(B * Hq, D))
+        parts_l.append(l.reshape(B * Hq))
+    merged, mlse = rt.merge_partials(torch.stack(parts_o), torch.stack(parts_l), out_dtype=torch.float32)
+    torch.cuda.synchronize()
+    _, ref, ref_lse = oracle.gqa_decode_cache(q, k, v, lens)
+    util.check_output(util.to_np(merged).reshape(B, Hq, D), ref, bf16_out=False, label="merged shards")
+    util.check_lse(util.to_np(mlse).reshape(B, Hq), ref_lse)
+    # the oracle's own partials + merge agree too (checks the merge algebra end to end)
+    po = np.stack([oracle.gqa_decode_cache(q, k, v, lens, r * 1024, (r + 1) * 1024)[1].reshape(B * Hq, D)
+                   for r in range(4)])
+    pl = np.stack([oracle.gqa_decode_cache(q, k, v, lens, r * 1024, (r + 1) * 1024)[2].reshape(B * Hq)
+                   for r in range(4)])
+    mo, ml = oracle.merge_partials(po, pl)
+    assert np.abs(mo.reshape(B, Hq, D) - ref).max() < 1e-5
+    assert np.isneginf(pl[2:, Hq:]).all()  # shards 2,3 of the short sequence are empty
+
+
+def test_reference_signature_gqa_decode_online_bf16(oracle):
+    """LlmKernels::gqa_decode_online_bf16(stream,q,k,v,out,n_heads,n_kv,kv_len,head_dim,max_seq) drop-in."""
+    import torch
+    import rustorch_b200 as rt
+    Hq, Hkv, D, S, L = 32, 8, 128, 2048, 1337
+    q, k, v, _ = _problem(oracle, 1, Hq, Hkv, D, S, [L])
+    dq, dk, dv = util.to_cuda_bf16(q[0]), util.to_cuda_bf16(k[0]), util.to_cuda_bf16(v[0])
+    out = torch.empty((Hq, D), dtype=torch.bfloat16, device="cuda")
+    kern = rt.LlmKernels()
+    kern.gqa_decode_online_bf16(torch.cuda.current_stream(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+                                out.data_ptr(), Hq, Hkv, L, D, S)
+    torch.cuda.synchronize()
+    _, ref, _ = oracle.gqa_decode_cache(q, k, v, [L])
+    util.check_output(util.to_np(out), ref[0], label="LlmKernels drop-in")
+    # and through the reference's CPU-side API shape: gqa_forward_f32(batch=1, seq_q=1, seq_kv=L) on the trimmed cache
+    rc, ref2 = oracle.gqa_forward_f32(q[0].ravel(), np.ascontiguousarray(k[0, :, :L]).ravel(),
+                                      np.ascontiguousarray(v[0, :, :L]).ravel(), 1, Hq, Hkv, 1, L, D)
+    assert rc == 0 and np.abs(ref2.reshape(Hq, D) - ref[0]).max() < 1e-6
+
+
+def test_kv_append_then_decode(oracle):
+    import torch
+    import rustorch_b200 as rt
+    B, Hq, Hkv, D, S = 2, 8, 2, 128, 256
+    q, k, v, lens = _problem(oracle, B, Hq, Hkv, D, S, [10, 200])
+    k_new = util.normal_bf16(oracle, (B, Hkv, D), 11)
+    v_new = util.normal_bf16(oracle, (B, Hkv, D), 12)
+    dk, dv = util.to_cuda_bf16(k), util.to_cuda_bf16(v)
+    rt.kv_append(dk, dv, util.to_cuda_bf16(k_new), util.to_cuda_bf16(v_new), positions=util.to_cuda(lens))
+    for b in range(B):
+        k[b, :, lens[b]] = k_new[b]
+        v[b, :, lens[b]] = v_new[b]
+    torch.cuda.synchronize()
+    assert np.array_equal(util.to_np(dk), k) and np.array_equal(util.to_np(dv), v)
+    out, _ = rt.gqa_decode(util.to_cuda_bf16(q), dk, dv, kv_lens=util.to_cuda(lens + 1))
+    _, ref, _ = oracle.gqa_decode_cache(q, k, v, lens + 1)
+    util.check_output(util.to_np(out), ref)
+
+
+def test_decode_validation_errors():
+    import torch
+    import rustorch_b200 as rt
+    from rustorch_b200 import _lib
+    q = torch.zeros((1, 5, 128), dtype=torch.bfloat16, device="cuda")
+    kc = torch.zeros((1, 2, 64, 128), dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(rt.HeadCountMismatch):
+        rt.gqa_decode(q, kc, kc, kv_len=3)
+    q = torch.zeros((1, 4, 128), dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(_lib.CudaError) as e:
+        rt.gqa_decode(q, kc, kc, kv_len=65)  # kv_len > max_seq
+    assert e.value.code == _lib.RT_ERR_BAD_LENGTH
+    big = torch.zeros((1, 2, 4096, 128), dtype=torch.bfloat16, device="cuda")
+    tiny_ws = torch.empty(16, dtype=torch.uint8, device="cuda")
+    with pytest.raises(_lib.CudaError) as e:
+        rt.gqa_decode(q, big, big, kv_len=100, workspace=tiny_ws)
+    assert e.value.code == _lib.RT_ERR_WORKSPACE
+    q96 = torch.zeros((1, 4, 96), dtype=torch.bfloat16, device="cuda")
+    k96 = torch.zeros((1, 2, 64, 96), dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(_lib.Unsupported):
+        rt.gqa_decode(q96, k96, k96, kv_len=3)
+
+
+def test_decode_cfg4_shape_slice(oracle):
+    """BASELINE config 4 geometry (Hq=32, Hkv=8, D=128, max_seq 8192, lens ~ U[1024,8192]) on 8 of its
+    64 sequences, full check against the oracle; plus split-invariance at the full batch."""
+    import torch
+    import rustorch_b200 as rt
+    B, Hq, Hkv, D, S = 8, 32, 8, 128, 8192
+    lens = oracle.fill_uniform_int(B, util.SEED_LEN, 1024, 8192)
+    q, k, v, lens = _problem(oracle, B, Hq, Hkv, D, S, lens)
+    out, lse = _run(q, k, v, lens)
+    _, ref, ref_lse = oracle.gqa_decode_cache(q, k, v, lens)
+    util.check_output(out, ref, label="cfg4 slice")
+    util.check_lse(lse, ref_lse)
+
+
+def test_decode_cfg4_full_size_split_invariance():
+    """Full config 4 (B=64): the result must not depend on how the KV range is sharded."""
+    import torch
+    import rustorch_b200 as rt
+    B, Hq, Hkv, D, S = 64, 32, 8, 128, 8192
+    g = torch.Generator(device="cuda").manual_seed(4)
+    q = torch.randn((B, Hq, D), device="cuda", generator=g).to(torch.bfloat16)
+    kc = torch.randn((B, Hkv, S, D), device="cuda", generator=g).to(torch.bfloat16)
+    vc = torch.randn((B, Hkv, S, D), device="cuda", generator=g).to(torch.bfloat16)
+    lens = torch.randint(1024, 8193, (B,), device="cuda", generator=g, dtype=torch.int32)
+    full, lse = rt.gqa_decode(q, kc, vc, kv_lens=lens, out_dtype=torch.float32)
+    po, pl = [], []
+    for lo, hi in ((0, 3000), (3000, 3001), (3001, 8192)):
+        o, l = rt.gqa_decode(q, kc, vc, kv_lens=lens, kv_begin=lo, kv_end=hi, out_dtype=torch.float32)
+        po.append(o.reshape(B * Hq, D))
+        pl.append(l.reshape(B * Hq))
+    merged, mlse = rt.merge_partials(torch.stack(po), torch.stack(pl), out_dtype=torch.float32)
+    torch.cuda.synchronize()
+    assert (merged.reshape(B, Hq, D) - full).abs().max().item() < 1e-4
+    assert (mlse.reshape(B, Hq) - lse).abs().max().item() < 1e-4
+    # independent check on a few rows with plain torch math in f32
+    for b in (0, 17, 63):
+        L = int(lens[b])
+        kk = kc[b, :, :L].float().repeat_interleave(4, dim=0)
+        vv = vc[b, :, :L].float().repeat_interleave(4, dim=0)
+        s = torch.einsum("hd,hld->hl", q[b].float(), kk) / (D ** 0.5)
+        ref = torch.einsum("hl,hld->hd", torch.softmax(s, dim=-1), vv)
+        assert (ref - full[b]).abs().max().item() < 2e-3

@@ -1,0 +1,184 @@
+"""GPU parity of the tcgen05 flash-attention forward (bf16) against the CPU oracle."""
+import numpy as np
+import pytest
+
+from tests import util
+
+pytestmark = pytest.mark.gpu
+
+
+def _clean_status():
+    from rustorch_b200 import _lib
+    st = _lib.device_status()
+    assert st == 0, f"device status word = {st}: a bounded wait inside a kernel expired"
+
+
+@pytest.mark.parametrize("D", [64, 128])
+def test_tensor_core_building_blocks(oracle, D):
+    """S = A B^T (SS MMA, K-major operands) and O = bf16(S/16) V (TS MMA, MN-major V) on one tile."""
+    import torch
+    from rustorch_b200 import _lib
+    a = util.normal_bf16(oracle, (128, D), 1)
+    b = util.normal_bf16(oracle, (128, D), 2)
+    v = util.normal_bf16(oracle, (128, D), 3)
+    da, db, dv = util.to_cuda_bf16(a), util.to_cuda_bf16(b), util.to_cuda_bf16(v)
+    s_out = torch.zeros((128, 128), dtype=torch.float32, device="cuda")
+    o_out = torch.zeros((128, D), dtype=torch.float32, device="cuda")
+    rc = _lib.lib().rt_debug_tc_selftest(da.data_ptr(), db.data_ptr(), dv.data_ptr(), s_out.data_ptr(),
+                                         o_out.data_ptr(), D, None)
+    assert rc == 0
+    torch.cuda.synchronize()
+    _clean_status()
+    s_ref = a.astype(np.float64) @ b.astype(np.float64).T
+    s_got = util.to_np(s_out)
+    assert np.abs(s_got - s_ref).max() < 1e-3, "S = A B^T mismatch"
+    p = oracle.round_to_bf16((s_got * np.float32(0.0625)).astype(np.float32))
+    o_ref = p.astype(np.float64) @ v.astype(np.float64)
+    assert np.abs(util.to_np(o_out) - o_ref).max() < 1e-2, "O = P V mismatch"
+
+
+def _run_tc(q, k, v, **kw):
+    import torch
+    import rustorch_b200 as rt
+    out, lse = rt.prefill_bf16(util.to_cuda_bf16(q), util.to_cuda_bf16(k), util.to_cuda_bf16(v), **kw)
+    torch.cuda.synchronize()
+    _clean_status()
+    return util.to_np(out), util.to_np(lse)
+
+
+def _qkv(orc, shape):
+    return tuple(util.normal_bf16(orc, shape, s) for s in (util.SEED_Q, util.SEED_K, util.SEED_V))
+
+
+@pytest.mark.parametrize("D", [128, 64])
+@pytest.mark.parametrize("N", [1, 63, 128, 129, 256, 257, 300, 512, 1000])
+@pytest.mark.parametrize("causal", [False, True])
+def test_prefill_tc_matches_oracle(oracle, D, N, causal):
+    shape = (2, 2, N, D)
+    q, k, v = _qkv(oracle, shape)
+    out, lse = _run_tc(q, k, v, causal=causal)
+    _, ref, ref_lse = oracle.flash_forward_ext(q, k, v, causal=causal)
+    util.check_output(out, ref, label=f"N{N} D{D} causal={causal}")
+    util.check_lse(lse, ref_lse)
+
+
+def test_prefill_tc_causal_row0_is_v0(oracle):
+    """causal_first_query_only_attends_to_self (cpu_forward.rs:955-980) on the tensor-core path: exact."""
+    q, k, v = _qkv(oracle, (1, 2, 384, 128))
+    out, _ = _run_tc(q, k, v, causal=True)
+    assert np.array_equal(out[:, :, 0], v[:, :, 0])
+
+
+@pytest.mark.parametrize("D", [128, 64])
+def test_prefill_tc_varlen_causal_padding(oracle, D):
+    """Config-3 style: causal AND per-sequence kv_len; padded query rows are computed like the oracle does."""
+    B, H, N = 4, 2, 512
+    q, k, v = _qkv(oracle, (B, H, N, D))
+    lens = np.array([512, 1, 130, 257], dtype=np.int32)
+    out, lse = _run_tc(q, k, v, causal=True, kv_lens=util.to_cuda(lens))
+    _, ref, ref_lse = oracle.flash_forward_ext(q, k, v, causal=True, kv_lens=lens)
+    util.check_output(out, ref, label="varlen causal")
+    util.check_lse(lse, ref_lse)
+    out, lse = _run_tc(q, k, v, causal=False, kv_lens=util.to_cuda(lens))
+    _, ref, ref_lse = oracle.flash_forward_ext(q, k, v, causal=False, kv_lens=lens)
+    util.check_output(out, ref, label="varlen")
+    util.check_lse(lse, ref_lse)
+
+
+def test_prefill_tc_zero_length_rows_are_nan(oracle):
+    q, k, v = _qkv(oracle, (2, 2, 200, 128))
+    lens = np.array([0, 200], dtype=np.int32)
+    out, lse = _run_tc(q, k, v, causal=False, kv_lens=util.to_cuda(lens))
+    assert np.isnan(out[0]).all() and np.isneginf(lse[0]).all()
+    _, ref, ref_lse = oracle.flash_forward_ext(q, k, v, kv_lens=lens)
+    util.check_output(out, ref)
+    util.check_lse(lse, ref_lse)
+
+
+@pytest.mark.parametrize("shared", [True, False])
+def test_prefill_tc_padding_keep_mask(oracle, shared):
+    """Mask::Padding keep flags (mask.rs:31-46), incl. a fully masked leading tile and fully masked rows under causal."""
+    B, H, N, D = 2, 2, 400, 128
+    q, k, v = _qkv(oracle, (B, H, N, D))
+    rng = np.random.default_rng(3)
+    keep = (rng.random((N,) if shared else (B, N)) > 0.4).astype(np.uint8)
+    keep[..., :140] = 0
+    out, lse = _run_tc(q, k, v, causal=False, key_keep=util.to_cuda(keep))
+    _, ref, ref_lse = oracle.flash_forward_ext(q, k, v, keep=keep)
+    util.check_output(out, ref, label="keep mask")
+    util.check_lse(lse, ref_lse)
+    out, lse = _run_tc(q, k, v, causal=True, key_keep=util.to_cuda(keep))
+    _, ref, ref_lse = oracle.flash_forward_ext(q, k, v, causal=True, keep=keep)
+    assert np.isnan(ref[:, :, :140]).all()  # rows that see no key at all
+    util.check_output(out, ref, label="keep + causal")
+    util.check_lse(lse, ref_lse)
+
+
+def test_prefill_tc_cfg1_shape(oracle):
+    """Config 1: B=1 H=8 N=2048 D=64 causal; the CPU-runnable reference case."""
+    q, k, v = _qkv(oracle, (1, 8, 2048, 64))
+    out, lse = _run_tc(q, k, v, causal=True)
+    _, ref, ref_lse = oracle.flash_forward_ext(q, k, v, causal=True)
+    util.check_output(out, ref, label="cfg1")
+    util.check_lse(lse, ref_lse)
+    # and through the reference-signature host entry in bf16 precision
+    import rustorch_b200 as rt
+    o2 = np.zeros_like(q)
+    rt.flash_forward_masked(rt.AttentionShape.new(1, 8, 2048, 64), q, k, v, rt.Mask.causal(), o2, precision="bf16")
+    util.check_output(o2, ref, label="cfg1 host entry")
+
+
+def test_prefill_tc_large_scores_lazy_rescale(oracle):
+    """Scores that grow along the key axis force the running max to move many times."""
+    B, H, N, D = 1, 2, 1024, 128
+    q, k, v = _qkv(oracle, (B, H, N, D))
+    ramp = np.linspace(0.2, 3.0, N, dtype=np.float32)[None, None, :, None]
+    k = oracle.round_to_bf16((k * ramp).astype(np.float32))
+    q = oracle.round_to_bf16((q * np.float32(2.0)).astype(np.float32))
+    out, lse = _run_tc(q, k, v, causal=False)
+    _, ref, ref_lse = oracle.flash_forward_ext(q, k, v)
+    util.check_output(out, ref, label="ramp")
+    util.check_lse(lse, ref_lse)
+
+
+def test_prefill_tc_validation_errors():
+    import torch
+    import rustorch_b200 as rt
+    from rustorch_b200 import _lib
+    x = torch.zeros((1, 1, 16, 96), dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(_lib.Unsupported):
+        rt.prefill_bf16(x, x, x)
+    e = torch.zeros((2, 2, 0, 128), dtype=torch.bfloat16, device="cuda")
+    out, _ = rt.prefill_bf16(e, e, e)  # empty sequence: no-op
+    assert out.numel() == 0
+
+
+@pytest.mark.parametrize("cfg", ["cfg2", "cfg3"])
+def test_prefill_tc_full_size_slabs(oracle, cfg):
+    """Configs 2 and 3 at full size: a few (b,h) slabs against the oracle, the rest through invariants
+    (row 0 equals v[0] under a causal mask; every output lies within the range of its V column)."""
+    import torch
+    import rustorch_b200 as rt
+    if cfg == "cfg2":
+        B, H, N, D = 4, 32, 4096, 128
+        lens = None
+    else:
+        B, H, N, D = 16, 16, 2048, 64
+        lens = oracle.fill_uniform_int(B, util.SEED_LEN, 256, 2048)
+    g = torch.Generator(device="cuda").manual_seed(2)
+    q, k, v = (torch.randn((B, H, N, D), device="cuda", generator=g).to(torch.bfloat16) for _ in range(3))
+    dl = util.to_cuda(lens) if lens is not None else None
+    out, lse = rt.prefill_bf16(q, k, v, causal=True, kv_lens=dl)
+    torch.cuda.synchronize()
+    _clean_status()
+    assert torch.equal(out[:, :, 0], v[:, :, 0])
+    assert bool(torch.isfinite(out.float()).all())
+    vmax = v.float().amax(dim=2, keepdim=True)
+    vmin = v.float().amin(dim=2, keepdim=True)
+    assert bool(((out.float() <= vmax + 0.05) & (out.float() >= vmin - 0.05)).all())
+    for (b, h) in ((0, 0), (B - 1, H - 1), (B // 2, 3)):
+        qs, ks, vs = (util.to_np(t[b:b + 1, h:h + 1]) for t in (q, k, v))
+        _, ref, ref_lse = oracle.flash_forward_ext(qs, ks, vs, causal=True,
+                                                   kv_lens=None if lens is None else lens[b:b + 1])
+        util.check_output(util.to_np(out[b:b + 1, h:h + 1]), ref, label=f"{cfg} slab {b},{h}")
+        util.check_lse(util.to_np(lse[b:b + 1, h:h + 1]), ref_lse)
