@@ -59,6 +59,8 @@ extern "C" {
 #define RT_ERR_ALIGNMENT (-11)
 /* a bounded device-side wait ran out; see rt_attn_device_status() */
 #define RT_ERR_DEVICE_TIMEOUT (-12)
+/* the problem needs more scratch than the library's built-in static buffer holds */
+#define RT_ERR_STATIC_SCRATCH (-13)
 
 /* ---- mask flags for the prefill entry points ---------------------------------------- */
 #define RT_MASK_NONE 0
@@ -195,6 +197,33 @@ int rt_gqa_decode_bf16(const void* q, const void* k_cache, const void* v_cache, 
 int rt_gqa_decode_online_bf16(const void* q, const void* k_cache, const void* v_cache, void* out,
                               int n_heads, int n_kv, int kv_len, int head_dim, int max_seq,
                               void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Size of the scratch array built into the library for rt_gqa_decode_online_bf16_static.
+ * 8 MiB holds the chunk partials of one sequence with Hq = 32, D = 128 up to 260,096 cached tokens.
+ */
+#define RT_DECODE_STATIC_SCRATCH_BYTES (8u << 20)
+
+/*
+ * rt_gqa_decode_online_bf16 for callers that cannot hand over scratch memory.  No counterpart in
+ * the reference (its kernel needs no scratch); the argument list is exactly the reference's
+ * LlmKernels::gqa_decode_online_bf16, which is the point: a binding with that fixed signature has
+ * nowhere to pass a workspace, and a serving loop that gave all device memory to its own pools
+ * must not trigger cudaMalloc.  The scratch is a static array in device memory that every GPU
+ * loading the library holds until exit (RT_DECODE_STATIC_SCRATCH_BYTES).
+ *   - Allocates nothing: no cudaMalloc / cudaFree, no allocating library call.
+ *   - The first call on each device resolves the array's device address (it may create the CUDA
+ *     context); make that first call before starting any stream capture.
+ *   - A problem whose partials exceed the array (rt_gqa_decode_workspace_bytes(1, n_heads, n_kv,
+ *     head_dim, max_seq) > RT_DECODE_STATIC_SCRATCH_BYTES) returns RT_ERR_STATIC_SCRATCH.
+ *   - All calls share the one array.  Nothing in it needs clearing between calls, but two calls
+ *     that overlap on the GPU (different streams, or different host threads) race on it:
+ *     serialise them, or use rt_gqa_decode_online_bf16 with separate workspaces.
+ * Results are identical to rt_gqa_decode_online_bf16.
+ */
+int rt_gqa_decode_online_bf16_static(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                     int n_heads, int n_kv, int kv_len, int head_dim, int max_seq,
+                                     void* stream);
 
 /*
  * Merge R partial results of the same rows (split-KV across GPUs or across calls):

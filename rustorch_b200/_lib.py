@@ -27,6 +27,7 @@ RT_ERR_BAD_LENGTH = -9
 RT_ERR_WORKSPACE = -10
 RT_ERR_ALIGNMENT = -11
 RT_ERR_DEVICE_TIMEOUT = -12
+RT_ERR_STATIC_SCRATCH = -13
 
 RT_MASK_NONE, RT_MASK_CAUSAL = 0, 1
 RT_MASKKIND_NONE, RT_MASKKIND_CAUSAL, RT_MASKKIND_PADDING = 0, 1, 2
@@ -55,6 +56,8 @@ PROTOTYPES = {
                                    c_size_t, c_void_p]),
     "rt_gqa_decode_online_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                           c_void_p, c_size_t, c_void_p]),
+    "rt_gqa_decode_online_bf16_static": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                                 c_int, c_void_p]),
     "rt_attn_merge_partials": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int, c_void_p, c_void_p, c_void_p,
                                        c_void_p]),
     "rt_gqa_forward_f32_host": (c_int, [_fp, c_size_t, _fp, c_size_t, _fp, c_size_t, _fp, c_size_t, c_int64, c_int64,

@@ -68,6 +68,7 @@ const char* rt_attn_error_string(int status) {
         case RT_ERR_WORKSPACE: return "workspace missing or too small";
         case RT_ERR_ALIGNMENT: return "device pointer not 16-byte aligned";
         case RT_ERR_DEVICE_TIMEOUT: return "a bounded device-side wait expired";
+        case RT_ERR_STATIC_SCRATCH: return "problem needs more scratch than the built-in static buffer holds";
         default: return status > 0 ? cudaGetErrorString((cudaError_t)status) : "unknown status";
     }
 }

@@ -108,6 +108,25 @@ class LlmKernels:
         _lib.check(rc, "kv_append_bf16::launch")
 
 
+STATIC_SCRATCH_BYTES = 8 << 20  # RT_DECODE_STATIC_SCRATCH_BYTES
+
+
+def gqa_decode_online_bf16_static(stream, q: int, k_cache: int, v_cache: int, out: int, n_heads: int, n_kv: int,
+                                  kv_len: int, head_dim: int, max_seq: int) -> None:
+    """``rt_gqa_decode_online_bf16_static``: the reference's exact ten-argument decode call for callers
+    that cannot pass scratch memory (a fixed FFI signature, or a runtime that forbids allocation once
+    its pools are set up).  Uses an 8 MiB scratch array built into the library, allocates nothing, and
+    gives the same result as ``LlmKernels.gqa_decode_online_bf16``.  Calls share that array, so calls
+    that overlap on the GPU race; the first call on a device should precede any stream capture."""
+    rc = _lib.lib().rt_gqa_decode_online_bf16_static(q, k_cache, v_cache, out, n_heads, n_kv, kv_len, head_dim,
+                                                     max_seq, _stream_ptr(stream))
+    if rc == _lib.RT_ERR_STATIC_SCRATCH:
+        need = decode_workspace_bytes(1, n_heads, max(n_kv, 1), head_dim, max_seq)
+        raise _lib.CudaError(rc, f"gqa_decode_online_bf16_static: needs {need} bytes of scratch, the built-in "
+                                 f"buffer holds {STATIC_SCRATCH_BYTES}")
+    _lib.check(rc, "gqa_decode_online_bf16_static::launch")
+
+
 _default_ws = {}
 
 

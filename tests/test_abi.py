@@ -36,7 +36,7 @@ def test_header_symbols_are_exported_and_bound(lib):
 def test_version_and_error_strings(lib):
     from rustorch_b200 import _lib
     assert lib.rt_attn_version() >= 100
-    for code in range(-12, 1):
+    for code in range(-13, 1):
         assert len(_lib.error_string(code)) > 0
     assert "dim" in _lib.error_string(_lib.RT_ERR_ZERO_DIM)
 
@@ -76,6 +76,7 @@ def test_validation_happens_before_any_device_work(lib):
     assert lib.rt_attn_merge_partials(p, p, 2, 4, 8, None, None, None, None) == L.RT_ERR_NULL_POINTER
     assert lib.rt_kv_append_bf16(p, p, p, p, 1, 2, 128, 64, 64, None, None) == L.RT_ERR_BAD_LENGTH
     assert lib.rt_debug_tc_selftest(None, p, p, p, p, 128, None) == L.RT_ERR_NULL_POINTER
+    assert lib.rt_gqa_decode_online_bf16_static(p, p, p, p, 32, 8, 10, 128, 1 << 20, None) == L.RT_ERR_STATIC_SCRATCH
 
 
 def test_python_mirror_validates_like_the_reference():
