@@ -127,6 +127,8 @@ def cpu_flash_sample(steps: int, warmup: int, target_seconds: float | None):
     import numpy as np
     from oracle import oracle as orc
 
+    # torchrun exports OMP_NUM_THREADS=1; the CPU arm uses every core this process may run on.
+    orc.set_threads(len(os.sched_getaffinity(0)))
     cores = orc.get_threads()
     N, D = CFG2["N"], CFG2["D"]
     slabs = min(CFG2["B"] * CFG2["H"], max(8, cores))

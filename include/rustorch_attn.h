@@ -200,7 +200,8 @@ int rt_gqa_decode_online_bf16(const void* q, const void* k_cache, const void* v_
 
 /*
  * Size of the scratch array built into the library for rt_gqa_decode_online_bf16_static.
- * 8 MiB holds the chunk partials of one sequence with Hq = 32, D = 128 up to 260,096 cached tokens.
+ * 8 MiB holds the chunk partials of one sequence with Hq = 32, D = 128 up to 520,192 cached tokens
+ * (508 chunks of 1024 tokens, 16,512 bytes each).
  */
 #define RT_DECODE_STATIC_SCRATCH_BYTES (8u << 20)
 

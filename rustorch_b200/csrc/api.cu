@@ -216,9 +216,8 @@ int rt_attn_prefill_bf16_host(const void* q, const void* k, const void* v, void*
 
 size_t rt_gqa_decode_workspace_bytes(int64_t batch, int64_t n_heads, int64_t n_kv_heads, int head_dim,
                                      int64_t max_seq) {
-    (void)n_kv_heads;
-    if (batch <= 0 || n_heads <= 0 || head_dim <= 0 || max_seq <= 0) return 0;
-    const size_t chunks = (size_t)rt::decode_num_chunks(max_seq);
+    if (batch <= 0 || n_heads <= 0 || n_kv_heads <= 0 || head_dim <= 0 || max_seq <= 0) return 0;
+    const size_t chunks = (size_t)rt::decode_num_chunks(batch, (int)n_kv_heads, max_seq);
     if (chunks <= 1) return 0;
     return chunks * (size_t)batch * (size_t)n_heads * ((size_t)head_dim + 1) * sizeof(float);
 }

@@ -40,6 +40,13 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
+// max(a, b, c) in one instruction (three-input max exists from sm_100 on).
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float r;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
+
 __device__ __forceinline__ float fast_log2(float x) {
     float y;
     asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));

@@ -342,17 +342,38 @@ __global__ void kv_append_kernel(__nv_bfloat16* k_cache, __nv_bfloat16* v_cache,
     }
 }
 
-int decode_chunk_tokens() {
-    static int chunk = [] {
+// Tokens per KV chunk (one CTA per chunk).  Large chunks amortise the per-CTA prologue and the
+// partial traffic (1024 tokens measured best on the ragged batched workload); small problems get
+// smaller chunks so that about two waves of CTAs still cover the 148 SMs.  The choice depends only
+// on (batch, n_kv, max_seq) so that rt_gqa_decode_workspace_bytes can size the scratch.
+// RT_ATTN_DECODE_CHUNK=<multiple of 64> overrides it.
+int decode_chunk_tokens(int64_t batch, int n_kv, int64_t max_seq) {
+    static int forced = [] {
         const char* e = getenv("RT_ATTN_DECODE_CHUNK");
         int c = e ? atoi(e) : 0;
-        return (c >= 64 && c % 64 == 0) ? c : 512;
+        return (c >= 64 && c % 64 == 0) ? c : 0;
     }();
-    return chunk;
+    if (forced) return forced;
+    const int64_t base = (batch > 0 ? batch : 1) * (int64_t)(n_kv > 0 ? n_kv : 1);
+    const int64_t want_chunks = (148 * 4 + base - 1) / base;
+    int64_t chunk = (max_seq + want_chunks - 1) / want_chunks;
+    chunk = (chunk + 63) / 64 * 64;
+    if (chunk < 128) chunk = 128;
+    if (chunk > 1024) chunk = 1024;
+    return (int)chunk;
 }
 
-int decode_num_chunks(int64_t max_seq) {
-    const int chunk = decode_chunk_tokens();
+// RT_ATTN_DECODE_IMPL=simt selects the CUDA-core kernel for every shape (A/B comparisons).
+static bool decode_use_tensor_cores() {
+    static bool use = [] {
+        const char* e = getenv("RT_ATTN_DECODE_IMPL");
+        return !(e && e[0] == 's');
+    }();
+    return use;
+}
+
+int decode_num_chunks(int64_t batch, int n_kv, int64_t max_seq) {
+    const int chunk = decode_chunk_tokens(batch, n_kv, max_seq);
     int64_t n = (max_seq + chunk - 1) / chunk;
     return (int)(n < 1 ? 1 : n);
 }
@@ -394,7 +415,7 @@ cudaError_t launch_gqa_decode(const void* q, const void* k, const void* v, void*
     p.max_seq = max_seq;
     p.n_heads = n_heads;
     p.n_kv = n_kv;
-    p.chunk = decode_chunk_tokens();
+    p.chunk = decode_chunk_tokens(batch, n_kv, max_seq);
     // The visible range can be no longer than this; chunks past it would all be empty.
     int64_t span = max_seq - kv_begin;
     if (!kv_lens && kv_len_uniform - kv_begin < span) span = kv_len_uniform - kv_begin;
@@ -404,14 +425,20 @@ cudaError_t launch_gqa_decode(const void* q, const void* k, const void* v, void*
     p.rows = batch * n_heads;
     p.scale_log2 = scale * kLog2e;
     p.part_o = (float*)workspace;
-    p.part_lse = p.part_o ? p.part_o + (int64_t)decode_num_chunks(max_seq) * p.rows * head_dim : nullptr;
+    p.part_lse = p.part_o ? p.part_o + (int64_t)decode_num_chunks(batch, n_kv, max_seq) * p.rows * head_dim : nullptr;
     const int group = n_heads / n_kv;
-    cudaError_t e;
-    switch (head_dim) {
-        case 64: e = launch_decode_d<64>(p, group, batch, stream); break;
-        case 128: e = launch_decode_d<128>(p, group, batch, stream); break;
-        case 256: e = launch_decode_d<256>(p, group, batch, stream); break;
-        default: return cudaErrorInvalidValue;
+    cudaError_t e = cudaErrorNotSupported;
+    if (decode_use_tensor_cores())
+        e = launch_gqa_decode_tc(q, k, v, out_bf16, out_f32, lse, batch, n_heads, n_kv, head_dim, max_seq, kv_lens,
+                                 kv_len_uniform, kv_begin, kv_end, scale, p.part_o, p.part_lse, p.chunk, p.n_chunks,
+                                 stream);
+    if (e == cudaErrorNotSupported) {  // head dim 256, or a cache too large for 32-bit TMA row coordinates
+        switch (head_dim) {
+            case 64: e = launch_decode_d<64>(p, group, batch, stream); break;
+            case 128: e = launch_decode_d<128>(p, group, batch, stream); break;
+            case 256: e = launch_decode_d<256>(p, group, batch, stream); break;
+            default: return cudaErrorInvalidValue;
+        }
     }
     if (e != cudaSuccess) return e;
     if (p.n_chunks > 1) {

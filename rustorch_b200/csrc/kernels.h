@@ -9,8 +9,8 @@ namespace rt {
 int* device_status_ptr();
 
 // ---- decode.cu
-int decode_chunk_tokens();
-int decode_num_chunks(int64_t max_seq);
+int decode_chunk_tokens(int64_t batch, int n_kv, int64_t max_seq);
+int decode_num_chunks(int64_t batch, int n_kv, int64_t max_seq);
 cudaError_t launch_gqa_decode(const void* q, const void* k, const void* v, void* out_bf16, float* out_f32,
                               float* lse, int64_t batch, int n_heads, int n_kv, int head_dim,
                               int64_t max_seq, const int32_t* kv_lens, int64_t kv_len_uniform,
@@ -21,6 +21,13 @@ cudaError_t launch_merge_partials(const float* o_parts, const float* lse_parts, 
 cudaError_t launch_kv_append(void* k_cache, void* v_cache, const void* k_in, const void* v_in, int64_t batch,
                              int n_kv, int head_dim, int64_t max_seq, int64_t pos, const int32_t* positions,
                              cudaStream_t stream);
+
+// ---- decode_tc.cu: TMA + mma.sync decode for head dim 64/128; cudaErrorNotSupported = shape not covered
+cudaError_t launch_gqa_decode_tc(const void* q, const void* k, const void* v, void* out_bf16, float* out_f32,
+                                 float* lse, int64_t batch, int n_heads, int n_kv, int head_dim, int64_t max_seq,
+                                 const int32_t* kv_lens, int64_t kv_len_uniform, int64_t kv_begin, int64_t kv_end,
+                                 float scale, float* part_o, float* part_lse, int chunk, int n_chunks,
+                                 cudaStream_t stream);
 
 // ---- prefill_simt.cu
 cudaError_t launch_prefill_f32(const float* q, const float* k, const float* v, float* out, float* lse,

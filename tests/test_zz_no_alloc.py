@@ -26,7 +26,7 @@ def test_static_scratch_decode_matches_workspace_decode_twice():
     vc = torch.randn((Hkv, S, D), device="cuda", generator=g).to(torch.bfloat16)
     kern = rt.LlmKernels()
     stream = torch.cuda.current_stream()
-    for kv_len in (8000, 700):  # 16 chunks, then 2: the second call must ignore the first call's leftovers
+    for kv_len in (8000, 700):  # 63 chunks of 128 tokens, then 6: the second call must ignore the first call's leftovers
         q = torch.randn((Hq, D), device="cuda", generator=g).to(torch.bfloat16)
         ref = torch.empty((Hq, D), dtype=torch.bfloat16, device="cuda")
         got = torch.full((Hq, D), float("nan"), dtype=torch.bfloat16, device="cuda")
@@ -37,7 +37,7 @@ def test_static_scratch_decode_matches_workspace_decode_twice():
         rt.gqa_decode_online_bf16_static(stream, q.data_ptr(), kc.data_ptr(), vc.data_ptr(), got.data_ptr(), Hq, Hkv,
                                          kv_len, D, S)
         torch.cuda.synchronize()
-        assert torch.cuda.memory_allocated() == before
+        assert torch.cuda.memory_allocated() <= before  # nothing new was allocated (the collector may free)
         assert torch.isfinite(got.float()).all()
         assert torch.equal(got, ref), f"kv_len={kv_len}: max diff {(got.float() - ref.float()).abs().max().item()}"
         # and it is the right answer, not merely the same one
@@ -56,7 +56,7 @@ def test_static_scratch_decode_rejects_oversized_problems():
 
     t = torch.zeros((8, 64, 128), dtype=torch.bfloat16, device="cuda")
     q = torch.zeros((32, 128), dtype=torch.bfloat16, device="cuda")
-    with pytest.raises(_lib.CudaError) as e:  # 2048 chunks x 32 heads x 129 floats = 33.8 MB > 8 MiB
+    with pytest.raises(_lib.CudaError) as e:  # 1024 chunks x 32 heads x 129 floats = 16.9 MB > 8 MiB
         rt.gqa_decode_online_bf16_static(torch.cuda.current_stream(), q.data_ptr(), t.data_ptr(), t.data_ptr(),
                                          q.data_ptr(), 32, 8, 10, 128, 1 << 20)
     assert e.value.code == _lib.RT_ERR_STATIC_SCRATCH and "8388608" in str(e.value)
