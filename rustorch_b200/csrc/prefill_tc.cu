@@ -13,8 +13,9 @@
 //   warp  9    : TMEM allocation and the single thread that issues every tcgen05.mma
 //   warps 10-11: idle (they complete the third warpgroup so that setmaxnreg can move its
 //                registers to the softmax warpgroups: 72 vs 216 registers per thread)
-// TMEM (512 columns x 128 lanes, f32): S0 [0,128) S1 [128,256) O0 [256,256+D) O1 [256+D,256+2D).
-// P (bf16) overwrites the first 64 columns of its S tile and feeds the PV MMA from TMEM.
+// TMEM (512 columns x 128 lanes, f32): per Q tile two 64-column S buffers (S[w][b] at w*128 + b*64),
+// O0 [256,256+D), O1 [256+D,256+2D).  K/V are loaded as 128-key tiles but multiplied in 64-key
+// steps; P (bf16) overwrites the first 32 columns of its S buffer and feeds the PV MMA from TMEM.
 // S = Q K^T is an SS MMA with both operands K-major in 128-byte-swizzled shared memory; O += P V
 // is a TS MMA whose B operand (V) is MN-major, i.e. V is used exactly as TMA lands it.
 // Every mbarrier wait is bounded; on expiry the kernel records a code in the device status
@@ -32,15 +33,18 @@ using namespace ptx;
 template <int D>
 struct TcCfg {
     static constexpr int BM = 128;                      // query rows per tile
-    static constexpr int BN = 128;                      // keys per KV tile
-    static constexpr int STAGES = (D == 128) ? 2 : 4;   // ring depth of K and of V
+    static constexpr int BL = 128;                      // keys per TMA-loaded K/V tile
+    static constexpr int BN = 64;                       // keys per MMA / softmax step
+    static constexpr int KS = (D == 128) ? 3 : 4;       // K ring depth (runs one tile ahead of V)
+    static constexpr int VS = (D == 128) ? 2 : 4;       // V ring depth
     static constexpr int TILE_BYTES = 128 * D * 2;
     static constexpr int SUB_BYTES = 128 * 64 * 2;      // one 64-column (128-byte) swizzled sub-tile
+    static constexpr int HALF_BYTES = 64 * 128;         // 64 rows inside a sub-tile
     static constexpr int NSUB = D / 64;
-    static constexpr int NBARS = 2 + 4 * STAGES + 6 + 1;
-    static constexpr int SMEM_BYTES = (2 + 2 * STAGES) * TILE_BYTES + NBARS * 8 + 16 + 1024;
+    static constexpr int NBARS = 2 + 2 * KS + 2 * VS + 4 + 4 + 2 + 2 + 1;
+    static constexpr int SMEM_BYTES = (2 + KS + VS) * TILE_BYTES + NBARS * 8 + 16 + 1024;
     static constexpr uint32_t TMEM_COLS = 512;
-    static constexpr uint32_t COL_S = 0, COL_O = 256;
+    static constexpr uint32_t COL_S = 0, COL_O = 256;   // S: tile w, buffer b at COL_S + w*128 + b*64
 };
 
 struct TcParams {
@@ -52,36 +56,64 @@ struct TcParams {
     int seq, heads;
     float scale_log2;  // scale * log2(e)
     int* status;       // device status word (bounded-wait expiry codes)
+#ifdef RT_TC_TIMELINE
+    long long* timeline;  // profiling builds only: clock64 stamps of CTA 0 (see TL_* below)
+#endif
 };
+
+#ifdef RT_TC_TIMELINE
+// Profiling aid, compiled only with -DRT_TC_TIMELINE: one thread per role of CTA 0 stamps clock64
+// at the phase boundaries of every step.  Layout: [role 0..2][step][8] (role 0/1 = softmax of Q
+// tile 0/1, role 2 = MMA issuer).
+#define TL_STAMP(role, step, slot)                                                                     \
+    do {                                                                                               \
+        if (p.timeline && blockIdx.x == 0 && (step) < 256)                                             \
+            p.timeline[(((role) * 256) + (step)) * 8 + (slot)] = clock64();                            \
+    } while (0)
+static long long* g_tc_timeline = nullptr;
+extern "C" void rt_debug_set_tc_timeline(void* ptr) { g_tc_timeline = (long long*)ptr; }
+#else
+#define TL_STAMP(role, step, slot) do { } while (0)
+#endif
 
 // Timeout codes written to the device status word (100 + site).
 enum { kToQ = 101, kToKFull, kToKEmpty, kToVFull, kToVEmpty, kToSFull, kToPFull, kToOFull, kToDone, kToDrain };
 
+// Pipeline, per Q tile w and 64-key step u (buffer b = u & 1):
+//   MMA:     S_w(u) -> TMEM S[w][b]            (SS, N = 64, D/16 k-steps)       commit s_full[w][b]
+//   softmax: S[w][b] -> registers -> P (bf16) over the first 32 columns of S[w][b]   arrive p_full[w][b]
+//   MMA:     O_w += P V(u)                      (TS, N = D, 4 k-steps)           commit o_full[w]
+//            then S_w(u+2) into the same buffer (in-order after the PV that read P from it)
+// S is double-buffered, so the softmax of step u+1 never waits for the PV of step u; the
+// softmax warps of both tiles keep the MUFU pipe busy while the tensor pipe runs behind them.
 template <int D, bool kCausal, bool kKeep>
 __global__ void __launch_bounds__(384, 1)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                   const __grid_constant__ CUtensorMap tm_v, const TcParams p) {
     using C = TcCfg<D>;
-    constexpr int STAGES = C::STAGES, TILE = C::TILE_BYTES, SUB = C::SUB_BYTES;
+    constexpr int KS = C::KS, VS = C::VS, TILE = C::TILE_BYTES, SUB = C::SUB_BYTES, HALF = C::HALF_BYTES;
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* sQ = smem;
     uint8_t* sK = sQ + 2 * TILE;
-    uint8_t* sV = sK + STAGES * TILE;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sV + STAGES * TILE);
-    uint64_t* q_full = bars;                  // [2]
-    uint64_t* k_full = q_full + 2;            // [STAGES]
-    uint64_t* k_empty = k_full + STAGES;      // [STAGES]
-    uint64_t* v_full = k_empty + STAGES;      // [STAGES]
-    uint64_t* v_empty = v_full + STAGES;      // [STAGES]
-    uint64_t* s_full = v_empty + STAGES;      // [2]
-    uint64_t* p_full = s_full + 2;            // [2]
-    uint64_t* o_full = p_full + 2;            // [2]
-    uint64_t* done_bar = o_full + 2;          // [1]
+    uint8_t* sV = sK + KS * TILE;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sV + VS * TILE);
+    uint64_t* q_full = bars;              // [2]
+    uint64_t* k_full = q_full + 2;        // [KS]
+    uint64_t* k_empty = k_full + KS;      // [KS]
+    uint64_t* v_full = k_empty + KS;      // [VS]
+    uint64_t* v_empty = v_full + VS;      // [VS]
+    uint64_t* s_full = v_empty + VS;      // [2 tiles][2 buffers]
+    uint64_t* p_full = s_full + 4;        // [2 tiles][2 buffers]
+    uint64_t* o_full = p_full + 4;        // [2]  one phase per PV step (O at rest for a rescale)
+    uint64_t* o_done = o_full + 2;        // [2]  single phase: the last PV of the tile has retired
+    uint64_t* done_bar = o_done + 2;      // [1]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done_bar + 1);
 
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // Broadcasting the warp index makes it provably warp-uniform, so role dispatch and the MMA
+    // operands stay on the uniform datapath.
+    const int warp = __shfl_sync(kFullMask, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
     const int N = p.seq;
     const int n_qb = (N + 255) / 256;
     const int bh = blockIdx.x / n_qb;
@@ -94,15 +126,16 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         const int l = p.kv_lens[b];
         kv_hi = l < 0 ? 0 : (l < N ? l : N);
     }
-    const int n_kv_tiles = (kv_hi + 127) / 128;
-    int nj[2];
-    nj[0] = kCausal ? min(n_kv_tiles, 2 * qb + 1) : n_kv_tiles;
-    nj[1] = kCausal ? min(n_kv_tiles, 2 * qb + 2) : n_kv_tiles;
-    const int nj_max = nj[1];
+    const int n_steps = (kv_hi + 63) / 64;  // 64-key steps that hold a visible key
+    int U[2];                               // steps of each Q tile
+    U[0] = kCausal ? min(n_steps, 4 * qb + 2) : n_steps;
+    U[1] = kCausal ? min(n_steps, 4 * qb + 4) : n_steps;
+    const int u_max = U[1];
+    const int n_tiles = (u_max + 1) / 2;    // 128-key K/V tiles to load
 
-    if (nj_max == 0) {  // no visible key at all: NaN rows, LSE = -inf (cpu_forward.rs:411-420)
+    if (u_max == 0) {  // no visible key at all: NaN rows, LSE = -inf (cpu_forward.rs:411-420)
         if (warp < 8) {
-            const int row = q0 + warp * 32 + lane;  // (warp/4)*128 + (warp%4)*32 + lane
+            const int row = q0 + warp * 32 + lane;
             if (row < N) {
                 uint4 nan4 = make_uint4(0x7fc07fc0u, 0x7fc07fc0u, 0x7fc07fc0u, 0x7fc07fc0u);
                 uint4* dst = reinterpret_cast<uint4*>(p.out + ((int64_t)bh * N + row) * D);
@@ -121,19 +154,38 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         prefetch_tensormap(&tm_v);
         for (int i = 0; i < 2; ++i) {
             mbar_init(&q_full[i], 1);
+            mbar_init(&o_full[i], 1);
+            mbar_init(&o_done[i], 1);
+        }
+        for (int i = 0; i < 4; ++i) {
             mbar_init(&s_full[i], 1);
             mbar_init(&p_full[i], 128);
-            mbar_init(&o_full[i], 1);
         }
-        for (int i = 0; i < STAGES; ++i) {
+        for (int i = 0; i < KS; ++i) {
             mbar_init(&k_full[i], 1);
             mbar_init(&k_empty[i], 1);
+        }
+        for (int i = 0; i < VS; ++i) {
             mbar_init(&v_full[i], 1);
             mbar_init(&v_empty[i], 1);
         }
         mbar_init(done_bar, 1);
         fence_barrier_init();
         fence_proxy_async();
+        // Q and the first K tile are requested right away, so their latency overlaps the TMEM
+        // allocation and the CTA-wide barrier below (the producer loop starts at K tile 1).
+        for (int w = 0; w < 2; ++w) {
+            mbar_arrive_expect_tx(&q_full[w], TILE);
+#pragma unroll
+            for (int s = 0; s < C::NSUB; ++s)
+                tma_load_3d(sQ + w * TILE + s * SUB, &tm_q, &q_full[w], s * 64, q0 + w * 128, bh);
+            if (w == 0) {
+                mbar_arrive_expect_tx(&k_full[0], TILE);
+#pragma unroll
+                for (int s = 0; s < C::NSUB; ++s)
+                    tma_load_3d(sK + s * SUB, &tm_k, &k_full[0], s * 64, 0, bh);
+            }
+        }
     }
     if (warp == 9) {
         tmem_alloc(tmem_slot, C::TMEM_COLS);
@@ -151,123 +203,133 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       if (warp == 8) {
         // ============================================================== TMA producer
         if (lane == 0) {
-            bool ok = true;
-            for (int w = 0; w < 2; ++w) {
-                mbar_arrive_expect_tx(&q_full[w], TILE);
+            int k_issued = 1, v_issued = 0;  // Q and K tile 0 were requested during setup
+            for (int j = 0; j < n_tiles; ++j) {
+                const int ks = j % KS, vs = j % VS;
+                if (j > 0) {
+                    if (!mbar_wait(&k_empty[ks], ((uint32_t)(j / KS) & 1u) ^ 1u, p.status, kToKEmpty)) break;
+                    mbar_arrive_expect_tx(&k_full[ks], TILE);
 #pragma unroll
-                for (int s = 0; s < C::NSUB; ++s)
-                    tma_load_3d(sQ + w * TILE + s * SUB, &tm_q, &q_full[w], s * 64, q0 + w * 128, bh);
-            }
-            int issued = 0;
-            for (int j = 0; j < nj_max && ok; ++j) {
-                const int st = j % STAGES;
-                const uint32_t ph = (uint32_t)(j / STAGES) & 1u;
-                if (!mbar_wait(&k_empty[st], ph ^ 1u, p.status, kToKEmpty)) { ok = false; break; }
-                mbar_arrive_expect_tx(&k_full[st], TILE);
-#pragma unroll
-                for (int s = 0; s < C::NSUB; ++s)
-                    tma_load_3d(sK + st * TILE + s * SUB, &tm_k, &k_full[st], s * 64, j * 128, bh);
-                if (!mbar_wait(&v_empty[st], ph ^ 1u, p.status, kToVEmpty)) {
-                    // K_j was issued but V_j was not: drain K below with `issued` excluding j.
-                    ok = false;
-                    mbar_wait(&k_full[st], ph, p.status, kToDrain);
-                    break;
+                    for (int s = 0; s < C::NSUB; ++s)
+                        tma_load_3d(sK + ks * TILE + s * SUB, &tm_k, &k_full[ks], s * 64, j * 128, bh);
+                    k_issued = j + 1;
                 }
-                mbar_arrive_expect_tx(&v_full[st], TILE);
+                if (!mbar_wait(&v_empty[vs], ((uint32_t)(j / VS) & 1u) ^ 1u, p.status, kToVEmpty)) break;
+                mbar_arrive_expect_tx(&v_full[vs], TILE);
 #pragma unroll
                 for (int s = 0; s < C::NSUB; ++s)
-                    tma_load_3d(sV + st * TILE + s * SUB, &tm_v, &v_full[st], s * 64, j * 128, bh);
-                issued = j + 1;
+                    tma_load_3d(sV + vs * TILE + s * SUB, &tm_v, &v_full[vs], s * 64, j * 128, bh);
+                v_issued = j + 1;
             }
             // Drain: every copy this thread issued must have landed before the CTA may exit.
             mbar_wait(&q_full[0], 0, p.status, kToDrain);
             mbar_wait(&q_full[1], 0, p.status, kToDrain);
-            for (int j = max(0, issued - STAGES); j < issued; ++j) {
-                const int st = j % STAGES;
-                const uint32_t ph = (uint32_t)(j / STAGES) & 1u;
-                mbar_wait(&k_full[st], ph, p.status, kToDrain);
-                mbar_wait(&v_full[st], ph, p.status, kToDrain);
-            }
+            for (int j = max(0, k_issued - KS); j < k_issued; ++j)
+                mbar_wait(&k_full[j % KS], (uint32_t)(j / KS) & 1u, p.status, kToDrain);
+            for (int j = max(0, v_issued - VS); j < v_issued; ++j)
+                mbar_wait(&v_full[j % VS], (uint32_t)(j / VS) & 1u, p.status, kToDrain);
         }
       } else if (warp == 9) {
         // ============================================================== MMA issuer
-        if (lane == 0) {
-            constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);
+        // The whole warp runs this loop with uniform control flow and only the elected lane
+        // executes the tcgen05 instructions: descriptors, addresses and loop state then live in
+        // uniform registers, which is what the MMA instruction takes its operands from.
+        {
+            const bool leader = elect_one();
+            constexpr uint32_t idesc_s = make_idesc_bf16(128, 64, 0, 0);
             constexpr uint32_t idesc_o = make_idesc_bf16(128, D, 0, 1);
-            // Descriptors are built once; each MMA only adds a compile-time offset (in 16-byte
-            // units) to the start-address field, so the issuing thread keeps ahead of the tensor pipe.
+            // Descriptors are built once; each MMA only adds an offset (in 16-byte units) to the
+            // start-address field, so the issuing thread keeps ahead of the tensor pipe.
             const uint64_t dq = make_smem_desc_sw128(smem_u32(sQ), 16, 1024);
             const uint64_t dk = make_smem_desc_sw128(smem_u32(sK), 16, 1024);
             const uint64_t dv = make_smem_desc_sw128(smem_u32(sV), SUB, 1024);
             const uint32_t tS0 = tmem_base + C::COL_S, tO0 = tmem_base + C::COL_O;
-            auto issue_S = [&](int w, int st) {
+            // S_w(u): keys [64u, 64u+64) = rows (u&1)*64.. of K tile u/2
+            auto issue_S = [&](int w, int u) {
                 const uint64_t a = dq + (uint64_t)((w * TILE) >> 4);
-                const uint64_t bq = dk + (uint64_t)((st * TILE) >> 4);
+                const uint64_t bk = dk + (uint64_t)((((u >> 1) % KS) * TILE + (u & 1) * HALF) >> 4);
+                const uint32_t d = tS0 + w * 128 + (u & 1) * 64;
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
                     const uint32_t off = (uint32_t)(((kk / 4) * SUB + (kk % 4) * 32) >> 4);
-                    mma_ss(tS0 + w * 128, a + off, bq + off, idesc_s, kk > 0);
+                    if (leader) mma_ss(d, a + off, bk + off, idesc_s, kk > 0);
                 }
             };
-            auto issue_PV = [&](int w, int st, bool acc) {
-                const uint64_t bv = dv + (uint64_t)((st * TILE) >> 4);
-                const uint32_t acc0 = acc ? 1u : 0u;
+            // O_w += P V(u): P (bf16) sits in the first 32 columns of S[w][u&1]
+            auto issue_PV = [&](int w, int u) {
+                const uint64_t bv = dv + (uint64_t)((((u >> 1) % VS) * TILE + (u & 1) * HALF) >> 4);
+                const uint32_t a = tS0 + w * 128 + (u & 1) * 64;
+                const uint32_t acc0 = u > 0 ? 1u : 0u;
 #pragma unroll
-                for (int kk = 0; kk < 8; ++kk)
-                    mma_ts(tO0 + w * D, tS0 + w * 128 + kk * 8, bv + (uint64_t)((kk * 2048) >> 4), idesc_o,
-                           kk > 0 ? 1u : acc0);
+                for (int kk = 0; kk < 4; ++kk)
+                    if (leader) mma_ts(tO0 + w * D, a + kk * 8, bv + (uint64_t)((kk * 2048) >> 4), idesc_o, kk > 0 ? 1u : acc0);
             };
-            bool ok = true;
-            // prologue: S_0(0), S_1(0)
-            ok = mbar_wait(&q_full[0], 0, p.status, kToQ) && mbar_wait(&k_full[0], 0, p.status, kToKFull);
+            auto commit = [&](uint64_t* bar) {
+                if (leader) mma_commit(bar);
+            };
+            auto wait = [&](uint64_t* bar, uint32_t parity, int code) {
+                return __all_sync(kFullMask, mbar_wait(bar, parity, p.status, code));
+            };
+            auto last_use = [&](int u) { return (u & 1) || u == U[1] - 1; };  // of a 128-key tile, by Q tile 1
+
+            bool ok = wait(&q_full[0], 0, kToQ) && wait(&k_full[0], 0, kToKFull);
             if (ok) {
                 tc_fence_after();
                 issue_S(0, 0);
-                mma_commit(&s_full[0]);
-                ok = mbar_wait(&q_full[1], 0, p.status, kToQ);
+                commit(&s_full[0]);
+                if (U[0] > 1) {
+                    issue_S(0, 1);
+                    commit(&s_full[1]);
+                }
+                ok = wait(&q_full[1], 0, kToQ);
             }
             if (ok) {
                 tc_fence_after();
                 issue_S(1, 0);
-                mma_commit(&s_full[1]);
-                mma_commit(&k_empty[0]);
-            }
-            for (int j = 0; j < nj_max && ok; ++j) {
-                const int st = j % STAGES;
-                const uint32_t ph = (uint32_t)(j / STAGES) & 1u;
-                const int st1 = (j + 1) % STAGES;
-                const uint32_t ph1 = (uint32_t)((j + 1) / STAGES) & 1u;
-                if (!mbar_wait(&v_full[st], ph, p.status, kToVFull)) { ok = false; break; }
-                bool k_next_ready = false;
-                if (j < nj[0]) {
-                    if (!mbar_wait(&p_full[0], (uint32_t)j & 1u, p.status, kToPFull)) { ok = false; break; }
-                    tc_fence_after();
-                    issue_PV(0, st, j > 0);
-                    mma_commit(&o_full[0]);
-                    if (j + 1 < nj[0]) {
-                        if (!mbar_wait(&k_full[st1], ph1, p.status, kToKFull)) { ok = false; break; }
-                        k_next_ready = true;
-                        tc_fence_after();
-                        issue_S(0, st1);
-                        mma_commit(&s_full[0]);
-                    }
+                commit(&s_full[2]);
+                if (last_use(0)) commit(&k_empty[0]);
+                if (U[1] > 1) {
+                    issue_S(1, 1);
+                    commit(&s_full[3]);
+                    commit(&k_empty[0]);
                 }
-                if (!mbar_wait(&p_full[1], (uint32_t)j & 1u, p.status, kToPFull)) { ok = false; break; }
-                tc_fence_after();
-                issue_PV(1, st, j > 0);
-                mma_commit(&o_full[1]);
-                mma_commit(&v_empty[st]);
-                if (j + 1 < nj[1]) {
-                    if (!k_next_ready && !mbar_wait(&k_full[st1], ph1, p.status, kToKFull)) { ok = false; break; }
+            }
+            int k_waited = 0, v_waited = -1;
+            for (int u = 0; u < u_max && ok; ++u) {
+#pragma unroll
+                for (int w = 0; w < 2; ++w) {
+                    if (!ok || u >= U[w]) continue;
+                    const int vt = u >> 1;
+                    if (vt > v_waited) {
+                        if (!wait(&v_full[vt % VS], (uint32_t)(vt / VS) & 1u, kToVFull)) { ok = false; continue; }
+                        v_waited = vt;
+                    }
+                    TL_STAMP(2, u, w * 4 + 0);
+                    if (!wait(&p_full[w * 2 + (u & 1)], (uint32_t)(u >> 1) & 1u, kToPFull)) { ok = false; continue; }
+                    TL_STAMP(2, u, w * 4 + 1);
                     tc_fence_after();
-                    issue_S(1, st1);
-                    mma_commit(&s_full[1]);
-                    mma_commit(&k_empty[st1]);
+                    issue_PV(w, u);
+                    commit(&o_full[w]);
+                    if (u == U[w] - 1) commit(&o_done[w]);
+                    if (w == 1 && last_use(u)) commit(&v_empty[vt % VS]);
+                    if (u + 2 < U[w]) {
+                        const int kt = (u + 2) >> 1;
+                        if (kt > k_waited) {
+                            if (!wait(&k_full[kt % KS], (uint32_t)(kt / KS) & 1u, kToKFull)) { ok = false; continue; }
+                            k_waited = kt;
+                            tc_fence_after();
+                        }
+                        TL_STAMP(2, u, w * 4 + 2);
+                        issue_S(w, u + 2);
+                        commit(&s_full[w * 2 + (u & 1)]);
+                        if (w == 1 && last_use(u + 2)) commit(&k_empty[kt % KS]);
+                    }
+                    TL_STAMP(2, u, w * 4 + 3);
                 }
             }
             // All MMAs issued by this thread must retire before TMEM is freed.
-            mma_commit(done_bar);
-            mbar_wait(done_bar, 0, p.status, kToDone);
+            commit(done_bar);
+            wait(done_bar, 0, kToDone);
         }
       }  // warps 10-11 idle: they only complete the warpgroup for setmaxnreg
     } else {
@@ -285,44 +347,47 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         float m_ref = -INFINITY;  // reference max (raw score units) the running sums are relative to
         float l = 0.f;
         bool ok = true;
-        const int n_iter = nj[w];
+        const int n_iter = U[w];
 
-        for (int j = 0; j < n_iter; ++j) {
-            if (!__all_sync(kFullMask, mbar_wait(&s_full[w], (uint32_t)j & 1u, p.status, kToSFull))) { ok = false; break; }
+        for (int u = 0; u < n_iter; ++u) {
+            const int buf = u & 1;
+            if ((warp & 3) == 0 && lane == 0) TL_STAMP(w, u, 0);
+            if (!__all_sync(kFullMask, mbar_wait(&s_full[w * 2 + buf], (uint32_t)(u >> 1) & 1u, p.status, kToSFull))) {
+                ok = false;
+                break;
+            }
             tc_fence_after();
+            if ((warp & 3) == 0 && lane == 0) TL_STAMP(w, u, 1);
 
-            uint32_t s[128];
+            uint32_t s[64];
             {
                 uint32_t(&s0)[32] = *reinterpret_cast<uint32_t(*)[32]>(&s[0]);
                 uint32_t(&s1)[32] = *reinterpret_cast<uint32_t(*)[32]>(&s[32]);
-                uint32_t(&s2)[32] = *reinterpret_cast<uint32_t(*)[32]>(&s[64]);
-                uint32_t(&s3)[32] = *reinterpret_cast<uint32_t(*)[32]>(&s[96]);
-                tmem_ld32(tS + 0, s0);
-                tmem_ld32(tS + 32, s1);
-                tmem_ld32(tS + 64, s2);
-                tmem_ld32(tS + 96, s3);
+                tmem_ld32(tS + buf * 64, s0);
+                tmem_ld32(tS + buf * 64 + 32, s1);
                 tc_wait_ld();
             }
+            if ((warp & 3) == 0 && lane == 0) TL_STAMP(w, u, 2);
 
             // ---- masks: keys beyond kv_hi, causal diagonal, keep flags
-            const int col0 = j * 128;
-            int lim = kv_hi - 1 - col0;                       // last visible column in this tile
+            const int col0 = u * 64;
+            int lim = kv_hi - 1 - col0;                       // last visible column in this step
             if (kCausal) lim = min(lim, row - col0);
-            if (lim < 127) {
+            if (lim < 63) {
 #pragma unroll
-                for (int i = 0; i < 128; ++i)
+                for (int i = 0; i < 64; ++i)
                     if (i > lim) s[i] = 0xff800000u;  // -inf
             }
             if (kKeep) {  // Mask::Padding keep flags (mask.rs:44); every thread reads the same bytes
 #pragma unroll
-                for (int i = 0; i < 128; ++i)
+                for (int i = 0; i < 64; ++i)
                     if (col0 + i < N && __ldg(keep + col0 + i) == 0) s[i] = 0xff800000u;
             }
 
             // ---- row max (three-input max halves the instruction count)
             float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
-            for (int i = 0; i < 128; i += 8) {
+            for (int i = 0; i < 64; i += 8) {
                 mx0 = max3(mx0, __uint_as_float(s[i]), __uint_as_float(s[i + 1]));
                 mx1 = max3(mx1, __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
                 mx2 = max3(mx2, __uint_as_float(s[i + 4]), __uint_as_float(s[i + 5]));
@@ -331,12 +396,13 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
 
             // ---- lazy rescale: move the reference max only when it would grow by > 2^8
-            if (j == 0) {
+            if (u == 0) {
                 m_ref = mx;
             } else {
                 const bool need = (mx > m_ref) && ((mx - m_ref) * c > 8.0f || m_ref == -INFINITY);
                 if (__any_sync(kFullMask, need)) {
-                    if (!__all_sync(kFullMask, mbar_wait(&o_full[w], (uint32_t)(j - 1) & 1u, p.status, kToOFull))) {
+                    // O must be at rest: the PV of the previous step has to be complete.
+                    if (!__all_sync(kFullMask, mbar_wait(&o_full[w], (uint32_t)(u - 1) & 1u, p.status, kToOFull))) {
                         ok = false;
                         break;
                     }
@@ -358,12 +424,13 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 }
             }
 
+            if ((warp & 3) == 0 && lane == 0) TL_STAMP(w, u, 3);
             // ---- P = exp2(s*c - m*c), row sum, bf16 pack, store to TMEM over S (packed f32x2 math)
             const float mc = (m_ref == -INFINITY) ? 0.f : m_ref * c;
             const float2 c2 = make_float2(c, c), nmc2 = make_float2(-mc, -mc);
             float2 sum_a = make_float2(0.f, 0.f), sum_b = make_float2(0.f, 0.f);
 #pragma unroll
-            for (int ch = 0; ch < 4; ++ch) {
+            for (int ch = 0; ch < 2; ++ch) {
                 uint32_t pk[16];
 #pragma unroll
                 for (int i = 0; i < 16; i += 2) {
@@ -379,16 +446,19 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                     pk[i] = float2_to_bf16x2(pa.x, pa.y);
                     pk[i + 1] = float2_to_bf16x2(pb.x, pb.y);
                 }
-                tmem_st16(tS + ch * 16, pk);
+                tmem_st16(tS + buf * 64 + ch * 16, pk);
             }
             l += (sum_a.x + sum_a.y) + (sum_b.x + sum_b.y);
+            if ((warp & 3) == 0 && lane == 0) TL_STAMP(w, u, 4);
             tc_wait_st();
+            if ((warp & 3) == 0 && lane == 0) TL_STAMP(w, u, 5);
             tc_fence_before();
-            mbar_arrive(&p_full[w]);
+            mbar_arrive(&p_full[w * 2 + buf]);
         }
 
-        // ---- epilogue: O / l -> bf16, LSE
-        if (ok && __all_sync(kFullMask, mbar_wait(&o_full[w], (uint32_t)(n_iter - 1) & 1u, p.status, kToOFull))) {
+        // ---- epilogue: O / l -> bf16, LSE.  (o_full cannot be used here: up to two PV steps may
+        // still be in flight, which a parity wait cannot tell from none.)
+        if (ok && __all_sync(kFullMask, mbar_wait(&o_done[w], 0, p.status, kToOFull))) {
             tc_fence_after();
             const bool valid = (l > 0.f);
             const float inv = valid ? 1.f / l : 0.f;
@@ -494,6 +564,9 @@ cudaError_t launch_prefill_tc(const void* q, const void* k, const void* v, void*
     p.scale_log2 = scale * kLog2e;
     p.status = device_status_ptr();
     if (!p.status) return cudaErrorInvalidSymbol;
+#ifdef RT_TC_TIMELINE
+    p.timeline = g_tc_timeline;
+#endif
     const int64_t n_ctas = bh * ((seq + 255) / 256);
     if (n_ctas > 0x7fffffff) return cudaErrorInvalidValue;
     const bool keep = key_keep != nullptr;
