@@ -14,7 +14,9 @@
  *   - `stream` is a `cudaStream_t` passed as `void*`; NULL = the legacy default stream.
  *     Device entry points only enqueue work and return; the caller synchronises, like
  *     `LlamaModelCuda::decode_step` does (crates/rustorch-llm/src/cuda_backend.rs:1088-1091).
- *     `*_host` entry points take host memory, copy both ways and block until done.
+ *     `*_host` entry points take host memory, copy both ways and block until done.  They stage
+ *     through device buffers that the library keeps per device and only ever grows, so repeated
+ *     calls of one size allocate once; one host entry runs at a time per process.
  *   - Tensors are dense row-major: prefill `[B,H,N,D]` (crates/rustorch-attention/src/cpu_forward.rs:22-27),
  *     KV cache `[B,Hkv,max_seq,D]` (crates/rustorch-nn/src/kv_cache.rs:49-60; the CUDA model's
  *     `[Hkv,max_seq,D]` of crates/rustorch-cuda/src/llm_kernels.rs:349-352 is the B = 1 case),
@@ -200,8 +202,8 @@ int rt_gqa_decode_online_bf16(const void* q, const void* k_cache, const void* v_
 
 /*
  * Size of the scratch array built into the library for rt_gqa_decode_online_bf16_static.
- * 8 MiB holds the chunk partials of one sequence with Hq = 32, D = 128 up to 520,192 cached tokens
- * (508 chunks of 1024 tokens, 16,512 bytes each).
+ * 8 MiB holds 508 chunk partials of one sequence with Hq = 32, D = 128 (16,512 bytes each), i.e.
+ * about 65,000 cached tokens at the smallest chunk size and up to 520,192 at the largest.
  */
 #define RT_DECODE_STATIC_SCRATCH_BYTES (8u << 20)
 

@@ -3,6 +3,7 @@
 // Nothing here computes attention on the host: without a CUDA device every compute entry fails.
 #include <cmath>
 #include <cstdlib>
+#include <mutex>
 
 #include "../../include/rustorch_attn.h"
 #include "common.cuh"
@@ -30,13 +31,44 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 inline cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
 inline float default_scale(float scale, int dim) { return scale > 0.f ? scale : 1.0f / std::sqrt((float)dim); }
 
-// RAII device buffer for the blocking host entry points.
+// Device staging buffers of the blocking host entry points.  They are kept per device and only
+// ever grow, so a caller that streams same-sized problems through a *_host entry pays for
+// cudaMalloc once, not per call.  One host entry runs at a time per process (the pool is locked
+// for the duration of the call); the device-pointer entries never touch it.
+struct HostStaging {
+    static constexpr int kSlots = 10;
+    void* ptr[64][kSlots] = {};
+    size_t cap[64][kSlots] = {};
+    std::mutex mu;
+    cudaError_t get(int slot, size_t bytes, void** out) {
+        int dev = 0;
+        cudaError_t e = cudaGetDevice(&dev);
+        if (e != cudaSuccess) return e;
+        if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+        if (bytes == 0) bytes = 1;
+        if (cap[dev][slot] < bytes) {
+            if (ptr[dev][slot]) {
+                e = cudaFree(ptr[dev][slot]);
+                ptr[dev][slot] = nullptr;
+                cap[dev][slot] = 0;
+                if (e != cudaSuccess) return e;
+            }
+            e = cudaMalloc(&ptr[dev][slot], bytes);
+            if (e != cudaSuccess) return e;
+            cap[dev][slot] = bytes;
+        }
+        *out = ptr[dev][slot];
+        return cudaSuccess;
+    }
+};
+HostStaging g_staging;
+
+// One staging buffer of the pool (slot = which of the call's tensors).
 struct DevBuf {
     void* p = nullptr;
-    cudaError_t alloc(size_t bytes) { return cudaMalloc(&p, bytes ? bytes : 1); }
-    ~DevBuf() {
-        if (p) cudaFree(p);
-    }
+    int slot;
+    explicit DevBuf(int s) : slot(s) {}
+    cudaError_t alloc(size_t bytes) { return g_staging.get(slot, bytes, &p); }
     template <class T>
     T* as() const { return static_cast<T*>(p); }
 };
@@ -141,7 +173,8 @@ int rt_flash_forward_f32_host(const float* q, size_t q_len, const float* k, size
     if (precision == RT_PRECISION_F32 && dim > 256) return RT_ERR_UNSUPPORTED;
 
     const size_t bytes = expected * sizeof(float);
-    DevBuf dq, dk, dv, dout, dkeep;
+    std::lock_guard<std::mutex> lock(g_staging.mu);
+    DevBuf dq(0), dk(1), dv(2), dout(3), dkeep(4);
     RT_CUDA(dq.alloc(bytes));
     RT_CUDA(dk.alloc(bytes));
     RT_CUDA(dv.alloc(bytes));
@@ -162,7 +195,7 @@ int rt_flash_forward_f32_host(const float* q, size_t q_len, const float* k, size
                                      nullptr);
         if (rc != RT_OK) return rc;
     } else {
-        DevBuf bq, bk, bv, bo;
+        DevBuf bq(5), bk(6), bv(7), bo(8);
         RT_CUDA(bq.alloc(expected * 2));
         RT_CUDA(bk.alloc(expected * 2));
         RT_CUDA(bv.alloc(expected * 2));
@@ -188,7 +221,8 @@ int rt_attn_prefill_bf16_host(const void* q, const void* k, const void* v, void*
     const size_t n = (size_t)batch * heads * seq * dim;
     if (n == 0) return RT_OK;
     if (!q || !k || !v || !out) return RT_ERR_NULL_POINTER;
-    DevBuf dq, dk, dv, dout, dlse, dlens;
+    std::lock_guard<std::mutex> lock(g_staging.mu);
+    DevBuf dq(0), dk(1), dv(2), dout(3), dlse(4), dlens(5);
     RT_CUDA(dq.alloc(n * 2));
     RT_CUDA(dk.alloc(n * 2));
     RT_CUDA(dv.alloc(n * 2));
@@ -256,6 +290,7 @@ int rt_attn_merge_partials(const float* o_parts, const float* lse_parts, int64_t
                            void* out_bf16, float* out_f32, float* lse, void* stream) {
     if (dim == 0) return RT_ERR_ZERO_DIM;
     if (n_parts < 0 || rows < 0 || dim < 0 || n_parts > 0x7fffffff) return RT_ERR_BAD_LENGTH;
+    if (dim > 256 || n_parts > 8192) return RT_ERR_UNSUPPORTED;
     if (rows == 0) return RT_OK;
     if ((n_parts > 0 && (!o_parts || !lse_parts)) || (!out_bf16 && !out_f32)) return RT_ERR_NULL_POINTER;
     RT_CUDA(rt::launch_merge_partials(o_parts, lse_parts, n_parts, rows, dim, out_bf16, out_f32, lse,
@@ -275,7 +310,8 @@ int rt_gqa_forward_f32_host(const float* q, size_t q_len, const float* k, size_t
     if (qn == 0) return RT_OK;
     if (head_dim > 256) return RT_ERR_UNSUPPORTED;
     if (!q || !out || (kn > 0 && (!k || !v))) return RT_ERR_NULL_POINTER;
-    DevBuf dq, dk, dv, dout;
+    std::lock_guard<std::mutex> lock(g_staging.mu);
+    DevBuf dq(0), dk(1), dv(2), dout(3);
     RT_CUDA(dq.alloc(qn * 4));
     RT_CUDA(dk.alloc(kn * 4));
     RT_CUDA(dv.alloc(kn * 4));

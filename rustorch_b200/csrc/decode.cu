@@ -270,30 +270,48 @@ __global__ void __launch_bounds__(128) gqa_decode_splitkv_kernel(const DecodePar
     }
 }
 
-// O = sum_r exp(LSE_r - LSE) O_r, LSE = logsumexp_r LSE_r; one CTA per output row.
-// A partial with LSE_r = -inf is skipped without reading its O (it may be uninitialised).
-__global__ void __launch_bounds__(128) merge_partials_kernel(const float* __restrict__ o_parts,
-                                                             const float* __restrict__ lse_parts,
-                                                             int n_parts, int64_t rows, int dim,
-                                                             __nv_bfloat16* out_bf16, float* out_f32,
-                                                             float* lse_out) {
+// O = sum_r exp(LSE_r - LSE) O_r, LSE = logsumexp_r LSE_r; one CTA of 256 threads per output row.
+// The weights exp(LSE_r - LSE) are computed once into shared memory; the accumulation then runs
+// over the partials with 8 warps in parallel (part r goes to warp r % 8) and four independent
+// loads in flight per lane, so a row with hundreds of partials (long-context split-KV) costs a few
+// memory latencies instead of one per partial.  Each lane owns dims lane, lane+32, ...
+// A partial with LSE_r = -inf gets weight 0 and its O is never read (it may be uninitialised).
+constexpr int kMergeWarps = 8;
+constexpr int kMergeMaxDimPerLane = 8;  // dim <= 256
+
+__global__ void __launch_bounds__(kMergeWarps * 32) merge_partials_kernel(const float* __restrict__ o_parts,
+                                                                         const float* __restrict__ lse_parts,
+                                                                         int n_parts, int64_t rows, int dim,
+                                                                         __nv_bfloat16* out_bf16, float* out_f32,
+                                                                         float* lse_out) {
     const int64_t row = blockIdx.x;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    __shared__ float red[4];
+    __shared__ float red[kMergeWarps];
     __shared__ float s_m, s_l;
+    extern __shared__ float merge_sm[];
+    float* acc_sm = merge_sm;                    // [kMergeWarps][dim]
+    float* w_sm = merge_sm + kMergeWarps * dim;  // [n_parts]: LSE_r, then the weight of part r
 
     float m = -INFINITY;
-    for (int r = tid; r < n_parts; r += 128) m = fmaxf(m, lse_parts[(int64_t)r * rows + row]);
+    for (int r = tid; r < n_parts; r += kMergeWarps * 32) {
+        const float x = lse_parts[(int64_t)r * rows + row];
+        w_sm[r] = x;
+        m = fmaxf(m, x);
+    }
 #pragma unroll
     for (int off = 16; off; off >>= 1) m = fmaxf(m, __shfl_xor_sync(kFullMask, m, off));
     if (lane == 0) red[warp] = m;
     __syncthreads();
-    if (tid == 0) s_m = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+    if (tid == 0) {
+        float x = red[0];
+        for (int i = 1; i < kMergeWarps; ++i) x = fmaxf(x, red[i]);
+        s_m = x;
+    }
     __syncthreads();
     m = s_m;
 
     if (m == -INFINITY) {  // every partial empty
-        for (int d = tid; d < dim; d += 128) {
+        for (int d = tid; d < dim; d += kMergeWarps * 32) {
             if (out_bf16) out_bf16[row * dim + d] = __float2bfloat16(0.f);
             if (out_f32) out_f32[row * dim + d] = 0.f;
         }
@@ -302,29 +320,66 @@ __global__ void __launch_bounds__(128) merge_partials_kernel(const float* __rest
     }
 
     float l = 0.f;
-    for (int r = tid; r < n_parts; r += 128) l += expf(lse_parts[(int64_t)r * rows + row] - m);
+    for (int r = tid; r < n_parts; r += kMergeWarps * 32) {
+        const float x = w_sm[r];
+        const float w = (x == -INFINITY) ? 0.f : expf(x - m);
+        w_sm[r] = w;
+        l += w;
+    }
 #pragma unroll
     for (int off = 16; off; off >>= 1) l += __shfl_xor_sync(kFullMask, l, off);
-    __syncthreads();
+    __syncthreads();  // weights visible; red[] free again
     if (lane == 0) red[warp] = l;
-    __syncthreads();
-    if (tid == 0) s_l = red[0] + red[1] + red[2] + red[3];
-    __syncthreads();
-    l = s_l;
-    const float inv = 1.f / l;
 
-    for (int d = tid; d < dim; d += 128) {
-        float acc = 0.f;
-        for (int r = 0; r < n_parts; ++r) {
-            const float lr = lse_parts[(int64_t)r * rows + row];
-            if (lr == -INFINITY) continue;
-            acc += expf(lr - m) * o_parts[((int64_t)r * rows + row) * dim + d];
+    float acc[kMergeMaxDimPerLane];
+#pragma unroll
+    for (int i = 0; i < kMergeMaxDimPerLane; ++i) acc[i] = 0.f;
+    const float* base = o_parts + row * dim;
+    const int64_t part_stride = rows * dim;
+    for (int r0 = warp; r0 < n_parts; r0 += 4 * kMergeWarps) {
+        float w[4];
+        float v[4][kMergeMaxDimPerLane];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int r = r0 + u * kMergeWarps;
+            w[u] = (r < n_parts) ? w_sm[r] : 0.f;
+#pragma unroll
+            for (int i = 0; i < kMergeMaxDimPerLane; ++i) {
+                const int d = lane + 32 * i;
+                v[u][i] = (w[u] != 0.f && d < dim) ? base[(int64_t)r * part_stride + d] : 0.f;
+            }
         }
-        const float o = acc * inv;
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+#pragma unroll
+            for (int i = 0; i < kMergeMaxDimPerLane; ++i) acc[i] = fmaf(w[u], v[u][i], acc[i]);
+    }
+#pragma unroll
+    for (int i = 0; i < kMergeMaxDimPerLane; ++i) {
+        const int d = lane + 32 * i;
+        if (d < dim) acc_sm[warp * dim + d] = acc[i];
+    }
+    __syncthreads();
+    if (tid == 0) {
+        float x = 0.f;
+        for (int i = 0; i < kMergeWarps; ++i) x += red[i];
+        s_l = x;
+    }
+    __syncthreads();
+    const float inv = 1.f / s_l;
+    for (int d = tid; d < dim; d += kMergeWarps * 32) {
+        float o = 0.f;
+#pragma unroll
+        for (int x = 0; x < kMergeWarps; ++x) o += acc_sm[x * dim + d];
+        o *= inv;
         if (out_bf16) out_bf16[row * dim + d] = __float2bfloat16(o);
         if (out_f32) out_f32[row * dim + d] = o;
     }
-    if (tid == 0 && lse_out) lse_out[row] = m + logf(l);
+    if (tid == 0 && lse_out) lse_out[row] = m + logf(s_l);
+}
+
+static size_t merge_smem_bytes(int64_t n_parts, int dim) {
+    return sizeof(float) * ((size_t)kMergeWarps * dim + (size_t)n_parts);
 }
 
 // Writes one token's K and V rows into the caches (llm_kernels.rs:345-373, batched).
@@ -343,9 +398,10 @@ __global__ void kv_append_kernel(__nv_bfloat16* k_cache, __nv_bfloat16* v_cache,
 }
 
 // Tokens per KV chunk (one CTA per chunk).  Large chunks amortise the per-CTA prologue and the
-// partial traffic (1024 tokens measured best on the ragged batched workload); small problems get
-// smaller chunks so that about two waves of CTAs still cover the 148 SMs.  The choice depends only
-// on (batch, n_kv, max_seq) so that rt_gqa_decode_workspace_bytes can size the scratch.
+// partial traffic (1024 tokens measured best on the ragged batched workload); the choice walks
+// down from 1024 until the grid both covers the 148 SMs x 2 resident CTAs and fills its last wave
+// to at least 95 % (a long single sequence otherwise loses up to a quarter of a wave).  It depends
+// only on (batch, n_kv, max_seq) so that rt_gqa_decode_workspace_bytes can size the scratch.
 // RT_ATTN_DECODE_CHUNK=<multiple of 64> overrides it.
 int decode_chunk_tokens(int64_t batch, int n_kv, int64_t max_seq) {
     static int forced = [] {
@@ -355,12 +411,21 @@ int decode_chunk_tokens(int64_t batch, int n_kv, int64_t max_seq) {
     }();
     if (forced) return forced;
     const int64_t base = (batch > 0 ? batch : 1) * (int64_t)(n_kv > 0 ? n_kv : 1);
-    const int64_t want_chunks = (148 * 4 + base - 1) / base;
-    int64_t chunk = (max_seq + want_chunks - 1) / want_chunks;
-    chunk = (chunk + 63) / 64 * 64;
-    if (chunk < 128) chunk = 128;
-    if (chunk > 1024) chunk = 1024;
-    return (int)chunk;
+    const int64_t slots = 148 * 2;
+    int best = 128;
+    double best_eff = -1.0;
+    for (int c = 1024; c >= 128; c -= 64) {
+        const int64_t ctas = base * ((max_seq + c - 1) / c);
+        if (ctas < slots && c > 128) continue;
+        const double waves = (double)ctas / (double)slots;
+        const double eff = waves / (double)((ctas + slots - 1) / slots);
+        if (eff >= 0.95) return c;
+        if (eff > best_eff) {
+            best_eff = eff;
+            best = c;
+        }
+    }
+    return best;
 }
 
 // RT_ATTN_DECODE_IMPL=simt selects the CUDA-core kernel for every shape (A/B comparisons).
@@ -442,8 +507,8 @@ cudaError_t launch_gqa_decode(const void* q, const void* k, const void* v, void*
     }
     if (e != cudaSuccess) return e;
     if (p.n_chunks > 1) {
-        merge_partials_kernel<<<(unsigned)p.rows, 128, 0, stream>>>(p.part_o, p.part_lse, p.n_chunks, p.rows,
-                                                                    head_dim, p.out_bf16, p.out_f32, lse);
+        merge_partials_kernel<<<(unsigned)p.rows, kMergeWarps * 32, merge_smem_bytes(p.n_chunks, head_dim), stream>>>(
+            p.part_o, p.part_lse, p.n_chunks, p.rows, head_dim, p.out_bf16, p.out_f32, lse);
         e = cudaGetLastError();
     }
     return e;
@@ -452,8 +517,9 @@ cudaError_t launch_gqa_decode(const void* q, const void* k, const void* v, void*
 cudaError_t launch_merge_partials(const float* o_parts, const float* lse_parts, int64_t n_parts, int64_t rows,
                                   int dim, void* out_bf16, float* out_f32, float* lse, cudaStream_t stream) {
     if (rows == 0) return cudaSuccess;
-    merge_partials_kernel<<<(unsigned)rows, 128, 0, stream>>>(o_parts, lse_parts, (int)n_parts, rows, dim,
-                                                              (__nv_bfloat16*)out_bf16, out_f32, lse);
+    if (dim > 32 * kMergeMaxDimPerLane || merge_smem_bytes(n_parts, dim) > 48 * 1024) return cudaErrorInvalidValue;
+    merge_partials_kernel<<<(unsigned)rows, kMergeWarps * 32, merge_smem_bytes(n_parts, dim), stream>>>(
+        o_parts, lse_parts, (int)n_parts, rows, dim, (__nv_bfloat16*)out_bf16, out_f32, lse);
     return cudaGetLastError();
 }
 

@@ -178,7 +178,9 @@ def test_decode_cfg4_full_size_split_invariance():
         pl.append(l.reshape(B * Hq))
     merged, mlse = rt.merge_partials(torch.stack(po), torch.stack(pl), out_dtype=torch.float32)
     torch.cuda.synchronize()
-    assert (merged.reshape(B, Hq, D) - full).abs().max().item() < 1e-4
+    # P is rounded to bf16 relative to a running maximum that depends on the chunking, so two shardings
+    # agree to ~2^-9 / sqrt(len) per element, not bit for bit; the row sums (LSE) stay in f32.
+    assert (merged.reshape(B, Hq, D) - full).abs().max().item() < 1e-3
     assert (mlse.reshape(B, Hq) - lse).abs().max().item() < 1e-4
     # independent check on a few rows with plain torch math in f32
     for b in (0, 17, 63):
