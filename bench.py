@@ -321,16 +321,14 @@ def main():
         g = torch.Generator(device="cuda").manual_seed(0xF00D + rank)
         k1 = torch.randn((1, Hkv, T, Dd), device="cuda", generator=g).to(torch.bfloat16)
         v1 = torch.randn((1, Hkv, T, Dd), device="cuda", generator=g).to(torch.bfloat16)
-        rec = torch.empty((Hq, Dd + 1), dtype=torch.float32, device="cuda")       # packed [O | LSE] of this rank
-        allrec = torch.empty((world, Hq, Dd + 1), dtype=torch.float32, device="cuda")
+        from rustorch_b200 import sharding
         ws = torch.empty(rt.decode_workspace_bytes(1, Hq, Hkv, Dd, T), dtype=torch.uint8, device="cuda")
 
         def step_splitkv():
+            # local shard -> (O f32, LSE) partial; one packed 16.5 KB record per rank over NCCL; local merge
             o32, l32 = rt.gqa_decode(q1, k1, v1, kv_len=T, out_dtype=torch.float32, workspace=ws)
-            rec[:, :Dd].copy_(o32[0])
-            rec[:, Dd].copy_(l32[0])
-            dist.all_gather_into_tensor(allrec, rec)
-            return rt.merge_partials(allrec[:, :, :Dd].contiguous(), allrec[:, :, Dd].contiguous())
+            allrec = sharding.all_gather_partials(sharding.pack_partial(o32[0], l32[0]))
+            return rt.merge_partials(*sharding.unpack_partials(allrec))
 
         sms = timed(step_splitkv, args.steps, args.warmup, dist, torch)
         total_bytes = 2.0 * Hkv * Dd * 2 * T * world

@@ -119,17 +119,38 @@ int rt_attn_prefill_bf16(const void* q, const void* k, const void* v, void* out,
                          float scale, void* stream);
 
 /*
+ * The same kernel for the shapes around self-attention that the reference's callers produce:
+ * grouped KV heads without materialising the repeated heads (the reference copies them,
+ * crates/rustorch-nn/src/gqa.rs:154-168), and a block of seq_q queries against seq_kv >= seq_q keys —
+ * a prompt chunk attending to an existing KV cache, which the reference's CUDA model cannot do
+ * (its prefill is a loop of single-token decode steps, crates/rustorch-llm/src/cuda_backend.rs:26-27)
+ * and its Metal backend does with gqa_decode_batched_f32 (crates/rustorch-metal/src/kernels.rs:14422-14516).
+ *   q, out : bf16 [B,Hq,seq_q,D];  k, v : bf16 [B,Hkv,seq_kv,D] (a cache passes seq_kv = max_seq);
+ *   lse    : NULL or f32 [B,Hq,seq_q].  Query head h reads KV head h / (Hq/Hkv) (gqa.rs:233).
+ *   kv_lens   : NULL or device int32 [B], visible keys per batch (<= seq_kv).
+ *   q_offsets : NULL or device int32 [B]; with RT_MASK_CAUSAL query row i of batch b sits at key
+ *               position i + q_offsets[b] and sees keys 0 .. i + q_offsets[b] (the Metal kernel's
+ *               pos_base).  NULL = 0, i.e. Mask::Causal of self-attention (mask.rs:43).
+ *   key_keep, keep_batch_stride, scale : as in rt_attn_prefill_bf16 (flags indexed by key, length seq_kv).
+ */
+int rt_attn_prefill_gqa_bf16(const void* q, const void* k, const void* v, void* out, float* lse,
+                             int64_t batch, int64_t heads_q, int64_t heads_kv, int64_t seq_q,
+                             int64_t seq_kv, int dim, int mask_flags, const int32_t* kv_lens,
+                             const int32_t* q_offsets, const uint8_t* key_keep,
+                             int64_t keep_batch_stride, float scale, void* stream);
+
+/*
  * The same operator on f32 device tensors with f32 arithmetic on CUDA cores (any D in
  * [1,256]); grouped KV heads and seq_q != seq_kv are allowed so that it also serves
  * gqa_forward_f32's prefill and cross-attention branches (gqa.rs:151-210).
  *   q, out : f32 [B,Hq,Nq,D];  k, v : f32 [B,Hkv,Nkv,D];  lse : NULL or f32 [B,Hq,Nq].
- *   Causal masking compares key j with query i directly (j > i masked), as mask.rs:43 does.
+ *   kv_lens, q_offsets, key_keep : as in rt_attn_prefill_gqa_bf16.
  */
 int rt_attn_prefill_f32(const float* q, const float* k, const float* v, float* out, float* lse,
                         int64_t batch, int64_t heads_q, int64_t heads_kv, int64_t seq_q,
                         int64_t seq_kv, int dim, int mask_flags, const int32_t* kv_lens,
-                        const uint8_t* key_keep, int64_t keep_batch_stride, float scale,
-                        void* stream);
+                        const int32_t* q_offsets, const uint8_t* key_keep, int64_t keep_batch_stride,
+                        float scale, void* stream);
 
 /*
  * Host-slice mirror of

@@ -313,6 +313,69 @@ int orc_naive_forward_masked(int64_t batch, int64_t heads, int64_t seq, int dim,
                                  mask_kind == 2 ? keep : NULL, keep_len, 0, NULL, -1.0f, out, NULL);
 }
 
+/*
+ * General naive attention for the shapes beyond self-attention that the callers of the path
+ * use: grouped KV heads (query head h reads KV head h / (Hq/Hkv), gqa.rs:233), seq_q != seq_kv
+ * (gqa.rs:190-210), per-batch visible key counts, and a causal mask for a block of queries that
+ * sits at positions q_offsets[b] .. q_offsets[b] + seq_q - 1 of a longer key sequence — the rule
+ * of the reference's batched decode kernel (rustorch-metal/src/kernels.rs:14422-14467:
+ * query b at pos_base + b sees keys 0 .. pos_base + b).  q_offsets = NULL means offset 0, which is
+ * Mask::Causal (mask.rs:43).  Same row semantics as naive_forward_masked: a row with no visible
+ * key is NaN with LSE = -inf.
+ *   q, out [B,Hq,Nq,D];  k, v [B,Hkv,Nkv,D];  lse NULL or [B,Hq,Nq].
+ */
+int orc_attention_general(const float* q, const float* k, const float* v, int64_t batch, int64_t heads_q,
+                          int64_t heads_kv, int64_t seq_q, int64_t seq_kv, int dim, int causal,
+                          const int32_t* kv_lens, const int32_t* q_offsets, float scale, float* out,
+                          float* lse) {
+    if (dim == 0) return ORC_ERR_ZERO_DIM;
+    if (heads_kv == 0 || heads_q % heads_kv != 0) return ORC_ERR_HEADS;
+    if (scale <= 0.0f) scale = 1.0f / sqrtf((float)dim);
+    const int64_t group = heads_q / heads_kv;
+    const int64_t n_bh = batch * heads_q;
+#pragma omp parallel for schedule(dynamic, 1) num_threads(orc_get_threads())
+    for (int64_t bh = 0; bh < n_bh; ++bh) {
+        const int64_t b = bh / heads_q, h = bh % heads_q, kvh = h / group;
+        const float* kb = k + (b * heads_kv + kvh) * seq_kv * dim;
+        const float* vb = v + (b * heads_kv + kvh) * seq_kv * dim;
+        int64_t hi = seq_kv;
+        if (kv_lens && kv_lens[b] < hi) hi = kv_lens[b] < 0 ? 0 : kv_lens[b];
+        const int64_t off = q_offsets ? q_offsets[b] : 0;
+        float* scores = (float*)malloc(sizeof(float) * (size_t)(seq_kv ? seq_kv : 1));
+        for (int64_t i = 0; i < seq_q; ++i) {
+            const float* qr = q + (bh * seq_q + i) * dim;
+            float* dst = out + (bh * seq_q + i) * dim;
+            int64_t vis = hi;
+            if (causal && i + off + 1 < vis) vis = i + off + 1;
+            if (vis < 0) vis = 0;
+            float mx = -INFINITY;
+            for (int64_t j = 0; j < vis; ++j) {
+                float s = 0.0f;
+                for (int d = 0; d < dim; ++d) s += qr[d] * kb[j * dim + d];
+                scores[j] = s * scale;
+                mx = fmaxf(mx, scores[j]);
+            }
+            float sum = 0.0f;
+            for (int64_t j = 0; j < vis; ++j) {
+                scores[j] = expf(scores[j] - mx);
+                sum += scores[j];
+            }
+            if (sum > 0.0f && isfinite(sum)) {
+                for (int d = 0; d < dim; ++d) dst[d] = 0.0f;
+                for (int64_t j = 0; j < vis; ++j) {
+                    const float w = scores[j] / sum;
+                    for (int d = 0; d < dim; ++d) dst[d] += w * vb[j * dim + d];
+                }
+            } else {
+                for (int d = 0; d < dim; ++d) dst[d] = NAN;
+            }
+            if (lse) lse[bh * seq_q + i] = (sum > 0.0f) ? mx + logf(sum) : (vis == 0 || mx == -INFINITY ? -INFINITY : NAN);
+        }
+        free(scores);
+    }
+    return ORC_OK;
+}
+
 /* ---------------------------------------------------------------- online softmax */
 
 /* online_softmax.rs:44-102: state is (m, l); EMPTY = (-inf, 0). */

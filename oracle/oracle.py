@@ -48,6 +48,8 @@ def lib() -> ctypes.CDLL:
                                                c_int64, c_int64, i32p, c_float, fp, fp]
         _lib.orc_naive_forward_masked.argtypes = [c_int64, c_int64, c_int64, c_int, fp, fp, fp, c_int, u8p,
                                                   c_int64, fp]
+        _lib.orc_attention_general.argtypes = [fp, fp, fp, c_int64, c_int64, c_int64, c_int64, c_int64, c_int, c_int,
+                                               i32p, i32p, c_float, fp, fp]
         _lib.orc_online_softmax_full.argtypes = [fp, c_int64, fp, fp]
         _lib.orc_combine_tiles.argtypes = [c_float, c_float, c_float, c_float, fp, fp]
         _lib.orc_gqa_forward_f32.argtypes = [fp, fp, fp, fp, c_int64, c_int64, c_int64, c_int64, c_int64, c_int]
@@ -175,6 +177,19 @@ def naive_forward_ext(q, k, v, causal=False, keep=None, kv_lens=None, scale=-1.0
     lens_a = None if kv_lens is None else np.ascontiguousarray(kv_lens, dtype=np.int32)
     rc = lib().orc_naive_forward_ext(B, H, N, D, _f(q), _f(k), _f(v), int(causal), _opt(keep_a, c_uint8),
                                      klen, stride, _opt(lens_a, c_int32), scale, _f(out), _f(lse))
+    return rc, out, lse
+
+
+def attention_general(q, k, v, causal=False, kv_lens=None, q_offsets=None, scale=-1.0):
+    """q [B,Hq,Nq,D], k/v [B,Hkv,Nkv,D] -> (rc, out [B,Hq,Nq,D], lse [B,Hq,Nq]); see orc_attention_general."""
+    B, Hq, Nq, D = q.shape
+    _, Hkv, Nkv, _ = k.shape
+    out = np.zeros_like(q)
+    lse = np.zeros((B, Hq, Nq), dtype=np.float32)
+    lens_a = None if kv_lens is None else np.ascontiguousarray(kv_lens, dtype=np.int32)
+    offs_a = None if q_offsets is None else np.ascontiguousarray(q_offsets, dtype=np.int32)
+    rc = lib().orc_attention_general(_f(q), _f(k), _f(v), B, Hq, Hkv, Nq, Nkv, D, int(causal),
+                                     _opt(lens_a, c_int32), _opt(offs_a, c_int32), scale, _f(out), _f(lse))
     return rc, out, lse
 
 

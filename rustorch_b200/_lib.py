@@ -44,8 +44,12 @@ PROTOTYPES = {
     "rt_attn_device_status": (c_int, [POINTER(c_int)]),
     "rt_attn_prefill_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
                                      c_int, c_int, c_void_p, c_void_p, c_int64, c_float, c_void_p]),
+    "rt_attn_prefill_gqa_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
+                                         c_int64, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int64,
+                                         c_float, c_void_p]),
     "rt_attn_prefill_f32": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
-                                    c_int64, c_int64, c_int, c_int, c_void_p, c_void_p, c_int64, c_float, c_void_p]),
+                                    c_int64, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int64, c_float,
+                                    c_void_p]),
     "rt_flash_forward_f32_host": (c_int, [_fp, c_size_t, _fp, c_size_t, _fp, c_size_t, _fp, c_size_t, c_int64,
                                           c_int64, c_int64, c_int64, c_int, _u8p, c_size_t, c_int]),
     "rt_attn_prefill_bf16_host": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,

@@ -157,19 +157,24 @@ def _stream_ptr():
 
 
 def prefill_bf16(q, k, v, causal: bool = False, kv_lens=None, key_keep=None, scale: Optional[float] = None,
-                 out=None, lse=None, return_lse: bool = True):
-    """Flash-attention forward on bf16 CUDA tensors [B,H,N,D] (D in {64,128}) via ``rt_attn_prefill_bf16``.
+                 out=None, lse=None, return_lse: bool = True, q_offsets=None):
+    """Flash-attention forward on bf16 CUDA tensors (D in {64,128}), tcgen05 kernel.
 
-    kv_lens: optional int32 CUDA tensor [B]; key_keep: optional uint8/bool CUDA tensor [N] or [B,N].
-    Returns (out bf16 [B,H,N,D], lse f32 [B,H,N] or None).  Enqueues on the current stream.
+    q [B,Hq,Nq,D]; k, v [B,Hkv,Nkv,D] with Hq a multiple of Hkv and Nkv >= 1 (self-attention: same
+    shape as q).  kv_lens: optional int32 CUDA [B] visible keys; q_offsets: optional int32 CUDA [B],
+    causal position of query row 0 (a prompt chunk against a cache); key_keep: optional uint8/bool
+    CUDA [Nkv] or [B,Nkv].  Returns (out bf16 [B,Hq,Nq,D], lse f32 [B,Hq,Nq] or None).  Enqueues on
+    the current stream.  Calls ``rt_attn_prefill_bf16`` for self-attention shapes and
+    ``rt_attn_prefill_gqa_bf16`` otherwise.
     """
     import torch
     for name, t in (("q", q), ("k", k), ("v", v)):
         if not (t.is_cuda and t.dtype == torch.bfloat16 and t.is_contiguous() and t.dim() == 4):
             raise TypeError(f"{name} must be a contiguous 4-D bfloat16 CUDA tensor")
     B, H, N, D = q.shape
-    if k.shape != q.shape or v.shape != q.shape:
-        raise BufferShapeMismatch("k/v", q.numel(), k.numel())
+    if v.shape != k.shape or k.shape[0] != B or k.shape[3] != D:
+        raise BufferShapeMismatch("k/v", k.numel(), v.numel())
+    Hkv, Nkv = k.shape[1], k.shape[2]
     if out is None:
         out = torch.empty_like(q)
     if lse is None and return_lse:
@@ -177,26 +182,35 @@ def prefill_bf16(q, k, v, causal: bool = False, kv_lens=None, key_keep=None, sca
     keep_ptr, keep_stride = None, 0
     if key_keep is not None:
         key_keep = key_keep.to(torch.uint8).contiguous()
-        if key_keep.shape[-1] != N:
-            raise PaddingLengthMismatch(N, key_keep.shape[-1])
-        keep_stride = N if key_keep.dim() == 2 else 0
+        if key_keep.shape[-1] != Nkv:
+            raise PaddingLengthMismatch(Nkv, key_keep.shape[-1])
+        keep_stride = Nkv if key_keep.dim() == 2 else 0
         keep_ptr = key_keep.data_ptr()
-    lens_ptr = None
-    if kv_lens is not None:
-        if not (kv_lens.is_cuda and kv_lens.dtype == torch.int32 and kv_lens.numel() == B):
-            raise TypeError("kv_lens must be an int32 CUDA tensor of B elements")
-        lens_ptr = kv_lens.data_ptr()
-    rc = _lib.lib().rt_attn_prefill_bf16(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
-                                         lse.data_ptr() if lse is not None else None, B, H, N, D,
-                                         _lib.RT_MASK_CAUSAL if causal else _lib.RT_MASK_NONE, lens_ptr, keep_ptr,
-                                         keep_stride, -1.0 if scale is None else float(scale), _stream_ptr())
+    for name, t in (("kv_lens", kv_lens), ("q_offsets", q_offsets)):
+        if t is not None and not (t.is_cuda and t.dtype == torch.int32 and t.numel() == B):
+            raise TypeError(f"{name} must be an int32 CUDA tensor of B elements")
+    lens_ptr = kv_lens.data_ptr() if kv_lens is not None else None
+    flags = _lib.RT_MASK_CAUSAL if causal else _lib.RT_MASK_NONE
+    sc = -1.0 if scale is None else float(scale)
+    lse_ptr = lse.data_ptr() if lse is not None else None
+    if Hkv == H and Nkv == N and q_offsets is None:
+        rc = _lib.lib().rt_attn_prefill_bf16(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse_ptr, B, H,
+                                             N, D, flags, lens_ptr, keep_ptr, keep_stride, sc, _stream_ptr())
+        where = "rt_attn_prefill_bf16"
+    else:
+        rc = _lib.lib().rt_attn_prefill_gqa_bf16(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse_ptr, B,
+                                                 H, Hkv, N, Nkv, D, flags, lens_ptr,
+                                                 q_offsets.data_ptr() if q_offsets is not None else None, keep_ptr,
+                                                 keep_stride, sc, _stream_ptr())
+        where = "rt_attn_prefill_gqa_bf16"
     if rc == _lib.RT_ERR_ZERO_DIM:
         raise ZeroDim()
-    _lib.check(rc, "rt_attn_prefill_bf16")
+    _lib.check(rc, where)
     return out, lse
 
 
-def prefill_f32(q, k, v, causal: bool = False, kv_lens=None, key_keep=None, scale: Optional[float] = None):
+def prefill_f32(q, k, v, causal: bool = False, kv_lens=None, key_keep=None, scale: Optional[float] = None,
+                q_offsets=None):
     """f32 CUDA-core forward on f32 CUDA tensors q [B,Hq,Nq,D], k/v [B,Hkv,Nkv,D] via ``rt_attn_prefill_f32``."""
     import torch
     B, Hq, Nq, D = q.shape
@@ -210,7 +224,8 @@ def prefill_f32(q, k, v, causal: bool = False, kv_lens=None, key_keep=None, scal
         keep_ptr = key_keep.data_ptr()
     rc = _lib.lib().rt_attn_prefill_f32(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(), B,
                                         Hq, Hkv, Nq, Nkv, D, _lib.RT_MASK_CAUSAL if causal else _lib.RT_MASK_NONE,
-                                        kv_lens.data_ptr() if kv_lens is not None else None, keep_ptr, keep_stride,
+                                        kv_lens.data_ptr() if kv_lens is not None else None,
+                                        q_offsets.data_ptr() if q_offsets is not None else None, keep_ptr, keep_stride,
                                         -1.0 if scale is None else float(scale), _stream_ptr())
     if rc == _lib.RT_ERR_ZERO_DIM:
         raise ZeroDim()

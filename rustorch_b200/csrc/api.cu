@@ -120,26 +120,38 @@ int rt_attn_device_status(int* status) {
 
 // ------------------------------------------------------------------------------ prefill
 
+int rt_attn_prefill_gqa_bf16(const void* q, const void* k, const void* v, void* out, float* lse, int64_t batch,
+                             int64_t heads_q, int64_t heads_kv, int64_t seq_q, int64_t seq_kv, int dim, int mask_flags,
+                             const int32_t* kv_lens, const int32_t* q_offsets, const uint8_t* key_keep,
+                             int64_t keep_batch_stride, float scale, void* stream) {
+    if (dim == 0) return RT_ERR_ZERO_DIM;
+    if (batch < 0 || heads_q < 0 || heads_kv < 0 || seq_q < 0 || seq_kv < 0 || dim < 0 || keep_batch_stride < 0)
+        return RT_ERR_BAD_LENGTH;
+    if (batch == 0 || heads_q == 0 || seq_q == 0) return RT_OK;  // cpu_forward.rs:203-206
+    if (heads_kv == 0 || heads_q % heads_kv != 0) return RT_ERR_HEAD_COUNT;  // gqa.rs:106-111
+    if (!q || !out || (seq_kv > 0 && (!k || !v))) return RT_ERR_NULL_POINTER;
+    if (dim != 64 && dim != 128) return RT_ERR_UNSUPPORTED;
+    if (seq_q > (1 << 30) || seq_kv > (1 << 30) || batch * heads_q > (1 << 30)) return RT_ERR_UNSUPPORTED;
+    if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(out)) return RT_ERR_ALIGNMENT;
+    if (mask_flags & ~RT_MASK_CAUSAL) return RT_ERR_UNSUPPORTED;
+    RT_CUDA(rt::launch_prefill_tc(q, k, v, out, lse, batch, heads_q, heads_kv, seq_q, seq_kv, dim,
+                                  mask_flags & RT_MASK_CAUSAL, kv_lens, q_offsets, key_keep, keep_batch_stride,
+                                  default_scale(scale, dim), as_stream(stream)));
+    return RT_OK;
+}
+
 int rt_attn_prefill_bf16(const void* q, const void* k, const void* v, void* out, float* lse, int64_t batch,
                          int64_t heads, int64_t seq, int dim, int mask_flags, const int32_t* kv_lens,
                          const uint8_t* key_keep, int64_t keep_batch_stride, float scale, void* stream) {
-    if (dim == 0) return RT_ERR_ZERO_DIM;
-    if (batch < 0 || heads < 0 || seq < 0 || dim < 0 || keep_batch_stride < 0) return RT_ERR_BAD_LENGTH;
-    if (batch == 0 || heads == 0 || seq == 0) return RT_OK;  // cpu_forward.rs:203-206
-    if (!q || !k || !v || !out) return RT_ERR_NULL_POINTER;
-    if (dim != 64 && dim != 128) return RT_ERR_UNSUPPORTED;
-    if (seq > (1 << 30) || batch * heads > (1 << 30)) return RT_ERR_UNSUPPORTED;
-    if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(out)) return RT_ERR_ALIGNMENT;
-    if (mask_flags & ~RT_MASK_CAUSAL) return RT_ERR_UNSUPPORTED;
-    RT_CUDA(rt::launch_prefill_tc(q, k, v, out, lse, batch, heads, seq, dim, mask_flags & RT_MASK_CAUSAL, kv_lens,
-                                  key_keep, keep_batch_stride, default_scale(scale, dim), as_stream(stream)));
-    return RT_OK;
+    if (batch > 0 && heads > 0 && seq > 0 && dim > 0 && (!k || !v)) return RT_ERR_NULL_POINTER;
+    return rt_attn_prefill_gqa_bf16(q, k, v, out, lse, batch, heads, heads > 0 ? heads : 1, seq, seq, dim, mask_flags,
+                                    kv_lens, nullptr, key_keep, keep_batch_stride, scale, stream);
 }
 
 int rt_attn_prefill_f32(const float* q, const float* k, const float* v, float* out, float* lse, int64_t batch,
                         int64_t heads_q, int64_t heads_kv, int64_t seq_q, int64_t seq_kv, int dim, int mask_flags,
-                        const int32_t* kv_lens, const uint8_t* key_keep, int64_t keep_batch_stride, float scale,
-                        void* stream) {
+                        const int32_t* kv_lens, const int32_t* q_offsets, const uint8_t* key_keep,
+                        int64_t keep_batch_stride, float scale, void* stream) {
     if (dim == 0) return RT_ERR_ZERO_DIM;
     if (batch < 0 || heads_q < 0 || heads_kv < 0 || seq_q < 0 || seq_kv < 0 || dim < 0) return RT_ERR_BAD_LENGTH;
     if (heads_kv == 0 || heads_q % heads_kv != 0) return heads_q == 0 ? RT_OK : RT_ERR_HEAD_COUNT;
@@ -148,7 +160,7 @@ int rt_attn_prefill_f32(const float* q, const float* k, const float* v, float* o
     if (dim > 256) return RT_ERR_UNSUPPORTED;
     if (mask_flags & ~RT_MASK_CAUSAL) return RT_ERR_UNSUPPORTED;
     RT_CUDA(rt::launch_prefill_f32(q, k, v, out, lse, batch, heads_q, heads_kv, seq_q, seq_kv, dim,
-                                   mask_flags & RT_MASK_CAUSAL, kv_lens, key_keep, keep_batch_stride,
+                                   mask_flags & RT_MASK_CAUSAL, kv_lens, q_offsets, key_keep, keep_batch_stride,
                                    default_scale(scale, dim), as_stream(stream)));
     return RT_OK;
 }
@@ -191,8 +203,8 @@ int rt_flash_forward_f32_host(const float* q, size_t q_len, const float* k, size
     const int flags = (mask_kind == RT_MASKKIND_CAUSAL) ? RT_MASK_CAUSAL : RT_MASK_NONE;
     if (precision == RT_PRECISION_F32) {
         int rc = rt_attn_prefill_f32(dq.as<float>(), dk.as<float>(), dv.as<float>(), dout.as<float>(), nullptr,
-                                     batch, heads, heads, seq, seq, (int)dim, flags, nullptr, keep_dev, 0, -1.f,
-                                     nullptr);
+                                     batch, heads, heads, seq, seq, (int)dim, flags, nullptr, nullptr, keep_dev, 0,
+                                     -1.f, nullptr);
         if (rc != RT_OK) return rc;
     } else {
         DevBuf bq(5), bk(6), bv(7), bo(8);
@@ -327,7 +339,7 @@ int rt_gqa_forward_f32_host(const float* q, size_t q_len, const float* k, size_t
     } else {
         int rc = rt_attn_prefill_f32(dq.as<float>(), dk.as<float>(), dv.as<float>(), dout.as<float>(), nullptr, batch,
                                      n_heads, n_kv_heads, seq_q, seq_kv, (int)head_dim, RT_MASK_NONE, nullptr,
-                                     nullptr, 0, -1.f, nullptr);
+                                     nullptr, nullptr, 0, -1.f, nullptr);
         if (rc != RT_OK) return rc;
     }
     RT_CUDA(cudaMemcpy(out, dout.p, qn * 4, cudaMemcpyDeviceToHost));

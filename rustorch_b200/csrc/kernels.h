@@ -33,15 +33,16 @@ cudaError_t launch_gqa_decode_tc(const void* q, const void* k, const void* v, vo
 cudaError_t launch_prefill_f32(const float* q, const float* k, const float* v, float* out, float* lse,
                                int64_t batch, int64_t heads_q, int64_t heads_kv, int64_t seq_q,
                                int64_t seq_kv, int dim, int causal, const int32_t* kv_lens,
-                               const uint8_t* key_keep, int64_t keep_batch_stride, float scale,
-                               cudaStream_t stream);
+                               const int32_t* q_offsets, const uint8_t* key_keep, int64_t keep_batch_stride,
+                               float scale, cudaStream_t stream);
 cudaError_t launch_f32_to_bf16(const float* src, void* dst, int64_t n, cudaStream_t stream);
 cudaError_t launch_bf16_to_f32(const void* src, float* dst, int64_t n, cudaStream_t stream);
 
 // ---- prefill_tc.cu (tcgen05 / TMEM / TMA)
 cudaError_t launch_prefill_tc(const void* q, const void* k, const void* v, void* out, float* lse,
-                              int64_t batch, int64_t heads, int64_t seq, int dim, int causal,
-                              const int32_t* kv_lens, const uint8_t* key_keep, int64_t keep_batch_stride,
-                              float scale, cudaStream_t stream);
+                              int64_t batch, int64_t heads, int64_t heads_kv, int64_t seq, int64_t seq_kv, int dim,
+                              int causal, const int32_t* kv_lens, const int32_t* q_offsets,
+                              const uint8_t* key_keep, int64_t keep_batch_stride, float scale,
+                              cudaStream_t stream);
 
 }  // namespace rt

@@ -21,6 +21,7 @@ struct SimtParams {
     int64_t heads_q, heads_kv, seq_q, seq_kv;
     int dim, causal;
     const int32_t* kv_lens;
+    const int32_t* q_offsets;
     const uint8_t* key_keep;
     int64_t keep_batch_stride;
     float scale;
@@ -52,10 +53,13 @@ __global__ void __launch_bounds__(kSimtRows * 32) prefill_f32_kernel(const SimtP
 
     int64_t k_hi = p.seq_kv;
     if (p.kv_lens && p.kv_lens[b] < k_hi) k_hi = p.kv_lens[b] < 0 ? 0 : p.kv_lens[b];
+    const int64_t q_off = p.q_offsets ? p.q_offsets[b] : 0;  // query row i sits at key position i + q_off
     int64_t k_loop = k_hi;
     if (p.causal) {
-        int64_t last = row0 + kSimtRows;  // keys <= last query row of the CTA
+        int64_t last = row0 + kSimtRows;  // keys <= position of the last query row of the CTA
         if (last > p.seq_q) last = p.seq_q;
+        last += q_off;
+        if (last < 0) last = 0;
         if (last < k_loop) k_loop = last;
     }
 
@@ -82,7 +86,7 @@ __global__ void __launch_bounds__(kSimtRows * 32) prefill_f32_kernel(const SimtP
         for (int d = 0; d < D; ++d) s = fmaf(qrow[d], krow[d], s);
         s *= p.scale;
         bool masked = key >= k_hi;
-        if (p.causal && key > qi) masked = true;
+        if (p.causal && key > qi + q_off) masked = true;
         if (keep && key < p.seq_kv && !keep[key]) masked = true;
         if (masked) s = -INFINITY;
 
@@ -127,10 +131,10 @@ __global__ void __launch_bounds__(kSimtRows * 32) prefill_f32_kernel(const SimtP
 cudaError_t launch_prefill_f32(const float* q, const float* k, const float* v, float* out, float* lse,
                                int64_t batch, int64_t heads_q, int64_t heads_kv, int64_t seq_q,
                                int64_t seq_kv, int dim, int causal, const int32_t* kv_lens,
-                               const uint8_t* key_keep, int64_t keep_batch_stride, float scale,
-                               cudaStream_t stream) {
+                               const int32_t* q_offsets, const uint8_t* key_keep, int64_t keep_batch_stride,
+                               float scale, cudaStream_t stream) {
     if (batch == 0 || heads_q == 0 || seq_q == 0) return cudaSuccess;
-    SimtParams p{q, k, v, out, lse, heads_q, heads_kv, seq_q, seq_kv, dim, causal, kv_lens, key_keep,
+    SimtParams p{q, k, v, out, lse, heads_q, heads_kv, seq_q, seq_kv, dim, causal, kv_lens, q_offsets, key_keep,
                  keep_batch_stride, scale};
     const size_t smem = sizeof(float) * ((size_t)kSimtKeys * (dim + 1) + (size_t)kSimtKeys * dim +
                                          (size_t)kSimtRows * dim);

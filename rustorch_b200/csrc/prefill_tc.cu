@@ -53,7 +53,9 @@ struct TcParams {
     const int32_t* kv_lens;
     const uint8_t* key_keep;
     int64_t keep_batch_stride;
-    int seq, heads;
+    int seq, heads;        // query rows per head, query heads
+    int seq_kv, heads_kv;  // key rows per KV head, KV heads (query head h reads KV head h / (heads/heads_kv))
+    const int32_t* q_offsets;  // NULL or [B]: causal position of query row 0 inside the key sequence
     float scale_log2;  // scale * log2(e)
     int* status;       // device status word (bounded-wait expiry codes)
 #ifdef RT_TC_TIMELINE
@@ -119,17 +121,23 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     const int bh = blockIdx.x / n_qb;
     const int qb = n_qb - 1 - (int)(blockIdx.x % n_qb);  // heaviest causal block of a head first
     const int b = bh / p.heads;
+    const int bh_kv = b * p.heads_kv + (bh % p.heads) / (p.heads / p.heads_kv);
     const int q0 = qb * 256;
+    const int Nkv = p.seq_kv;
 
-    int kv_hi = N;
+    int kv_hi = Nkv;
     if (p.kv_lens) {
         const int l = p.kv_lens[b];
-        kv_hi = l < 0 ? 0 : (l < N ? l : N);
+        kv_hi = l < 0 ? 0 : (l < Nkv ? l : Nkv);
     }
+    const int q_off = p.q_offsets ? p.q_offsets[b] : 0;  // query row i sits at key position i + q_off
     const int n_steps = (kv_hi + 63) / 64;  // 64-key steps that hold a visible key
-    int U[2];                               // steps of each Q tile
-    U[0] = kCausal ? min(n_steps, 4 * qb + 2) : n_steps;
-    U[1] = kCausal ? min(n_steps, 4 * qb + 4) : n_steps;
+    int U[2];                               // steps of each Q tile (U[0] <= U[1])
+#pragma unroll
+    for (int w = 0; w < 2; ++w) {
+        const int last_key = q0 + 128 * w + 127 + q_off;  // last key the tile's last row may see
+        U[w] = !kCausal ? n_steps : (last_key < 0 ? 0 : min(n_steps, last_key / 64 + 1));
+    }
     const int u_max = U[1];
     const int n_tiles = (u_max + 1) / 2;    // 128-key K/V tiles to load
 
@@ -183,7 +191,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 mbar_arrive_expect_tx(&k_full[0], TILE);
 #pragma unroll
                 for (int s = 0; s < C::NSUB; ++s)
-                    tma_load_3d(sK + s * SUB, &tm_k, &k_full[0], s * 64, 0, bh);
+                    tma_load_3d(sK + s * SUB, &tm_k, &k_full[0], s * 64, 0, bh_kv);
             }
         }
     }
@@ -211,14 +219,14 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                     mbar_arrive_expect_tx(&k_full[ks], TILE);
 #pragma unroll
                     for (int s = 0; s < C::NSUB; ++s)
-                        tma_load_3d(sK + ks * TILE + s * SUB, &tm_k, &k_full[ks], s * 64, j * 128, bh);
+                        tma_load_3d(sK + ks * TILE + s * SUB, &tm_k, &k_full[ks], s * 64, j * 128, bh_kv);
                     k_issued = j + 1;
                 }
                 if (!mbar_wait(&v_empty[vs], ((uint32_t)(j / VS) & 1u) ^ 1u, p.status, kToVEmpty)) break;
                 mbar_arrive_expect_tx(&v_full[vs], TILE);
 #pragma unroll
                 for (int s = 0; s < C::NSUB; ++s)
-                    tma_load_3d(sV + vs * TILE + s * SUB, &tm_v, &v_full[vs], s * 64, j * 128, bh);
+                    tma_load_3d(sV + vs * TILE + s * SUB, &tm_v, &v_full[vs], s * 64, j * 128, bh_kv);
                 v_issued = j + 1;
             }
             // Drain: every copy this thread issued must have landed before the CTA may exit.
@@ -272,17 +280,20 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             };
             auto last_use = [&](int u) { return (u & 1) || u == U[1] - 1; };  // of a 128-key tile, by Q tile 1
 
-            bool ok = wait(&q_full[0], 0, kToQ) && wait(&k_full[0], 0, kToKFull);
-            if (ok) {
-                tc_fence_after();
-                issue_S(0, 0);
-                commit(&s_full[0]);
-                if (U[0] > 1) {
-                    issue_S(0, 1);
-                    commit(&s_full[1]);
+            bool ok = wait(&k_full[0], 0, kToKFull);
+            if (ok && U[0] > 0) {
+                ok = wait(&q_full[0], 0, kToQ);
+                if (ok) {
+                    tc_fence_after();
+                    issue_S(0, 0);
+                    commit(&s_full[0]);
+                    if (U[0] > 1) {
+                        issue_S(0, 1);
+                        commit(&s_full[1]);
+                    }
                 }
-                ok = wait(&q_full[1], 0, kToQ);
             }
+            if (ok) ok = wait(&q_full[1], 0, kToQ);
             if (ok) {
                 tc_fence_after();
                 issue_S(1, 0);
@@ -372,7 +383,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             // ---- masks: keys beyond kv_hi, causal diagonal, keep flags
             const int col0 = u * 64;
             int lim = kv_hi - 1 - col0;                       // last visible column in this step
-            if (kCausal) lim = min(lim, row - col0);
+            if (kCausal) lim = min(lim, row + q_off - col0);
             if (lim < 63) {
 #pragma unroll
                 for (int i = 0; i < 64; ++i)
@@ -381,7 +392,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             if (kKeep) {  // Mask::Padding keep flags (mask.rs:44); every thread reads the same bytes
 #pragma unroll
                 for (int i = 0; i < 64; ++i)
-                    if (col0 + i < N && __ldg(keep + col0 + i) == 0) s[i] = 0xff800000u;
+                    if (col0 + i < Nkv && __ldg(keep + col0 + i) == 0) s[i] = 0xff800000u;
             }
 
             // ---- row max (three-input max halves the instruction count)
@@ -456,6 +467,15 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             mbar_arrive(&p_full[w * 2 + buf]);
         }
 
+        if (n_iter == 0) {  // this tile sees no key (its rows lie before the first visible position)
+            if (row < N) {
+                uint4* dst = reinterpret_cast<uint4*>(p.out + ((int64_t)bh * N + row) * D);
+#pragma unroll
+                for (int i = 0; i < D / 8; ++i) dst[i] = make_uint4(0x7fc07fc0u, 0x7fc07fc0u, 0x7fc07fc0u, 0x7fc07fc0u);
+                if (p.lse) p.lse[(int64_t)bh * N + row] = -INFINITY;
+            }
+            ok = false;
+        }
         // ---- epilogue: O / l -> bf16, LSE.  (o_full cannot be used here: up to two PV steps may
         // still be in flight, which a parity wait cannot tell from none.)
         if (ok && __all_sync(kFullMask, mbar_wait(&o_done[w], 0, p.status, kToOFull))) {
@@ -544,14 +564,15 @@ static cudaError_t launch_tc(const CUtensorMap& mq, const CUtensorMap& mk, const
 }
 
 cudaError_t launch_prefill_tc(const void* q, const void* k, const void* v, void* out, float* lse, int64_t batch,
-                              int64_t heads, int64_t seq, int dim, int causal, const int32_t* kv_lens,
-                              const uint8_t* key_keep, int64_t keep_batch_stride, float scale,
-                              cudaStream_t stream) {
+                              int64_t heads, int64_t heads_kv, int64_t seq, int64_t seq_kv, int dim, int causal,
+                              const int32_t* kv_lens, const int32_t* q_offsets, const uint8_t* key_keep,
+                              int64_t keep_batch_stride, float scale, cudaStream_t stream) {
     const int64_t bh = batch * heads;
     if (bh == 0 || seq == 0) return cudaSuccess;
     CUtensorMap mq, mk, mv;
-    if (!make_tensor_map_bf16_3d(&mq, q, bh, seq, dim) || !make_tensor_map_bf16_3d(&mk, k, bh, seq, dim) ||
-        !make_tensor_map_bf16_3d(&mv, v, bh, seq, dim))
+    if (!make_tensor_map_bf16_3d(&mq, q, bh, seq, dim) ||
+        !make_tensor_map_bf16_3d(&mk, k, batch * heads_kv, seq_kv, dim) ||
+        !make_tensor_map_bf16_3d(&mv, v, batch * heads_kv, seq_kv, dim))
         return cudaErrorInvalidValue;
     TcParams p;
     p.out = (__nv_bfloat16*)out;
@@ -561,6 +582,9 @@ cudaError_t launch_prefill_tc(const void* q, const void* k, const void* v, void*
     p.keep_batch_stride = keep_batch_stride;
     p.seq = (int)seq;
     p.heads = (int)heads;
+    p.seq_kv = (int)seq_kv;
+    p.heads_kv = (int)heads_kv;
+    p.q_offsets = q_offsets;
     p.scale_log2 = scale * kLog2e;
     p.status = device_status_ptr();
     if (!p.status) return cudaErrorInvalidSymbol;

@@ -187,3 +187,72 @@ def test_prefill_tc_full_size_slabs(oracle, cfg):
                                                    kv_lens=None if lens is None else lens[b:b + 1])
         util.check_output(util.to_np(out[b:b + 1, h:h + 1]), ref, label=f"{cfg} slab {b},{h}")
         util.check_lse(util.to_np(lse[b:b + 1, h:h + 1]), ref_lse)
+
+
+@pytest.mark.parametrize("D", [128, 64])
+@pytest.mark.parametrize("causal", [False, True])
+def test_prefill_gqa_without_replication(oracle, D, causal):
+    """Grouped KV heads: query head h reads KV head h / (Hq/Hkv) (gqa.rs:233); no repeated K/V in memory."""
+    B, Hq, Hkv, N = 2, 8, 2, 300
+    q = util.normal_bf16(oracle, (B, Hq, N, D), util.SEED_Q)
+    k = util.normal_bf16(oracle, (B, Hkv, N, D), util.SEED_K)
+    v = util.normal_bf16(oracle, (B, Hkv, N, D), util.SEED_V)
+    out, lse = _run_tc(q, k, v, causal=causal)
+    _, ref, ref_lse = oracle.attention_general(q, k, v, causal=causal)
+    util.check_output(out, ref, label=f"gqa D{D} causal={causal}")
+    util.check_lse(lse, ref_lse)
+    if not causal:  # the reference's own prefill branch (repeat KV heads, unmasked flash) gives the same numbers
+        rc, ref2 = oracle.gqa_forward_f32(q.ravel(), k.ravel(), v.ravel(), B, Hq, Hkv, N, N, D)
+        assert rc == 0 and np.abs(ref2.reshape(ref.shape) - ref).max() < 1e-4
+
+
+@pytest.mark.parametrize("D,Hq,Hkv", [(128, 8, 2), (64, 4, 4)])
+def test_prefill_chunk_against_kv_cache(oracle, D, Hq, Hkv):
+    """A block of Nq new queries at positions pos_base .. pos_base+Nq-1 over a cache of max_seq rows, causal:
+    the rule of the reference's batched decode kernel (rustorch-metal/src/kernels.rs:14422-14467)."""
+    B, Nq, S = 3, 200, 1024
+    q = util.normal_bf16(oracle, (B, Hq, Nq, D), util.SEED_Q)
+    kc = util.normal_bf16(oracle, (B, Hkv, S, D), util.SEED_K)
+    vc = util.normal_bf16(oracle, (B, Hkv, S, D), util.SEED_V)
+    lens = np.array([1024, 200, 517], dtype=np.int32)       # visible keys including the new chunk
+    offs = (lens - Nq).astype(np.int32)                      # pos_base of each sequence
+    out, lse = _run_tc(q, kc, vc, causal=True, kv_lens=util.to_cuda(lens), q_offsets=util.to_cuda(offs))
+    _, ref, ref_lse = oracle.attention_general(q, kc, vc, causal=True, kv_lens=lens, q_offsets=offs)
+    util.check_output(out, ref, label="chunked prefill")
+    util.check_lse(lse, ref_lse)
+    # the last query row of each chunk equals a single-token decode over the same cache
+    import rustorch_b200 as rt
+    o_dec, _ = rt.gqa_decode(util.to_cuda_bf16(np.ascontiguousarray(q[:, :, -1])), util.to_cuda_bf16(kc),
+                             util.to_cuda_bf16(vc), kv_lens=util.to_cuda(lens))
+    assert np.abs(util.to_np(o_dec) - out[:, :, -1]).max() <= 1.6e-2
+
+
+def test_prefill_query_rows_before_the_first_key(oracle):
+    """Negative offsets: leading query rows (even a whole 128-row tile) see no key -> NaN rows, LSE = -inf."""
+    B, H, Nq, S, D = 2, 2, 400, 512, 128
+    q = util.normal_bf16(oracle, (B, H, Nq, D), util.SEED_Q)
+    kc = util.normal_bf16(oracle, (B, H, S, D), util.SEED_K)
+    vc = util.normal_bf16(oracle, (B, H, S, D), util.SEED_V)
+    lens = np.array([250, 512], dtype=np.int32)
+    offs = np.array([-150, 112], dtype=np.int32)
+    out, lse = _run_tc(q, kc, vc, causal=True, kv_lens=util.to_cuda(lens), q_offsets=util.to_cuda(offs))
+    _, ref, ref_lse = oracle.attention_general(q, kc, vc, causal=True, kv_lens=lens, q_offsets=offs)
+    assert np.isnan(ref[0, :, :150]).all() and not np.isnan(ref[0, :, 150:]).any()
+    util.check_output(out, ref, label="negative offset")
+    util.check_lse(lse, ref_lse)
+
+
+def test_prefill_f32_chunk_against_cache(oracle):
+    import torch
+    import rustorch_b200 as rt
+    B, Hq, Hkv, Nq, S, D = 2, 4, 2, 37, 150, 40
+    q = oracle.fill_normal((B, Hq, Nq, D), 1)
+    kc, vc = oracle.fill_normal((B, Hkv, S, D), 2), oracle.fill_normal((B, Hkv, S, D), 3)
+    lens = np.array([150, 60], dtype=np.int32)
+    offs = (lens - Nq).astype(np.int32)
+    out, lse = rt.prefill_f32(util.to_cuda(q), util.to_cuda(kc), util.to_cuda(vc), causal=True,
+                              kv_lens=util.to_cuda(lens), q_offsets=util.to_cuda(offs))
+    torch.cuda.synchronize()
+    _, ref, ref_lse = oracle.attention_general(q, kc, vc, causal=True, kv_lens=lens, q_offsets=offs)
+    assert np.abs(util.to_np(out) - ref).max() < 1e-4
+    util.check_lse(util.to_np(lse), ref_lse)
