@@ -225,6 +225,33 @@ int rt_flash_forward_f32_host(const float* q, size_t q_len, const float* k, size
     return RT_OK;
 }
 
+// Streams and events of the pipelined host entry, created once per device.
+namespace {
+struct HostPipeline {
+    static constexpr int kMaxChunks = 32;
+    cudaStream_t in[64] = {}, comp[64] = {}, out[64] = {};
+    cudaEvent_t ev_in[64][kMaxChunks] = {}, ev_comp[64][kMaxChunks] = {};
+    bool ready[64] = {};
+    cudaError_t init(int dev) {
+        if (ready[dev]) return cudaSuccess;
+        cudaError_t e;
+        if ((e = cudaStreamCreateWithFlags(&in[dev], cudaStreamNonBlocking)) != cudaSuccess) return e;
+        if ((e = cudaStreamCreateWithFlags(&comp[dev], cudaStreamNonBlocking)) != cudaSuccess) return e;
+        if ((e = cudaStreamCreateWithFlags(&out[dev], cudaStreamNonBlocking)) != cudaSuccess) return e;
+        for (int i = 0; i < kMaxChunks; ++i) {
+            if ((e = cudaEventCreateWithFlags(&ev_in[dev][i], cudaEventDisableTiming)) != cudaSuccess) return e;
+            if ((e = cudaEventCreateWithFlags(&ev_comp[dev][i], cudaEventDisableTiming)) != cudaSuccess) return e;
+        }
+        ready[dev] = true;
+        return cudaSuccess;
+    }
+};
+HostPipeline g_pipe;
+}  // namespace
+
+// The (b, head-range) chunks run through three streams (copy in, kernel, copy out), so the upload
+// of chunk c+1, the kernel of chunk c and the download of chunk c-1 overlap; with pinned host
+// memory the call is bounded by the slower PCIe direction instead of the sum of both.
 int rt_attn_prefill_bf16_host(const void* q, const void* k, const void* v, void* out, float* lse, int64_t batch,
                               int64_t heads, int64_t seq, int dim, int mask_flags, const int32_t* kv_lens,
                               float scale) {
@@ -233,28 +260,76 @@ int rt_attn_prefill_bf16_host(const void* q, const void* k, const void* v, void*
     const size_t n = (size_t)batch * heads * seq * dim;
     if (n == 0) return RT_OK;
     if (!q || !k || !v || !out) return RT_ERR_NULL_POINTER;
+    if (dim != 64 && dim != 128) return RT_ERR_UNSUPPORTED;
+    if (mask_flags & ~RT_MASK_CAUSAL) return RT_ERR_UNSUPPORTED;
     std::lock_guard<std::mutex> lock(g_staging.mu);
+    int dev = 0;
+    RT_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return RT_ERR_UNSUPPORTED;
+    RT_CUDA(g_pipe.init(dev));
     DevBuf dq(0), dk(1), dv(2), dout(3), dlse(4), dlens(5);
     RT_CUDA(dq.alloc(n * 2));
     RT_CUDA(dk.alloc(n * 2));
     RT_CUDA(dv.alloc(n * 2));
     RT_CUDA(dout.alloc(n * 2));
-    cudaStream_t s = nullptr;
-    RT_CUDA(cudaMemcpyAsync(dq.p, q, n * 2, cudaMemcpyHostToDevice, s));
-    RT_CUDA(cudaMemcpyAsync(dk.p, k, n * 2, cudaMemcpyHostToDevice, s));
-    RT_CUDA(cudaMemcpyAsync(dv.p, v, n * 2, cudaMemcpyHostToDevice, s));
     const size_t rows = (size_t)batch * heads * seq;
     if (lse) RT_CUDA(dlse.alloc(rows * 4));
+    cudaStream_t s_in = g_pipe.in[dev], s_comp = g_pipe.comp[dev], s_out = g_pipe.out[dev];
     if (kv_lens) {
         RT_CUDA(dlens.alloc((size_t)batch * 4));
-        RT_CUDA(cudaMemcpyAsync(dlens.p, kv_lens, (size_t)batch * 4, cudaMemcpyHostToDevice, s));
+        RT_CUDA(cudaMemcpyAsync(dlens.p, kv_lens, (size_t)batch * 4, cudaMemcpyHostToDevice, s_in));
     }
-    int rc = rt_attn_prefill_bf16(dq.p, dk.p, dv.p, dout.p, lse ? dlse.as<float>() : nullptr, batch, heads, seq, dim,
-                                  mask_flags, kv_lens ? dlens.as<int32_t>() : nullptr, nullptr, 0, scale, s);
-    if (rc != RT_OK) return rc;
-    RT_CUDA(cudaMemcpyAsync(out, dout.p, n * 2, cudaMemcpyDeviceToHost, s));
-    if (lse) RT_CUDA(cudaMemcpyAsync(lse, dlse.p, rows * 4, cudaMemcpyDeviceToHost, s));
-    RT_CUDA(cudaStreamSynchronize(s));
+    // chunking: whole batch elements, each split into head ranges so that there are >= 4 chunks
+    int64_t per_batch = (4 + batch - 1) / batch;
+    if (per_batch > heads) per_batch = heads;
+    if (batch * per_batch > HostPipeline::kMaxChunks) per_batch = 1;
+    if (batch > HostPipeline::kMaxChunks) {  // very large batch: one chunk per group of batch elements is not
+        per_batch = 0;                       // expressible with per-batch kv_lens offsets; run unpipelined
+    }
+    const size_t slab = (size_t)seq * dim;  // elements of one (b,h)
+    int c = 0;
+    if (per_batch == 0) {
+        RT_CUDA(cudaMemcpyAsync(dq.p, q, n * 2, cudaMemcpyHostToDevice, s_in));
+        RT_CUDA(cudaMemcpyAsync(dk.p, k, n * 2, cudaMemcpyHostToDevice, s_in));
+        RT_CUDA(cudaMemcpyAsync(dv.p, v, n * 2, cudaMemcpyHostToDevice, s_in));
+        int rc = rt_attn_prefill_bf16(dq.p, dk.p, dv.p, dout.p, lse ? dlse.as<float>() : nullptr, batch, heads, seq,
+                                      dim, mask_flags, kv_lens ? dlens.as<int32_t>() : nullptr, nullptr, 0, scale, s_in);
+        if (rc != RT_OK) return rc;
+        RT_CUDA(cudaMemcpyAsync(out, dout.p, n * 2, cudaMemcpyDeviceToHost, s_in));
+        if (lse) RT_CUDA(cudaMemcpyAsync(lse, dlse.p, rows * 4, cudaMemcpyDeviceToHost, s_in));
+        RT_CUDA(cudaStreamSynchronize(s_in));
+        return RT_OK;
+    }
+    for (int64_t b = 0; b < batch; ++b) {
+        for (int64_t part = 0; part < per_batch; ++part, ++c) {
+            const int64_t h0 = heads * part / per_batch, h1 = heads * (part + 1) / per_batch;
+            const size_t off = ((size_t)b * heads + h0) * slab, cnt = (size_t)(h1 - h0) * slab;
+            const size_t roff = ((size_t)b * heads + h0) * seq, rcnt = (size_t)(h1 - h0) * seq;
+            const char* hq = (const char*)q + off * 2;
+            const char* hk = (const char*)k + off * 2;
+            const char* hv = (const char*)v + off * 2;
+            RT_CUDA(cudaMemcpyAsync(dq.as<char>() + off * 2, hq, cnt * 2, cudaMemcpyHostToDevice, s_in));
+            RT_CUDA(cudaMemcpyAsync(dk.as<char>() + off * 2, hk, cnt * 2, cudaMemcpyHostToDevice, s_in));
+            RT_CUDA(cudaMemcpyAsync(dv.as<char>() + off * 2, hv, cnt * 2, cudaMemcpyHostToDevice, s_in));
+            RT_CUDA(cudaEventRecord(g_pipe.ev_in[dev][c], s_in));
+            RT_CUDA(cudaStreamWaitEvent(s_comp, g_pipe.ev_in[dev][c], 0));
+            int rc = rt_attn_prefill_bf16(dq.as<char>() + off * 2, dk.as<char>() + off * 2, dv.as<char>() + off * 2,
+                                          dout.as<char>() + off * 2, lse ? dlse.as<float>() + roff : nullptr, 1, h1 - h0,
+                                          seq, dim, mask_flags, kv_lens ? dlens.as<int32_t>() + b : nullptr, nullptr, 0,
+                                          scale, s_comp);
+            if (rc != RT_OK) {
+                cudaDeviceSynchronize();
+                return rc;
+            }
+            RT_CUDA(cudaEventRecord(g_pipe.ev_comp[dev][c], s_comp));
+            RT_CUDA(cudaStreamWaitEvent(s_out, g_pipe.ev_comp[dev][c], 0));
+            RT_CUDA(cudaMemcpyAsync((char*)out + off * 2, dout.as<char>() + off * 2, cnt * 2, cudaMemcpyDeviceToHost,
+                                    s_out));
+            if (lse) RT_CUDA(cudaMemcpyAsync(lse + roff, dlse.as<float>() + roff, rcnt * 4, cudaMemcpyDeviceToHost, s_out));
+        }
+    }
+    RT_CUDA(cudaStreamSynchronize(s_out));
+    RT_CUDA(cudaStreamSynchronize(s_comp));
     return RT_OK;
 }
 

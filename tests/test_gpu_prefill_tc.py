@@ -256,3 +256,25 @@ def test_prefill_f32_chunk_against_cache(oracle):
     _, ref, ref_lse = oracle.attention_general(q, kc, vc, causal=True, kv_lens=lens, q_offsets=offs)
     assert np.abs(util.to_np(out) - ref).max() < 1e-4
     util.check_lse(util.to_np(lse), ref_lse)
+
+
+@pytest.mark.parametrize("B,H", [(3, 5), (1, 7), (40, 1)])
+def test_prefill_bf16_host_entry_matches_device_entry(oracle, B, H):
+    """rt_attn_prefill_bf16_host (pinned host buffers, chunks pipelined over three streams) returns exactly
+    what the device entry returns, for chunkings that split heads unevenly and for the unpipelined path."""
+    import torch
+    import rustorch_b200 as rt
+    from rustorch_b200 import _lib
+    N, D = 300, 64
+    g = torch.Generator().manual_seed(5)
+    hq, hk, hv = (torch.randn((B, H, N, D), generator=g).to(torch.bfloat16).pin_memory() for _ in range(3))
+    lens = torch.randint(1, N + 1, (B,), generator=g, dtype=torch.int32)
+    ho = torch.empty_like(hq).pin_memory()
+    hl = torch.empty((B, H, N), dtype=torch.float32).pin_memory()
+    rc = _lib.lib().rt_attn_prefill_bf16_host(hq.data_ptr(), hk.data_ptr(), hv.data_ptr(), ho.data_ptr(), hl.data_ptr(),
+                                              B, H, N, D, _lib.RT_MASK_CAUSAL, lens.data_ptr(), -1.0)
+    assert rc == 0
+    out, lse = rt.prefill_bf16(hq.cuda(), hk.cuda(), hv.cuda(), causal=True, kv_lens=lens.cuda())
+    torch.cuda.synchronize()
+    assert torch.equal(ho, out.cpu()) and torch.equal(hl, lse.cpu())
+    _clean_status()
