@@ -307,7 +307,7 @@ def main():
                              "l2": "1.2 GB of KV streamed per step, far larger than L2"},
                   "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                                "frac": gbs / peaks["hbm_gbs"], "peak_source": peaks["source"],
-                               "traffic": traffic.get("gqa_decode_splitkv_kernel")},
+                               "traffic": traffic.get("gqa_decode_tc_kernel")},
                   "gpu_launches": 2 * args.steps, "clocks": dclk.summary()}
         del qd, kc, vc
         torch.cuda.empty_cache()
