@@ -53,11 +53,16 @@ def load_peaks():
 
 def load_traffic():
     """DRAM bytes per launch of the dominant kernels, taken from the committed ncu summaries."""
+    out = {}
     try:
-        with open(os.path.join(ROOT, "profiles", "dram_traffic.json")) as f:
-            return json.load(f)
+        with open(os.path.join(ROOT, "profiles", "dram_traffic.txt")) as f:
+            for line in f:
+                parts = line.split()
+                if len(parts) == 2 and not line.startswith("#"):
+                    out[parts[0]] = int(parts[1])
     except Exception:
-        return {}
+        pass
+    return out
 
 
 def prefill_flops(B, H, N, D):
