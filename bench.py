@@ -330,10 +330,9 @@ def main():
         ws = torch.empty(rt.decode_workspace_bytes(1, Hq, Hkv, Dd, T), dtype=torch.uint8, device="cuda")
 
         def step_splitkv():
-            # local shard -> (O f32, LSE) partial; one packed 16.5 KB record per rank over NCCL; local merge
-            o32, l32 = rt.gqa_decode(q1, k1, v1, kv_len=T, out_dtype=torch.float32, workspace=ws)
-            allrec = sharding.all_gather_partials(sharding.pack_partial(o32[0], l32[0]))
-            return rt.merge_partials(*sharding.unpack_partials(allrec))
+            # local shard -> packed (O | LSE) record; one 16.5 KB record per rank over NCCL; local merge
+            rec = rt.gqa_decode_record(q1, k1, v1, kv_len=T, workspace=ws)
+            return rt.merge_records(sharding.all_gather_partials(rec))
 
         sms = timed(step_splitkv, args.steps, args.warmup, dist, torch)
         total_bytes = 2.0 * Hkv * Dd * 2 * T * world

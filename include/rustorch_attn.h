@@ -210,6 +210,17 @@ int rt_gqa_decode_bf16(const void* q, const void* k_cache, const void* v_cache, 
                        size_t workspace_bytes, void* stream);
 
 /*
+ * rt_gqa_decode_bf16 for a KV shard, writing the partial as one packed record per output row:
+ *   record f32 [B*Hq, D+1] = normalised O (D floats) followed by LSE — the unit that the ranks of a
+ * split-KV decode exchange (one all-gather of B*Hq*(D+1) floats per rank) and that
+ * rt_attn_merge_records consumes.  Same arguments and rules as rt_gqa_decode_bf16 otherwise.
+ */
+int rt_gqa_decode_record_bf16(const void* q, const void* k_cache, const void* v_cache, float* record,
+                              int64_t batch, int64_t n_heads, int64_t n_kv_heads, int head_dim, int64_t max_seq,
+                              const int32_t* kv_lens, int64_t kv_len_uniform, int64_t kv_begin, int64_t kv_end,
+                              float scale, void* workspace, size_t workspace_bytes, void* stream);
+
+/*
  * Drop-in for
  *   LlmKernels::gqa_decode_online_bf16(stream, q, k_cache, v_cache, out, n_heads, n_kv, kv_len, head_dim, max_seq)
  * (llm_kernels.rs:915-927): one sequence, caches [n_kv,max_seq,head_dim], scale = 1/sqrt(head_dim)
@@ -259,6 +270,13 @@ int rt_gqa_decode_online_bf16_static(const void* q, const void* k_cache, const v
  */
 int rt_attn_merge_partials(const float* o_parts, const float* lse_parts, int64_t n_parts, int64_t rows,
                            int dim, void* out_bf16, float* out_f32, float* lse, void* stream);
+
+/*
+ * rt_attn_merge_partials over packed records: records f32 [R, rows, D+1] as written by
+ * rt_gqa_decode_record_bf16 (and gathered from R ranks).  n_parts <= 8192, D <= 256.
+ */
+int rt_attn_merge_records(const float* records, int64_t n_parts, int64_t rows, int dim, void* out_bf16,
+                          float* out_f32, float* lse, void* stream);
 
 /*
  * Host-slice mirror of

@@ -58,6 +58,10 @@ PROTOTYPES = {
     "rt_gqa_decode_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
                                    c_int64, c_int, c_int64, c_void_p, c_int64, c_int64, c_int64, c_float, c_void_p,
                                    c_size_t, c_void_p]),
+    "rt_gqa_decode_record_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int,
+                                          c_int64, c_void_p, c_int64, c_int64, c_int64, c_float, c_void_p, c_size_t,
+                                          c_void_p]),
+    "rt_attn_merge_records": (c_int, [c_void_p, c_int64, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
     "rt_gqa_decode_online_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                           c_void_p, c_size_t, c_void_p]),
     "rt_gqa_decode_online_bf16_static": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,

@@ -343,10 +343,13 @@ size_t rt_gqa_decode_workspace_bytes(int64_t batch, int64_t n_heads, int64_t n_k
     return chunks * (size_t)batch * (size_t)n_heads * ((size_t)head_dim + 1) * sizeof(float);
 }
 
-int rt_gqa_decode_bf16(const void* q, const void* k_cache, const void* v_cache, void* out_bf16, float* out_f32,
-                       float* lse, int64_t batch, int64_t n_heads, int64_t n_kv_heads, int head_dim, int64_t max_seq,
-                       const int32_t* kv_lens, int64_t kv_len_uniform, int64_t kv_begin, int64_t kv_end, float scale,
-                       void* workspace, size_t workspace_bytes, void* stream) {
+// Shared validation + launch of the decode entries; of_stride / lse_stride are the row pitches (in
+// floats) of out_f32 / lse (0 = dense).
+static int decode_common(const void* q, const void* k_cache, const void* v_cache, void* out_bf16, float* out_f32,
+                         float* lse, int64_t of_stride, int64_t lse_stride, int64_t batch, int64_t n_heads,
+                         int64_t n_kv_heads, int head_dim, int64_t max_seq, const int32_t* kv_lens,
+                         int64_t kv_len_uniform, int64_t kv_begin, int64_t kv_end, float scale, void* workspace,
+                         size_t workspace_bytes, void* stream) {
     if (n_kv_heads <= 0 || n_heads <= 0 || n_heads % n_kv_heads != 0) return RT_ERR_HEAD_COUNT;  // gqa.rs:106-111
     if (head_dim == 0) return RT_ERR_ZERO_DIM;
     if (batch < 0 || max_seq <= 0 || kv_begin < 0 || head_dim < 0) return RT_ERR_BAD_LENGTH;
@@ -362,8 +365,27 @@ int rt_gqa_decode_bf16(const void* q, const void* k_cache, const void* v_cache, 
     if (need > 0 && (!workspace || workspace_bytes < need)) return RT_ERR_WORKSPACE;
     RT_CUDA(rt::launch_gqa_decode(q, k_cache, v_cache, out_bf16, out_f32, lse, batch, (int)n_heads, (int)n_kv_heads,
                                   head_dim, max_seq, kv_lens, kv_len_uniform, kv_begin, kv_end,
-                                  default_scale(scale, head_dim), need ? workspace : nullptr, as_stream(stream)));
+                                  default_scale(scale, head_dim), need ? workspace : nullptr, of_stride, lse_stride,
+                                  as_stream(stream)));
     return RT_OK;
+}
+
+int rt_gqa_decode_bf16(const void* q, const void* k_cache, const void* v_cache, void* out_bf16, float* out_f32,
+                       float* lse, int64_t batch, int64_t n_heads, int64_t n_kv_heads, int head_dim, int64_t max_seq,
+                       const int32_t* kv_lens, int64_t kv_len_uniform, int64_t kv_begin, int64_t kv_end, float scale,
+                       void* workspace, size_t workspace_bytes, void* stream) {
+    return decode_common(q, k_cache, v_cache, out_bf16, out_f32, lse, 0, 0, batch, n_heads, n_kv_heads, head_dim,
+                         max_seq, kv_lens, kv_len_uniform, kv_begin, kv_end, scale, workspace, workspace_bytes, stream);
+}
+
+int rt_gqa_decode_record_bf16(const void* q, const void* k_cache, const void* v_cache, float* record, int64_t batch,
+                              int64_t n_heads, int64_t n_kv_heads, int head_dim, int64_t max_seq,
+                              const int32_t* kv_lens, int64_t kv_len_uniform, int64_t kv_begin, int64_t kv_end,
+                              float scale, void* workspace, size_t workspace_bytes, void* stream) {
+    if (batch > 0 && !record) return RT_ERR_NULL_POINTER;
+    return decode_common(q, k_cache, v_cache, nullptr, record, record ? record + head_dim : nullptr, head_dim + 1,
+                         head_dim + 1, batch, n_heads, n_kv_heads, head_dim, max_seq, kv_lens, kv_len_uniform, kv_begin,
+                         kv_end, scale, workspace, workspace_bytes, stream);
 }
 
 int rt_gqa_decode_online_bf16(const void* q, const void* k_cache, const void* v_cache, void* out, int n_heads,
@@ -380,8 +402,20 @@ int rt_attn_merge_partials(const float* o_parts, const float* lse_parts, int64_t
     if (dim > 256 || n_parts > 8192) return RT_ERR_UNSUPPORTED;
     if (rows == 0) return RT_OK;
     if ((n_parts > 0 && (!o_parts || !lse_parts)) || (!out_bf16 && !out_f32)) return RT_ERR_NULL_POINTER;
-    RT_CUDA(rt::launch_merge_partials(o_parts, lse_parts, n_parts, rows, dim, out_bf16, out_f32, lse,
+    RT_CUDA(rt::launch_merge_partials(o_parts, lse_parts, n_parts, rows, dim, dim, 1, out_bf16, out_f32, lse,
                                       as_stream(stream)));
+    return RT_OK;
+}
+
+int rt_attn_merge_records(const float* records, int64_t n_parts, int64_t rows, int dim, void* out_bf16,
+                          float* out_f32, float* lse, void* stream) {
+    if (dim == 0) return RT_ERR_ZERO_DIM;
+    if (n_parts < 0 || rows < 0 || dim < 0 || n_parts > 0x7fffffff) return RT_ERR_BAD_LENGTH;
+    if (dim > 256 || n_parts > 8192) return RT_ERR_UNSUPPORTED;
+    if (rows == 0) return RT_OK;
+    if ((n_parts > 0 && !records) || (!out_bf16 && !out_f32)) return RT_ERR_NULL_POINTER;
+    RT_CUDA(rt::launch_merge_partials(records, records + dim, n_parts, rows, dim, dim + 1, dim + 1, out_bf16, out_f32,
+                                      lse, as_stream(stream)));
     return RT_OK;
 }
 

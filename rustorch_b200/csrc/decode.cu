@@ -52,6 +52,7 @@ struct DecodeParams {
     int n_heads, n_kv;
     int chunk, n_chunks;
     int64_t rows;  // B * Hq
+    int64_t of_stride, lse_stride;  // floats between consecutive rows of out_f32 / lse (D and 1 unless packed)
     float scale_log2;
 };
 
@@ -86,9 +87,9 @@ __global__ void __launch_bounds__(128) gqa_decode_splitkv_kernel(const DecodePar
             for (int i = tid; i < G * D; i += 128) {
                 const int64_t o = (row0 + i / D) * D + i % D;
                 if (p.out_bf16) p.out_bf16[o] = __float2bfloat16(0.f);
-                if (p.out_f32) p.out_f32[o] = 0.f;
+                if (p.out_f32) p.out_f32[(row0 + i / D) * p.of_stride + i % D] = 0.f;
             }
-            if (tid < G && p.lse) p.lse[row0 + tid] = -INFINITY;
+            if (tid < G && p.lse) p.lse[(row0 + tid) * p.lse_stride] = -INFINITY;
         } else if (tid < G) {
             p.part_lse[(int64_t)chunk_idx * p.rows + row0 + tid] = -INFINITY;
         }
@@ -261,8 +262,8 @@ __global__ void __launch_bounds__(128) gqa_decode_splitkv_kernel(const DecodePar
         const int64_t row = row0 + g;
         if (direct) {
             if (p.out_bf16) p.out_bf16[row * D + d] = __float2bfloat16(outv);
-            if (p.out_f32) p.out_f32[row * D + d] = outv;
-            if (d == 0 && p.lse) p.lse[row] = lse;
+            if (p.out_f32) p.out_f32[row * p.of_stride + d] = outv;
+            if (d == 0 && p.lse) p.lse[row * p.lse_stride] = lse;
         } else {
             p.part_o[((int64_t)chunk_idx * p.rows + row) * D + d] = outv;
             if (d == 0) p.part_lse[(int64_t)chunk_idx * p.rows + row] = lse;
@@ -282,8 +283,10 @@ constexpr int kMergeMaxDimPerLane = 8;  // dim <= 256
 __global__ void __launch_bounds__(kMergeWarps * 32) merge_partials_kernel(const float* __restrict__ o_parts,
                                                                          const float* __restrict__ lse_parts,
                                                                          int n_parts, int64_t rows, int dim,
+                                                                         int64_t in_row_stride, int64_t in_lse_stride,
                                                                          __nv_bfloat16* out_bf16, float* out_f32,
-                                                                         float* lse_out) {
+                                                                         float* lse_out, int64_t of_stride,
+                                                                         int64_t lse_stride) {
     const int64_t row = blockIdx.x;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     __shared__ float red[kMergeWarps];
@@ -294,7 +297,7 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_partials_kernel(const 
 
     float m = -INFINITY;
     for (int r = tid; r < n_parts; r += kMergeWarps * 32) {
-        const float x = lse_parts[(int64_t)r * rows + row];
+        const float x = lse_parts[((int64_t)r * rows + row) * in_lse_stride];
         w_sm[r] = x;
         m = fmaxf(m, x);
     }
@@ -313,9 +316,9 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_partials_kernel(const 
     if (m == -INFINITY) {  // every partial empty
         for (int d = tid; d < dim; d += kMergeWarps * 32) {
             if (out_bf16) out_bf16[row * dim + d] = __float2bfloat16(0.f);
-            if (out_f32) out_f32[row * dim + d] = 0.f;
+            if (out_f32) out_f32[row * of_stride + d] = 0.f;
         }
-        if (tid == 0 && lse_out) lse_out[row] = -INFINITY;
+        if (tid == 0 && lse_out) lse_out[row * lse_stride] = -INFINITY;
         return;
     }
 
@@ -334,8 +337,8 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_partials_kernel(const 
     float acc[kMergeMaxDimPerLane];
 #pragma unroll
     for (int i = 0; i < kMergeMaxDimPerLane; ++i) acc[i] = 0.f;
-    const float* base = o_parts + row * dim;
-    const int64_t part_stride = rows * dim;
+    const float* base = o_parts + row * in_row_stride;
+    const int64_t part_stride = rows * in_row_stride;
     for (int r0 = warp; r0 < n_parts; r0 += 4 * kMergeWarps) {
         float w[4];
         float v[4][kMergeMaxDimPerLane];
@@ -373,9 +376,9 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_partials_kernel(const 
         for (int x = 0; x < kMergeWarps; ++x) o += acc_sm[x * dim + d];
         o *= inv;
         if (out_bf16) out_bf16[row * dim + d] = __float2bfloat16(o);
-        if (out_f32) out_f32[row * dim + d] = o;
+        if (out_f32) out_f32[row * of_stride + d] = o;
     }
-    if (tid == 0 && lse_out) lse_out[row] = m + logf(s_l);
+    if (tid == 0 && lse_out) lse_out[row * lse_stride] = m + logf(s_l);
 }
 
 static size_t merge_smem_bytes(int64_t n_parts, int dim) {
@@ -465,7 +468,7 @@ cudaError_t launch_gqa_decode(const void* q, const void* k, const void* v, void*
                               float* lse, int64_t batch, int n_heads, int n_kv, int head_dim,
                               int64_t max_seq, const int32_t* kv_lens, int64_t kv_len_uniform,
                               int64_t kv_begin, int64_t kv_end, float scale, void* workspace,
-                              cudaStream_t stream) {
+                              int64_t of_stride, int64_t lse_stride, cudaStream_t stream) {
     DecodeParams p;
     p.q = (const __nv_bfloat16*)q;
     p.k = (const __nv_bfloat16*)k;
@@ -488,6 +491,8 @@ cudaError_t launch_gqa_decode(const void* q, const void* k, const void* v, void*
     if (span < 1) span = 1;
     p.n_chunks = (int)((span + p.chunk - 1) / p.chunk);
     p.rows = batch * n_heads;
+    p.of_stride = of_stride > 0 ? of_stride : head_dim;
+    p.lse_stride = lse_stride > 0 ? lse_stride : 1;
     p.scale_log2 = scale * kLog2e;
     p.part_o = (float*)workspace;
     p.part_lse = p.part_o ? p.part_o + (int64_t)decode_num_chunks(batch, n_kv, max_seq) * p.rows * head_dim : nullptr;
@@ -496,7 +501,7 @@ cudaError_t launch_gqa_decode(const void* q, const void* k, const void* v, void*
     if (decode_use_tensor_cores())
         e = launch_gqa_decode_tc(q, k, v, out_bf16, out_f32, lse, batch, n_heads, n_kv, head_dim, max_seq, kv_lens,
                                  kv_len_uniform, kv_begin, kv_end, scale, p.part_o, p.part_lse, p.chunk, p.n_chunks,
-                                 stream);
+                                 p.of_stride, p.lse_stride, stream);
     if (e == cudaErrorNotSupported) {  // head dim 256, or a cache too large for 32-bit TMA row coordinates
         switch (head_dim) {
             case 64: e = launch_decode_d<64>(p, group, batch, stream); break;
@@ -508,18 +513,21 @@ cudaError_t launch_gqa_decode(const void* q, const void* k, const void* v, void*
     if (e != cudaSuccess) return e;
     if (p.n_chunks > 1) {
         merge_partials_kernel<<<(unsigned)p.rows, kMergeWarps * 32, merge_smem_bytes(p.n_chunks, head_dim), stream>>>(
-            p.part_o, p.part_lse, p.n_chunks, p.rows, head_dim, p.out_bf16, p.out_f32, lse);
+            p.part_o, p.part_lse, p.n_chunks, p.rows, head_dim, head_dim, 1, p.out_bf16, p.out_f32, lse, p.of_stride,
+            p.lse_stride);
         e = cudaGetLastError();
     }
     return e;
 }
 
 cudaError_t launch_merge_partials(const float* o_parts, const float* lse_parts, int64_t n_parts, int64_t rows,
-                                  int dim, void* out_bf16, float* out_f32, float* lse, cudaStream_t stream) {
+                                  int dim, int64_t in_row_stride, int64_t in_lse_stride, void* out_bf16,
+                                  float* out_f32, float* lse, cudaStream_t stream) {
     if (rows == 0) return cudaSuccess;
     if (dim > 32 * kMergeMaxDimPerLane || merge_smem_bytes(n_parts, dim) > 48 * 1024) return cudaErrorInvalidValue;
     merge_partials_kernel<<<(unsigned)rows, kMergeWarps * 32, merge_smem_bytes(n_parts, dim), stream>>>(
-        o_parts, lse_parts, (int)n_parts, rows, dim, (__nv_bfloat16*)out_bf16, out_f32, lse);
+        o_parts, lse_parts, (int)n_parts, rows, dim, in_row_stride, in_lse_stride, (__nv_bfloat16*)out_bf16, out_f32, lse,
+        dim, 1);
     return cudaGetLastError();
 }
 

@@ -39,6 +39,7 @@ struct DecodeTcParams {
     int n_heads, n_kv;
     int chunk, n_chunks;
     int64_t rows;
+    int64_t of_stride, lse_stride;  // floats between consecutive rows of out_f32 / lse
     float scale_log2;
     int* status;
 };
@@ -115,9 +116,9 @@ gqa_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
             for (int i = tid; i < G * D; i += 128) {
                 const int64_t o = (row0 + i / D) * D + i % D;
                 if (p.out_bf16) p.out_bf16[o] = __float2bfloat16(0.f);
-                if (p.out_f32) p.out_f32[o] = 0.f;
+                if (p.out_f32) p.out_f32[(row0 + i / D) * p.of_stride + i % D] = 0.f;
             }
-            if (tid < G && p.lse) p.lse[row0 + tid] = -INFINITY;
+            if (tid < G && p.lse) p.lse[(row0 + tid) * p.lse_stride] = -INFINITY;
         } else if (tid < G) {
             p.part_lse[(int64_t)chunk_idx * p.rows + row0 + tid] = -INFINITY;
         }
@@ -305,8 +306,8 @@ gqa_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
         const int64_t row = row0 + gg;
         if (direct) {
             if (p.out_bf16) p.out_bf16[row * D + d] = __float2bfloat16(outv);
-            if (p.out_f32) p.out_f32[row * D + d] = outv;
-            if (d == 0 && p.lse) p.lse[row] = lse;
+            if (p.out_f32) p.out_f32[row * p.of_stride + d] = outv;
+            if (d == 0 && p.lse) p.lse[row * p.lse_stride] = lse;
         } else {
             p.part_o[((int64_t)chunk_idx * p.rows + row) * D + d] = outv;
             if (d == 0) p.part_lse[(int64_t)chunk_idx * p.rows + row] = lse;
@@ -361,7 +362,7 @@ cudaError_t launch_gqa_decode_tc(const void* q, const void* k, const void* v, vo
                                  float* lse, int64_t batch, int n_heads, int n_kv, int head_dim, int64_t max_seq,
                                  const int32_t* kv_lens, int64_t kv_len_uniform, int64_t kv_begin, int64_t kv_end,
                                  float scale, float* part_o, float* part_lse, int chunk, int n_chunks,
-                                 cudaStream_t stream) {
+                                 int64_t of_stride, int64_t lse_stride, cudaStream_t stream) {
     const int64_t cache_rows = batch * n_kv * max_seq;
     if ((head_dim != 64 && head_dim != 128) || cache_rows >= (1ll << 31) - 64) return cudaErrorNotSupported;
     CUtensorMap mk, mv;
@@ -384,6 +385,8 @@ cudaError_t launch_gqa_decode_tc(const void* q, const void* k, const void* v, vo
     p.chunk = chunk;
     p.n_chunks = n_chunks;
     p.rows = batch * n_heads;
+    p.of_stride = of_stride;
+    p.lse_stride = lse_stride;
     p.scale_log2 = scale * kLog2e;
     p.status = device_status_ptr();
     if (!p.status) return cudaErrorInvalidSymbol;

@@ -15,9 +15,11 @@ cudaError_t launch_gqa_decode(const void* q, const void* k, const void* v, void*
                               float* lse, int64_t batch, int n_heads, int n_kv, int head_dim,
                               int64_t max_seq, const int32_t* kv_lens, int64_t kv_len_uniform,
                               int64_t kv_begin, int64_t kv_end, float scale, void* workspace,
-                              cudaStream_t stream);
+                              int64_t of_stride, int64_t lse_stride, cudaStream_t stream);
+// o_parts rows are in_row_stride floats apart, lse_parts entries in_lse_stride floats apart
 cudaError_t launch_merge_partials(const float* o_parts, const float* lse_parts, int64_t n_parts, int64_t rows,
-                                  int dim, void* out_bf16, float* out_f32, float* lse, cudaStream_t stream);
+                                  int dim, int64_t in_row_stride, int64_t in_lse_stride, void* out_bf16,
+                                  float* out_f32, float* lse, cudaStream_t stream);
 cudaError_t launch_kv_append(void* k_cache, void* v_cache, const void* k_in, const void* v_in, int64_t batch,
                              int n_kv, int head_dim, int64_t max_seq, int64_t pos, const int32_t* positions,
                              cudaStream_t stream);
@@ -27,7 +29,7 @@ cudaError_t launch_gqa_decode_tc(const void* q, const void* k, const void* v, vo
                                  float* lse, int64_t batch, int n_heads, int n_kv, int head_dim, int64_t max_seq,
                                  const int32_t* kv_lens, int64_t kv_len_uniform, int64_t kv_begin, int64_t kv_end,
                                  float scale, float* part_o, float* part_lse, int chunk, int n_chunks,
-                                 cudaStream_t stream);
+                                 int64_t of_stride, int64_t lse_stride, cudaStream_t stream);
 
 // ---- prefill_simt.cu
 cudaError_t launch_prefill_f32(const float* q, const float* k, const float* v, float* out, float* lse,

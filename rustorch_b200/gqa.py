@@ -163,6 +163,48 @@ def gqa_decode(q, k_cache, v_cache, kv_lens=None, kv_len: Optional[int] = None, 
     return out, lse
 
 
+def gqa_decode_record(q, k_cache, v_cache, kv_lens=None, kv_len: Optional[int] = None, kv_begin: int = 0,
+                      kv_end: int = -1, scale: Optional[float] = None, record=None, workspace=None):
+    """Decode one KV shard into a packed partial record f32 [B*Hq, D+1] (O | LSE) via
+    ``rt_gqa_decode_record_bf16`` — the unit the ranks of a split-KV decode all-gather."""
+    import torch
+    B, Hq, D = q.shape
+    _, Hkv, max_seq, _ = k_cache.shape
+    if record is None:
+        record = torch.empty((B * Hq, D + 1), dtype=torch.float32, device=q.device)
+    need = decode_workspace_bytes(B, Hq, Hkv, D, max_seq)
+    if workspace is None and need:
+        key = (q.device.index, need)
+        workspace = _default_ws.get(key)
+        if workspace is None:
+            workspace = _default_ws[key] = torch.empty(need, dtype=torch.uint8, device=q.device)
+    rc = _lib.lib().rt_gqa_decode_record_bf16(
+        q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), record.data_ptr(), B, Hq, Hkv, D, max_seq,
+        kv_lens.data_ptr() if kv_lens is not None else None, 0 if kv_len is None else int(kv_len), kv_begin, kv_end,
+        -1.0 if scale is None else float(scale), workspace.data_ptr() if workspace is not None else None,
+        workspace.numel() if workspace is not None else 0, _stream_ptr())
+    if rc == _lib.RT_ERR_HEAD_COUNT:
+        raise HeadCountMismatch(Hq, Hkv)
+    _lib.check(rc, "rt_gqa_decode_record_bf16")
+    return record
+
+
+def merge_records(records, out_dtype=None):
+    """records f32 [R, rows, D+1] (CUDA) -> (out [rows, D], lse [rows]) via ``rt_attn_merge_records``."""
+    import torch
+    R, rows, D1 = records.shape
+    D = D1 - 1
+    out_dtype = out_dtype or torch.bfloat16
+    out = torch.empty((rows, D), dtype=out_dtype, device=records.device)
+    lse = torch.empty((rows,), dtype=torch.float32, device=records.device)
+    rc = _lib.lib().rt_attn_merge_records(records.data_ptr(), R, rows, D,
+                                          out.data_ptr() if out_dtype == torch.bfloat16 else None,
+                                          out.data_ptr() if out_dtype == torch.float32 else None, lse.data_ptr(),
+                                          _stream_ptr())
+    _lib.check(rc, "rt_attn_merge_records")
+    return out, lse
+
+
 def merge_partials(o_parts, lse_parts, out_dtype=None):
     """o_parts f32 [R,rows,D], lse_parts f32 [R,rows] (CUDA) -> (out [rows,D], lse [rows])."""
     import torch

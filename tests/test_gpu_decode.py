@@ -190,3 +190,36 @@ def test_decode_cfg4_full_size_split_invariance():
         s = torch.einsum("hd,hld->hl", q[b].float(), kk) / (D ** 0.5)
         ref = torch.einsum("hl,hld->hd", torch.softmax(s, dim=-1), vv)
         assert (ref - full[b]).abs().max().item() < 2e-3
+
+
+def test_packed_records_equal_separate_partials(oracle):
+    """rt_gqa_decode_record_bf16 + rt_attn_merge_records (the split-KV exchange format, one [rows, D+1]
+    record per shard) against the separate (O, LSE) outputs and against the oracle."""
+    import torch
+    import rustorch_b200 as rt
+    B, Hq, Hkv, D, S = 2, 32, 8, 128, 4096
+    q, k, v, lens = _problem(oracle, B, Hq, Hkv, D, S, [4096, 900])
+    dq, dk, dv, dl = util.to_cuda_bf16(q), util.to_cuda_bf16(k), util.to_cuda_bf16(v), util.to_cuda(lens)
+    recs = []
+    for r in range(4):
+        rec = rt.gqa_decode_record(dq, dk, dv, kv_lens=dl, kv_begin=r * 1024, kv_end=(r + 1) * 1024)
+        o, l = rt.gqa_decode(dq, dk, dv, kv_lens=dl, kv_begin=r * 1024, kv_end=(r + 1) * 1024,
+                             out_dtype=torch.float32)
+        assert rec.shape == (B * Hq, D + 1)
+        assert torch.equal(rec[:, :D], o.reshape(B * Hq, D)) and torch.equal(rec[:, D], l.reshape(B * Hq))
+        recs.append(rec)
+    allrec = torch.stack(recs)
+    merged, mlse = rt.merge_records(allrec, out_dtype=torch.float32)
+    m2, l2 = rt.merge_partials(allrec[:, :, :D].contiguous(), allrec[:, :, D].contiguous(), out_dtype=torch.float32)
+    torch.cuda.synchronize()
+    assert torch.equal(merged, m2) and torch.equal(mlse, l2)
+    _, ref, ref_lse = oracle.gqa_decode_cache(q, k, v, lens)
+    util.check_output(util.to_np(merged).reshape(B, Hq, D), ref, bf16_out=False, label="records")
+    util.check_lse(util.to_np(mlse).reshape(B, Hq), ref_lse)
+    # a single-chunk launch (short cache) writes the record directly from the decode kernel
+    q1, k1, v1, l1 = _problem(oracle, 1, 8, 2, 64, 128, [100])
+    rec = rt.gqa_decode_record(util.to_cuda_bf16(q1), util.to_cuda_bf16(k1), util.to_cuda_bf16(v1),
+                               kv_lens=util.to_cuda(l1))
+    _, r1, rl1 = oracle.gqa_decode_cache(q1, k1, v1, l1)
+    util.check_output(util.to_np(rec[:, :64]).reshape(1, 8, 64), r1, bf16_out=False)
+    util.check_lse(util.to_np(rec[:, 64]).reshape(1, 8), rl1)
