@@ -299,6 +299,24 @@ int rt_kv_append_bf16(void* k_cache, void* v_cache, const void* k_in, const void
                       int n_kv, int head_dim, int64_t max_seq, int64_t pos, const int32_t* positions,
                       void* stream);
 
+/* Pairing of dimensions for the rotary embedding */
+#define RT_ROPE_HALF_SPLIT 0 /* (k, k + D/2): crates/rustorch-nn/src/rope.rs:162-205, the CPU model and HF weights */
+#define RT_ROPE_ADJACENT 1   /* (2k, 2k+1): rope.rs:96-150 and the CUDA kernel at llm_kernels.rs:109-143 */
+
+/*
+ * One launch for what LlamaModelCuda::decode_step does with three per layer and token
+ * (rope_half_split_bf16 on Q, the same on K, kv_append_bf16: crates/rustorch-llm/src/cuda_backend.rs:917-966):
+ * rotates q in place, rotates the new K row and writes it and the V row into the caches at the
+ * sequence's position.  The caches are then ready for rt_gqa_decode_bf16 with kv_len = pos + 1.
+ *   q [B,Hq,D] bf16 (in place); k_in, v_in [B,Hkv,D] bf16; caches [B,Hkv,max_seq,D] bf16;
+ *   inv_freq device f32 [D/2] = theta^(-2k/D) as the reference uploads it (cuda_backend.rs:221-226);
+ *   positions device int32 [B], or NULL to use `pos` for every sequence;  D must be even.
+ * angle = pos * inv_freq[k] in f32 (RoPE::new, rope.rs:73-83); results are rounded to bf16 (RNE).
+ */
+int rt_rope_kv_append_bf16(void* q, const void* k_in, const void* v_in, void* k_cache, void* v_cache,
+                           const float* inv_freq, int64_t batch, int n_heads, int n_kv, int head_dim,
+                           int64_t max_seq, int64_t pos, const int32_t* positions, int rope_style, void* stream);
+
 /* f32 <-> bf16 (RNE) conversion of n elements on the device; helpers of the host entries. */
 int rt_convert_f32_to_bf16(const float* src, void* dst, int64_t n, void* stream);
 int rt_convert_bf16_to_f32(const void* src, float* dst, int64_t n, void* stream);

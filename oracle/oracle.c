@@ -565,6 +565,34 @@ int64_t orc_kv_cache_append(float* k_cache, float* v_cache, const float* k_new, 
     return cur_len + n_new;
 }
 
+/*
+ * Rotary position embedding of one token per sequence, in place: x [B, n_heads, head_dim], token b at
+ * position positions[b].  theta_k = 1 / base^(2k/D), angle = pos * theta_k in f32, as RoPE::new builds its
+ * tables (crates/rustorch-nn/src/rope.rs:63-89).
+ *   style 0: half-split pairs (k, k + D/2), rope.rs:162-205 — the convention the CPU model uses
+ *            (crates/rustorch-llm/src/model.rs:622-628) and Hugging Face weights expect;
+ *   style 1: adjacent pairs (2k, 2k+1), rope.rs:96-150 and the CUDA kernel rope_half_split_bf16
+ *            (crates/rustorch-cuda/src/llm_kernels.rs:109-143), which despite its name rotates adjacent pairs.
+ */
+void orc_rope_token(float* x, int64_t batch, int64_t n_heads, int head_dim, const int32_t* positions,
+                    float base, int style) {
+    const int half = head_dim / 2;
+    for (int64_t b = 0; b < batch; ++b)
+        for (int64_t h = 0; h < n_heads; ++h) {
+            float* row = x + (b * n_heads + h) * head_dim;
+            for (int k = 0; k < half; ++k) {
+                const float inv_theta = 1.0f / powf(base, (float)(2 * k) / (float)head_dim);
+                const float angle = (float)positions[b] * inv_theta;
+                const float c = cosf(angle), s = sinf(angle);
+                const int i0 = style == 0 ? k : 2 * k;
+                const int i1 = style == 0 ? k + half : 2 * k + 1;
+                const float x0 = row[i0], x1 = row[i1];
+                row[i0] = x0 * c - x1 * s;
+                row[i1] = x1 * c + x0 * s;
+            }
+        }
+}
+
 /* ---------------------------------------------------------------- inputs */
 
 /* f32 -> bf16 with round-to-nearest-even, the rule of the `half` crate the reference

@@ -58,6 +58,7 @@ def lib() -> ctypes.CDLL:
         _lib.orc_merge_partials.argtypes = [fp, fp, c_int64, c_int64, c_int, fp, fp]
         _lib.orc_kv_cache_append.argtypes = [fp, fp, fp, fp, c_int64, c_int64, c_int64, c_int, c_int64, c_int64]
         _lib.orc_kv_cache_append.restype = c_int64
+        _lib.orc_rope_token.argtypes = [fp, c_int64, c_int64, c_int, i32p, c_float, c_int]
         _lib.orc_f32_to_bf16.argtypes = [fp, POINTER(c_uint16), c_int64]
         _lib.orc_bf16_to_f32.argtypes = [POINTER(c_uint16), fp, c_int64]
         _lib.orc_round_to_bf16.argtypes = [fp, c_int64]
@@ -246,3 +247,12 @@ def kv_cache_append(k_cache, v_cache, k_new, v_new, cur_len):
     n_new = k_new.shape[2]
     return int(lib().orc_kv_cache_append(_f(k_cache), _f(v_cache), _f(np.ascontiguousarray(k_new)),
                                          _f(np.ascontiguousarray(v_new)), B, Hkv, max_seq, D, cur_len, n_new))
+
+
+def rope_token(x, positions, base=10000.0, style=0):
+    """x [B, n_heads, D] f32 -> rotated copy; token b at positions[b]. style 0 half-split, 1 adjacent pairs."""
+    B, H, D = x.shape
+    out = np.ascontiguousarray(x, dtype=np.float32).copy()
+    pos = np.ascontiguousarray(positions, dtype=np.int32)
+    lib().orc_rope_token(_f(out), B, H, D, pos.ctypes.data_as(POINTER(c_int32)), base, style)
+    return out

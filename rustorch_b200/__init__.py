@@ -11,12 +11,12 @@ from .attention import (AttentionError, AttentionShape, BufferShapeMismatch, Mas
                         prefill_f32)
 from .gqa import (GQAError, HeadCountMismatch, LlmKernels, WrongInputLen, decode_workspace_bytes, gqa_decode,
                   gqa_decode_online_bf16_static, gqa_decode_record, gqa_forward_f32, kv_append, merge_partials,
-                  merge_records)
+                  merge_records, rope_inv_freq, rope_kv_append)
 
 __all__ = [
     "AttentionError", "AttentionShape", "BufferShapeMismatch", "Mask", "MaskError", "OutputShapeMismatch",
     "PaddingLengthMismatch", "ZeroDim", "flash_forward", "flash_forward_masked", "prefill_bf16", "prefill_f32",
     "GQAError", "HeadCountMismatch", "LlmKernels", "WrongInputLen", "decode_workspace_bytes", "gqa_decode",
     "gqa_decode_online_bf16_static", "gqa_decode_record", "gqa_forward_f32", "kv_append", "merge_partials",
-    "merge_records",
+    "merge_records", "rope_inv_freq", "rope_kv_append",
 ]

@@ -32,6 +32,7 @@ RT_ERR_STATIC_SCRATCH = -13
 RT_MASK_NONE, RT_MASK_CAUSAL = 0, 1
 RT_MASKKIND_NONE, RT_MASKKIND_CAUSAL, RT_MASKKIND_PADDING = 0, 1, 2
 RT_PRECISION_F32, RT_PRECISION_BF16 = 0, 1
+RT_ROPE_HALF_SPLIT, RT_ROPE_ADJACENT = 0, 1
 
 _fp = POINTER(c_float)
 _i32p = POINTER(c_int32)
@@ -72,6 +73,8 @@ PROTOTYPES = {
                                         c_int64, c_int64, c_int64, c_int64]),
     "rt_kv_append_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int64, c_int64,
                                   c_void_p, c_void_p]),
+    "rt_rope_kv_append_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int,
+                                       c_int, c_int64, c_int64, c_void_p, c_int, c_void_p]),
     "rt_convert_f32_to_bf16": (c_int, [c_void_p, c_void_p, c_int64, c_void_p]),
     "rt_convert_bf16_to_f32": (c_int, [c_void_p, c_void_p, c_int64, c_void_p]),
     "rt_debug_tc_selftest": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),

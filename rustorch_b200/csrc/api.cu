@@ -467,6 +467,23 @@ int rt_kv_append_bf16(void* k_cache, void* v_cache, const void* k_in, const void
     return RT_OK;
 }
 
+int rt_rope_kv_append_bf16(void* q, const void* k_in, const void* v_in, void* k_cache, void* v_cache,
+                           const float* inv_freq, int64_t batch, int n_heads, int n_kv, int head_dim, int64_t max_seq,
+                           int64_t pos, const int32_t* positions, int rope_style, void* stream) {
+    if (batch < 0 || n_heads < 0 || n_kv < 0 || head_dim < 0 || max_seq < 0) return RT_ERR_BAD_LENGTH;
+    if (head_dim == 0) return RT_ERR_ZERO_DIM;
+    if (head_dim % 2 != 0 || (rope_style != RT_ROPE_HALF_SPLIT && rope_style != RT_ROPE_ADJACENT))
+        return RT_ERR_UNSUPPORTED;  // RoPE::new asserts an even head_dim (rope.rs:64-68)
+    if (!positions && (pos < 0 || pos >= max_seq)) return RT_ERR_BAD_LENGTH;  // RoPEError::PositionOverflow
+    if (batch == 0 || n_heads + n_kv == 0) return RT_OK;
+    if (batch > 65535) return RT_ERR_UNSUPPORTED;
+    if (!inv_freq || (n_heads > 0 && !q) || (n_kv > 0 && (!k_in || !v_in || !k_cache || !v_cache)))
+        return RT_ERR_NULL_POINTER;
+    RT_CUDA(rt::launch_rope_kv_append(q, k_in, v_in, k_cache, v_cache, inv_freq, positions, pos, batch, n_heads, n_kv,
+                                      head_dim, max_seq, rope_style, as_stream(stream)));
+    return RT_OK;
+}
+
 int rt_convert_f32_to_bf16(const float* src, void* dst, int64_t n, void* stream) {
     if (n < 0) return RT_ERR_BAD_LENGTH;
     if (n == 0) return RT_OK;

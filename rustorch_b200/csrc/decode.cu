@@ -400,6 +400,56 @@ __global__ void kv_append_kernel(__nv_bfloat16* k_cache, __nv_bfloat16* v_cache,
     }
 }
 
+// One decode step's preparation in a single launch: rotary embedding of q (in place) and of the new K
+// row, then the K and V rows go into the caches at each sequence's position.  The reference issues
+// three kernels per layer and token for this (rope on Q, rope on K, kv_append:
+// crates/rustorch-llm/src/cuda_backend.rs:917-966).  angle = pos * inv_freq[k] in f32, accurate sincosf.
+//   style 0: pairs (k, k + D/2) (crates/rustorch-nn/src/rope.rs:162-205, the CPU model's convention)
+//   style 1: pairs (2k, 2k+1)   (crates/rustorch-cuda/src/llm_kernels.rs:109-143)
+// Grid (Hq + Hkv, B), D/2 threads: CTA y handles one head row; rows >= Hq are the KV heads.
+__global__ void rope_kv_append_kernel(__nv_bfloat16* q, const __nv_bfloat16* k_in, const __nv_bfloat16* v_in,
+                                      __nv_bfloat16* k_cache, __nv_bfloat16* v_cache, const float* inv_freq,
+                                      const int32_t* positions, int64_t pos_uniform, int n_heads, int n_kv,
+                                      int head_dim, int64_t max_seq, int style) {
+    const int b = blockIdx.y, hrow = blockIdx.x, half = head_dim / 2;
+    const int64_t pos = positions ? (int64_t)positions[b] : pos_uniform;
+    if (pos < 0 || pos >= max_seq) return;
+    const bool is_q = hrow < n_heads;
+    const int h = is_q ? hrow : hrow - n_heads;
+    const __nv_bfloat16* src = is_q ? q + ((int64_t)b * n_heads + h) * head_dim
+                                    : k_in + ((int64_t)b * n_kv + h) * head_dim;
+    __nv_bfloat16* dst = is_q ? q + ((int64_t)b * n_heads + h) * head_dim
+                              : k_cache + (((int64_t)b * n_kv + h) * max_seq + pos) * head_dim;
+    for (int k = threadIdx.x; k < half; k += blockDim.x) {
+        const int i0 = style == 0 ? k : 2 * k, i1 = style == 0 ? k + half : 2 * k + 1;
+        float s, c;
+        sincosf((float)pos * inv_freq[k], &s, &c);
+        const float x0 = __bfloat162float(src[i0]), x1 = __bfloat162float(src[i1]);
+        dst[i0] = __float2bfloat16_rn(x0 * c - x1 * s);
+        dst[i1] = __float2bfloat16_rn(x1 * c + x0 * s);
+    }
+    if (!is_q) {
+        const __nv_bfloat16* vs = v_in + ((int64_t)b * n_kv + h) * head_dim;
+        __nv_bfloat16* vd = v_cache + (((int64_t)b * n_kv + h) * max_seq + pos) * head_dim;
+        for (int i = threadIdx.x; i < head_dim; i += blockDim.x) vd[i] = vs[i];
+    }
+}
+
+cudaError_t launch_rope_kv_append(void* q, const void* k_in, const void* v_in, void* k_cache, void* v_cache,
+                                  const float* inv_freq, const int32_t* positions, int64_t pos_uniform,
+                                  int64_t batch, int n_heads, int n_kv, int head_dim, int64_t max_seq, int style,
+                                  cudaStream_t stream) {
+    if (batch == 0 || n_heads + n_kv == 0) return cudaSuccess;
+    dim3 grid(n_heads + n_kv, (unsigned)batch);
+    int threads = head_dim / 2;
+    threads = threads < 32 ? 32 : (threads > 128 ? 128 : threads);
+    rope_kv_append_kernel<<<grid, threads, 0, stream>>>((__nv_bfloat16*)q, (const __nv_bfloat16*)k_in,
+                                                        (const __nv_bfloat16*)v_in, (__nv_bfloat16*)k_cache,
+                                                        (__nv_bfloat16*)v_cache, inv_freq, positions, pos_uniform,
+                                                        n_heads, n_kv, head_dim, max_seq, style);
+    return cudaGetLastError();
+}
+
 // Tokens per KV chunk (one CTA per chunk).  Large chunks amortise the per-CTA prologue and the
 // partial traffic (1024 tokens measured best on the ragged batched workload); the choice walks
 // down from 1024 until the grid both covers the 148 SMs x 2 resident CTAs and fills its last wave

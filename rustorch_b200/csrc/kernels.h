@@ -24,6 +24,11 @@ cudaError_t launch_kv_append(void* k_cache, void* v_cache, const void* k_in, con
                              int n_kv, int head_dim, int64_t max_seq, int64_t pos, const int32_t* positions,
                              cudaStream_t stream);
 
+cudaError_t launch_rope_kv_append(void* q, const void* k_in, const void* v_in, void* k_cache, void* v_cache,
+                                  const float* inv_freq, const int32_t* positions, int64_t pos_uniform,
+                                  int64_t batch, int n_heads, int n_kv, int head_dim, int64_t max_seq, int style,
+                                  cudaStream_t stream);
+
 // ---- decode_tc.cu: TMA + mma.sync decode for head dim 64/128; cudaErrorNotSupported = shape not covered
 cudaError_t launch_gqa_decode_tc(const void* q, const void* k, const void* v, void* out_bf16, float* out_f32,
                                  float* lse, int64_t batch, int n_heads, int n_kv, int head_dim, int64_t max_seq,

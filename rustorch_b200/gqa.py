@@ -227,3 +227,24 @@ def kv_append(k_cache, v_cache, k_in, v_in, pos=None, positions=None) -> None:
                                       D, max_seq, 0 if pos is None else int(pos),
                                       positions.data_ptr() if positions is not None else None, _stream_ptr())
     _lib.check(rc, "rt_kv_append_bf16")
+
+
+def rope_inv_freq(head_dim: int, base: float = 10000.0, device="cuda"):
+    """theta^(-2k/D) for k in 0..D/2, the table the reference uploads once (cuda_backend.rs:221-226)."""
+    import torch
+    k = torch.arange(head_dim // 2, dtype=torch.float32)
+    return (1.0 / torch.pow(torch.tensor(float(base), dtype=torch.float32), 2.0 * k / head_dim)).to(device)
+
+
+def rope_kv_append(q, k_in, v_in, k_cache, v_cache, inv_freq, pos=None, positions=None, style: str = "half_split") -> None:
+    """Rotary embedding of q (in place) and of the new K row + append of K, V at each sequence's position, one
+    launch (``rt_rope_kv_append_bf16``).  q [B,Hq,D], k_in/v_in [B,Hkv,D], caches [B,Hkv,max_seq,D]."""
+    B, Hq, D = q.shape
+    _, Hkv, max_seq, _ = k_cache.shape
+    rc = _lib.lib().rt_rope_kv_append_bf16(q.data_ptr(), k_in.data_ptr(), v_in.data_ptr(), k_cache.data_ptr(),
+                                           v_cache.data_ptr(), inv_freq.data_ptr(), B, Hq, Hkv, D, max_seq,
+                                           0 if pos is None else int(pos),
+                                           positions.data_ptr() if positions is not None else None,
+                                           {"half_split": _lib.RT_ROPE_HALF_SPLIT, "adjacent": _lib.RT_ROPE_ADJACENT}[style],
+                                           _stream_ptr())
+    _lib.check(rc, "rt_rope_kv_append_bf16")

@@ -78,6 +78,11 @@ def test_validation_happens_before_any_device_work(lib):
     assert lib.rt_attn_merge_partials(p, p, 2, 4, 8, None, None, None, None) == L.RT_ERR_NULL_POINTER
     assert lib.rt_kv_append_bf16(p, p, p, p, 1, 2, 128, 64, 64, None, None) == L.RT_ERR_BAD_LENGTH
     assert lib.rt_debug_tc_selftest(None, p, p, p, p, 128, None) == L.RT_ERR_NULL_POINTER
+    assert lib.rt_rope_kv_append_bf16(p, p, p, p, p, p, 1, 4, 2, 127, 64, 3, None, 0, None) == L.RT_ERR_UNSUPPORTED
+    assert lib.rt_rope_kv_append_bf16(p, p, p, p, p, p, 1, 4, 2, 128, 64, 64, None, 0, None) == L.RT_ERR_BAD_LENGTH
+    assert lib.rt_rope_kv_append_bf16(p, p, p, p, p, None, 1, 4, 2, 128, 64, 3, None, 0, None) == L.RT_ERR_NULL_POINTER
+    assert lib.rt_attn_merge_records(None, 2, 4, 8, p, None, None, None) == L.RT_ERR_NULL_POINTER
+    assert lib.rt_gqa_decode_record_bf16(p, p, p, None, 1, 4, 2, 128, 64, None, 3, 0, -1, -1.0, None, 0, None) == L.RT_ERR_NULL_POINTER
     assert lib.rt_gqa_decode_online_bf16_static(p, p, p, p, 32, 8, 10, 128, 1 << 20, None) == L.RT_ERR_STATIC_SCRATCH
 
 

@@ -223,3 +223,35 @@ def test_packed_records_equal_separate_partials(oracle):
     _, r1, rl1 = oracle.gqa_decode_cache(q1, k1, v1, l1)
     util.check_output(util.to_np(rec[:, :64]).reshape(1, 8, 64), r1, bf16_out=False)
     util.check_lse(util.to_np(rec[:, 64]).reshape(1, 8), rl1)
+
+
+@pytest.mark.parametrize("style,code", [("half_split", 0), ("adjacent", 1)])
+def test_rope_kv_append_then_decode(oracle, style, code):
+    """The fused step before the decode: rotate q and the new K row, append K and V at each sequence's position."""
+    import torch
+    import rustorch_b200 as rt
+    B, Hq, Hkv, D, S = 3, 8, 2, 128, 512
+    q, kc, vc, lens = _problem(oracle, B, Hq, Hkv, D, S, [17, 300, 511])
+    k_new = util.normal_bf16(oracle, (B, Hkv, D), 21)
+    v_new = util.normal_bf16(oracle, (B, Hkv, D), 22)
+    dq, dk, dv = util.to_cuda_bf16(q), util.to_cuda_bf16(kc), util.to_cuda_bf16(vc)
+    inv_freq = rt.rope_inv_freq(D, 10000.0)
+    rt.rope_kv_append(dq, util.to_cuda_bf16(k_new), util.to_cuda_bf16(v_new), dk, dv, inv_freq,
+                      positions=util.to_cuda(lens), style=style)
+    torch.cuda.synchronize()
+    q_ref = oracle.rope_token(q, lens, 10000.0, code)
+    k_ref = oracle.rope_token(k_new, lens, 10000.0, code)
+    # bf16 storage: equal to the rounded oracle value up to one bf16 ulp (sincosf vs libm in the last bit)
+    assert np.abs(util.to_np(dq) - q_ref).max() <= 2.0 ** -7 * np.abs(q_ref).max()
+    got_k, got_v = util.to_np(dk), util.to_np(dv)
+    for b in range(B):
+        assert np.abs(got_k[b, :, lens[b]] - k_ref[b]).max() <= 2.0 ** -7 * np.abs(k_ref).max()
+        assert np.array_equal(got_v[b, :, lens[b]], v_new[b])
+        kc[b, :, lens[b]] = got_k[b, :, lens[b]]
+        vc[b, :, lens[b]] = v_new[b]
+    assert np.array_equal(got_k, kc) and np.array_equal(got_v, vc)  # nothing else in the caches moved
+    # rotation preserves the norm of every pair, hence of the row
+    assert np.allclose(np.linalg.norm(util.to_np(dq), axis=-1), np.linalg.norm(q, axis=-1), rtol=1e-2)
+    out, _ = rt.gqa_decode(dq, dk, dv, kv_lens=util.to_cuda(lens + 1))
+    _, ref, _ = oracle.gqa_decode_cache(util.to_np(dq), kc, vc, lens + 1)
+    util.check_output(util.to_np(out), ref, label="rope + append + decode")

@@ -155,3 +155,19 @@ def test_counter_based_inputs(oracle):
     assert abs(a.mean()) < 0.02 and abs(a.std() - 1.0) < 0.02 and not np.array_equal(a, oracle.fill_normal(1 << 16, 43))
     lens = oracle.fill_uniform_int(4096, 0x5EED, 1024, 8192)
     assert lens.min() >= 1024 and lens.max() <= 8192 and abs(lens.mean() - 4608) < 150
+
+
+def test_rope_restatement(oracle):
+    """rope.rs:162-205 (half-split) and :96-150 (adjacent): position 0 is the identity, a rotation keeps
+    pair norms, and the two layouts are the same rotation under the (k, k+D/2) <-> (2k, 2k+1) relabelling."""
+    x = oracle.fill_normal((2, 3, 16), 5)
+    assert np.array_equal(oracle.rope_token(x, [0, 0]), x)
+    pos = np.array([7, 123], dtype=np.int32)
+    a = oracle.rope_token(x, pos, 10000.0, 0)
+    b = oracle.rope_token(x, pos, 10000.0, 1)
+    assert np.allclose(np.hypot(a[..., :8], a[..., 8:]), np.hypot(x[..., :8], x[..., 8:]), atol=1e-5)
+    perm = np.concatenate([np.arange(0, 16, 2), np.arange(1, 16, 2)])  # adjacent layout -> half-split layout
+    assert np.allclose(oracle.rope_token(x[..., perm], pos, 10000.0, 0), b[..., perm], atol=1e-6)
+    # known value: D = 2, pos = 1, theta_0 = 1 -> rotation by 1 radian
+    v = oracle.rope_token(np.array([[[1.0, 0.0]]], dtype=np.float32), [1])
+    assert np.allclose(v[0, 0], [math.cos(1.0), math.sin(1.0)], atol=1e-6)
