@@ -1,0 +1,137 @@
+"""Committed golden fixtures (tests/golden/, produced by make_golden.py from the oracle) and the reference's
+own known-answer vectors (reference_kats.json): the oracle must reproduce them on CPU, the CUDA kernels on GPU."""
+import json
+import os
+
+import numpy as np
+import pytest
+
+from tests import util
+
+GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+def _load(name, orc):
+    z = np.load(os.path.join(GOLD, name + ".npz"))
+    d = {k: z[k] for k in z.files}
+    for k in ("q", "k", "v"):
+        d[k] = orc.bf16_bits_to_f32(d[k])
+    return d
+
+
+def _same(a, b, tol=1e-6):
+    return np.array_equal(np.isnan(a), np.isnan(b)) and np.array_equal(np.isneginf(a), np.isneginf(b)) and \
+        np.nanmax(np.abs(np.where(np.isfinite(a) & np.isfinite(b), a - b, 0.0)), initial=0.0) <= tol
+
+
+# ------------------------------------------------------------------ CPU: the oracle against the fixtures
+def test_oracle_reproduces_golden_prefill(oracle):
+    g = _load("prefill_causal_d64", oracle)
+    _, out, lse = oracle.flash_forward_ext(g["q"], g["k"], g["v"], causal=True)
+    assert _same(out, g["out"]) and _same(lse, g["lse"])
+    g = _load("prefill_varlen_d128", oracle)
+    _, out, lse = oracle.flash_forward_ext(g["q"], g["k"], g["v"], causal=True, kv_lens=g["kv_lens"])
+    assert _same(out, g["out"]) and _same(lse, g["lse"])
+    _, out, lse = oracle.naive_forward_ext(g["q"], g["k"], g["v"], causal=True, kv_lens=g["kv_lens"])
+    assert _same(out, g["out"], 2e-5) and _same(lse, g["lse"], 2e-5)  # tiled == naive on the fixture too
+    g = _load("prefill_keep_d64", oracle)
+    _, out, lse = oracle.flash_forward_ext(g["q"], g["k"], g["v"], keep=g["keep"])
+    assert _same(out, g["out"]) and _same(lse, g["lse"])
+    g = _load("prefill_chunk_gqa_d64", oracle)
+    _, out, lse = oracle.attention_general(g["q"], g["k"], g["v"], causal=True, kv_lens=g["kv_lens"],
+                                           q_offsets=g["q_offsets"])
+    assert _same(out, g["out"]) and _same(lse, g["lse"])
+
+
+def test_oracle_reproduces_golden_decode(oracle):
+    g = _load("decode_gqa_d128", oracle)
+    _, out, lse = oracle.gqa_decode_cache(g["q"], g["k"], g["v"], g["kv_lens"])
+    assert _same(out, g["out"]) and _same(lse, g["lse"])
+    B, Hq, D = out.shape
+    mo, ml = oracle.merge_partials(g["part_o"].reshape(2, B * Hq, D), g["part_lse"].reshape(2, B * Hq))
+    assert _same(mo.reshape(B, Hq, D), g["out"], 1e-5) and _same(ml.reshape(B, Hq), g["lse"], 1e-5)
+
+
+def test_reference_kats_on_the_oracle(oracle):
+    kats = json.load(open(os.path.join(GOLD, "reference_kats.json")))
+    for name in ("scaling_factor_is_one_over_sqrt_d", "causal_first_query_only_attends_to_self",
+                 "padding_mask_excludes_padded_positions_exactly"):
+        c = kats[name]
+        q, k, v = (np.array(c[x], dtype=np.float32).reshape(c["shape"]) for x in ("q", "k", "v"))
+        kind = {"none": oracle.MASK_NONE, "causal": oracle.MASK_CAUSAL, "padding": oracle.MASK_PADDING}[c["mask"]]
+        rc, out = oracle.flash_forward_masked(q, k, v, kind, c.get("keep"))
+        assert rc == 0
+        _check_kat(c, out)
+    f = kats["online_softmax_fixtures"]
+    m, l = oracle.online_softmax_full(f["huge"])
+    assert [m, l] == [np.float32(f["huge_expect"][0]), f["huge_expect"][1]]
+
+
+def _check_kat(c, out):
+    if "expect_out" in c:
+        assert np.abs(out.ravel() - np.array(c["expect_out"], dtype=np.float32)).max() <= c["atol"] * 10
+    if "expect_row0" in c:
+        assert np.abs(out[0, 0, 0] - np.array(c["expect_row0"], dtype=np.float32)).max() <= c["atol"] * 10
+    if "expect_out00" in c:
+        assert abs(out[0, 0, 0, 0] - c["expect_out00"]) <= c["atol"] * 30
+
+
+# ------------------------------------------------------------------ GPU: the kernels against the fixtures
+@pytest.mark.gpu
+@pytest.mark.parametrize("name,kw", [("prefill_causal_d64", dict(causal=True)), ("prefill_varlen_d128", dict(causal=True)),
+                                     ("prefill_keep_d64", dict()), ("prefill_chunk_gqa_d64", dict(causal=True))])
+def test_gpu_prefill_matches_golden(oracle, name, kw):
+    import torch
+    import rustorch_b200 as rt
+    g = _load(name, oracle)
+    args = dict(kw)
+    if "kv_lens" in g:
+        args["kv_lens"] = util.to_cuda(g["kv_lens"])
+    if "q_offsets" in g:
+        args["q_offsets"] = util.to_cuda(g["q_offsets"])
+    if "keep" in g:
+        args["key_keep"] = util.to_cuda(g["keep"])
+    out, lse = rt.prefill_bf16(util.to_cuda_bf16(g["q"]), util.to_cuda_bf16(g["k"]), util.to_cuda_bf16(g["v"]), **args)
+    torch.cuda.synchronize()
+    util.check_output(util.to_np(out), g["out"], label=name)
+    util.check_lse(util.to_np(lse), g["lse"], label=name)
+    # the f32 CUDA-core kernel on the same fixture, at its own 1e-4 gate
+    o32, l32 = rt.prefill_f32(util.to_cuda(g["q"]), util.to_cuda(g["k"]), util.to_cuda(g["v"]), **args)
+    got = util.to_np(o32)
+    ok = ~np.isnan(g["out"])
+    assert np.array_equal(np.isnan(got), ~ok) and np.abs(got[ok] - g["out"][ok]).max() < 1e-4
+    util.check_lse(util.to_np(l32), g["lse"], label=name + " f32")
+
+
+@pytest.mark.gpu
+def test_gpu_decode_matches_golden(oracle):
+    import torch
+    import rustorch_b200 as rt
+    g = _load("decode_gqa_d128", oracle)
+    dq, dk, dv, dl = util.to_cuda_bf16(g["q"]), util.to_cuda_bf16(g["k"]), util.to_cuda_bf16(g["v"]), util.to_cuda(g["kv_lens"])
+    out, lse = rt.gqa_decode(dq, dk, dv, kv_lens=dl)
+    util.check_output(util.to_np(out), g["out"], label="decode golden")
+    util.check_lse(util.to_np(lse), g["lse"])
+    recs = torch.stack([rt.gqa_decode_record(dq, dk, dv, kv_lens=dl, kv_begin=0, kv_end=64),
+                        rt.gqa_decode_record(dq, dk, dv, kv_lens=dl, kv_begin=64, kv_end=-1)])
+    B, Hq, D = g["out"].shape
+    util.check_output(util.to_np(recs[:, :, :D]).reshape(2, B, Hq, D), g["part_o"], bf16_out=False, label="shard partials")
+    util.check_lse(util.to_np(recs[:, :, D]).reshape(2, B, Hq), g["part_lse"])
+    merged, mlse = rt.merge_records(recs, out_dtype=torch.float32)
+    util.check_output(util.to_np(merged).reshape(B, Hq, D), g["out"], bf16_out=False)
+    util.check_lse(util.to_np(mlse).reshape(B, Hq), g["lse"])
+
+
+@pytest.mark.gpu
+def test_gpu_reference_kats_through_the_host_mirror():
+    import rustorch_b200 as rt
+    kats = json.load(open(os.path.join(GOLD, "reference_kats.json")))
+    for name in ("scaling_factor_is_one_over_sqrt_d", "causal_first_query_only_attends_to_self",
+                 "padding_mask_excludes_padded_positions_exactly"):
+        c = kats[name]
+        q, k, v = (np.array(c[x], dtype=np.float32).reshape(c["shape"]) for x in ("q", "k", "v"))
+        mask = {"none": rt.Mask.none(), "causal": rt.Mask.causal(),
+                "padding": rt.Mask.padding(c.get("keep", []))}[c["mask"]]
+        out = np.zeros_like(q)
+        rt.flash_forward_masked(rt.AttentionShape.new(*c["shape"]), q, k, v, mask, out)
+        _check_kat(c, out)
