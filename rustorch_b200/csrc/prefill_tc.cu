@@ -91,7 +91,8 @@ enum { kToQ = 101, kToKFull, kToKEmpty, kToVFull, kToVEmpty, kToSFull, kToPFull,
 template <int D, bool kCausal, bool kKeep>
 __global__ void __launch_bounds__(384, 1)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                  const __grid_constant__ CUtensorMap tm_v, const TcParams p) {
+                  const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
+                  const TcParams p) {
     using C = TcCfg<D>;
     constexpr int KS = C::KS, VS = C::VS, TILE = C::TILE_BYTES, SUB = C::SUB_BYTES, HALF = C::HALF_BYTES;
 
@@ -160,6 +161,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         prefetch_tensormap(&tm_q);
         prefetch_tensormap(&tm_k);
         prefetch_tensormap(&tm_v);
+        prefetch_tensormap(&tm_o);
         for (int i = 0; i < 2; ++i) {
             mbar_init(&q_full[i], 1);
             mbar_init(&o_full[i], 1);
@@ -476,36 +478,48 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             }
             ok = false;
         }
-        // ---- epilogue: O / l -> bf16, LSE.  (o_full cannot be used here: up to two PV steps may
-        // still be in flight, which a parity wait cannot tell from none.)
+        // ---- epilogue: O / l -> bf16 into the (now idle) shared-memory tile of Q_w in the swizzled
+        // layout of the output tensor map, then one TMA store per 64-column half: 16-byte shared stores
+        // instead of row-strided global stores, and rows past N are clipped by the hardware.
+        // (o_full cannot be used for the wait: up to two PV steps may still be in flight, which a
+        // parity wait cannot tell from none.)
+        bool stored = false;
         if (ok && __all_sync(kFullMask, mbar_wait(&o_done[w], 0, p.status, kToOFull))) {
             tc_fence_after();
             const bool valid = (l > 0.f);
             const float inv = valid ? 1.f / l : 0.f;
-            __nv_bfloat16* dst = p.out + ((int64_t)bh * N + row) * D;
+            uint8_t* stage = sQ + w * TILE + row_in_tile * 128;  // every score MMA that read Q_w has retired
 #pragma unroll
             for (int ch = 0; ch < D / 32; ++ch) {
                 uint32_t o[32];
                 tmem_ld32(tO + ch * 32, o);
                 tc_wait_ld();
-                if (row < N) {
 #pragma unroll
-                    for (int v4 = 0; v4 < 4; ++v4) {
-                        uint4 pack;
-                        uint32_t* pw = reinterpret_cast<uint32_t*>(&pack);
+                for (int v4 = 0; v4 < 4; ++v4) {
+                    uint4 pack;
+                    uint32_t* pw = reinterpret_cast<uint32_t*>(&pack);
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            const float a = __uint_as_float(o[v4 * 8 + 2 * i]) * inv;
-                            const float bb = __uint_as_float(o[v4 * 8 + 2 * i + 1]) * inv;
-                            pw[i] = valid ? float2_to_bf16x2(a, bb) : 0x7fc07fc0u;
-                        }
-                        *reinterpret_cast<uint4*>(dst + ch * 32 + v4 * 8) = pack;
+                    for (int i = 0; i < 4; ++i) {
+                        const float a = __uint_as_float(o[v4 * 8 + 2 * i]) * inv;
+                        const float bb = __uint_as_float(o[v4 * 8 + 2 * i + 1]) * inv;
+                        pw[i] = valid ? float2_to_bf16x2(a, bb) : 0x7fc07fc0u;
                     }
+                    const int cc = ch * 4 + v4;  // 16-byte chunk of the row: sub-tile cc/8, chunk cc%8
+                    *reinterpret_cast<uint4*>(stage + (cc / 8) * SUB + (((cc % 8) ^ (row_in_tile & 7)) << 4)) = pack;
                 }
             }
             if (p.lse && row < N)
                 p.lse[(int64_t)bh * N + row] =
                     valid ? (m_ref * c + fast_log2(l)) * kLn2 : (l == 0.f ? -INFINITY : NAN);
+            fence_proxy_async();  // generic-proxy writes above -> visible to the TMA (async proxy) read
+            stored = true;
+        }
+        named_barrier_sync(1 + w, 128);  // all four warps of the tile, whatever happened above
+        if (row_in_tile == 0 && stored) {
+#pragma unroll
+            for (int s = 0; s < C::NSUB; ++s)
+                tma_store_3d(&tm_o, sQ + w * TILE + s * SUB, s * 64, q0 + w * 128, bh);
+            tma_store_commit_and_wait();  // the tile must be read out before the CTA gives up its shared memory
         }
     }
 
@@ -554,12 +568,12 @@ bool make_tensor_map_bf16_3d(CUtensorMap* map, const void* base, int64_t bh, int
 }
 
 template <int D, bool kCausal, bool kKeep>
-static cudaError_t launch_tc(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const TcParams& p,
-                             int64_t n_ctas, cudaStream_t stream) {
+static cudaError_t launch_tc(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mo,
+                             const TcParams& p, int64_t n_ctas, cudaStream_t stream) {
     auto kern = prefill_tc_kernel<D, kCausal, kKeep>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TcCfg<D>::SMEM_BYTES);
     if (e != cudaSuccess) return e;
-    kern<<<(unsigned)n_ctas, 384, TcCfg<D>::SMEM_BYTES, stream>>>(mq, mk, mv, p);
+    kern<<<(unsigned)n_ctas, 384, TcCfg<D>::SMEM_BYTES, stream>>>(mq, mk, mv, mo, p);
     return cudaGetLastError();
 }
 
@@ -569,8 +583,8 @@ cudaError_t launch_prefill_tc(const void* q, const void* k, const void* v, void*
                               int64_t keep_batch_stride, float scale, cudaStream_t stream) {
     const int64_t bh = batch * heads;
     if (bh == 0 || seq == 0) return cudaSuccess;
-    CUtensorMap mq, mk, mv;
-    if (!make_tensor_map_bf16_3d(&mq, q, bh, seq, dim) ||
+    CUtensorMap mq, mk, mv, mo;
+    if (!make_tensor_map_bf16_3d(&mq, q, bh, seq, dim) || !make_tensor_map_bf16_3d(&mo, out, bh, seq, dim) ||
         !make_tensor_map_bf16_3d(&mk, k, batch * heads_kv, seq_kv, dim) ||
         !make_tensor_map_bf16_3d(&mv, v, batch * heads_kv, seq_kv, dim))
         return cudaErrorInvalidValue;
@@ -596,11 +610,11 @@ cudaError_t launch_prefill_tc(const void* q, const void* k, const void* v, void*
     const bool keep = key_keep != nullptr;
 #define RT_TC_DISPATCH(DD)                                                                         \
     if (causal) {                                                                                  \
-        return keep ? launch_tc<DD, true, true>(mq, mk, mv, p, n_ctas, stream)                     \
-                    : launch_tc<DD, true, false>(mq, mk, mv, p, n_ctas, stream);                   \
+        return keep ? launch_tc<DD, true, true>(mq, mk, mv, mo, p, n_ctas, stream)                     \
+                    : launch_tc<DD, true, false>(mq, mk, mv, mo, p, n_ctas, stream);                   \
     } else {                                                                                       \
-        return keep ? launch_tc<DD, false, true>(mq, mk, mv, p, n_ctas, stream)                    \
-                    : launch_tc<DD, false, false>(mq, mk, mv, p, n_ctas, stream);                  \
+        return keep ? launch_tc<DD, false, true>(mq, mk, mv, mo, p, n_ctas, stream)                    \
+                    : launch_tc<DD, false, false>(mq, mk, mv, mo, p, n_ctas, stream);                  \
     }
     if (dim == 128) { RT_TC_DISPATCH(128) }
     if (dim == 64) { RT_TC_DISPATCH(64) }
