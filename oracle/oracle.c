@@ -314,6 +314,116 @@ int orc_naive_forward_masked(int64_t batch, int64_t heads, int64_t seq, int dim,
 }
 
 /*
+ * flash_backward (crates/rustorch-attention/src/cpu_backward.rs:46-185): (dQ, dK, dV) of
+ * O = softmax(scale * Q K^T) V for an upstream gradient dO, all [B,H,N,D] f32.  Same sequence as
+ * the reference: recompute the probabilities P from Q and K (:96-127; rows whose sum is not a
+ * positive finite number keep their unnormalised values, :121), dV = P^T dO (:128-139),
+ * dP = dO V^T (:140-153), dS_ij = P_ij (dP_ij - sum_k P_ik dP_ik) (:154-167), dQ = scale dS K
+ * (:168-178), dK = scale dS^T Q (:179-189).  Accumulation runs in the reference's order inside a
+ * (b,h); the (b,h) slabs are independent and run in parallel.
+ * Extension (the reference's backward has no mask): causal != 0 treats P_ij = 0 for j > i, the
+ * gradient of flash_forward_masked with Mask::Causal.  scale <= 0 means 1/sqrt(D) (:77).
+ * lse_out, if not NULL, receives the row statistics m + ln(l) that a tiled backward consumes.
+ */
+int orc_flash_backward_ext(int64_t batch, int64_t heads, int64_t seq, int dim, const float* q, const float* k,
+                           const float* v, const float* d_out, int causal, float scale, float* dq, float* dk,
+                           float* dv, float* lse_out) {
+    if (dim == 0) return ORC_ERR_ZERO_DIM;
+    if (seq == 0) return ORC_OK;
+    if (scale <= 0.0f) scale = 1.0f / sqrtf((float)dim);
+    const int64_t n = seq, s_h = seq * dim, n_bh = batch * heads;
+    memset(dq, 0, sizeof(float) * (size_t)(n_bh * s_h));
+    memset(dk, 0, sizeof(float) * (size_t)(n_bh * s_h));
+    memset(dv, 0, sizeof(float) * (size_t)(n_bh * s_h));
+    int failed = 0;
+#pragma omp parallel for schedule(dynamic, 1) num_threads(orc_get_threads())
+    for (int64_t bh = 0; bh < n_bh; ++bh) {
+        const int64_t base = bh * s_h;
+        float* p = (float*)malloc(sizeof(float) * (size_t)n * n);
+        float* dp = (float*)malloc(sizeof(float) * (size_t)n * n);
+        if (!p || !dp) {
+            failed = 1;
+            free(p);
+            free(dp);
+            continue;
+        }
+        for (int64_t i = 0; i < n; ++i) {
+            float row_max = -INFINITY;
+            const float* qi = q + base + i * dim;
+            const int64_t vis = causal ? i + 1 : n;
+            for (int64_t j = 0; j < n; ++j) {
+                if (j >= vis) {
+                    p[i * n + j] = -INFINITY;
+                    continue;
+                }
+                const float* kj = k + base + j * dim;
+                float s = 0.0f;
+                for (int d = 0; d < dim; ++d) s += qi[d] * kj[d];
+                const float scaled = s * scale;
+                p[i * n + j] = scaled;
+                if (scaled > row_max) row_max = scaled;
+            }
+            float row_sum = 0.0f;
+            for (int64_t j = 0; j < n; ++j) {
+                const float e = (j < vis) ? expf(p[i * n + j] - row_max) : 0.0f;
+                p[i * n + j] = e;
+                row_sum += e;
+            }
+            if (row_sum > 0.0f && isfinite(row_sum))
+                for (int64_t j = 0; j < n; ++j) p[i * n + j] /= row_sum;
+            if (lse_out) lse_out[bh * n + i] = row_max + logf(row_sum);
+        }
+        for (int64_t j = 0; j < n; ++j) {
+            float* dvj = dv + base + j * dim;
+            for (int64_t i = 0; i < n; ++i) {
+                const float pij = p[i * n + j];
+                const float* doi = d_out + base + i * dim;
+                for (int d = 0; d < dim; ++d) dvj[d] += pij * doi[d];
+            }
+        }
+        for (int64_t i = 0; i < n; ++i) {
+            const float* doi = d_out + base + i * dim;
+            for (int64_t j = 0; j < n; ++j) {
+                const float* vj = v + base + j * dim;
+                float acc = 0.0f;
+                for (int d = 0; d < dim; ++d) acc += doi[d] * vj[d];
+                dp[i * n + j] = acc;
+            }
+        }
+        for (int64_t i = 0; i < n; ++i) { /* dS overwrites dP */
+            float row_dot = 0.0f;
+            for (int64_t j = 0; j < n; ++j) row_dot += p[i * n + j] * dp[i * n + j];
+            for (int64_t j = 0; j < n; ++j) dp[i * n + j] = p[i * n + j] * (dp[i * n + j] - row_dot);
+        }
+        for (int64_t i = 0; i < n; ++i) {
+            float* dqi = dq + base + i * dim;
+            for (int64_t j = 0; j < n; ++j) {
+                const float* kj = k + base + j * dim;
+                const float ds = dp[i * n + j];
+                for (int d = 0; d < dim; ++d) dqi[d] += scale * ds * kj[d];
+            }
+        }
+        for (int64_t j = 0; j < n; ++j) {
+            float* dkj = dk + base + j * dim;
+            for (int64_t i = 0; i < n; ++i) {
+                const float* qi = q + base + i * dim;
+                const float ds = dp[i * n + j];
+                for (int d = 0; d < dim; ++d) dkj[d] += scale * ds * qi[d];
+            }
+        }
+        free(p);
+        free(dp);
+    }
+    return failed ? ORC_ERR_ALLOC : ORC_OK;
+}
+
+/* The reference signature: unmasked, scale = 1/sqrt(D). */
+int orc_flash_backward(int64_t batch, int64_t heads, int64_t seq, int dim, const float* q, const float* k,
+                       const float* v, const float* d_out, float* dq, float* dk, float* dv) {
+    return orc_flash_backward_ext(batch, heads, seq, dim, q, k, v, d_out, 0, -1.0f, dq, dk, dv, NULL);
+}
+
+/*
  * General naive attention for the shapes beyond self-attention that the callers of the path
  * use: grouped KV heads (query head h reads KV head h / (Hq/Hkv), gqa.rs:233), seq_q != seq_kv
  * (gqa.rs:190-210), per-batch visible key counts, and a causal mask for a block of queries that

@@ -50,6 +50,9 @@ def lib() -> ctypes.CDLL:
                                                   c_int64, fp]
         _lib.orc_attention_general.argtypes = [fp, fp, fp, c_int64, c_int64, c_int64, c_int64, c_int64, c_int, c_int,
                                                i32p, i32p, c_float, fp, fp]
+        _lib.orc_flash_backward_ext.argtypes = [c_int64, c_int64, c_int64, c_int, fp, fp, fp, fp, c_int, c_float,
+                                                fp, fp, fp, fp]
+        _lib.orc_flash_backward.argtypes = [c_int64, c_int64, c_int64, c_int, fp, fp, fp, fp, fp, fp, fp]
         _lib.orc_online_softmax_full.argtypes = [fp, c_int64, fp, fp]
         _lib.orc_combine_tiles.argtypes = [c_float, c_float, c_float, c_float, fp, fp]
         _lib.orc_gqa_forward_f32.argtypes = [fp, fp, fp, fp, c_int64, c_int64, c_int64, c_int64, c_int64, c_int]
@@ -195,6 +198,16 @@ def attention_general(q, k, v, causal=False, kv_lens=None, q_offsets=None, scale
 
 
 # ----------------------------------------------------------------- online softmax
+
+def flash_backward(q, k, v, d_out, causal=False, scale=-1.0, with_lse=False):
+    """cpu_backward.rs:46-185 (+ causal extension): returns (rc, dq, dk, dv[, lse])."""
+    B, H, N, D = q.shape
+    dq, dk, dv = np.zeros_like(q), np.zeros_like(q), np.zeros_like(q)
+    lse = np.zeros((B, H, N), dtype=np.float32) if with_lse else None
+    rc = lib().orc_flash_backward_ext(B, H, N, D, _f(q), _f(k), _f(v), _f(d_out), int(causal), scale, _f(dq), _f(dk),
+                                      _f(dv), _opt(lse, c_float))
+    return (rc, dq, dk, dv, lse) if with_lse else (rc, dq, dk, dv)
+
 
 def online_softmax_full(xs):
     xs = np.ascontiguousarray(xs, dtype=np.float32)

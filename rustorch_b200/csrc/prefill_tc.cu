@@ -5,22 +5,32 @@
 // softmax (cpu_forward.rs:355-386) evaluated in the log2 domain; unlike the reference, KV tiles
 // that a causal mask or a per-batch kv_len hides completely are never visited.
 //
-// CTA = 256 query rows of one (batch, head) = two 128-row Q tiles that ping-pong on the tensor
-// pipe, so the softmax of one tile overlaps the MMAs of the other.  384 threads = 3 warpgroups:
+// Work item = 256 query rows of one (batch, head) = two 128-row Q tiles that share the K/V tiles
+// in shared memory and ping-pong on the tensor pipe.  The kernel is persistent: one CTA per SM
+// walks a static list of items (see tc_item), and every barrier runs on phase counters that
+// carry over from item to item, so the next item's loads and first score MMAs overlap the
+// previous item's last steps and write-back.  384 threads = 3 warpgroups:
 //   warps 0-3  : softmax + lazy O rescale + epilogue of Q tile 0 (one thread per query row)
 //   warps 4-7  : the same for Q tile 1
-//   warp  8    : TMA producer (Q once, then K_j / V_j through their rings)
-//   warp  9    : TMEM allocation and the single thread that issues every tcgen05.mma
-//   warps 10-11: idle (they complete the third warpgroup so that setmaxnreg can move its
-//                registers to the softmax warpgroups: 72 vs 216 registers per thread)
+//   warp  8    : TMA producer (Q per item, K_j / V_j through their rings)
+//   warp  9    : TMEM allocation; issues the tcgen05.mma of Q tile 0
+//   warp  10   : issues the tcgen05.mma of Q tile 1 (two issuers, so that the barrier waits and
+//                commits of one tile hide behind the queued MMAs of the other, and one tile can
+//                move on to the next item while the other finishes)
+//   warp  11   : idle (it completes the third warpgroup so that setmaxnreg can move its
+//                registers to the softmax warpgroups: 72 vs 216 registers per thread; the split
+//                must stay below the 64 K register file or setmaxnreg.inc never returns)
 // TMEM (512 columns x 128 lanes, f32): per Q tile two 64-column S buffers (S[w][b] at w*128 + b*64),
 // O0 [256,256+D), O1 [256+D,256+2D).  K/V are loaded as 128-key tiles but multiplied in 64-key
 // steps; P (bf16) overwrites the first 32 columns of its S buffer and feeds the PV MMA from TMEM.
 // S = Q K^T is an SS MMA with both operands K-major in 128-byte-swizzled shared memory; O += P V
 // is a TS MMA whose B operand (V) is MN-major, i.e. V is used exactly as TMA lands it.
-// Every mbarrier wait is bounded; on expiry the kernel records a code in the device status
-// word, drains its own copies and MMAs, frees TMEM and returns.
+// The normalised O tile is staged in the tile's own (by then idle) Q buffer and leaves through
+// TMA stores.  Every mbarrier wait is bounded; on expiry the kernel records a code in the device
+// status word, drains its own copies and MMAs, frees TMEM and returns.
 #include <cuda.h>
+#include <cstdlib>
+#include <cstring>
 #include <mutex>
 
 #include "kernels.h"
@@ -41,7 +51,7 @@ struct TcCfg {
     static constexpr int SUB_BYTES = 128 * 64 * 2;      // one 64-column (128-byte) swizzled sub-tile
     static constexpr int HALF_BYTES = 64 * 128;         // 64 rows inside a sub-tile
     static constexpr int NSUB = D / 64;
-    static constexpr int NBARS = 2 + 2 * KS + 2 * VS + 4 + 4 + 2 + 2 + 1;
+    static constexpr int NBARS = 2 + 2 + 3 * KS + 3 * VS + 4 + 4 + 2 + 2 + 2 + 2 + 1;
     static constexpr int SMEM_BYTES = (2 + KS + VS) * TILE_BYTES + NBARS * 8 + 16 + 1024;
     static constexpr uint32_t TMEM_COLS = 512;
     static constexpr uint32_t COL_S = 0, COL_O = 256;   // S: tile w, buffer b at COL_S + w*128 + b*64
@@ -58,41 +68,149 @@ struct TcParams {
     const int32_t* q_offsets;  // NULL or [B]: causal position of query row 0 inside the key sequence
     float scale_log2;  // scale * log2(e)
     int* status;       // device status word (bounded-wait expiry codes)
+    int n_qb;          // 256-row blocks per head
+    int slots_per_head, n_slots, paired;  // static schedule, see tc_item
 #ifdef RT_TC_TIMELINE
-    long long* timeline;  // profiling builds only: clock64 stamps of CTA 0 (see TL_* below)
+    long long* timeline;  // profiling builds only, see TL_* below
 #endif
 };
 
 #ifdef RT_TC_TIMELINE
-// Profiling aid, compiled only with -DRT_TC_TIMELINE: one thread per role of CTA 0 stamps clock64
-// at the phase boundaries of every step.  Layout: [role 0..2][step][8] (role 0/1 = softmax of Q
-// tile 0/1, role 2 = MMA issuer).
+// Profiling aid, compiled only with -DRT_TC_TIMELINE.  Per CTA 64 entries: {start ns, end ns, SM id,
+// items}, then per item j < 15 {softmax of tile 0 reaches the item, its steps are done, its
+// epilogue is done, steps}.
+__device__ __forceinline__ long long tl_globaltimer() {
+    long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ int tl_smid() {
+    int s;
+    asm volatile("mov.u32 %0, %smid;" : "=r"(s));
+    return s;
+}
+#define TL_CTA_BEGIN() const long long tl_t0 = tl_globaltimer(), tl_c0 = clock64()
+#define TL_CTA_END(items)                                                       \
+    do {                                                                        \
+        if (p.timeline && threadIdx.x == 0) {                                   \
+            long long* e = p.timeline + (long long)blockIdx.x * 64;             \
+            e[0] = tl_t0; e[1] = tl_globaltimer(); e[2] = tl_smid(); e[3] = (items); \
+            e[62] = tl_c0; e[63] = clock64();                                   \
+        }                                                                       \
+    } while (0)
+#define TL_ITEM(j, slot, val)                                                   \
+    do {                                                                        \
+        if (p.timeline && threadIdx.x == 0 && (j) < 15)                         \
+            p.timeline[(long long)blockIdx.x * 64 + 4 + (j) * 4 + (slot)] = (val); \
+    } while (0)
+// After the CTA log (gridDim.x * 64 entries): clock64 stamps of the first item of CTA 0,
+// [role 0..3][step][8] (role 0/1 = softmax of Q tile 0/1, role 2/3 = MMA issuer of Q tile 0/1).
 #define TL_STAMP(role, step, slot)                                                                     \
     do {                                                                                               \
-        if (p.timeline && blockIdx.x == 0 && (step) < 256)                                             \
-            p.timeline[(((role) * 256) + (step)) * 8 + (slot)] = clock64();                            \
+        if (p.timeline && blockIdx.x == 0 && j == 0 && (step) < 256)                                   \
+            p.timeline[(long long)gridDim.x * 64 + (((role) * 256) + (step)) * 8 + (slot)] = clock64(); \
     } while (0)
 static long long* g_tc_timeline = nullptr;
 extern "C" void rt_debug_set_tc_timeline(void* ptr) { g_tc_timeline = (long long*)ptr; }
 #else
+#define TL_CTA_BEGIN() do { } while (0)
+#define TL_CTA_END(items) do { } while (0)
+#define TL_ITEM(j, slot, val) do { } while (0)
 #define TL_STAMP(role, step, slot) do { } while (0)
 #endif
 
 // Timeout codes written to the device status word (100 + site).
-enum { kToQ = 101, kToKFull, kToKEmpty, kToVFull, kToVEmpty, kToSFull, kToPFull, kToOFull, kToDone, kToDrain };
+enum { kToQ = 101, kToKFull, kToKEmpty, kToVFull, kToVEmpty, kToSFull, kToPFull, kToOFull, kToDone, kToDrain,
+       kToQEmpty, kToOFree, kToStage };
+
+// 2^x for a pair of arguments on the FMA and integer pipes (x <= ~100): round to the nearest
+// integer n with the 1.5*2^23 trick, a cubic for 2^r on r = x - n in [-0.5, 0.5] (relative error
+// 7.5e-5, far below the bf16 rounding of P), and n added into the exponent field.  Arguments
+// below -125 (masked scores are -inf) give 2^-125, not 0: invisible next to any visible score,
+// and a row without one is recognised by a flag instead of by a zero sum.
+// The MUFU pipe (16 ex2 per clock per SM) is the softmax warps' bottleneck; sending a share of
+// the exponentials here balances it against the FMA pipe.
+__device__ __forceinline__ float2 exp2_poly2(float2 x) {
+    x.x = fmaxf(x.x, -125.f);
+    x.y = fmaxf(x.y, -125.f);
+    const float2 magic = make_float2(12582912.f, 12582912.f), nmagic = make_float2(-12582912.f, -12582912.f);
+    const float2 t = __fadd2_rn(x, magic);
+    const float2 nf = __fadd2_rn(t, nmagic);
+    const float2 r = __fadd2_rn(x, make_float2(-nf.x, -nf.y));
+    float2 y = __ffma2_rn(r, make_float2(0.0551716685f, 0.0551716685f), make_float2(0.242611125f, 0.242611125f));
+    y = __ffma2_rn(y, r, make_float2(0.693260968f, 0.693260968f));
+    y = __ffma2_rn(y, r, make_float2(0.999928057f, 0.999928057f));
+    y.x = __int_as_float(__float_as_int(y.x) + (__float_as_int(t.x) << 23));
+    y.y = __int_as_float(__float_as_int(y.y) + (__float_as_int(t.y) << 23));
+    return y;
+}
+// Which of the 16 element pairs of a 32-column chunk take the polynomial path.
+// Which of the 16 element pairs of a 32-column chunk take the polynomial path (a quarter: more
+// than that costs more issue slots on the FMA pipe than it frees on the MUFU pipe).
+__host__ __device__ constexpr bool poly_pair(int q) { return (q & 3) == 3; }
+
+// One work item of a CTA's static list.
+struct TcItem {
+    int bh, bh_kv, b, q0, kv_hi, q_off;
+    int U0, U1;    // 64-key steps of each Q tile (U0 <= U1); scalars, so nothing is indexed dynamically
+    int n_tiles;   // 128-key K/V tiles to load
+    bool end;      // the list is exhausted
+    bool valid;    // false: this position of the list holds no item
+    __device__ __forceinline__ int steps(int w) const { return w ? U1 : U0; }
+};
+
+// Static schedule.  The (batch, head)-major slot list is dealt round-robin to the CTAs, so the
+// CTAs running at one time work on a few neighbouring heads and share their K/V in L2.  In
+// paired mode a slot holds the 256-row blocks r and n_qb-1-r of one head, heavy one first: under
+// a causal mask every slot then costs the same, and the CTAs finish together.
+template <bool kCausal>
+__device__ __forceinline__ TcItem tc_item(int j, const TcParams& p) {
+    TcItem it;
+    const int slot = (int)blockIdx.x + (p.paired ? (j >> 1) : j) * (int)gridDim.x;
+    it.end = slot >= p.n_slots;
+    it.valid = false;
+    if (it.end) return it;
+    it.bh = slot / p.slots_per_head;
+    const int r = slot % p.slots_per_head;
+    int qb = p.n_qb - 1 - r;
+    if (p.paired && (j & 1)) {
+        if (r == qb) return it;  // the middle block of an odd count has no partner
+        qb = r;
+    }
+    it.valid = true;
+    it.b = it.bh / p.heads;
+    it.bh_kv = it.b * p.heads_kv + (it.bh % p.heads) / (p.heads / p.heads_kv);
+    it.q0 = qb * 256;
+    it.kv_hi = p.seq_kv;
+    if (p.kv_lens) {
+        const int l = p.kv_lens[it.b];
+        it.kv_hi = l < 0 ? 0 : (l < p.seq_kv ? l : p.seq_kv);
+    }
+    it.q_off = p.q_offsets ? p.q_offsets[it.b] : 0;  // query row i sits at key position i + q_off
+    const int n_steps = (it.kv_hi + 63) / 64;        // 64-key steps that hold a visible key
+    const int last0 = it.q0 + 127 + it.q_off, last1 = last0 + 128;  // last key each tile's last row may see
+    it.U0 = !kCausal ? n_steps : (last0 < 0 ? 0 : min(n_steps, last0 / 64 + 1));
+    it.U1 = !kCausal ? n_steps : (last1 < 0 ? 0 : min(n_steps, last1 / 64 + 1));
+    it.n_tiles = (it.U1 + 1) / 2;
+    return it;
+}
 
 // Pipeline, per Q tile w and 64-key step u (buffer b = u & 1):
 //   MMA:     S_w(u) -> TMEM S[w][b]            (SS, N = 64, D/16 k-steps)       commit s_full[w][b]
 //   softmax: S[w][b] -> registers -> P (bf16) over the first 32 columns of S[w][b]   arrive p_full[w][b]
 //   MMA:     O_w += P V(u)                      (TS, N = D, 4 k-steps)           commit o_full[w]
 //            then S_w(u+2) into the same buffer (in-order after the PV that read P from it)
-// S is double-buffered, so the softmax of step u+1 never waits for the PV of step u; the
-// softmax warps of both tiles keep the MUFU pipe busy while the tensor pipe runs behind them.
+// S is double-buffered, so the softmax of step u+1 never waits for the PV of step u.
+// Per item and tile: q_full (Q landed) -> ... -> o_done (last PV retired) -> epilogue reads O
+// (o_free: the next item's first PV may overwrite it), stages it in the Q buffer (stage_full),
+// one thread stores it (q_empty: the next item's Q may land).  A tile that sees no key in an
+// item takes no part in these (its rows are written as NaN directly).
 template <int D, bool kCausal, bool kKeep>
 __global__ void __launch_bounds__(384, 1)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                   const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
                   const TcParams p) {
+    TL_CTA_BEGIN();
     using C = TcCfg<D>;
     constexpr int KS = C::KS, VS = C::VS, TILE = C::TILE_BYTES, SUB = C::SUB_BYTES, HALF = C::HALF_BYTES;
 
@@ -103,60 +221,28 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     uint8_t* sV = sK + KS * TILE;
     uint64_t* bars = reinterpret_cast<uint64_t*>(sV + VS * TILE);
     uint64_t* q_full = bars;              // [2]
-    uint64_t* k_full = q_full + 2;        // [KS]
-    uint64_t* k_empty = k_full + KS;      // [KS]
-    uint64_t* v_full = k_empty + KS;      // [VS]
-    uint64_t* v_empty = v_full + VS;      // [VS]
-    uint64_t* s_full = v_empty + VS;      // [2 tiles][2 buffers]
+    uint64_t* q_empty = q_full + 2;       // [2]  the O tile staged in the Q buffer has been read out
+    uint64_t* k_full = q_empty + 2;       // [KS]
+    uint64_t* k_empty = k_full + KS;      // [2 tiles][KS]: the issuer of tile w is done with the slot
+    uint64_t* v_full = k_empty + 2 * KS;  // [VS]
+    uint64_t* v_empty = v_full + VS;      // [2 tiles][VS]
+    uint64_t* s_full = v_empty + 2 * VS;  // [2 tiles][2 buffers]
     uint64_t* p_full = s_full + 4;        // [2 tiles][2 buffers]
     uint64_t* o_full = p_full + 4;        // [2]  one phase per PV step (O at rest for a rescale)
-    uint64_t* o_done = o_full + 2;        // [2]  single phase: the last PV of the tile has retired
-    uint64_t* done_bar = o_done + 2;      // [1]
+    uint64_t* o_done = o_full + 2;        // [2]  one phase per item: the last PV of the tile has retired
+    uint64_t* o_free = o_done + 2;        // [2]  one phase per item: the epilogue has read O out of TMEM
+    uint64_t* stage_full = o_free + 2;    // [2]  one phase per item: the O tile is staged in shared memory
+    uint64_t* done_bar = stage_full + 2;  // [1]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done_bar + 1);
 
     // Broadcasting the warp index makes it provably warp-uniform, so role dispatch and the MMA
     // operands stay on the uniform datapath.
     const int warp = __shfl_sync(kFullMask, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
     const int N = p.seq;
-    const int n_qb = (N + 255) / 256;
-    const int bh = blockIdx.x / n_qb;
-    const int qb = n_qb - 1 - (int)(blockIdx.x % n_qb);  // heaviest causal block of a head first
-    const int b = bh / p.heads;
-    const int bh_kv = b * p.heads_kv + (bh % p.heads) / (p.heads / p.heads_kv);
-    const int q0 = qb * 256;
     const int Nkv = p.seq_kv;
 
-    int kv_hi = Nkv;
-    if (p.kv_lens) {
-        const int l = p.kv_lens[b];
-        kv_hi = l < 0 ? 0 : (l < Nkv ? l : Nkv);
-    }
-    const int q_off = p.q_offsets ? p.q_offsets[b] : 0;  // query row i sits at key position i + q_off
-    const int n_steps = (kv_hi + 63) / 64;  // 64-key steps that hold a visible key
-    int U[2];                               // steps of each Q tile (U[0] <= U[1])
-#pragma unroll
-    for (int w = 0; w < 2; ++w) {
-        const int last_key = q0 + 128 * w + 127 + q_off;  // last key the tile's last row may see
-        U[w] = !kCausal ? n_steps : (last_key < 0 ? 0 : min(n_steps, last_key / 64 + 1));
-    }
-    const int u_max = U[1];
-    const int n_tiles = (u_max + 1) / 2;    // 128-key K/V tiles to load
-
-    if (u_max == 0) {  // no visible key at all: NaN rows, LSE = -inf (cpu_forward.rs:411-420)
-        if (warp < 8) {
-            const int row = q0 + warp * 32 + lane;
-            if (row < N) {
-                uint4 nan4 = make_uint4(0x7fc07fc0u, 0x7fc07fc0u, 0x7fc07fc0u, 0x7fc07fc0u);
-                uint4* dst = reinterpret_cast<uint4*>(p.out + ((int64_t)bh * N + row) * D);
-#pragma unroll
-                for (int i = 0; i < D / 8; ++i) dst[i] = nan4;
-                if (p.lse) p.lse[(int64_t)bh * N + row] = -INFINITY;
-            }
-        }
-        return;
-    }
-
     // ------------------------------------------------------------------ setup
+    bool first_preloaded = false;  // meaningful in the producer thread only
     if (warp == 8 && lane == 0) {
         prefetch_tensormap(&tm_q);
         prefetch_tensormap(&tm_k);
@@ -164,8 +250,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         prefetch_tensormap(&tm_o);
         for (int i = 0; i < 2; ++i) {
             mbar_init(&q_full[i], 1);
+            mbar_init(&q_empty[i], 1);
             mbar_init(&o_full[i], 1);
             mbar_init(&o_done[i], 1);
+            mbar_init(&o_free[i], 128);
+            mbar_init(&stage_full[i], 128);
         }
         for (int i = 0; i < 4; ++i) {
             mbar_init(&s_full[i], 1);
@@ -174,26 +263,33 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         for (int i = 0; i < KS; ++i) {
             mbar_init(&k_full[i], 1);
             mbar_init(&k_empty[i], 1);
+            mbar_init(&k_empty[KS + i], 1);
         }
         for (int i = 0; i < VS; ++i) {
             mbar_init(&v_full[i], 1);
             mbar_init(&v_empty[i], 1);
+            mbar_init(&v_empty[VS + i], 1);
         }
-        mbar_init(done_bar, 1);
+        mbar_init(done_bar, 2);
         fence_barrier_init();
         fence_proxy_async();
-        // Q and the first K tile are requested right away, so their latency overlaps the TMEM
-        // allocation and the CTA-wide barrier below (the producer loop starts at K tile 1).
-        for (int w = 0; w < 2; ++w) {
-            mbar_arrive_expect_tx(&q_full[w], TILE);
-#pragma unroll
-            for (int s = 0; s < C::NSUB; ++s)
-                tma_load_3d(sQ + w * TILE + s * SUB, &tm_q, &q_full[w], s * 64, q0 + w * 128, bh);
-            if (w == 0) {
-                mbar_arrive_expect_tx(&k_full[0], TILE);
+        // Q and the first K tile of the first item are requested right away, so their latency
+        // overlaps the TMEM allocation and the CTA-wide barrier below.
+        const TcItem it = tc_item<kCausal>(0, p);
+        if (!it.end && it.valid && it.U1 > 0) {
+            first_preloaded = true;
+            for (int w = 0; w < 2; ++w) {
+                if (w == 0 && it.U0 == 0) continue;
+                mbar_arrive_expect_tx(&q_full[w], TILE);
 #pragma unroll
                 for (int s = 0; s < C::NSUB; ++s)
-                    tma_load_3d(sK + s * SUB, &tm_k, &k_full[0], s * 64, 0, bh_kv);
+                    tma_load_3d(sQ + w * TILE + s * SUB, &tm_q, &q_full[w], s * 64, it.q0 + w * 128, it.bh);
+                if (w == 0 || it.U0 == 0) {
+                    mbar_arrive_expect_tx(&k_full[0], TILE);
+#pragma unroll
+                    for (int s = 0; s < C::NSUB; ++s)
+                        tma_load_3d(sK + s * SUB, &tm_k, &k_full[0], s * 64, 0, it.bh_kv);
+                }
             }
         }
     }
@@ -205,6 +301,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    int n_items_done = 0;
 
     // The register hand-over sits inside each role's own branch: the compiler budgets the code
     // that follows a setmaxnreg only when no path with a different budget merges into it.
@@ -213,313 +310,402 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       if (warp == 8) {
         // ============================================================== TMA producer
         if (lane == 0) {
-            int k_issued = 1, v_issued = 0;  // Q and K tile 0 were requested during setup
-            for (int j = 0; j < n_tiles; ++j) {
-                const int ks = j % KS, vs = j % VS;
-                if (j > 0) {
-                    if (!mbar_wait(&k_empty[ks], ((uint32_t)(j / KS) & 1u) ^ 1u, p.status, kToKEmpty)) break;
-                    mbar_arrive_expect_tx(&k_full[ks], TILE);
+            int kg = 0, vg = 0;    // K / V tiles requested so far (ring position and phase)
+            int na0 = 0, na1 = 0;  // items so far in which tile w took part (phase of its per-item barriers)
+            bool ok = true;
+            for (int j = 0; ok; ++j) {
+                const TcItem it = tc_item<kCausal>(j, p);
+                if (it.end) break;
+                if (!it.valid || it.U1 == 0) continue;  // nothing to load
+                auto load_q = [&](int w, int na) {
+                    // the previous item's O tile must have left the buffer
+                    if (!mbar_wait(&q_empty[w], ((uint32_t)na & 1u) ^ 1u, p.status, kToQEmpty)) return false;
+                    mbar_arrive_expect_tx(&q_full[w], TILE);
 #pragma unroll
                     for (int s = 0; s < C::NSUB; ++s)
-                        tma_load_3d(sK + ks * TILE + s * SUB, &tm_k, &k_full[ks], s * 64, j * 128, bh_kv);
-                    k_issued = j + 1;
+                        tma_load_3d(sQ + w * TILE + s * SUB, &tm_q, &q_full[w], s * 64, it.q0 + w * 128, it.bh);
+                    return true;
+                };
+                const bool pre = first_preloaded && j == 0;  // Q and K tile 0 were requested during setup
+                if (it.U0 > 0) {
+                    if (!pre && !load_q(0, na0)) break;
+                    ++na0;
                 }
-                if (!mbar_wait(&v_empty[vs], ((uint32_t)(j / VS) & 1u) ^ 1u, p.status, kToVEmpty)) break;
-                mbar_arrive_expect_tx(&v_full[vs], TILE);
+                for (int t = 0; t < it.n_tiles && ok; ++t) {
+                    // A slot is free once both issuers have released the tile it held.
+                    const int ks = kg % KS, vs = vg % VS;
+                    const uint32_t kpar = ((uint32_t)(kg / KS) & 1u) ^ 1u, vpar = ((uint32_t)(vg / VS) & 1u) ^ 1u;
+                    if (!(pre && t == 0)) {
+                        if (!mbar_wait(&k_empty[ks], kpar, p.status, kToKEmpty) ||
+                            !mbar_wait(&k_empty[KS + ks], kpar, p.status, kToKEmpty)) {
+                            ok = false;
+                            break;
+                        }
+                        mbar_arrive_expect_tx(&k_full[ks], TILE);
 #pragma unroll
-                for (int s = 0; s < C::NSUB; ++s)
-                    tma_load_3d(sV + vs * TILE + s * SUB, &tm_v, &v_full[vs], s * 64, j * 128, bh_kv);
-                v_issued = j + 1;
+                        for (int s = 0; s < C::NSUB; ++s)
+                            tma_load_3d(sK + ks * TILE + s * SUB, &tm_k, &k_full[ks], s * 64, t * 128, it.bh_kv);
+                    }
+                    ++kg;
+                    if (t == 0) {  // tile 1 usually still works on the previous item: its Q comes second
+                        if (!pre && !load_q(1, na1)) {
+                            ok = false;
+                            break;
+                        }
+                        ++na1;
+                    }
+                    if (!mbar_wait(&v_empty[vs], vpar, p.status, kToVEmpty) ||
+                        !mbar_wait(&v_empty[VS + vs], vpar, p.status, kToVEmpty)) {
+                        ok = false;
+                        break;
+                    }
+                    mbar_arrive_expect_tx(&v_full[vs], TILE);
+#pragma unroll
+                    for (int s = 0; s < C::NSUB; ++s)
+                        tma_load_3d(sV + vs * TILE + s * SUB, &tm_v, &v_full[vs], s * 64, t * 128, it.bh_kv);
+                    ++vg;
+                }
             }
             // Drain: every copy this thread issued must have landed before the CTA may exit.
-            mbar_wait(&q_full[0], 0, p.status, kToDrain);
-            mbar_wait(&q_full[1], 0, p.status, kToDrain);
-            for (int j = max(0, k_issued - KS); j < k_issued; ++j)
-                mbar_wait(&k_full[j % KS], (uint32_t)(j / KS) & 1u, p.status, kToDrain);
-            for (int j = max(0, v_issued - VS); j < v_issued; ++j)
-                mbar_wait(&v_full[j % VS], (uint32_t)(j / VS) & 1u, p.status, kToDrain);
+            if (na0 > 0) mbar_wait(&q_full[0], (uint32_t)(na0 - 1) & 1u, p.status, kToDrain);
+            if (na1 > 0) mbar_wait(&q_full[1], (uint32_t)(na1 - 1) & 1u, p.status, kToDrain);
+            for (int t = max(0, kg - KS); t < kg; ++t)
+                mbar_wait(&k_full[t % KS], (uint32_t)(t / KS) & 1u, p.status, kToDrain);
+            for (int t = max(0, vg - VS); t < vg; ++t)
+                mbar_wait(&v_full[t % VS], (uint32_t)(t / VS) & 1u, p.status, kToDrain);
         }
-      } else if (warp == 9) {
-        // ============================================================== MMA issuer
+      } else if (warp == 9 || warp == 10) {
+        // ============================================================== MMA issuer of Q tile w
         // The whole warp runs this loop with uniform control flow and only the elected lane
         // executes the tcgen05 instructions: descriptors, addresses and loop state then live in
         // uniform registers, which is what the MMA instruction takes its operands from.
         {
+            const int w = warp - 9;
             const bool leader = elect_one();
             constexpr uint32_t idesc_s = make_idesc_bf16(128, 64, 0, 0);
             constexpr uint32_t idesc_o = make_idesc_bf16(128, D, 0, 1);
             // Descriptors are built once; each MMA only adds an offset (in 16-byte units) to the
             // start-address field, so the issuing thread keeps ahead of the tensor pipe.
-            const uint64_t dq = make_smem_desc_sw128(smem_u32(sQ), 16, 1024);
+            const uint64_t dq = make_smem_desc_sw128(smem_u32(sQ + w * TILE), 16, 1024);
             const uint64_t dk = make_smem_desc_sw128(smem_u32(sK), 16, 1024);
             const uint64_t dv = make_smem_desc_sw128(smem_u32(sV), SUB, 1024);
-            const uint32_t tS0 = tmem_base + C::COL_S, tO0 = tmem_base + C::COL_O;
-            // S_w(u): keys [64u, 64u+64) = rows (u&1)*64.. of K tile u/2
-            auto issue_S = [&](int w, int u) {
-                const uint64_t a = dq + (uint64_t)((w * TILE) >> 4);
-                const uint64_t bk = dk + (uint64_t)((((u >> 1) % KS) * TILE + (u & 1) * HALF) >> 4);
-                const uint32_t d = tS0 + w * 128 + (u & 1) * 64;
-#pragma unroll
-                for (int kk = 0; kk < D / 16; ++kk) {
-                    const uint32_t off = (uint32_t)(((kk / 4) * SUB + (kk % 4) * 32) >> 4);
-                    if (leader) mma_ss(d, a + off, bk + off, idesc_s, kk > 0);
-                }
-            };
-            // O_w += P V(u): P (bf16) sits in the first 32 columns of S[w][u&1]
-            auto issue_PV = [&](int w, int u) {
-                const uint64_t bv = dv + (uint64_t)((((u >> 1) % VS) * TILE + (u & 1) * HALF) >> 4);
-                const uint32_t a = tS0 + w * 128 + (u & 1) * 64;
-                const uint32_t acc0 = u > 0 ? 1u : 0u;
-#pragma unroll
-                for (int kk = 0; kk < 4; ++kk)
-                    if (leader) mma_ts(tO0 + w * D, a + kk * 8, bv + (uint64_t)((kk * 2048) >> 4), idesc_o, kk > 0 ? 1u : acc0);
-            };
+            const uint32_t tS = tmem_base + C::COL_S + w * 128, tO = tmem_base + C::COL_O + w * D;
+            uint64_t* const ke = k_empty + w * KS;
+            uint64_t* const ve = v_empty + w * VS;
+            int kg = 0, vg = 0;    // ring index of the item's first K / V tile
+            int na = 0;            // items so far in which this tile took part
+            int cp0 = 0, cp1 = 0;  // p_full phases of each S buffer consumed before the item
             auto commit = [&](uint64_t* bar) {
                 if (leader) mma_commit(bar);
             };
             auto wait = [&](uint64_t* bar, uint32_t parity, int code) {
                 return __all_sync(kFullMask, mbar_wait(bar, parity, p.status, code));
             };
-            auto last_use = [&](int u) { return (u & 1) || u == U[1] - 1; };  // of a 128-key tile, by Q tile 1
-
-            bool ok = wait(&k_full[0], 0, kToKFull);
-            if (ok && U[0] > 0) {
-                ok = wait(&q_full[0], 0, kToQ);
-                if (ok) {
-                    tc_fence_after();
-                    issue_S(0, 0);
-                    commit(&s_full[0]);
-                    if (U[0] > 1) {
-                        issue_S(0, 1);
-                        commit(&s_full[1]);
-                    }
-                }
-            }
-            if (ok) ok = wait(&q_full[1], 0, kToQ);
-            if (ok) {
-                tc_fence_after();
-                issue_S(1, 0);
-                commit(&s_full[2]);
-                if (last_use(0)) commit(&k_empty[0]);
-                if (U[1] > 1) {
-                    issue_S(1, 1);
-                    commit(&s_full[3]);
-                    commit(&k_empty[0]);
-                }
-            }
-            int k_waited = 0, v_waited = -1;
-            for (int u = 0; u < u_max && ok; ++u) {
+            bool ok = true;
+            for (int j = 0; ok; ++j) {
+                const TcItem it = tc_item<kCausal>(j, p);
+                if (it.end) break;
+                if (!it.valid || it.U1 == 0) continue;
+                const int n_u = it.steps(w);
+                // S_w(u): keys [64u, 64u+64) = rows (u&1)*64.. of the item's K tile u/2
+                auto issue_S = [&](int u) {
+                    const uint64_t bk = dk + (uint64_t)((((kg + (u >> 1)) % KS) * TILE + (u & 1) * HALF) >> 4);
+                    const uint32_t d = tS + (u & 1) * 64;
 #pragma unroll
-                for (int w = 0; w < 2; ++w) {
-                    if (!ok || u >= U[w]) continue;
-                    const int vt = u >> 1;
-                    if (vt > v_waited) {
-                        if (!wait(&v_full[vt % VS], (uint32_t)(vt / VS) & 1u, kToVFull)) { ok = false; continue; }
-                        v_waited = vt;
+                    for (int kk = 0; kk < D / 16; ++kk) {
+                        const uint32_t off = (uint32_t)(((kk / 4) * SUB + (kk % 4) * 32) >> 4);
+                        if (leader) mma_ss(d, dq + off, bk + off, idesc_s, kk > 0);
                     }
-                    TL_STAMP(2, u, w * 4 + 0);
-                    if (!wait(&p_full[w * 2 + (u & 1)], (uint32_t)(u >> 1) & 1u, kToPFull)) { ok = false; continue; }
-                    TL_STAMP(2, u, w * 4 + 1);
+                };
+                // O_w += P V(u): P (bf16) sits in the first 32 columns of S[w][u&1]
+                auto issue_PV = [&](int u) {
+                    const uint64_t bv = dv + (uint64_t)((((vg + (u >> 1)) % VS) * TILE + (u & 1) * HALF) >> 4);
+                    const uint32_t a = tS + (u & 1) * 64;
+                    const uint32_t acc0 = u > 0 ? 1u : 0u;
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk)
+                        if (leader)
+                            mma_ts(tO, a + kk * 8, bv + (uint64_t)((kk * 2048) >> 4), idesc_o, kk > 0 ? 1u : acc0);
+                };
+                auto last_use = [&](int u) { return (u & 1) || u == n_u - 1; };  // of a 128-key tile, by this Q tile
+
+                if (n_u > 0) {
+                    ok = wait(&k_full[kg % KS], (uint32_t)(kg / KS) & 1u, kToKFull) &&
+                         wait(&q_full[w], (uint32_t)na & 1u, kToQ);
+                    if (!ok) break;
                     tc_fence_after();
-                    issue_PV(w, u);
-                    commit(&o_full[w]);
-                    if (u == U[w] - 1) commit(&o_done[w]);
-                    if (w == 1 && last_use(u)) commit(&v_empty[vt % VS]);
-                    if (u + 2 < U[w]) {
-                        const int kt = (u + 2) >> 1;
-                        if (kt > k_waited) {
-                            if (!wait(&k_full[kt % KS], (uint32_t)(kt / KS) & 1u, kToKFull)) { ok = false; continue; }
-                            k_waited = kt;
-                            tc_fence_after();
-                        }
-                        TL_STAMP(2, u, w * 4 + 2);
-                        issue_S(w, u + 2);
-                        commit(&s_full[w * 2 + (u & 1)]);
-                        if (w == 1 && last_use(u + 2)) commit(&k_empty[kt % KS]);
+                    issue_S(0);
+                    commit(&s_full[w * 2]);
+                    if (n_u > 1) {
+                        issue_S(1);
+                        commit(&s_full[w * 2 + 1]);
                     }
-                    TL_STAMP(2, u, w * 4 + 3);
+                    commit(&ke[kg % KS]);
+                    int k_waited = 0, v_waited = -1;  // item-local tile indices already waited for
+                    for (int u = 0; u < n_u && ok; ++u) {
+                        const int vt = u >> 1;
+                        if (vt > v_waited) {
+                            if (!wait(&v_full[(vg + vt) % VS], (uint32_t)((vg + vt) / VS) & 1u, kToVFull)) { ok = false; break; }
+                            v_waited = vt;
+                        }
+                        TL_STAMP(2 + w, u, 0);
+                        if (!wait(&p_full[w * 2 + (u & 1)], (uint32_t)(((u & 1) ? cp1 : cp0) + (u >> 1)) & 1u, kToPFull)) { ok = false; break; }
+                        TL_STAMP(2 + w, u, 1);
+                        // the previous item's epilogue must have read O_w before it is overwritten
+                        if (u == 0 && na > 0 && !wait(&o_free[w], (uint32_t)(na - 1) & 1u, kToOFree)) { ok = false; break; }
+                        tc_fence_after();
+                        issue_PV(u);
+                        commit(&o_full[w]);
+                        if (u == n_u - 1) commit(&o_done[w]);
+                        if (last_use(u)) commit(&ve[(vg + vt) % VS]);
+                        if (u + 2 < n_u) {
+                            const int kt = (u + 2) >> 1;
+                            if (kt > k_waited) {
+                                if (!wait(&k_full[(kg + kt) % KS], (uint32_t)((kg + kt) / KS) & 1u, kToKFull)) { ok = false; break; }
+                                k_waited = kt;
+                                tc_fence_after();
+                            }
+                            TL_STAMP(2 + w, u, 2);
+                            issue_S(u + 2);
+                            commit(&s_full[w * 2 + (u & 1)]);
+                            if (last_use(u + 2)) commit(&ke[(kg + kt) % KS]);
+                        }
+                        TL_STAMP(2 + w, u, 3);
+                    }
+                    ++na;
+                    cp0 += (n_u + 1) / 2;
+                    cp1 += n_u / 2;
                 }
+                // Tiles this Q tile does not read (it sees fewer keys than the other one) are passed on
+                // once they have landed, which keeps this issuer inside the ring window.
+                for (int t = (n_u + 1) / 2; t < it.n_tiles && ok; ++t) {
+                    ok = wait(&k_full[(kg + t) % KS], (uint32_t)((kg + t) / KS) & 1u, kToKFull);
+                    if (ok) commit(&ke[(kg + t) % KS]);
+                    ok = ok && wait(&v_full[(vg + t) % VS], (uint32_t)((vg + t) / VS) & 1u, kToVFull);
+                    if (ok) commit(&ve[(vg + t) % VS]);
+                }
+                kg += it.n_tiles;
+                vg += it.n_tiles;
             }
-            // All MMAs issued by this thread must retire before TMEM is freed.
+            // All MMAs of both issuers must retire before TMEM is freed.
             commit(done_bar);
             wait(done_bar, 0, kToDone);
         }
-      }  // warps 10-11 idle: they only complete the warpgroup for setmaxnreg
+      }  // warp 11 idle: it only completes the warpgroup for setmaxnreg
     } else {
         asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
         // ============================================================== softmax / epilogue warps
         const int w = warp >> 2;                       // Q tile
         const int row_in_tile = (warp & 3) * 32 + lane;
-        const int row = q0 + w * 128 + row_in_tile;    // query index within the sequence
         const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
         const uint32_t tS = tmem_base + lane_sel + C::COL_S + w * 128;
         const uint32_t tO = tmem_base + lane_sel + C::COL_O + w * D;
         const float c = p.scale_log2;
-        const uint8_t* keep = kKeep ? p.key_keep + (int64_t)b * p.keep_batch_stride : nullptr;
-
-        float m_ref = -INFINITY;  // reference max (raw score units) the running sums are relative to
-        float l = 0.f;
+        int na = 0;            // items so far in which this tile took part
+        int cs0 = 0, cs1 = 0;  // s_full phases of each S buffer consumed before the item
+        int co = 0;            // PV steps of this tile before the item (phase of o_full)
         bool ok = true;
-        const int n_iter = U[w];
 
-        for (int u = 0; u < n_iter; ++u) {
-            const int buf = u & 1;
-            if ((warp & 3) == 0 && lane == 0) TL_STAMP(w, u, 0);
-            if (!__all_sync(kFullMask, mbar_wait(&s_full[w * 2 + buf], (uint32_t)(u >> 1) & 1u, p.status, kToSFull))) {
+        for (int j = 0; ok; ++j) {
+            const TcItem it = tc_item<kCausal>(j, p);
+            if (it.end) break;
+            if (!it.valid) continue;
+            ++n_items_done;
+            const int n_iter = it.steps(w);
+            const int bh = it.bh, kv_hi = it.kv_hi, q_off = it.q_off;
+            const int row = it.q0 + w * 128 + row_in_tile;  // query index within the sequence
+            const uint8_t* keep = kKeep ? p.key_keep + (int64_t)it.b * p.keep_batch_stride : nullptr;
+            if (w == 0) TL_ITEM(j, 0, tl_globaltimer());
+
+            if (n_iter == 0) {  // the tile sees no key: NaN rows, LSE = -inf (cpu_forward.rs:411-420)
+                if (row < N) {
+                    uint4* dst = reinterpret_cast<uint4*>(p.out + ((int64_t)bh * N + row) * D);
+#pragma unroll
+                    for (int i = 0; i < D / 8; ++i) dst[i] = make_uint4(0x7fc07fc0u, 0x7fc07fc0u, 0x7fc07fc0u, 0x7fc07fc0u);
+                    if (p.lse) p.lse[(int64_t)bh * N + row] = -INFINITY;
+                }
+                continue;
+            }
+
+            float m_ref = -INFINITY;  // reference max (raw score units) the running sums are relative to
+            float l = 0.f;
+            bool seen = false;  // the row has met a score that no mask hides
+            for (int u = 0; u < n_iter; ++u) {
+                const int buf = u & 1;
+                if ((warp & 3) == 0 && lane == 0) TL_STAMP(w, u, 0);
+                if (!__all_sync(kFullMask, mbar_wait(&s_full[w * 2 + buf], (uint32_t)((buf ? cs1 : cs0) + (u >> 1)) & 1u,
+                                                     p.status, kToSFull))) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                if ((warp & 3) == 0 && lane == 0) TL_STAMP(w, u, 1);
+
+                uint32_t s[64];
+                {
+                    uint32_t(&s0)[32] = *reinterpret_cast<uint32_t(*)[32]>(&s[0]);
+                    uint32_t(&s1)[32] = *reinterpret_cast<uint32_t(*)[32]>(&s[32]);
+                    tmem_ld32(tS + buf * 64, s0);
+                    tmem_ld32(tS + buf * 64 + 32, s1);
+                    tc_wait_ld();
+                }
+                if ((warp & 3) == 0 && lane == 0) TL_STAMP(w, u, 2);
+
+                // ---- masks: keys beyond kv_hi, causal diagonal, keep flags
+                const int col0 = u * 64;
+                int lim = kv_hi - 1 - col0;                       // last visible column in this step
+                if (kCausal) lim = min(lim, row + q_off - col0);
+                if (lim < 63) {
+#pragma unroll
+                    for (int i = 0; i < 64; ++i)
+                        if (i > lim) s[i] = 0xff800000u;  // -inf
+                }
+                if (kKeep) {  // Mask::Padding keep flags (mask.rs:44); every thread reads the same bytes
+#pragma unroll
+                    for (int i = 0; i < 64; ++i)
+                        if (col0 + i < Nkv && __ldg(keep + col0 + i) == 0) s[i] = 0xff800000u;
+                }
+
+                // ---- row max (three-input max halves the instruction count)
+                float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+                for (int i = 0; i < 64; i += 8) {
+                    mx0 = max3(mx0, __uint_as_float(s[i]), __uint_as_float(s[i + 1]));
+                    mx1 = max3(mx1, __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
+                    mx2 = max3(mx2, __uint_as_float(s[i + 4]), __uint_as_float(s[i + 5]));
+                    mx3 = max3(mx3, __uint_as_float(s[i + 6]), __uint_as_float(s[i + 7]));
+                }
+                const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+                seen = seen || (mx > -INFINITY);
+
+                // ---- lazy rescale: move the reference max only when it would grow by > 2^8
+                if (u == 0) {
+                    m_ref = mx;
+                } else {
+                    const bool need = (mx > m_ref) && ((mx - m_ref) * c > 8.0f || m_ref == -INFINITY);
+                    if (__any_sync(kFullMask, need)) {
+                        // O must be at rest: the PV of the previous step has to be complete.  (The score
+                        // MMA just waited for was issued after the PV before that one, so the barrier is
+                        // at most one phase behind and the parity wait is unambiguous.)
+                        if (!__all_sync(kFullMask, mbar_wait(&o_full[w], (uint32_t)(co + u - 1) & 1u, p.status, kToOFull))) {
+                            ok = false;
+                            break;
+                        }
+                        tc_fence_after();
+                        const float m_new = fmaxf(m_ref, mx);
+                        const float alpha = (m_new == -INFINITY) ? 1.f : fast_exp2((m_ref - m_new) * c);
+                        l *= alpha;
+                        m_ref = m_new;
+#pragma unroll
+                        for (int ch = 0; ch < D / 32; ++ch) {
+                            uint32_t o[32];
+                            tmem_ld32(tO + ch * 32, o);
+                            tc_wait_ld();
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                            tmem_st32(tO + ch * 32, o);
+                        }
+                        tc_wait_st();
+                    }
+                }
+                if ((warp & 3) == 0 && lane == 0) TL_STAMP(w, u, 3);
+
+                // ---- P = exp2(s*c - m*c), row sum, bf16 pack, store to TMEM over S (packed f32x2 math)
+                const float mc = (m_ref == -INFINITY) ? 0.f : m_ref * c;
+                const float2 c2 = make_float2(c, c), nmc2 = make_float2(-mc, -mc);
+                float2 sum_a = make_float2(0.f, 0.f), sum_b = make_float2(0.f, 0.f);
+#pragma unroll
+                for (int ch = 0; ch < 2; ++ch) {
+                    uint32_t pk[16];
+#pragma unroll
+                    for (int i = 0; i < 16; i += 2) {
+                        const float2 xa = __ffma2_rn(
+                            make_float2(__uint_as_float(s[ch * 32 + 2 * i]), __uint_as_float(s[ch * 32 + 2 * i + 1])), c2,
+                            nmc2);
+                        const float2 xb = __ffma2_rn(
+                            make_float2(__uint_as_float(s[ch * 32 + 2 * i + 2]), __uint_as_float(s[ch * 32 + 2 * i + 3])),
+                            c2, nmc2);
+                        // a quarter of the exponentials go to the polynomial (see exp2_poly2)
+                        const float2 pa = poly_pair(i) ? exp2_poly2(xa) : make_float2(fast_exp2(xa.x), fast_exp2(xa.y));
+                        const float2 pb = poly_pair(i + 1) ? exp2_poly2(xb) : make_float2(fast_exp2(xb.x), fast_exp2(xb.y));
+                        sum_a = __fadd2_rn(sum_a, pa);
+                        sum_b = __fadd2_rn(sum_b, pb);
+                        pk[i] = float2_to_bf16x2(pa.x, pa.y);
+                        pk[i + 1] = float2_to_bf16x2(pb.x, pb.y);
+                    }
+                    tmem_st16(tS + buf * 64 + ch * 16, pk);
+                }
+                l += (sum_a.x + sum_a.y) + (sum_b.x + sum_b.y);
+                if ((warp & 3) == 0 && lane == 0) TL_STAMP(w, u, 4);
+                tc_wait_st();
+                tc_fence_before();
+                mbar_arrive(&p_full[w * 2 + buf]);
+                if ((warp & 3) == 0 && lane == 0) TL_STAMP(w, u, 5);
+            }
+            if (!ok) break;
+            if (w == 0) TL_ITEM(j, 1, tl_globaltimer());
+
+            // ---- epilogue: O / l -> bf16 into the (now idle) shared-memory tile of Q_w in the swizzled
+            // layout of the output tensor map, then one TMA store per 64-column half: 16-byte shared
+            // stores instead of row-strided global stores, and rows past N are clipped by the hardware.
+            if (!__all_sync(kFullMask, mbar_wait(&o_done[w], (uint32_t)na & 1u, p.status, kToOFull))) {
                 ok = false;
                 break;
             }
             tc_fence_after();
-            if ((warp & 3) == 0 && lane == 0) TL_STAMP(w, u, 1);
-
-            uint32_t s[64];
             {
-                uint32_t(&s0)[32] = *reinterpret_cast<uint32_t(*)[32]>(&s[0]);
-                uint32_t(&s1)[32] = *reinterpret_cast<uint32_t(*)[32]>(&s[32]);
-                tmem_ld32(tS + buf * 64, s0);
-                tmem_ld32(tS + buf * 64 + 32, s1);
-                tc_wait_ld();
-            }
-            if ((warp & 3) == 0 && lane == 0) TL_STAMP(w, u, 2);
-
-            // ---- masks: keys beyond kv_hi, causal diagonal, keep flags
-            const int col0 = u * 64;
-            int lim = kv_hi - 1 - col0;                       // last visible column in this step
-            if (kCausal) lim = min(lim, row + q_off - col0);
-            if (lim < 63) {
+                // A masked score costs the polynomial path 2^-125 instead of 0, so a row counts as
+                // empty when it never saw a visible score, not when its sum is exactly 0.
+                const bool valid = seen && (l > 0.f);
+                const float inv = valid ? 1.f / l : 0.f;
+                uint8_t* stage = sQ + w * TILE + row_in_tile * 128;  // every score MMA that read Q_w has retired
 #pragma unroll
-                for (int i = 0; i < 64; ++i)
-                    if (i > lim) s[i] = 0xff800000u;  // -inf
-            }
-            if (kKeep) {  // Mask::Padding keep flags (mask.rs:44); every thread reads the same bytes
-#pragma unroll
-                for (int i = 0; i < 64; ++i)
-                    if (col0 + i < Nkv && __ldg(keep + col0 + i) == 0) s[i] = 0xff800000u;
-            }
-
-            // ---- row max (three-input max halves the instruction count)
-            float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
-#pragma unroll
-            for (int i = 0; i < 64; i += 8) {
-                mx0 = max3(mx0, __uint_as_float(s[i]), __uint_as_float(s[i + 1]));
-                mx1 = max3(mx1, __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
-                mx2 = max3(mx2, __uint_as_float(s[i + 4]), __uint_as_float(s[i + 5]));
-                mx3 = max3(mx3, __uint_as_float(s[i + 6]), __uint_as_float(s[i + 7]));
-            }
-            const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
-
-            // ---- lazy rescale: move the reference max only when it would grow by > 2^8
-            if (u == 0) {
-                m_ref = mx;
-            } else {
-                const bool need = (mx > m_ref) && ((mx - m_ref) * c > 8.0f || m_ref == -INFINITY);
-                if (__any_sync(kFullMask, need)) {
-                    // O must be at rest: the PV of the previous step has to be complete.
-                    if (!__all_sync(kFullMask, mbar_wait(&o_full[w], (uint32_t)(u - 1) & 1u, p.status, kToOFull))) {
-                        ok = false;
-                        break;
+                for (int ch = 0; ch < D / 32; ++ch) {
+                    uint32_t o[32];
+                    tmem_ld32(tO + ch * 32, o);
+                    tc_wait_ld();
+                    if (ch == D / 32 - 1) {  // O_w is in registers: the next item's first PV may overwrite it
+                        tc_fence_before();
+                        mbar_arrive(&o_free[w]);
                     }
-                    tc_fence_after();
-                    const float m_new = fmaxf(m_ref, mx);
-                    const float alpha = (m_new == -INFINITY) ? 1.f : fast_exp2((m_ref - m_new) * c);
-                    l *= alpha;
-                    m_ref = m_new;
 #pragma unroll
-                    for (int ch = 0; ch < D / 32; ++ch) {
-                        uint32_t o[32];
-                        tmem_ld32(tO + ch * 32, o);
-                        tc_wait_ld();
+                    for (int v4 = 0; v4 < 4; ++v4) {
+                        uint4 pack;
+                        uint32_t* pw = reinterpret_cast<uint32_t*>(&pack);
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                        tmem_st32(tO + ch * 32, o);
+                        for (int i = 0; i < 4; ++i) {
+                            const float a = __uint_as_float(o[v4 * 8 + 2 * i]) * inv;
+                            const float bb = __uint_as_float(o[v4 * 8 + 2 * i + 1]) * inv;
+                            pw[i] = valid ? float2_to_bf16x2(a, bb) : 0x7fc07fc0u;
+                        }
+                        const int cc = ch * 4 + v4;  // 16-byte chunk of the row: sub-tile cc/8, chunk cc%8
+                        *reinterpret_cast<uint4*>(stage + (cc / 8) * SUB + (((cc % 8) ^ (row_in_tile & 7)) << 4)) = pack;
                     }
-                    tc_wait_st();
+                }
+                if (p.lse && row < N)
+                    p.lse[(int64_t)bh * N + row] =
+                        valid ? (m_ref * c + fast_log2(l)) * kLn2 : (seen ? NAN : -INFINITY);
+                fence_proxy_async();  // generic-proxy writes above -> visible to the TMA (async proxy) read
+                mbar_arrive(&stage_full[w]);
+            }
+            if (row_in_tile == 0) {
+                if (!mbar_wait(&stage_full[w], (uint32_t)na & 1u, p.status, kToStage)) {
+                    ok = false;
+                } else {
+#pragma unroll
+                    for (int s = 0; s < C::NSUB; ++s)
+                        tma_store_3d(&tm_o, sQ + w * TILE + s * SUB, s * 64, it.q0 + w * 128, bh);
+                    tma_store_commit_and_wait_read();  // the staged tile has been read: the next Q may land
+                    mbar_arrive(&q_empty[w]);
                 }
             }
-
-            if ((warp & 3) == 0 && lane == 0) TL_STAMP(w, u, 3);
-            // ---- P = exp2(s*c - m*c), row sum, bf16 pack, store to TMEM over S (packed f32x2 math)
-            const float mc = (m_ref == -INFINITY) ? 0.f : m_ref * c;
-            const float2 c2 = make_float2(c, c), nmc2 = make_float2(-mc, -mc);
-            float2 sum_a = make_float2(0.f, 0.f), sum_b = make_float2(0.f, 0.f);
-#pragma unroll
-            for (int ch = 0; ch < 2; ++ch) {
-                uint32_t pk[16];
-#pragma unroll
-                for (int i = 0; i < 16; i += 2) {
-                    const float2 xa = __ffma2_rn(
-                        make_float2(__uint_as_float(s[ch * 32 + 2 * i]), __uint_as_float(s[ch * 32 + 2 * i + 1])), c2, nmc2);
-                    const float2 xb = __ffma2_rn(
-                        make_float2(__uint_as_float(s[ch * 32 + 2 * i + 2]), __uint_as_float(s[ch * 32 + 2 * i + 3])), c2,
-                        nmc2);
-                    const float2 pa = make_float2(fast_exp2(xa.x), fast_exp2(xa.y));
-                    const float2 pb = make_float2(fast_exp2(xb.x), fast_exp2(xb.y));
-                    sum_a = __fadd2_rn(sum_a, pa);
-                    sum_b = __fadd2_rn(sum_b, pb);
-                    pk[i] = float2_to_bf16x2(pa.x, pa.y);
-                    pk[i + 1] = float2_to_bf16x2(pb.x, pb.y);
-                }
-                tmem_st16(tS + buf * 64 + ch * 16, pk);
-            }
-            l += (sum_a.x + sum_a.y) + (sum_b.x + sum_b.y);
-            if ((warp & 3) == 0 && lane == 0) TL_STAMP(w, u, 4);
-            tc_wait_st();
-            if ((warp & 3) == 0 && lane == 0) TL_STAMP(w, u, 5);
-            tc_fence_before();
-            mbar_arrive(&p_full[w * 2 + buf]);
-        }
-
-        if (n_iter == 0) {  // this tile sees no key (its rows lie before the first visible position)
-            if (row < N) {
-                uint4* dst = reinterpret_cast<uint4*>(p.out + ((int64_t)bh * N + row) * D);
-#pragma unroll
-                for (int i = 0; i < D / 8; ++i) dst[i] = make_uint4(0x7fc07fc0u, 0x7fc07fc0u, 0x7fc07fc0u, 0x7fc07fc0u);
-                if (p.lse) p.lse[(int64_t)bh * N + row] = -INFINITY;
-            }
-            ok = false;
-        }
-        // ---- epilogue: O / l -> bf16 into the (now idle) shared-memory tile of Q_w in the swizzled
-        // layout of the output tensor map, then one TMA store per 64-column half: 16-byte shared stores
-        // instead of row-strided global stores, and rows past N are clipped by the hardware.
-        // (o_full cannot be used for the wait: up to two PV steps may still be in flight, which a
-        // parity wait cannot tell from none.)
-        bool stored = false;
-        if (ok && __all_sync(kFullMask, mbar_wait(&o_done[w], 0, p.status, kToOFull))) {
-            tc_fence_after();
-            const bool valid = (l > 0.f);
-            const float inv = valid ? 1.f / l : 0.f;
-            uint8_t* stage = sQ + w * TILE + row_in_tile * 128;  // every score MMA that read Q_w has retired
-#pragma unroll
-            for (int ch = 0; ch < D / 32; ++ch) {
-                uint32_t o[32];
-                tmem_ld32(tO + ch * 32, o);
-                tc_wait_ld();
-#pragma unroll
-                for (int v4 = 0; v4 < 4; ++v4) {
-                    uint4 pack;
-                    uint32_t* pw = reinterpret_cast<uint32_t*>(&pack);
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const float a = __uint_as_float(o[v4 * 8 + 2 * i]) * inv;
-                        const float bb = __uint_as_float(o[v4 * 8 + 2 * i + 1]) * inv;
-                        pw[i] = valid ? float2_to_bf16x2(a, bb) : 0x7fc07fc0u;
-                    }
-                    const int cc = ch * 4 + v4;  // 16-byte chunk of the row: sub-tile cc/8, chunk cc%8
-                    *reinterpret_cast<uint4*>(stage + (cc / 8) * SUB + (((cc % 8) ^ (row_in_tile & 7)) << 4)) = pack;
-                }
-            }
-            if (p.lse && row < N)
-                p.lse[(int64_t)bh * N + row] =
-                    valid ? (m_ref * c + fast_log2(l)) * kLn2 : (l == 0.f ? -INFINITY : NAN);
-            fence_proxy_async();  // generic-proxy writes above -> visible to the TMA (async proxy) read
-            stored = true;
-        }
-        named_barrier_sync(1 + w, 128);  // all four warps of the tile, whatever happened above
-        if (row_in_tile == 0 && stored) {
-#pragma unroll
-            for (int s = 0; s < C::NSUB; ++s)
-                tma_store_3d(&tm_o, sQ + w * TILE + s * SUB, s * 64, q0 + w * 128, bh);
-            tma_store_commit_and_wait();  // the tile must be read out before the CTA gives up its shared memory
+            ok = __all_sync(kFullMask, ok);
+            if (w == 0) TL_ITEM(j, 2, tl_globaltimer());
+            if (w == 0) TL_ITEM(j, 3, (long long)(it.U0 + it.U1));
+            ++na;
+            cs0 += (n_iter + 1) / 2;
+            cs1 += n_iter / 2;
+            co += n_iter;
         }
     }
 
@@ -530,6 +716,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         tc_fence_after();
         tmem_dealloc(tmem_base, C::TMEM_COLS);
     }
+    TL_CTA_END(n_items_done);
 }
 
 // ---------------------------------------------------------------------- host side
@@ -605,8 +792,29 @@ cudaError_t launch_prefill_tc(const void* q, const void* k, const void* v, void*
 #ifdef RT_TC_TIMELINE
     p.timeline = g_tc_timeline;
 #endif
-    const int64_t n_ctas = bh * ((seq + 255) / 256);
-    if (n_ctas > 0x7fffffff) return cudaErrorInvalidValue;
+    // Schedule (tc_item).  A causal launch without per-batch lengths has a known cost per item, so
+    // it runs one CTA per SM over a static list in which the 256-row blocks of a head are paired
+    // heavy + light: every CTA gets the same work and the per-item set-up overlaps the previous
+    // item.  Other launches (uniform items, or lengths only the device knows) use one CTA per item
+    // and leave the balancing to the hardware scheduler.  RT_ATTN_PREFILL_SCHED=persistent|percta
+    // overrides the choice.
+    const int64_t n_qb = (seq + 255) / 256;
+    const int64_t n_items = bh * n_qb;
+    if (n_items > 0x3fffffff) return cudaErrorInvalidValue;
+    int dev = 0, n_sm = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return e;
+    p.n_qb = (int)n_qb;
+    bool persistent = causal && kv_lens == nullptr && n_items >= 2 * (int64_t)n_sm;
+    if (const char* s = getenv("RT_ATTN_PREFILL_SCHED")) {
+        if (!strcmp(s, "persistent")) persistent = true;
+        if (!strcmp(s, "percta")) persistent = false;
+    }
+    p.paired = (persistent && n_items >= 2 * (int64_t)n_sm) ? 1 : 0;
+    p.slots_per_head = p.paired ? (int)((n_qb + 1) / 2) : (int)n_qb;
+    p.n_slots = (int)(bh * p.slots_per_head);
+    const int64_t n_ctas = (persistent && p.n_slots > n_sm) ? n_sm : p.n_slots;
     const bool keep = key_keep != nullptr;
 #define RT_TC_DISPATCH(DD)                                                                         \
     if (causal) {                                                                                  \

@@ -54,10 +54,27 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // Bounded wait: gives up after ~2^31 SM clocks (about a second), records `code` in the
 // device status word and returns false.  Callers then skip their remaining work and fall
 // through to the common teardown so the context stays usable.
+// try_wait with a suspend-time hint: the thread may sleep in hardware for up to `ns` nanoseconds
+// (it is woken when the phase completes), which keeps a polling warp out of the issue slots.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(ns)
+        : "memory");
+    return ok != 0;
+}
+
+#ifndef RT_WAIT_HINT_NS
+#define RT_WAIT_HINT_NS 0
+#endif
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
-    while (!mbar_try_wait(bar, parity)) {
+    while (!(RT_WAIT_HINT_NS ? mbar_try_wait_hint(bar, parity, RT_WAIT_HINT_NS) : mbar_try_wait(bar, parity))) {
         if (clock64() - t0 > (1ll << 31)) {
             report_timeout(status, code);
             return false;
@@ -91,6 +108,12 @@ __device__ __forceinline__ void tma_store_3d(const CUtensorMap* m, const void* s
 __device__ __forceinline__ void tma_store_commit_and_wait() {
     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
     asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+}
+
+// Waits only until the staged source has been read; the global writes complete on their own.
+__device__ __forceinline__ void tma_store_commit_and_wait_read() {
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
 }
 
 // ---------------------------------------------------------------- tcgen05: TMEM management
