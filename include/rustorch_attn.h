@@ -140,6 +140,26 @@ int rt_attn_prefill_gqa_bf16(const void* q, const void* k, const void* v, void* 
                              int64_t keep_batch_stride, float scale, void* stream);
 
 /*
+ * rt_attn_prefill_gqa_bf16 on strided views.  The reference's attention modules keep activations
+ * as [B, T, H*hd] and pay a full-tensor transpose to [B, H, T, hd] for each of Q, K and V before
+ * the kernel and one back after it (crates/rustorch-nn/src/attention.rs:468-485 and 499-543,
+ * gqa.rs:151-168).  Here the layout is described to the TMA unit instead: each tensor is given by
+ * the element strides {batch, head, row} of its [B, H, N, D] view, the head dim being contiguous.
+ * A [B, T, H*hd] activation is the view with strides {T*H*hd, hd, H*hd}; a contiguous
+ * [B, H, N, D] tensor has {H*N*D, N*D, D}.
+ *   q_strides, k_strides, v_strides, out_strides : HOST pointers to 3 int64 each; every stride
+ *       a positive multiple of 8 elements (16 bytes), row stride >= D.
+ *   lse stays a contiguous f32 [B,Hq,seq_q]; all other arguments as in rt_attn_prefill_gqa_bf16.
+ */
+int rt_attn_prefill_strided_bf16(const void* q, const void* k, const void* v, void* out, float* lse,
+                                 int64_t batch, int64_t heads_q, int64_t heads_kv, int64_t seq_q,
+                                 int64_t seq_kv, int dim, const int64_t* q_strides,
+                                 const int64_t* k_strides, const int64_t* v_strides,
+                                 const int64_t* out_strides, int mask_flags, const int32_t* kv_lens,
+                                 const int32_t* q_offsets, const uint8_t* key_keep,
+                                 int64_t keep_batch_stride, float scale, void* stream);
+
+/*
  * The same operator on f32 device tensors with f32 arithmetic on CUDA cores (any D in
  * [1,256]); grouped KV heads and seq_q != seq_kv are allowed so that it also serves
  * gqa_forward_f32's prefill and cross-attention branches (gqa.rs:151-210).
@@ -151,6 +171,39 @@ int rt_attn_prefill_f32(const float* q, const float* k, const float* v, float* o
                         int64_t seq_kv, int dim, int mask_flags, const int32_t* kv_lens,
                         const int32_t* q_offsets, const uint8_t* key_keep, int64_t keep_batch_stride,
                         float scale, void* stream);
+
+/*
+ * Flash-attention backward on f32 device tensors, CUDA cores: (dQ, dK, dV) of
+ * O = softmax(scale * Q K^T [+ causal mask]) V for an upstream gradient dO.  Replaces
+ * flash_backward (crates/rustorch-attention/src/cpu_backward.rs:46-185), which rebuilds the whole
+ * N x N probability matrix per (batch, head); this entry consumes what the forward pass saved
+ * instead (the module header of cpu_backward.rs, :29-34, names that as the GPU recomputation path):
+ *   q, k, v, out, d_out, dq, dk, dv : f32 [B,H,N,D], D in [1,256];
+ *   lse : f32 [B,H,N], the LSE output of rt_attn_prefill_f32 on the same q, k, mask and scale;
+ *   mask_flags : RT_MASK_NONE (the reference's case) or RT_MASK_CAUSAL;
+ *   workspace  : device scratch of rt_attn_backward_workspace_bytes() bytes (holds dO . O per row).
+ * The outputs are fully overwritten (the reference zeroes them first, :78-87).  N = 0 is a no-op
+ * (:74-76).  Deterministic: no atomics, fixed summation order.
+ */
+size_t rt_attn_backward_workspace_bytes(int64_t batch, int64_t heads, int64_t seq);
+int rt_attn_backward_f32(const float* q, const float* k, const float* v, const float* out,
+                         const float* d_out, const float* lse, float* dq, float* dk, float* dv,
+                         int64_t batch, int64_t heads, int64_t seq, int dim, int mask_flags,
+                         float scale, void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Host-slice mirror of
+ *   flash_backward(shape:&AttentionShape, q, k, v, do_:&[f32], dq, dk, dv:&mut [f32])
+ * (cpu_backward.rs:46-55).  Lengths are validated in the reference's order: q, k, v, do give
+ * RT_ERR_BUFFER_SHAPE (:57-65), dq, dk, dv give RT_ERR_OUTPUT_SHAPE (:66-73).  Runs the f32 forward
+ * for O and LSE, then rt_attn_backward_f32; copies back, blocks.  mask_kind: RT_MASKKIND_NONE
+ * (the reference) or RT_MASKKIND_CAUSAL.
+ */
+int rt_flash_backward_f32_host(const float* q, size_t q_len, const float* k, size_t k_len,
+                               const float* v, size_t v_len, const float* d_out, size_t d_out_len,
+                               float* dq, size_t dq_len, float* dk, size_t dk_len, float* dv,
+                               size_t dv_len, int64_t batch, int64_t heads, int64_t seq,
+                               int64_t dim, int mask_kind);
 
 /*
  * Host-slice mirror of

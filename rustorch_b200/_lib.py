@@ -48,9 +48,18 @@ PROTOTYPES = {
     "rt_attn_prefill_gqa_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
                                          c_int64, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int64,
                                          c_float, c_void_p]),
+    "rt_attn_prefill_strided_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
+                                             c_int64, c_int64, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                             c_int, c_void_p, c_void_p, c_void_p, c_int64, c_float, c_void_p]),
     "rt_attn_prefill_f32": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
                                     c_int64, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int64, c_float,
                                     c_void_p]),
+    "rt_attn_backward_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64]),
+    "rt_attn_backward_f32": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                     c_void_p, c_int64, c_int64, c_int64, c_int, c_int, c_float, c_void_p, c_size_t,
+                                     c_void_p]),
+    "rt_flash_backward_f32_host": (c_int, [_fp, c_size_t, _fp, c_size_t, _fp, c_size_t, _fp, c_size_t, _fp, c_size_t,
+                                           _fp, c_size_t, _fp, c_size_t, c_int64, c_int64, c_int64, c_int64, c_int]),
     "rt_flash_forward_f32_host": (c_int, [_fp, c_size_t, _fp, c_size_t, _fp, c_size_t, _fp, c_size_t, c_int64,
                                           c_int64, c_int64, c_int64, c_int, _u8p, c_size_t, c_int]),
     "rt_attn_prefill_bf16_host": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,

@@ -150,10 +150,66 @@ def flash_forward_masked(shape: AttentionShape, q, k, v, mask: Mask, out, precis
     _lib.check(rc, "rt_flash_forward_f32_host")
 
 
+def flash_backward(shape: AttentionShape, q, k, v, do_, dq, dk, dv, causal: bool = False) -> None:
+    """cpu_backward.rs:46-185 on the GPU: host numpy f32 slices in, (dq, dk, dv) overwritten.
+
+    Validation order and errors follow the reference (:57-73): q, k, v, do -> BufferShapeMismatch,
+    then dq/dk/dv -> OutputShapeMismatch(expected, largest length); seq == 0 is a no-op (:74-76).
+    ``causal=True`` is an extension (the gradient of flash_forward_masked with Mask::Causal).
+    """
+    expected = shape.buffer_len()
+    for which, buf in (("q", q), ("k", k), ("v", v), ("do", do_)):
+        if buf.size != expected:
+            raise BufferShapeMismatch(which, expected, buf.size)
+    if dq.size != expected or dk.size != expected or dv.size != expected:
+        raise OutputShapeMismatch(expected, max(dq.size, dk.size, dv.size))
+    if shape.seq == 0 or expected == 0:
+        return
+    rc = _lib.lib().rt_flash_backward_f32_host(_f32(q, "q"), q.size, _f32(k, "k"), k.size, _f32(v, "v"), v.size,
+                                               _f32(do_, "do"), do_.size, _f32(dq, "dq"), dq.size, _f32(dk, "dk"),
+                                               dk.size, _f32(dv, "dv"), dv.size, shape.batch, shape.heads, shape.seq,
+                                               shape.dim, Mask.CAUSAL if causal else Mask.NONE)
+    _lib.check(rc, "rt_flash_backward_f32_host")
+
+
 # ---------------------------------------------------------------- device-resident entry (torch tensors)
 def _stream_ptr():
     import torch
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _dense_view(t) -> bool:
+    """True if t is a permutation of a dense tensor (every element addressed once, no gaps)."""
+    if t.numel() == 0:
+        return True
+    expect = 1
+    for size, stride in sorted(zip(t.shape, t.stride()), key=lambda x: x[1]):
+        if size == 1:
+            continue
+        if stride != expect:
+            return False
+        expect *= size
+    return True
+
+
+def mha_prefill_bf16(q, k, v, n_heads: int, n_kv_heads: Optional[int] = None, causal: bool = False, **kw):
+    """Attention on activations in the layout the reference's modules keep them in: q [B,T,Hq*hd],
+    k, v [B,S,Hkv*hd] bf16 CUDA tensors (crates/rustorch-nn/src/attention.rs:468-485 transposes them
+    to [B,H,T,hd] before the kernel and :499-543 transposes the result back; gqa.rs:151-168 also
+    repeats the KV heads).  The transposes and the repeat are folded into the TMA descriptors:
+    returns (out [B,T,Hq*hd], lse [B,Hq,T]) without any full-tensor copy.
+    """
+    n_kv_heads = n_heads if n_kv_heads is None else n_kv_heads
+    B, T, E = q.shape
+    S = k.shape[1]
+    hd = E // n_heads
+    if hd * n_heads != E or k.shape[2] != n_kv_heads * hd or v.shape != k.shape:
+        raise BufferShapeMismatch("q/k/v", E, k.shape[2])
+    qv = q.view(B, T, n_heads, hd).permute(0, 2, 1, 3)
+    kv = k.view(B, S, n_kv_heads, hd).permute(0, 2, 1, 3)
+    vv = v.view(B, S, n_kv_heads, hd).permute(0, 2, 1, 3)
+    out, lse = prefill_bf16(qv, kv, vv, causal=causal, **kw)
+    return out.permute(0, 2, 1, 3).reshape(B, T, E), lse
 
 
 def prefill_bf16(q, k, v, causal: bool = False, kv_lens=None, key_keep=None, scale: Optional[float] = None,
@@ -164,19 +220,28 @@ def prefill_bf16(q, k, v, causal: bool = False, kv_lens=None, key_keep=None, sca
     shape as q).  kv_lens: optional int32 CUDA [B] visible keys; q_offsets: optional int32 CUDA [B],
     causal position of query row 0 (a prompt chunk against a cache); key_keep: optional uint8/bool
     CUDA [Nkv] or [B,Nkv].  Returns (out bf16 [B,Hq,Nq,D], lse f32 [B,Hq,Nq] or None).  Enqueues on
-    the current stream.  Calls ``rt_attn_prefill_bf16`` for self-attention shapes and
-    ``rt_attn_prefill_gqa_bf16`` otherwise.
+    the current stream.  Calls ``rt_attn_prefill_bf16`` for self-attention shapes,
+    ``rt_attn_prefill_gqa_bf16`` for other contiguous shapes, and ``rt_attn_prefill_strided_bf16``
+    when any of q, k, v, out is a strided view whose last dim is contiguous (e.g. a
+    ``[B,T,H,hd]`` activation permuted to ``[B,H,T,hd]``): no transpose copy is made.
     """
     import torch
     for name, t in (("q", q), ("k", k), ("v", v)):
-        if not (t.is_cuda and t.dtype == torch.bfloat16 and t.is_contiguous() and t.dim() == 4):
-            raise TypeError(f"{name} must be a contiguous 4-D bfloat16 CUDA tensor")
+        if not (t.is_cuda and t.dtype == torch.bfloat16 and t.dim() == 4):
+            raise TypeError(f"{name} must be a 4-D bfloat16 CUDA tensor")
     B, H, N, D = q.shape
     if v.shape != k.shape or k.shape[0] != B or k.shape[3] != D:
         raise BufferShapeMismatch("k/v", k.numel(), v.numel())
     Hkv, Nkv = k.shape[1], k.shape[2]
     if out is None:
-        out = torch.empty_like(q)
+        # the output takes q's layout, so a permuted activation view gets a result in the same layout
+        out = torch.empty_strided(q.shape, q.stride(), dtype=q.dtype, device=q.device) if _dense_view(q) \
+            else torch.empty_like(q, memory_format=torch.contiguous_format)
+    strided = not all(t.is_contiguous() for t in (q, k, v, out))
+    if strided:
+        for name, t in (("q", q), ("k", k), ("v", v), ("out", out)):
+            if t.numel() and t.stride(3) != 1:
+                raise TypeError(f"{name}: the head dim must be contiguous")
     if lse is None and return_lse:
         lse = torch.empty((B, H, N), dtype=torch.float32, device=q.device)
     keep_ptr, keep_stride = None, 0
@@ -193,7 +258,15 @@ def prefill_bf16(q, k, v, causal: bool = False, kv_lens=None, key_keep=None, sca
     flags = _lib.RT_MASK_CAUSAL if causal else _lib.RT_MASK_NONE
     sc = -1.0 if scale is None else float(scale)
     lse_ptr = lse.data_ptr() if lse is not None else None
-    if Hkv == H and Nkv == N and q_offsets is None:
+    if strided:
+        import ctypes
+        arrs = [(ctypes.c_int64 * 3)(*t.stride()[:3]) for t in (q, k, v, out)]
+        rc = _lib.lib().rt_attn_prefill_strided_bf16(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse_ptr,
+                                                     B, H, Hkv, N, Nkv, D, arrs[0], arrs[1], arrs[2], arrs[3], flags,
+                                                     lens_ptr, q_offsets.data_ptr() if q_offsets is not None else None,
+                                                     keep_ptr, keep_stride, sc, _stream_ptr())
+        where = "rt_attn_prefill_strided_bf16"
+    elif Hkv == H and Nkv == N and q_offsets is None:
         rc = _lib.lib().rt_attn_prefill_bf16(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse_ptr, B, H,
                                              N, D, flags, lens_ptr, keep_ptr, keep_stride, sc, _stream_ptr())
         where = "rt_attn_prefill_bf16"
@@ -231,3 +304,26 @@ def prefill_f32(q, k, v, causal: bool = False, kv_lens=None, key_keep=None, scal
         raise ZeroDim()
     _lib.check(rc, "rt_attn_prefill_f32")
     return out, lse
+
+
+def backward_f32(q, k, v, out, d_out, lse, causal: bool = False, scale: Optional[float] = None):
+    """(dq, dk, dv) on f32 CUDA tensors [B,H,N,D] via ``rt_attn_backward_f32``; ``out`` and ``lse`` are
+    the results of ``prefill_f32`` on the same q, k, v, mask and scale."""
+    import torch
+    B, H, N, D = q.shape
+    for name, t in (("q", q), ("k", k), ("v", v), ("out", out), ("d_out", d_out)):
+        if not (t.is_cuda and t.dtype == torch.float32 and t.is_contiguous() and tuple(t.shape) == (B, H, N, D)):
+            raise TypeError(f"{name} must be a contiguous float32 CUDA tensor of shape {(B, H, N, D)}")
+    if not (lse.is_cuda and lse.dtype == torch.float32 and lse.is_contiguous() and tuple(lse.shape) == (B, H, N)):
+        raise TypeError("lse must be a contiguous float32 CUDA tensor [B,H,N]")
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    need = _lib.lib().rt_attn_backward_workspace_bytes(B, H, N)
+    ws = torch.empty((max(need, 4) // 4,), dtype=torch.float32, device=q.device)
+    rc = _lib.lib().rt_attn_backward_f32(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), d_out.data_ptr(),
+                                         lse.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), B, H, N, D,
+                                         _lib.RT_MASK_CAUSAL if causal else _lib.RT_MASK_NONE,
+                                         -1.0 if scale is None else float(scale), ws.data_ptr(), need, _stream_ptr())
+    if rc == _lib.RT_ERR_ZERO_DIM:
+        raise ZeroDim()
+    _lib.check(rc, "rt_attn_backward_f32")
+    return dq, dk, dv

@@ -120,10 +120,13 @@ int rt_attn_device_status(int* status) {
 
 // ------------------------------------------------------------------------------ prefill
 
-int rt_attn_prefill_gqa_bf16(const void* q, const void* k, const void* v, void* out, float* lse, int64_t batch,
-                             int64_t heads_q, int64_t heads_kv, int64_t seq_q, int64_t seq_kv, int dim, int mask_flags,
-                             const int32_t* kv_lens, const int32_t* q_offsets, const uint8_t* key_keep,
-                             int64_t keep_batch_stride, float scale, void* stream) {
+// Shared body of the bf16 prefill entries; strides are in elements.
+static int prefill_bf16_common(const void* q, const void* k, const void* v, void* out, float* lse, int64_t batch,
+                               int64_t heads_q, int64_t heads_kv, int64_t seq_q, int64_t seq_kv, int dim,
+                               const rt::TensorStrides& sq, const rt::TensorStrides& sk, const rt::TensorStrides& sv,
+                               const rt::TensorStrides& so, int mask_flags, const int32_t* kv_lens,
+                               const int32_t* q_offsets, const uint8_t* key_keep, int64_t keep_batch_stride,
+                               float scale, void* stream) {
     if (dim == 0) return RT_ERR_ZERO_DIM;
     if (batch < 0 || heads_q < 0 || heads_kv < 0 || seq_q < 0 || seq_kv < 0 || dim < 0 || keep_batch_stride < 0)
         return RT_ERR_BAD_LENGTH;
@@ -134,10 +137,42 @@ int rt_attn_prefill_gqa_bf16(const void* q, const void* k, const void* v, void* 
     if (seq_q > (1 << 30) || seq_kv > (1 << 30) || batch * heads_q > (1 << 30)) return RT_ERR_UNSUPPORTED;
     if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(out)) return RT_ERR_ALIGNMENT;
     if (mask_flags & ~RT_MASK_CAUSAL) return RT_ERR_UNSUPPORTED;
-    RT_CUDA(rt::launch_prefill_tc(q, k, v, out, lse, batch, heads_q, heads_kv, seq_q, seq_kv, dim,
+    for (const rt::TensorStrides* s : {&sq, &sk, &sv, &so}) {
+        // TMA strides: positive multiples of 16 bytes below 2^40; a row must hold the head dim
+        if (s->batch <= 0 || s->head <= 0 || s->row < dim) return RT_ERR_BAD_LENGTH;
+        if ((s->batch | s->head | s->row) & 7) return RT_ERR_ALIGNMENT;
+        if (s->batch >= (1ll << 39) || s->head >= (1ll << 39) || s->row >= (1ll << 39)) return RT_ERR_UNSUPPORTED;
+    }
+    RT_CUDA(rt::launch_prefill_tc(q, k, v, out, lse, batch, heads_q, heads_kv, seq_q, seq_kv, dim, sq, sk, sv, so,
                                   mask_flags & RT_MASK_CAUSAL, kv_lens, q_offsets, key_keep, keep_batch_stride,
                                   default_scale(scale, dim), as_stream(stream)));
     return RT_OK;
+}
+
+int rt_attn_prefill_gqa_bf16(const void* q, const void* k, const void* v, void* out, float* lse, int64_t batch,
+                             int64_t heads_q, int64_t heads_kv, int64_t seq_q, int64_t seq_kv, int dim, int mask_flags,
+                             const int32_t* kv_lens, const int32_t* q_offsets, const uint8_t* key_keep,
+                             int64_t keep_batch_stride, float scale, void* stream) {
+    const int d = dim > 0 ? dim : 1;
+    const rt::TensorStrides sq = rt::TensorStrides::contiguous(heads_q > 0 ? heads_q : 1, seq_q > 0 ? seq_q : 1, d);
+    const rt::TensorStrides sk = rt::TensorStrides::contiguous(heads_kv > 0 ? heads_kv : 1, seq_kv > 0 ? seq_kv : 1, d);
+    return prefill_bf16_common(q, k, v, out, lse, batch, heads_q, heads_kv, seq_q, seq_kv, dim, sq, sk, sk, sq,
+                               mask_flags, kv_lens, q_offsets, key_keep, keep_batch_stride, scale, stream);
+}
+
+int rt_attn_prefill_strided_bf16(const void* q, const void* k, const void* v, void* out, float* lse, int64_t batch,
+                                 int64_t heads_q, int64_t heads_kv, int64_t seq_q, int64_t seq_kv, int dim,
+                                 const int64_t* q_strides, const int64_t* k_strides, const int64_t* v_strides,
+                                 const int64_t* out_strides, int mask_flags, const int32_t* kv_lens,
+                                 const int32_t* q_offsets, const uint8_t* key_keep, int64_t keep_batch_stride,
+                                 float scale, void* stream) {
+    if (!q_strides || !k_strides || !v_strides || !out_strides) return RT_ERR_NULL_POINTER;
+    const rt::TensorStrides sq{q_strides[0], q_strides[1], q_strides[2]};
+    const rt::TensorStrides sk{k_strides[0], k_strides[1], k_strides[2]};
+    const rt::TensorStrides sv{v_strides[0], v_strides[1], v_strides[2]};
+    const rt::TensorStrides so{out_strides[0], out_strides[1], out_strides[2]};
+    return prefill_bf16_common(q, k, v, out, lse, batch, heads_q, heads_kv, seq_q, seq_kv, dim, sq, sk, sv, so,
+                               mask_flags, kv_lens, q_offsets, key_keep, keep_batch_stride, scale, stream);
 }
 
 int rt_attn_prefill_bf16(const void* q, const void* k, const void* v, void* out, float* lse, int64_t batch,
@@ -330,6 +365,80 @@ int rt_attn_prefill_bf16_host(const void* q, const void* k, const void* v, void*
     }
     RT_CUDA(cudaStreamSynchronize(s_out));
     RT_CUDA(cudaStreamSynchronize(s_comp));
+    return RT_OK;
+}
+
+// ------------------------------------------------------------------------------ backward
+
+size_t rt_attn_backward_workspace_bytes(int64_t batch, int64_t heads, int64_t seq) {
+    if (batch <= 0 || heads <= 0 || seq <= 0) return 0;
+    return (size_t)batch * (size_t)heads * (size_t)seq * sizeof(float);
+}
+
+int rt_attn_backward_f32(const float* q, const float* k, const float* v, const float* out, const float* d_out,
+                         const float* lse, float* dq, float* dk, float* dv, int64_t batch, int64_t heads, int64_t seq,
+                         int dim, int mask_flags, float scale, void* workspace, size_t workspace_bytes, void* stream) {
+    if (dim == 0) return RT_ERR_ZERO_DIM;
+    if (batch < 0 || heads < 0 || seq < 0 || dim < 0) return RT_ERR_BAD_LENGTH;
+    if (batch == 0 || heads == 0 || seq == 0) return RT_OK;  // cpu_backward.rs:74-76
+    if (!q || !k || !v || !out || !d_out || !lse || !dq || !dk || !dv) return RT_ERR_NULL_POINTER;
+    if (dim > 256 || batch * heads > 65535) return RT_ERR_UNSUPPORTED;
+    if (mask_flags & ~RT_MASK_CAUSAL) return RT_ERR_UNSUPPORTED;
+    if (!workspace || workspace_bytes < rt_attn_backward_workspace_bytes(batch, heads, seq)) return RT_ERR_WORKSPACE;
+    RT_CUDA(rt::launch_backward_f32(q, k, v, out, d_out, lse, dq, dk, dv, static_cast<float*>(workspace), batch, heads,
+                                    seq, dim, mask_flags & RT_MASK_CAUSAL, default_scale(scale, dim),
+                                    as_stream(stream)));
+    return RT_OK;
+}
+
+int rt_flash_backward_f32_host(const float* q, size_t q_len, const float* k, size_t k_len, const float* v,
+                               size_t v_len, const float* d_out, size_t d_out_len, float* dq, size_t dq_len, float* dk,
+                               size_t dk_len, float* dv, size_t dv_len, int64_t batch, int64_t heads, int64_t seq,
+                               int64_t dim, int mask_kind) {
+    // flash_backward has no dim check of its own: with dim = 0 every length is 0 and the call is a no-op
+    if (batch < 0 || heads < 0 || seq < 0 || dim < 0) return RT_ERR_BAD_LENGTH;
+    const size_t expected = (size_t)batch * (size_t)heads * (size_t)seq * (size_t)dim;
+    // cpu_backward.rs:57-73: inputs first (q, k, v, do), then the three outputs
+    if (q_len != expected || k_len != expected || v_len != expected || d_out_len != expected)
+        return RT_ERR_BUFFER_SHAPE;
+    if (dq_len != expected || dk_len != expected || dv_len != expected) return RT_ERR_OUTPUT_SHAPE;
+    if (mask_kind != RT_MASKKIND_NONE && mask_kind != RT_MASKKIND_CAUSAL) return RT_ERR_UNSUPPORTED;
+    if (seq == 0 || expected == 0) return RT_OK;  // :74-76
+    if (!q || !k || !v || !d_out || !dq || !dk || !dv) return RT_ERR_NULL_POINTER;
+    if (dim > 256 || batch * heads > 65535) return RT_ERR_UNSUPPORTED;
+
+    const size_t bytes = expected * sizeof(float);
+    const size_t stat_bytes = rt_attn_backward_workspace_bytes(batch, heads, seq);
+    std::lock_guard<std::mutex> lock(g_staging.mu);
+    DevBuf bq(0), bk(1), bv(2), bo(3), bdo(4), blse(5), bdelta(6), bdq(7), bdk(8), bdv(9);
+    RT_CUDA(bq.alloc(bytes));
+    RT_CUDA(bk.alloc(bytes));
+    RT_CUDA(bv.alloc(bytes));
+    RT_CUDA(bo.alloc(bytes));
+    RT_CUDA(bdo.alloc(bytes));
+    RT_CUDA(blse.alloc(stat_bytes));
+    RT_CUDA(bdelta.alloc(stat_bytes));
+    RT_CUDA(bdq.alloc(bytes));
+    RT_CUDA(bdk.alloc(bytes));
+    RT_CUDA(bdv.alloc(bytes));
+    RT_CUDA(cudaMemcpy(bq.p, q, bytes, cudaMemcpyHostToDevice));
+    RT_CUDA(cudaMemcpy(bk.p, k, bytes, cudaMemcpyHostToDevice));
+    RT_CUDA(cudaMemcpy(bv.p, v, bytes, cudaMemcpyHostToDevice));
+    RT_CUDA(cudaMemcpy(bdo.p, d_out, bytes, cudaMemcpyHostToDevice));
+    const int flags = (mask_kind == RT_MASKKIND_CAUSAL) ? RT_MASK_CAUSAL : RT_MASK_NONE;
+    // the reference recomputes the probabilities from Q and K (:96-127); here the forward pass supplies
+    // O and the row statistics that the tiled backward consumes
+    int rc = rt_attn_prefill_f32(bq.as<float>(), bk.as<float>(), bv.as<float>(), bo.as<float>(), blse.as<float>(),
+                                 batch, heads, heads, seq, seq, (int)dim, flags, nullptr, nullptr, nullptr, 0, -1.f,
+                                 nullptr);
+    if (rc != RT_OK) return rc;
+    rc = rt_attn_backward_f32(bq.as<float>(), bk.as<float>(), bv.as<float>(), bo.as<float>(), bdo.as<float>(),
+                              blse.as<float>(), bdq.as<float>(), bdk.as<float>(), bdv.as<float>(), batch, heads, seq,
+                              (int)dim, flags, -1.f, bdelta.p, stat_bytes, nullptr);
+    if (rc != RT_OK) return rc;
+    RT_CUDA(cudaMemcpy(dq, bdq.p, bytes, cudaMemcpyDeviceToHost));
+    RT_CUDA(cudaMemcpy(dk, bdk.p, bytes, cudaMemcpyDeviceToHost));
+    RT_CUDA(cudaMemcpy(dv, bdv.p, bytes, cudaMemcpyDeviceToHost));
     return RT_OK;
 }
 

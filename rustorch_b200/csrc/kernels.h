@@ -45,11 +45,24 @@ cudaError_t launch_prefill_f32(const float* q, const float* k, const float* v, f
 cudaError_t launch_f32_to_bf16(const float* src, void* dst, int64_t n, cudaStream_t stream);
 cudaError_t launch_bf16_to_f32(const void* src, float* dst, int64_t n, cudaStream_t stream);
 
+// ---- backward_simt.cu
+cudaError_t launch_backward_f32(const float* q, const float* k, const float* v, const float* out, const float* d_out,
+                                const float* lse, float* dq, float* dk, float* dv, float* delta_ws, int64_t batch,
+                                int64_t heads, int64_t seq, int dim, int causal, float scale, cudaStream_t stream);
+
 // ---- prefill_tc.cu (tcgen05 / TMEM / TMA)
+// Element strides of a [B, H, N, D] view whose inner dim is contiguous.
+struct TensorStrides {
+    int64_t batch, head, row;
+    static TensorStrides contiguous(int64_t heads, int64_t seq, int dim) {
+        return TensorStrides{heads * seq * dim, seq * dim, (int64_t)dim};
+    }
+};
 cudaError_t launch_prefill_tc(const void* q, const void* k, const void* v, void* out, float* lse,
                               int64_t batch, int64_t heads, int64_t heads_kv, int64_t seq, int64_t seq_kv, int dim,
-                              int causal, const int32_t* kv_lens, const int32_t* q_offsets,
-                              const uint8_t* key_keep, int64_t keep_batch_stride, float scale,
-                              cudaStream_t stream);
+                              const TensorStrides& sq, const TensorStrides& sk, const TensorStrides& sv,
+                              const TensorStrides& so, int causal, const int32_t* kv_lens,
+                              const int32_t* q_offsets, const uint8_t* key_keep, int64_t keep_batch_stride,
+                              float scale, cudaStream_t stream);
 
 }  // namespace rt

@@ -68,6 +68,7 @@ struct TcParams {
     const int32_t* q_offsets;  // NULL or [B]: causal position of query row 0 inside the key sequence
     float scale_log2;  // scale * log2(e)
     int* status;       // device status word (bounded-wait expiry codes)
+    int64_t o_stride_b, o_stride_h, o_stride_row;  // element strides of the output (inner dim contiguous)
     int n_qb;          // 256-row blocks per head
     int slots_per_head, n_slots, paired;  // static schedule, see tc_item
 #ifdef RT_TC_TIMELINE
@@ -151,7 +152,7 @@ __host__ __device__ constexpr bool poly_pair(int q) { return (q & 3) == 3; }
 
 // One work item of a CTA's static list.
 struct TcItem {
-    int bh, bh_kv, b, q0, kv_hi, q_off;
+    int bh, b, h, h_kv, q0, kv_hi, q_off;  // bh = b * heads + h indexes LSE; h_kv is the KV head h reads
     int U0, U1;    // 64-key steps of each Q tile (U0 <= U1); scalars, so nothing is indexed dynamically
     int n_tiles;   // 128-key K/V tiles to load
     bool end;      // the list is exhausted
@@ -179,7 +180,8 @@ __device__ __forceinline__ TcItem tc_item(int j, const TcParams& p) {
     }
     it.valid = true;
     it.b = it.bh / p.heads;
-    it.bh_kv = it.b * p.heads_kv + (it.bh % p.heads) / (p.heads / p.heads_kv);
+    it.h = it.bh % p.heads;
+    it.h_kv = it.h / (p.heads / p.heads_kv);
     it.q0 = qb * 256;
     it.kv_hi = p.seq_kv;
     if (p.kv_lens) {
@@ -283,12 +285,12 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 mbar_arrive_expect_tx(&q_full[w], TILE);
 #pragma unroll
                 for (int s = 0; s < C::NSUB; ++s)
-                    tma_load_3d(sQ + w * TILE + s * SUB, &tm_q, &q_full[w], s * 64, it.q0 + w * 128, it.bh);
+                    tma_load_4d(sQ + w * TILE + s * SUB, &tm_q, &q_full[w], s * 64, it.q0 + w * 128, it.h, it.b);
                 if (w == 0 || it.U0 == 0) {
                     mbar_arrive_expect_tx(&k_full[0], TILE);
 #pragma unroll
                     for (int s = 0; s < C::NSUB; ++s)
-                        tma_load_3d(sK + s * SUB, &tm_k, &k_full[0], s * 64, 0, it.bh_kv);
+                        tma_load_4d(sK + s * SUB, &tm_k, &k_full[0], s * 64, 0, it.h_kv, it.b);
                 }
             }
         }
@@ -323,7 +325,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                     mbar_arrive_expect_tx(&q_full[w], TILE);
 #pragma unroll
                     for (int s = 0; s < C::NSUB; ++s)
-                        tma_load_3d(sQ + w * TILE + s * SUB, &tm_q, &q_full[w], s * 64, it.q0 + w * 128, it.bh);
+                        tma_load_4d(sQ + w * TILE + s * SUB, &tm_q, &q_full[w], s * 64, it.q0 + w * 128, it.h, it.b);
                     return true;
                 };
                 const bool pre = first_preloaded && j == 0;  // Q and K tile 0 were requested during setup
@@ -344,7 +346,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                         mbar_arrive_expect_tx(&k_full[ks], TILE);
 #pragma unroll
                         for (int s = 0; s < C::NSUB; ++s)
-                            tma_load_3d(sK + ks * TILE + s * SUB, &tm_k, &k_full[ks], s * 64, t * 128, it.bh_kv);
+                            tma_load_4d(sK + ks * TILE + s * SUB, &tm_k, &k_full[ks], s * 64, t * 128, it.h_kv, it.b);
                     }
                     ++kg;
                     if (t == 0) {  // tile 1 usually still works on the previous item: its Q comes second
@@ -362,7 +364,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                     mbar_arrive_expect_tx(&v_full[vs], TILE);
 #pragma unroll
                     for (int s = 0; s < C::NSUB; ++s)
-                        tma_load_3d(sV + vs * TILE + s * SUB, &tm_v, &v_full[vs], s * 64, t * 128, it.bh_kv);
+                        tma_load_4d(sV + vs * TILE + s * SUB, &tm_v, &v_full[vs], s * 64, t * 128, it.h_kv, it.b);
                     ++vg;
                 }
             }
@@ -519,7 +521,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 
             if (n_iter == 0) {  // the tile sees no key: NaN rows, LSE = -inf (cpu_forward.rs:411-420)
                 if (row < N) {
-                    uint4* dst = reinterpret_cast<uint4*>(p.out + ((int64_t)bh * N + row) * D);
+                    uint4* dst = reinterpret_cast<uint4*>(p.out + it.b * p.o_stride_b + it.h * p.o_stride_h +
+                                                          (int64_t)row * p.o_stride_row);
 #pragma unroll
                     for (int i = 0; i < D / 8; ++i) dst[i] = make_uint4(0x7fc07fc0u, 0x7fc07fc0u, 0x7fc07fc0u, 0x7fc07fc0u);
                     if (p.lse) p.lse[(int64_t)bh * N + row] = -INFINITY;
@@ -694,7 +697,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 } else {
 #pragma unroll
                     for (int s = 0; s < C::NSUB; ++s)
-                        tma_store_3d(&tm_o, sQ + w * TILE + s * SUB, s * 64, it.q0 + w * 128, bh);
+                        tma_store_4d(&tm_o, sQ + w * TILE + s * SUB, s * 64, it.q0 + w * 128, it.h, it.b);
                     tma_store_commit_and_wait_read();  // the staged tile has been read: the next Q may land
                     mbar_arrive(&q_empty[w]);
                 }
@@ -740,8 +743,24 @@ static EncodeTiledFn get_encode_fn() {
 
 EncodeTiledFn tensor_map_encoder() { return get_encode_fn(); }
 
-// View of a [B*H, N, D] bf16 tensor as a 3-D TMA tensor; box = 64 columns x 128 rows of one
-// (b,h), 128-byte swizzle.  Rows past N are zero-filled, so tiles never read a neighbour head.
+// View of a [B, H, N, D] bf16 tensor with arbitrary batch / head / row strides (inner dim contiguous)
+// as a 4-D TMA tensor (d, row, head, batch); box = 64 columns x 128 rows of one (b,h), 128-byte
+// swizzle.  Rows past N are zero-filled on loads and clipped on stores, so tiles never touch a
+// neighbouring head.  Strides are in elements and must be multiples of 8 (16 bytes).
+bool make_tensor_map_bf16_4d(CUtensorMap* map, const void* base, int64_t batch, int64_t heads, int64_t seq, int dim,
+                             int64_t stride_b, int64_t stride_h, int64_t stride_row) {
+    EncodeTiledFn enc = get_encode_fn();
+    if (!enc) return false;
+    cuuint64_t dims[4] = {(cuuint64_t)dim, (cuuint64_t)seq, (cuuint64_t)heads, (cuuint64_t)batch};
+    cuuint64_t strides[3] = {(cuuint64_t)stride_row * 2, (cuuint64_t)stride_h * 2, (cuuint64_t)stride_b * 2};
+    cuuint32_t box[4] = {64, 128, 1, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// The contiguous [B*H, N, D] view used by the self-test kernel.
 bool make_tensor_map_bf16_3d(CUtensorMap* map, const void* base, int64_t bh, int64_t seq, int dim) {
     EncodeTiledFn enc = get_encode_fn();
     if (!enc) return false;
@@ -765,17 +784,26 @@ static cudaError_t launch_tc(const CUtensorMap& mq, const CUtensorMap& mk, const
 }
 
 cudaError_t launch_prefill_tc(const void* q, const void* k, const void* v, void* out, float* lse, int64_t batch,
-                              int64_t heads, int64_t heads_kv, int64_t seq, int64_t seq_kv, int dim, int causal,
-                              const int32_t* kv_lens, const int32_t* q_offsets, const uint8_t* key_keep,
-                              int64_t keep_batch_stride, float scale, cudaStream_t stream) {
+                              int64_t heads, int64_t heads_kv, int64_t seq, int64_t seq_kv, int dim,
+                              const TensorStrides& sq, const TensorStrides& sk, const TensorStrides& sv,
+                              const TensorStrides& so, int causal, const int32_t* kv_lens, const int32_t* q_offsets,
+                              const uint8_t* key_keep, int64_t keep_batch_stride, float scale, cudaStream_t stream) {
     const int64_t bh = batch * heads;
     if (bh == 0 || seq == 0) return cudaSuccess;
     CUtensorMap mq, mk, mv, mo;
-    if (!make_tensor_map_bf16_3d(&mq, q, bh, seq, dim) || !make_tensor_map_bf16_3d(&mo, out, bh, seq, dim) ||
-        !make_tensor_map_bf16_3d(&mk, k, batch * heads_kv, seq_kv, dim) ||
-        !make_tensor_map_bf16_3d(&mv, v, batch * heads_kv, seq_kv, dim))
+    // With no key at all nothing is loaded through the K/V maps; they still have to be valid.
+    const void* kk = seq_kv > 0 ? k : q;
+    const void* vv = seq_kv > 0 ? v : q;
+    const int64_t skv = seq_kv > 0 ? seq_kv : 1;
+    if (!make_tensor_map_bf16_4d(&mq, q, batch, heads, seq, dim, sq.batch, sq.head, sq.row) ||
+        !make_tensor_map_bf16_4d(&mo, out, batch, heads, seq, dim, so.batch, so.head, so.row) ||
+        !make_tensor_map_bf16_4d(&mk, kk, batch, heads_kv, skv, dim, sk.batch, sk.head, sk.row) ||
+        !make_tensor_map_bf16_4d(&mv, vv, batch, heads_kv, skv, dim, sv.batch, sv.head, sv.row))
         return cudaErrorInvalidValue;
     TcParams p;
+    p.o_stride_b = so.batch;
+    p.o_stride_h = so.head;
+    p.o_stride_row = so.row;
     p.out = (__nv_bfloat16*)out;
     p.lse = lse;
     p.kv_lens = kv_lens;

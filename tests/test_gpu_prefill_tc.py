@@ -278,3 +278,71 @@ def test_prefill_bf16_host_entry_matches_device_entry(oracle, B, H):
     torch.cuda.synchronize()
     assert torch.equal(ho, out.cpu()) and torch.equal(hl, lse.cpu())
     _clean_status()
+
+
+@pytest.mark.parametrize("D,Hq,Hkv,causal", [(128, 8, 2, True), (64, 4, 4, False), (128, 3, 3, True)])
+def test_prefill_on_mha_activation_layout(oracle, D, Hq, Hkv, causal):
+    """Activations kept as [B,T,H*hd] (crates/rustorch-nn/src/attention.rs:468-485 transposes them before the
+    kernel and :499-543 back after it): the strided entry reads and writes that layout directly and gives
+    bit-identical numbers to the contiguous entry on transposed copies."""
+    import torch
+    import rustorch_b200 as rt
+    B, T = 2, 333
+    q = util.normal_bf16(oracle, (B, T, Hq * D), util.SEED_Q)
+    k = util.normal_bf16(oracle, (B, T, Hkv * D), util.SEED_K)
+    v = util.normal_bf16(oracle, (B, T, Hkv * D), util.SEED_V)
+    dq, dk, dv = util.to_cuda_bf16(q), util.to_cuda_bf16(k), util.to_cuda_bf16(v)
+    out, lse = rt.mha_prefill_bf16(dq, dk, dv, Hq, Hkv, causal=causal)
+    torch.cuda.synchronize()
+    _clean_status()
+    assert out.shape == (B, T, Hq * D) and out.is_contiguous()
+
+    def heads_first(x, h):
+        return x.view(B, T, h, D).permute(0, 2, 1, 3).contiguous()
+    out_c, lse_c = rt.prefill_bf16(heads_first(dq, Hq), heads_first(dk, Hkv), heads_first(dv, Hkv), causal=causal)
+    torch.cuda.synchronize()
+    assert torch.equal(out.view(B, T, Hq, D).permute(0, 2, 1, 3), out_c)
+    assert torch.equal(lse, lse_c)
+    to_bhnd = lambda x, h: np.ascontiguousarray(x.reshape(B, T, h, D).transpose(0, 2, 1, 3))
+    _, ref, ref_lse = oracle.attention_general(to_bhnd(q, Hq), to_bhnd(k, Hkv), to_bhnd(v, Hkv), causal=causal)
+    util.check_output(util.to_np(out_c), ref, label="mha layout")
+    util.check_lse(util.to_np(lse), ref_lse)
+
+
+def test_prefill_strided_kv_cache_slice_and_padded_rows(oracle):
+    """Strides that are not a permutation: K/V are the first S rows of a longer cache and Q rows are padded
+    to a wider pitch; the output goes to a tensor with its own pitch."""
+    import torch
+    import rustorch_b200 as rt
+    B, H, Hkv, N, S, D = 2, 4, 2, 130, 1024, 128
+    q = util.normal_bf16(oracle, (B, H, N, D), util.SEED_Q)
+    k = util.normal_bf16(oracle, (B, Hkv, N, D), util.SEED_K)
+    v = util.normal_bf16(oracle, (B, Hkv, N, D), util.SEED_V)
+    q_wide = torch.zeros((B, H, N, D + 64), dtype=torch.bfloat16, device="cuda")
+    q_wide[..., :D] = util.to_cuda_bf16(q)
+    k_cache = torch.zeros((B, Hkv, S, D), dtype=torch.bfloat16, device="cuda")
+    v_cache = torch.zeros_like(k_cache)
+    k_cache[:, :, :N] = util.to_cuda_bf16(k)
+    v_cache[:, :, :N] = util.to_cuda_bf16(v)
+    out_wide = torch.full((B, H, N, D + 8), 7.0, dtype=torch.bfloat16, device="cuda")
+    out, lse = rt.prefill_bf16(q_wide[..., :D], k_cache[:, :, :N], v_cache[:, :, :N], causal=True, out=out_wide[..., :D])
+    torch.cuda.synchronize()
+    _clean_status()
+    _, ref, ref_lse = oracle.attention_general(q, k, v, causal=True)
+    util.check_output(util.to_np(out.contiguous()), ref, label="strided slices")
+    util.check_lse(util.to_np(lse), ref_lse)
+    assert torch.all(out_wide[..., D:] == 7.0), "bytes outside the output view were written"
+
+
+def test_prefill_strided_validation():
+    import torch
+    import rustorch_b200 as rt
+    from rustorch_b200 import _lib
+    q = torch.zeros((1, 2, 64, 128), dtype=torch.bfloat16, device="cuda")
+    bad_inner = torch.zeros((1, 2, 128, 64), dtype=torch.bfloat16, device="cuda").transpose(2, 3)
+    with pytest.raises(TypeError):
+        rt.prefill_bf16(bad_inner, q, q)
+    odd_pitch = torch.zeros((1, 2, 64, 132), dtype=torch.bfloat16, device="cuda")[..., :128]  # 264-byte rows
+    with pytest.raises(_lib.CudaError) as e:
+        rt.prefill_bf16(odd_pitch, q, q)
+    assert e.value.code == _lib.RT_ERR_ALIGNMENT
