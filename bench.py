@@ -207,7 +207,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-cpu", action="store_true", help="skip the cpu_baseline leg (profiling runs)")
-    ap.add_argument("--only", default="", help="comma list of legs: prefill,e2e,decode,splitkv (default all)")
+    ap.add_argument("--only", default="", help="comma list of legs: prefill,e2e,decode,splitkv,backward (default all)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -228,7 +228,7 @@ def main():
         dist_mod.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
         dist = dist_mod
     n_gpus = world
-    legs = set(args.only.split(",")) if args.only else {"prefill", "e2e", "decode", "splitkv"}
+    legs = set(args.only.split(",")) if args.only else {"prefill", "e2e", "decode", "splitkv", "backward"}
     peaks = load_peaks()
     traffic = load_traffic()
     lib = _lib.lib()
@@ -344,6 +344,36 @@ def main():
         del k1, v1
         torch.cuda.empty_cache()
 
+    # ---------------------------------------------------------------- f32 backward (CUDA cores; auxiliary line)
+    backward = None
+    if "backward" in legs and n_gpus == 1:
+        Bb, Hb, Nb, Db = 4, 16, 2048, 64
+        g = torch.Generator(device="cuda").manual_seed(0xBAC0 + rank)
+        qb, kb, vb, dob = (torch.randn((Bb, Hb, Nb, Db), device="cuda", generator=g) for _ in range(4))
+        ob, lseb = rt.prefill_f32(qb, kb, vb, causal=True)
+
+        def step_backward():
+            rt.backward_f32(qb, kb, vb, ob, dob, lseb, causal=True)
+
+        bsteps = max(3, min(args.steps, 10))
+        bms = timed(step_backward, bsteps, 3, dist, torch)
+        # five N x N x D products (S, dP, dV, dQ, dK) over the unmasked pairs, 2 flops per multiply-add
+        pairs = Bb * Hb * (Nb * (Nb + 1) / 2)
+        btf = 10.0 * Db * pairs / (bms * 1e-3) / 1e12
+        backward = {"metric": "attn_backward_tflops", "value": btf, "unit": "TFLOP/s", "ms_per_step": bms, "dtype": "f32",
+                    "steps": bsteps,
+                    "config": {"workload": f"causal backward f32 B={Bb} H={Hb} N={Nb} D={Db} (dQ, dK, dV from saved O, LSE)",
+                               "flop_convention": "10*D*unmasked (q,k) pairs; the two-pass kernel executes 14*D (scores "
+                                                  "and dP are recomputed in the second pass)",
+                               "l2": "Q,K,V,O,dO,dQ,dK,dV = 268 MB per step, larger than the 126 MB L2"},
+                    "roofline": {"bound": "fp32 CUDA cores", "achieved": btf * 1.4, "peak": 74.4, "unit": "TFLOP/s",
+                                 "frac": btf * 1.4 / 74.4,
+                                 "peak_source": "nominal 148 SM x 128 FMA x 2 x 1.965 GHz (no measured f32 peak on file); "
+                                                "achieved counts the executed 14*D flops"},
+                    "gpu_launches": 3 * bsteps}
+        del qb, kb, vb, dob, ob, lseb
+        torch.cuda.empty_cache()
+
     # ---------------------------------------------------------------- CPU baseline (rank 0, N = 1 only)
     cpu = None
     if rank == 0 and n_gpus == 1 and not args.skip_cpu:
@@ -366,7 +396,7 @@ def main():
                          "frac_of_sustained": per_gpu_tflops / peaks["bf16_tflops_sustained"],
                          "traffic": traffic.get("prefill_tc_kernel")},
             "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": args.steps, "clocks": clocks,
-            "decode": decode, "decode_splitkv": splitkv,
+            "decode": decode, "decode_splitkv": splitkv, "backward": backward,
         }
         print(json.dumps(out_line), flush=True)
     if dist is not None:
