@@ -329,18 +329,40 @@ def main():
         from rustorch_b200 import sharding
         ws = torch.empty(rt.decode_workspace_bytes(1, Hq, Hkv, Dd, T), dtype=torch.uint8, device="cuda")
 
-        def step_splitkv():
+        def step_splitkv_nccl():
             # local shard -> packed (O | LSE) record; one 16.5 KB record per rank over NCCL; local merge
             rec = rt.gqa_decode_record(q1, k1, v1, kv_len=T, workspace=ws)
             return rt.merge_records(sharding.all_gather_partials(rec))
 
-        sms = timed(step_splitkv, args.steps, args.warmup, dist, torch)
+        # The same exchange over peer memory: the record is decoded straight into this rank's slot, pushed
+        # to every peer with NVLink stores + a flag, and the merge kernel waits (bounded) for all flags.
+        exchange, exchange_note = None, "peer stores over NVLink (symmetric memory) + flag, merge waits in-kernel"
+        try:
+            exchange = sharding.PeerRecordExchange.create(Hq, Dd)
+        except Exception as exc:  # symmetric memory not available: keep the NCCL form, and say so
+            exchange_note = f"NCCL all-gather (peer exchange unavailable: {type(exc).__name__}: {exc})"[:200]
+
+        def step_splitkv_p2p():
+            rt.gqa_decode_record(q1, k1, v1, kv_len=T, workspace=ws, record=exchange.next_epoch())
+            exchange.push()
+            return exchange.merge()
+
+        nccl_ms = timed(step_splitkv_nccl, args.steps, args.warmup, dist, torch)
+        sms = nccl_ms
+        if exchange is not None:
+            a, b = step_splitkv_nccl(), step_splitkv_p2p()
+            torch.cuda.synchronize()
+            assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1]), "peer exchange and NCCL exchange disagree"
+            sms = timed(step_splitkv_p2p, args.steps, args.warmup, dist, torch)
+            from rustorch_b200 import _lib
+            assert _lib.device_status() == 0, "a bounded wait of the peer exchange expired"
         total_bytes = 2.0 * Hkv * Dd * 2 * T * world
         splitkv = {"metric": "kv_read_gbs", "value": total_bytes / (sms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": sms,
                    "config": {"workload": f"split-KV decode B=1 Hq=32 Hkv=8 D=128, {T} KV positions per GPU "
-                                          f"(BASELINE config 5 sharding), NCCL all-gather of (O,LSE) + merge",
-                              "kv_len_total": T * world},
-                   "per_gpu_gbs": total_bytes / world / (sms * 1e-3) / 1e9}
+                                          f"(BASELINE config 5 sharding), exchange of (O,LSE) records + merge",
+                              "kv_len_total": T * world, "exchange": exchange_note},
+                   "per_gpu_gbs": total_bytes / world / (sms * 1e-3) / 1e9,
+                   "nccl_all_gather_ms_per_step": nccl_ms}
         del k1, v1
         torch.cuda.empty_cache()
 

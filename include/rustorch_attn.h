@@ -192,6 +192,18 @@ int rt_attn_backward_f32(const float* q, const float* k, const float* v, const f
                          float scale, void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * The backward of rt_attn_prefill_bf16 on the tensor cores (mma.sync, bf16 operands, f32
+ * accumulation; D in {64,128}): the same math as rt_attn_backward_f32 with P and dS rounded to
+ * bf16 for the accumulating products, as the forward rounds P.
+ *   q, k, v, out, d_out : bf16 [B,H,N,D];  lse : f32 [B,H,N] from the forward on the same inputs;
+ *   dq, dk, dv : f32 [B,H,N,D], fully overwritten;  workspace as for rt_attn_backward_f32.
+ */
+int rt_attn_backward_bf16(const void* q, const void* k, const void* v, const void* out,
+                          const void* d_out, const float* lse, float* dq, float* dk, float* dv,
+                          int64_t batch, int64_t heads, int64_t seq, int dim, int mask_flags,
+                          float scale, void* workspace, size_t workspace_bytes, void* stream);
+
+/*
  * Host-slice mirror of
  *   flash_backward(shape:&AttentionShape, q, k, v, do_:&[f32], dq, dk, dv:&mut [f32])
  * (cpu_backward.rs:46-55).  Lengths are validated in the reference's order: q, k, v, do give
@@ -330,6 +342,28 @@ int rt_attn_merge_partials(const float* o_parts, const float* lse_parts, int64_t
  */
 int rt_attn_merge_records(const float* records, int64_t n_parts, int64_t rows, int dim, void* out_bf16,
                           float* out_f32, float* lse, void* stream);
+
+/*
+ * Split-KV exchange over peer memory (NVLink), the fused form of "all-gather the records, then
+ * merge": each rank owns a buffer of `world` record slots and `world` 32-bit flags that its peers
+ * can write (symmetric memory / IPC mappings; the reference's NCCL layer is a stub,
+ * crates/rustorch-cuda/src/nccl.rs, so there is no reference counterpart).
+ *   rt_splitkv_push_record : copies this rank's packed record ([rows, D+1] f32, as written by
+ *       rt_gqa_decode_record_bf16) into peer_slots[r] on every rank r with plain peer stores and then
+ *       sets *peer_flags[r] = epoch with a system-scope release.  peer_slots / peer_flags are HOST
+ *       arrays of `world` device pointers (the entry for this rank may alias `record`, which skips
+ *       the copy).  Never waits.  rows * (D+1) must be a multiple of 4.
+ *   rt_attn_merge_records_after : rt_attn_merge_records on the local slots once flags[r] >= epoch
+ *       for every r < n_parts.  The wait is bounded by wait_clocks SM clocks (<= 0: 2^31, about a
+ *       second); on expiry the kernel writes nothing and rt_attn_device_status reports 301.
+ * Epochs must increase by one per exchange; with two slot sets used alternately a rank can never
+ * overwrite a record that a slower peer is still merging.
+ */
+int rt_splitkv_push_record(const float* record, void* const* peer_slots, void* const* peer_flags,
+                           int world, int64_t rows, int dim, uint32_t epoch, void* stream);
+int rt_attn_merge_records_after(const float* records, const uint32_t* flags, uint32_t epoch,
+                                int64_t wait_clocks, int64_t n_parts, int64_t rows, int dim,
+                                void* out_bf16, float* out_f32, float* lse, void* stream);
 
 /*
  * Host-slice mirror of

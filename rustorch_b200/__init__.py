@@ -8,7 +8,7 @@ This package is the thin host-side mirror of the reference's Rust entry points f
     rustorch_b200.gqa       : gqa_forward_f32, LlmKernels.gqa_decode_online_bf16, gqa_decode, merge_partials
 """
 from .attention import (AttentionError, AttentionShape, BufferShapeMismatch, Mask, MaskError, OutputShapeMismatch,
-                        PaddingLengthMismatch, ZeroDim, backward_f32, flash_backward, flash_forward,
+                        PaddingLengthMismatch, ZeroDim, backward_bf16, backward_f32, flash_backward, flash_forward,
                         flash_forward_masked, mha_prefill_bf16, prefill_bf16, prefill_f32)
 from .gqa import (GQAError, HeadCountMismatch, LlmKernels, WrongInputLen, decode_workspace_bytes, gqa_decode,
                   gqa_decode_online_bf16_static, gqa_decode_record, gqa_forward_f32, kv_append, merge_partials,
@@ -16,7 +16,7 @@ from .gqa import (GQAError, HeadCountMismatch, LlmKernels, WrongInputLen, decode
 
 __all__ = [
     "AttentionError", "AttentionShape", "BufferShapeMismatch", "Mask", "MaskError", "OutputShapeMismatch",
-    "PaddingLengthMismatch", "ZeroDim", "flash_forward", "flash_forward_masked", "flash_backward", "backward_f32",
+    "PaddingLengthMismatch", "ZeroDim", "flash_forward", "flash_forward_masked", "flash_backward", "backward_f32", "backward_bf16",
     "mha_prefill_bf16", "prefill_bf16", "prefill_f32",
     "GQAError", "HeadCountMismatch", "LlmKernels", "WrongInputLen", "decode_workspace_bytes", "gqa_decode",
     "gqa_decode_online_bf16_static", "gqa_decode_record", "gqa_forward_f32", "kv_append", "merge_partials",

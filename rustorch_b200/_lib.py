@@ -58,6 +58,9 @@ PROTOTYPES = {
     "rt_attn_backward_f32": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                      c_void_p, c_int64, c_int64, c_int64, c_int, c_int, c_float, c_void_p, c_size_t,
                                      c_void_p]),
+    "rt_attn_backward_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                      c_void_p, c_int64, c_int64, c_int64, c_int, c_int, c_float, c_void_p, c_size_t,
+                                      c_void_p]),
     "rt_flash_backward_f32_host": (c_int, [_fp, c_size_t, _fp, c_size_t, _fp, c_size_t, _fp, c_size_t, _fp, c_size_t,
                                            _fp, c_size_t, _fp, c_size_t, c_int64, c_int64, c_int64, c_int64, c_int]),
     "rt_flash_forward_f32_host": (c_int, [_fp, c_size_t, _fp, c_size_t, _fp, c_size_t, _fp, c_size_t, c_int64,
@@ -71,6 +74,9 @@ PROTOTYPES = {
     "rt_gqa_decode_record_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int,
                                           c_int64, c_void_p, c_int64, c_int64, c_int64, c_float, c_void_p, c_size_t,
                                           c_void_p]),
+    "rt_splitkv_push_record": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int, ctypes.c_uint32, c_void_p]),
+    "rt_attn_merge_records_after": (c_int, [c_void_p, c_void_p, ctypes.c_uint32, c_int64, c_int64, c_int64, c_int,
+                                            c_void_p, c_void_p, c_void_p, c_void_p]),
     "rt_attn_merge_records": (c_int, [c_void_p, c_int64, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
     "rt_gqa_decode_online_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                           c_void_p, c_size_t, c_void_p]),

@@ -327,3 +327,26 @@ def backward_f32(q, k, v, out, d_out, lse, causal: bool = False, scale: Optional
         raise ZeroDim()
     _lib.check(rc, "rt_attn_backward_f32")
     return dq, dk, dv
+
+
+def backward_bf16(q, k, v, out, d_out, lse, causal: bool = False, scale: Optional[float] = None):
+    """(dq, dk, dv) f32 from bf16 CUDA tensors [B,H,N,D] (D in {64,128}) via ``rt_attn_backward_bf16``;
+    ``out`` and ``lse`` are the results of ``prefill_bf16`` on the same q, k, v, mask and scale."""
+    import torch
+    B, H, N, D = q.shape
+    for name, t in (("q", q), ("k", k), ("v", v), ("out", out), ("d_out", d_out)):
+        if not (t.is_cuda and t.dtype == torch.bfloat16 and t.is_contiguous() and tuple(t.shape) == (B, H, N, D)):
+            raise TypeError(f"{name} must be a contiguous bfloat16 CUDA tensor of shape {(B, H, N, D)}")
+    if not (lse.is_cuda and lse.dtype == torch.float32 and lse.is_contiguous() and tuple(lse.shape) == (B, H, N)):
+        raise TypeError("lse must be a contiguous float32 CUDA tensor [B,H,N]")
+    dq, dk, dv = (torch.empty((B, H, N, D), dtype=torch.float32, device=q.device) for _ in range(3))
+    need = _lib.lib().rt_attn_backward_workspace_bytes(B, H, N)
+    ws = torch.empty((max(need, 4) // 4,), dtype=torch.float32, device=q.device)
+    rc = _lib.lib().rt_attn_backward_bf16(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), d_out.data_ptr(),
+                                          lse.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), B, H, N, D,
+                                          _lib.RT_MASK_CAUSAL if causal else _lib.RT_MASK_NONE,
+                                          -1.0 if scale is None else float(scale), ws.data_ptr(), need, _stream_ptr())
+    if rc == _lib.RT_ERR_ZERO_DIM:
+        raise ZeroDim()
+    _lib.check(rc, "rt_attn_backward_bf16")
+    return dq, dk, dv

@@ -391,6 +391,23 @@ int rt_attn_backward_f32(const float* q, const float* k, const float* v, const f
     return RT_OK;
 }
 
+int rt_attn_backward_bf16(const void* q, const void* k, const void* v, const void* out, const void* d_out,
+                          const float* lse, float* dq, float* dk, float* dv, int64_t batch, int64_t heads, int64_t seq,
+                          int dim, int mask_flags, float scale, void* workspace, size_t workspace_bytes, void* stream) {
+    if (dim == 0) return RT_ERR_ZERO_DIM;
+    if (batch < 0 || heads < 0 || seq < 0 || dim < 0) return RT_ERR_BAD_LENGTH;
+    if (batch == 0 || heads == 0 || seq == 0) return RT_OK;
+    if (!q || !k || !v || !out || !d_out || !lse || !dq || !dk || !dv) return RT_ERR_NULL_POINTER;
+    if ((dim != 64 && dim != 128) || batch * heads > 65535) return RT_ERR_UNSUPPORTED;
+    if (mask_flags & ~RT_MASK_CAUSAL) return RT_ERR_UNSUPPORTED;
+    if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(d_out) || !aligned16(out)) return RT_ERR_ALIGNMENT;
+    if (!workspace || workspace_bytes < rt_attn_backward_workspace_bytes(batch, heads, seq)) return RT_ERR_WORKSPACE;
+    RT_CUDA(rt::launch_backward_bf16(q, k, v, out, d_out, lse, dq, dk, dv, static_cast<float*>(workspace), batch, heads,
+                                     seq, dim, mask_flags & RT_MASK_CAUSAL, default_scale(scale, dim),
+                                     as_stream(stream)));
+    return RT_OK;
+}
+
 int rt_flash_backward_f32_host(const float* q, size_t q_len, const float* k, size_t k_len, const float* v,
                                size_t v_len, const float* d_out, size_t d_out_len, float* dq, size_t dq_len, float* dk,
                                size_t dk_len, float* dv, size_t dv_len, int64_t batch, int64_t heads, int64_t seq,
@@ -525,6 +542,40 @@ int rt_attn_merge_records(const float* records, int64_t n_parts, int64_t rows, i
     if ((n_parts > 0 && !records) || (!out_bf16 && !out_f32)) return RT_ERR_NULL_POINTER;
     RT_CUDA(rt::launch_merge_partials(records, records + dim, n_parts, rows, dim, dim + 1, dim + 1, out_bf16, out_f32,
                                       lse, as_stream(stream)));
+    return RT_OK;
+}
+
+int rt_splitkv_push_record(const float* record, void* const* peer_slots, void* const* peer_flags, int world,
+                           int64_t rows, int dim, uint32_t epoch, void* stream) {
+    if (dim == 0) return RT_ERR_ZERO_DIM;
+    if (world <= 0 || rows < 0 || dim < 0) return RT_ERR_BAD_LENGTH;
+    if (world > rt::kMaxPeers || dim > 256) return RT_ERR_UNSUPPORTED;
+    if (rows == 0) return RT_OK;
+    if (!record || !peer_slots || !peer_flags) return RT_ERR_NULL_POINTER;
+    const int64_t n = rows * (dim + 1);
+    if (n & 3) return RT_ERR_ALIGNMENT;  // the record is copied in 16-byte pieces
+    for (int r = 0; r < world; ++r) {
+        if (!peer_slots[r] || !peer_flags[r]) return RT_ERR_NULL_POINTER;
+        if (!aligned16(peer_slots[r])) return RT_ERR_ALIGNMENT;
+    }
+    if (!aligned16(record)) return RT_ERR_ALIGNMENT;
+    RT_CUDA(rt::launch_push_records(record, peer_slots, peer_flags, world, n, epoch, as_stream(stream)));
+    return RT_OK;
+}
+
+int rt_attn_merge_records_after(const float* records, const uint32_t* flags, uint32_t epoch, int64_t wait_clocks,
+                                int64_t n_parts, int64_t rows, int dim, void* out_bf16, float* out_f32, float* lse,
+                                void* stream) {
+    if (dim == 0) return RT_ERR_ZERO_DIM;
+    if (n_parts <= 0 || rows < 0 || dim < 0) return RT_ERR_BAD_LENGTH;
+    if (dim > 256 || n_parts > rt::kMaxPeers) return RT_ERR_UNSUPPORTED;
+    if (rows == 0) return RT_OK;
+    if (!records || !flags || (!out_bf16 && !out_f32)) return RT_ERR_NULL_POINTER;
+    rt::MergeWait w{flags, (int)n_parts, epoch, wait_clocks > 0 ? (long long)wait_clocks : (1ll << 31),
+                    rt::device_status_ptr()};
+    if (!w.status) return (int)cudaErrorInvalidSymbol;
+    RT_CUDA(rt::launch_merge_partials(records, records + dim, n_parts, rows, dim, dim + 1, dim + 1, out_bf16, out_f32,
+                                      lse, as_stream(stream), &w));
     return RT_OK;
 }
 

@@ -1,0 +1,286 @@
+// bf16 flash-attention backward on the tensor cores (mma.sync.m16n8k16, f32 accumulate).
+//
+// Same math as rustorch_attention::flash_backward (crates/rustorch-attention/src/cpu_backward.rs:16-27,
+// 96-189) with the saved row statistics in place of the N x N probability matrix:
+//   P = exp(scale * Q K^T - LSE),  dP = dO V^T,  dS = P o (dP - delta),  delta_i = dO_i . O_i,
+//   dV = P^T dO,  dQ = scale * dS K,  dK = scale * dS^T Q.
+// Two deterministic passes share one kernel template.  A CTA owns 64 rows of one side (4 warps x 16
+// rows) and walks the 64-row tiles of the other side:
+//   query side: X1 = Q, X2 = dO (own rows);  per key tile  T1 = Q K^T, T2 = dO V^T -> dS;  dQ += dS K
+//   key side:   X1 = K, X2 = V  (own rows);  per query tile T1 = K Q^T, T2 = V dO^T -> P^T, dS^T;
+//               dV += P^T dO,  dK += dS^T Q
+// so every product has the shape "own rows (A, from shared memory via ldmatrix) x other tile (B)":
+// B comes from the other tile untransposed for the score-like products and through ldmatrix.trans
+// for the accumulating ones, and the score accumulators are re-packed in registers as the A operand
+// of the accumulating product.  P and dS are rounded to bf16 for those products, as the forward
+// rounds P.  No atomics; a causal launch skips the tiles beyond the diagonal.
+// Tiles are staged with plain 16-byte loads into 128-byte-swizzled shared memory.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace rt {
+
+namespace {
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr));
+}
+// D = A(16x16, row) * B(16x8, col) + D, bf16 inputs, f32 accumulate.
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+constexpr int kRows = 64;  // rows per tile (own side and other side)
+
+// Byte offset of the 16-byte chunk (row, chunk16) of a [64 x D] bf16 tile: 64-column sub-tiles of
+// 128-byte rows, chunk index XORed with the row (conflict-free ldmatrix in both orientations).
+__device__ __forceinline__ uint32_t tile_off(int row, int chunk16) {
+    return (uint32_t)((chunk16 >> 3) * (kRows * 128) + row * 128 + (((chunk16 & 7) ^ (row & 7)) << 4));
+}
+
+// Cooperative load of rows [r0, r0+64) of a [N x D] bf16 matrix into a swizzled tile; rows >= N are zero.
+template <int D>
+__device__ __forceinline__ void load_tile(uint8_t* tile, const __nv_bfloat16* src, int64_t r0, int64_t n_rows) {
+    constexpr int CH = D / 8;  // 16-byte chunks per row
+    for (int i = threadIdx.x; i < kRows * CH; i += blockDim.x) {
+        const int r = i / CH, c = i % CH;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (r0 + r < n_rows) v = *reinterpret_cast<const uint4*>(src + (r0 + r) * D + c * 8);
+        *reinterpret_cast<uint4*>(tile + tile_off(r, c)) = v;
+    }
+}
+
+}  // namespace
+
+struct BwdTcParams {
+    const __nv_bfloat16 *q, *k, *v, *d_out;
+    const float *lse, *delta;
+    float *dq, *dk, *dv;
+    int64_t seq;
+    int causal;
+    float scale, scale_log2;
+};
+
+// delta_i = dO_i . O_i from the bf16 forward output, one warp per row.
+__global__ void __launch_bounds__(256) bwd_delta_bf16_kernel(const __nv_bfloat16* __restrict__ out,
+                                                             const __nv_bfloat16* __restrict__ d_out,
+                                                             float* __restrict__ delta, int64_t rows, int dim) {
+    const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    float acc = 0.f;
+    for (int d = lane * 2; d < dim; d += 64) {
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(out + row * dim + d));
+        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(d_out + row * dim + d));
+        acc = fmaf(a.x, b.x, fmaf(a.y, b.y, acc));
+    }
+#pragma unroll
+    for (int off = 16; off; off >>= 1) acc += __shfl_xor_sync(kFullMask, acc, off);
+    if (lane == 0) delta[row] = acc;
+}
+
+template <int D, bool kKeySide>
+__global__ void __launch_bounds__(128) bwd_tc_kernel(const BwdTcParams p) {
+    constexpr int TILE = kRows * D * 2;
+    constexpr int NT_D = D / 8;   // n-tiles across the head dim
+    extern __shared__ __align__(1024) uint8_t smem_bwd[];
+    uint8_t* sX1 = smem_bwd;             // own rows: Q (query side) / K (key side)
+    uint8_t* sX2 = sX1 + TILE;           // own rows: dO           / V
+    uint8_t* sY1 = sX2 + TILE;           // other tile: K          / Q
+    uint8_t* sY2 = sY1 + TILE;           // other tile: V          / dO
+    float* sLse = reinterpret_cast<float*>(sY2 + TILE);  // [64] statistics of the tile's QUERY rows (log2 units)
+    float* sDelta = sLse + kRows;                        // [64]
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int64_t bh = blockIdx.y, N = p.seq;
+    const int64_t own0 = (int64_t)blockIdx.x * kRows;
+    const int64_t base = bh * N * D;
+    const __nv_bfloat16* X1 = (kKeySide ? p.k : p.q) + base;
+    const __nv_bfloat16* X2 = (kKeySide ? p.v : p.d_out) + base;
+    const __nv_bfloat16* Y1 = (kKeySide ? p.q : p.k) + base;
+    const __nv_bfloat16* Y2 = (kKeySide ? p.d_out : p.v) + base;
+
+    load_tile<D>(sX1, X1, own0, N);
+    load_tile<D>(sX2, X2, own0, N);
+    if (!kKeySide && threadIdx.x < kRows) {  // the own rows are the query rows: their statistics never change
+        const int64_t r = own0 + threadIdx.x;
+        sLse[threadIdx.x] = r < N ? p.lse[bh * N + r] * kLog2e : -INFINITY;
+        sDelta[threadIdx.x] = r < N ? p.delta[bh * N + r] : 0.f;
+    }
+
+    // other-side tile range
+    int64_t t_lo = 0, t_hi = N;
+    if (p.causal) {
+        if (kKeySide) t_lo = own0;                                   // queries >= the first own key
+        else t_hi = own0 + kRows < N ? own0 + kRows : N;             // keys <= the last own query
+    }
+
+    float z1[NT_D][4];                    // query side: dQ; key side: dK
+    float z2[kKeySide ? NT_D : 1][4];     // key side: dV
+#pragma unroll
+    for (int j = 0; j < NT_D; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) z1[j][e] = 0.f;
+#pragma unroll
+    for (int j = 0; j < (kKeySide ? NT_D : 1); ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) z2[j][e] = 0.f;
+
+    const uint32_t x1_a = smem_u32(sX1), x2_a = smem_u32(sX2), y1_a = smem_u32(sY1), y2_a = smem_u32(sY2);
+    const int lr = lane & 7, lm = lane >> 3;          // ldmatrix: this lane addresses row lr of matrix lm
+    const int a_row = warp * 16 + (lm & 1) * 8 + lr;  // A operand: matrices 0,2 rows 0-7; 1,3 rows 8-15
+
+    for (int64_t t0 = t_lo; t0 < t_hi; t0 += kRows) {
+        __syncthreads();  // the previous tile is no longer read (also orders the X loads before first use)
+        load_tile<D>(sY1, Y1, t0, N);
+        load_tile<D>(sY2, Y2, t0, N);
+        if (kKeySide && threadIdx.x < kRows) {
+            const int64_t r = t0 + threadIdx.x;
+            sLse[threadIdx.x] = r < N ? p.lse[bh * N + r] * kLog2e : -INFINITY;
+            sDelta[threadIdx.x] = r < N ? p.delta[bh * N + r] : 0.f;
+        }
+        __syncthreads();
+
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {  // 32 columns of the other tile at a time (register budget)
+            float t1[4][4], t2[4][4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) t1[j][e] = t2[j][e] = 0.f;
+
+            // ---- T1 = X1 Y1^T, T2 = X2 Y2^T over the head dim (D/16 k-steps, two per B ldmatrix)
+#pragma unroll
+            for (int kp = 0; kp < D / 32; ++kp) {
+                uint32_t a1[2][4], a2[2][4];
+#pragma unroll
+                for (int s = 0; s < 2; ++s) {
+                    const int chunk = (kp * 2 + s) * 2 + (lm >> 1);
+                    ldsm_x4(x1_a + tile_off(a_row, chunk), a1[s][0], a1[s][1], a1[s][2], a1[s][3]);
+                    ldsm_x4(x2_a + tile_off(a_row, chunk), a2[s][0], a2[s][1], a2[s][2], a2[s][3]);
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int n_row = half * 32 + j * 8 + lr;
+                    uint32_t b0, b1, b2, b3;
+                    ldsm_x4(y1_a + tile_off(n_row, kp * 4 + lm), b0, b1, b2, b3);
+                    mma_bf16(t1[j], a1[0], b0, b1);
+                    mma_bf16(t1[j], a1[1], b2, b3);
+                    ldsm_x4(y2_a + tile_off(n_row, kp * 4 + lm), b0, b1, b2, b3);
+                    mma_bf16(t2[j], a2[0], b0, b1);
+                    mma_bf16(t2[j], a2[1], b2, b3);
+                }
+            }
+
+            // ---- P and dS on the accumulator fragments; element e of n-tile j sits at
+            //      own row g + 8*(e>>1), other column half*32 + j*8 + 2t + (e&1)
+            uint32_t wp[2][4], wd[2][4];  // A fragments (two k-steps of 16 columns): P (key side only) and dS
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                float pv[4], dv[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int r_own = warp * 16 + g + 8 * (e >> 1);
+                    const int c_oth = half * 32 + j * 8 + 2 * t + (e & 1);
+                    const int64_t own = own0 + r_own, oth = t0 + c_oth;
+                    const int64_t qi = kKeySide ? oth : own, kj = kKeySide ? own : oth;
+                    const int stat = kKeySide ? c_oth : r_own;
+                    const float lse2 = sLse[stat];
+                    const bool vis = own < N && oth < N && !(p.causal && kj > qi) && lse2 != -INFINITY;
+                    const float prob = vis ? fast_exp2(t1[j][e] * p.scale_log2 - lse2) : 0.f;
+                    pv[e] = prob;
+                    dv[e] = prob * (t2[j][e] - sDelta[stat]) * p.scale;
+                }
+                // n-tiles 2s and 2s+1 of this half form k-step s of the accumulating product
+                const int s = j >> 1, hi = (j & 1) * 2;
+                if (kKeySide) {
+                    wp[s][hi] = float2_to_bf16x2(pv[0], pv[1]);
+                    wp[s][hi + 1] = float2_to_bf16x2(pv[2], pv[3]);
+                }
+                wd[s][hi] = float2_to_bf16x2(dv[0], dv[1]);
+                wd[s][hi + 1] = float2_to_bf16x2(dv[2], dv[3]);
+            }
+
+            // ---- Z1 += dS Y1 (dQ += dS K / dK += dS^T Q);  key side also Z2 += P^T Y2 (dV += P^T dO)
+#pragma unroll
+            for (int s = 0; s < 2; ++s) {
+                const int k_row = half * 32 + s * 16 + (lm & 1) * 8 + lr;  // matrices 0,2: k 0-7; 1,3: k 8-15
+#pragma unroll
+                for (int jp = 0; jp < NT_D / 2; ++jp) {  // two n-tiles of the head dim per ldmatrix.trans
+                    const int chunk = jp * 2 + (lm >> 1);
+                    uint32_t b0, b1, b2, b3;
+                    ldsm_x4_trans(y1_a + tile_off(k_row, chunk), b0, b1, b2, b3);
+                    mma_bf16(z1[2 * jp], wd[s], b0, b1);
+                    mma_bf16(z1[2 * jp + 1], wd[s], b2, b3);
+                    if (kKeySide) {
+                        ldsm_x4_trans(y2_a + tile_off(k_row, chunk), b0, b1, b2, b3);
+                        mma_bf16(z2[2 * jp], wp[s], b0, b1);
+                        mma_bf16(z2[2 * jp + 1], wp[s], b2, b3);
+                    }
+                }
+            }
+        }
+    }
+
+    // ---- write the own rows: element e of n-tile j = row g + 8*(e>>1), column j*8 + 2t + (e&1)
+    float* out1 = (kKeySide ? p.dk : p.dq) + base;
+#pragma unroll
+    for (int j = 0; j < NT_D; ++j) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int64_t r = own0 + warp * 16 + g + 8 * h;
+            if (r < N) {
+                *reinterpret_cast<float2*>(out1 + r * D + j * 8 + 2 * t) = make_float2(z1[j][2 * h], z1[j][2 * h + 1]);
+                if (kKeySide)
+                    *reinterpret_cast<float2*>(p.dv + base + r * D + j * 8 + 2 * t) =
+                        make_float2(z2[j][2 * h], z2[j][2 * h + 1]);
+            }
+        }
+    }
+}
+
+template <int D>
+static cudaError_t launch_bwd_tc(const BwdTcParams& p, int64_t bh, cudaStream_t stream) {
+    const size_t smem = (size_t)4 * kRows * D * 2 + 2 * kRows * sizeof(float);
+    cudaError_t e = cudaFuncSetAttribute(bwd_tc_kernel<D, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(bwd_tc_kernel<D, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    dim3 grid((unsigned)((p.seq + kRows - 1) / kRows), (unsigned)bh);
+    bwd_tc_kernel<D, false><<<grid, 128, smem, stream>>>(p);
+    bwd_tc_kernel<D, true><<<grid, 128, smem, stream>>>(p);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_backward_bf16(const void* q, const void* k, const void* v, const void* out, const void* d_out,
+                                 const float* lse, float* dq, float* dk, float* dv, float* delta_ws, int64_t batch,
+                                 int64_t heads, int64_t seq, int dim, int causal, float scale, cudaStream_t stream) {
+    const int64_t bh = batch * heads;
+    if (bh == 0 || seq == 0) return cudaSuccess;
+    if (bh > 65535) return cudaErrorInvalidValue;
+    const int64_t rows = bh * seq;
+    bwd_delta_bf16_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, stream>>>((const __nv_bfloat16*)out,
+                                                                          (const __nv_bfloat16*)d_out, delta_ws, rows, dim);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    BwdTcParams p{(const __nv_bfloat16*)q, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v,
+                  (const __nv_bfloat16*)d_out, lse, delta_ws, dq, dk, dv, seq, causal, scale, scale * kLog2e};
+    if (dim == 128) return launch_bwd_tc<128>(p, bh, stream);
+    if (dim == 64) return launch_bwd_tc<64>(p, bh, stream);
+    return cudaErrorInvalidValue;
+}
+
+}  // namespace rt

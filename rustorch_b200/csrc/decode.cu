@@ -277,6 +277,14 @@ __global__ void __launch_bounds__(128) gqa_decode_splitkv_kernel(const DecodePar
 // loads in flight per lane, so a row with hundreds of partials (long-context split-KV) costs a few
 // memory latencies instead of one per partial.  Each lane owns dims lane, lane+32, ...
 // A partial with LSE_r = -inf gets weight 0 and its O is never read (it may be uninitialised).
+constexpr int kToPeerFlag = 301;  // device status code: a peer's record did not arrive in time
+
+__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
 constexpr int kMergeWarps = 8;
 constexpr int kMergeMaxDimPerLane = 8;  // dim <= 256
 
@@ -286,9 +294,29 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_partials_kernel(const 
                                                                          int64_t in_row_stride, int64_t in_lse_stride,
                                                                          __nv_bfloat16* out_bf16, float* out_f32,
                                                                          float* lse_out, int64_t of_stride,
-                                                                         int64_t lse_stride) {
+                                                                         int64_t lse_stride, MergeWait wait) {
     const int64_t row = blockIdx.x;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (wait.flags) {
+        // Part r of this merge is written into local memory by rank r (push_records_kernel on that GPU),
+        // which then raises flags[r] to the epoch with a system-scope release.  The wait is bounded: on
+        // expiry the kernel records the code and returns without touching the outputs.
+        __shared__ int wait_failed;
+        if (tid == 0) wait_failed = 0;
+        __syncthreads();
+        if (tid < wait.n_flags) {
+            const long long t0 = clock64();
+            while (ld_acquire_sys_u32(wait.flags + tid) < wait.epoch) {
+                if (clock64() - t0 > wait.max_clocks) {
+                    report_timeout(wait.status, kToPeerFlag);
+                    wait_failed = 1;
+                    break;
+                }
+            }
+        }
+        __syncthreads();
+        if (wait_failed) return;
+    }
     __shared__ float red[kMergeWarps];
     __shared__ float s_m, s_l;
     extern __shared__ float merge_sm[];
@@ -564,7 +592,7 @@ cudaError_t launch_gqa_decode(const void* q, const void* k, const void* v, void*
     if (p.n_chunks > 1) {
         merge_partials_kernel<<<(unsigned)p.rows, kMergeWarps * 32, merge_smem_bytes(p.n_chunks, head_dim), stream>>>(
             p.part_o, p.part_lse, p.n_chunks, p.rows, head_dim, head_dim, 1, p.out_bf16, p.out_f32, lse, p.of_stride,
-            p.lse_stride);
+            p.lse_stride, MergeWait{nullptr, 0, 0u, 0, nullptr});
         e = cudaGetLastError();
     }
     return e;
@@ -572,12 +600,51 @@ cudaError_t launch_gqa_decode(const void* q, const void* k, const void* v, void*
 
 cudaError_t launch_merge_partials(const float* o_parts, const float* lse_parts, int64_t n_parts, int64_t rows,
                                   int dim, int64_t in_row_stride, int64_t in_lse_stride, void* out_bf16,
-                                  float* out_f32, float* lse, cudaStream_t stream) {
+                                  float* out_f32, float* lse, cudaStream_t stream, const MergeWait* wait) {
     if (rows == 0) return cudaSuccess;
     if (dim > 32 * kMergeMaxDimPerLane || merge_smem_bytes(n_parts, dim) > 48 * 1024) return cudaErrorInvalidValue;
+    if (wait && wait->n_flags > kMergeWarps * 32) return cudaErrorInvalidValue;
     merge_partials_kernel<<<(unsigned)rows, kMergeWarps * 32, merge_smem_bytes(n_parts, dim), stream>>>(
         o_parts, lse_parts, (int)n_parts, rows, dim, in_row_stride, in_lse_stride, (__nv_bfloat16*)out_bf16, out_f32, lse,
-        dim, 1);
+        dim, 1, wait ? *wait : MergeWait{nullptr, 0, 0u, 0, nullptr});
+    return cudaGetLastError();
+}
+
+// Copies this rank's packed (O | LSE) record into the slot every peer keeps for it and raises the
+// peer's flag.  One CTA per destination; plain peer stores over NVLink (no multicast, no multimem),
+// a system-scope fence, then one release store of the epoch.  The kernel never waits.
+struct PushParams {
+    const float* src;
+    float* dst[kMaxPeers];
+    uint32_t* flag[kMaxPeers];
+    int64_t n_vec4;
+    uint32_t epoch;
+};
+
+__global__ void __launch_bounds__(256) push_records_kernel(const PushParams p) {
+    const int peer = blockIdx.x;
+    float4* dst = reinterpret_cast<float4*>(p.dst[peer]);
+    const float4* src = reinterpret_cast<const float4*>(p.src);
+    if (reinterpret_cast<const float4*>(dst) != src)
+        for (int64_t i = threadIdx.x; i < p.n_vec4; i += blockDim.x) dst[i] = src[i];
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0)
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.flag[peer]), "r"(p.epoch) : "memory");
+}
+
+cudaError_t launch_push_records(const float* record, void* const* peer_slots, void* const* peer_flags, int world,
+                                int64_t record_floats, uint32_t epoch, cudaStream_t stream) {
+    if (world <= 0 || world > kMaxPeers || (record_floats & 3)) return cudaErrorInvalidValue;
+    PushParams p;
+    p.src = record;
+    for (int r = 0; r < kMaxPeers; ++r) {
+        p.dst[r] = r < world ? static_cast<float*>(peer_slots[r]) : nullptr;
+        p.flag[r] = r < world ? static_cast<uint32_t*>(peer_flags[r]) : nullptr;
+    }
+    p.n_vec4 = record_floats / 4;
+    p.epoch = epoch;
+    push_records_kernel<<<world, 256, 0, stream>>>(p);
     return cudaGetLastError();
 }
 

@@ -17,9 +17,20 @@ cudaError_t launch_gqa_decode(const void* q, const void* k, const void* v, void*
                               int64_t kv_begin, int64_t kv_end, float scale, void* workspace,
                               int64_t of_stride, int64_t lse_stride, cudaStream_t stream);
 // o_parts rows are in_row_stride floats apart, lse_parts entries in_lse_stride floats apart
+// Optional bounded wait in front of a merge: flags[r] >= epoch means part r has arrived.
+struct MergeWait {
+    const uint32_t* flags;
+    int n_flags;
+    uint32_t epoch;
+    long long max_clocks;
+    int* status;
+};
+constexpr int kMaxPeers = 16;
 cudaError_t launch_merge_partials(const float* o_parts, const float* lse_parts, int64_t n_parts, int64_t rows,
                                   int dim, int64_t in_row_stride, int64_t in_lse_stride, void* out_bf16,
-                                  float* out_f32, float* lse, cudaStream_t stream);
+                                  float* out_f32, float* lse, cudaStream_t stream, const MergeWait* wait = nullptr);
+cudaError_t launch_push_records(const float* record, void* const* peer_slots, void* const* peer_flags, int world,
+                                int64_t record_floats, uint32_t epoch, cudaStream_t stream);
 cudaError_t launch_kv_append(void* k_cache, void* v_cache, const void* k_in, const void* v_in, int64_t batch,
                              int n_kv, int head_dim, int64_t max_seq, int64_t pos, const int32_t* positions,
                              cudaStream_t stream);
@@ -49,6 +60,11 @@ cudaError_t launch_bf16_to_f32(const void* src, float* dst, int64_t n, cudaStrea
 cudaError_t launch_backward_f32(const float* q, const float* k, const float* v, const float* out, const float* d_out,
                                 const float* lse, float* dq, float* dk, float* dv, float* delta_ws, int64_t batch,
                                 int64_t heads, int64_t seq, int dim, int causal, float scale, cudaStream_t stream);
+
+// ---- backward_tc.cu (mma.sync bf16)
+cudaError_t launch_backward_bf16(const void* q, const void* k, const void* v, const void* out, const void* d_out,
+                                 const float* lse, float* dq, float* dk, float* dv, float* delta_ws, int64_t batch,
+                                 int64_t heads, int64_t seq, int dim, int causal, float scale, cudaStream_t stream);
 
 // ---- prefill_tc.cu (tcgen05 / TMEM / TMA)
 // Element strides of a [B, H, N, D] view whose inner dim is contiguous.

@@ -73,3 +73,93 @@ def all_gather_partials(record, group=None):
     else:  # gloo has no flat-tensor all-gather
         dist.all_gather(list(out.unbind(0)), record.contiguous(), group=group)
     return out
+
+
+class PeerRecordExchange:
+    """Split-KV exchange over peer memory instead of an NCCL all-gather.
+
+    Every rank holds two sets of `world` record slots ([rows, D+1] f32 each) and `world` flags that
+    its peers can write.  One exchange = `rt_splitkv_push_record` (this rank's record goes to its
+    slot on every peer with plain NVLink stores, then the peer's flag is set to the epoch) followed
+    by `rt_attn_merge_records_after` (bounded wait for all flags, then the usual merge).  The two
+    slot sets alternate, so a fast rank cannot overwrite what a slow peer still merges.
+
+    `slots[r]` / `flags[r]` are (tensor, peer base pointers) pairs: with `torch.distributed`
+    they come from symmetric memory (`create`); `local_pair` builds the same structure from ordinary
+    tensors of ONE device so that the kernels can be exercised without a second GPU.
+    """
+
+    def __init__(self, rank: int, world: int, rows: int, dim: int, records, flags, record_ptrs, flag_ptrs):
+        self.rank, self.world, self.rows, self.dim = rank, world, rows, dim
+        self.records = records          # local f32 [2, world, rows, dim + 1]
+        self.flags = flags              # local int32 [2, world]
+        self.record_ptrs = list(record_ptrs)  # base address of every rank's `records`
+        self.flag_ptrs = list(flag_ptrs)      # base address of every rank's `flags`
+        self.epoch = 0
+        if (rows * (dim + 1)) % 4:
+            raise ValueError("rows * (dim + 1) must be a multiple of 4 (16-byte copies)")
+
+    @classmethod
+    def create(cls, rows: int, dim: int, group=None, device=None):
+        """Collective: allocates the slots in symmetric memory and exchanges the peer mappings."""
+        import torch
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+        group = group if group is not None else dist.group.WORLD
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+        records = symm.empty((2, world, rows, dim + 1), dtype=torch.float32, device=device)
+        flags = symm.empty((2, world), dtype=torch.int32, device=device)
+        flags.zero_()
+        h_rec = symm.rendezvous(records, group.group_name)
+        h_flag = symm.rendezvous(flags, group.group_name)
+        torch.cuda.synchronize()
+        dist.barrier(group)  # every rank's flags are zero before anyone pushes
+        ex = cls(rank, world, rows, dim, records, flags, h_rec.buffer_ptrs, h_flag.buffer_ptrs)
+        ex._handles = (h_rec, h_flag)  # keep the mappings alive
+        return ex
+
+    @classmethod
+    def local_pair(cls, world: int, rows: int, dim: int, device="cuda"):
+        """`world` exchange objects whose "peers" are buffers of one device (tests, single GPU)."""
+        import torch
+        recs = [torch.zeros((2, world, rows, dim + 1), dtype=torch.float32, device=device) for _ in range(world)]
+        flgs = [torch.zeros((2, world), dtype=torch.int32, device=device) for _ in range(world)]
+        return [cls(r, world, rows, dim, recs[r], flgs[r], [t.data_ptr() for t in recs], [t.data_ptr() for t in flgs])
+                for r in range(world)]
+
+    def next_epoch(self):
+        """Advances the epoch; returns the slot (a [rows, D+1] view of local memory) that this rank's
+        decode kernel should write its record into for this exchange."""
+        self.epoch += 1
+        return self.records[self.epoch & 1, self.rank]
+
+    def push(self):
+        import ctypes
+        from . import _lib
+        from .gqa import _stream_ptr
+        par = self.epoch & 1
+        rec_bytes = self.rows * (self.dim + 1) * 4
+        slot_off = (par * self.world + self.rank) * rec_bytes
+        flag_off = (par * self.world + self.rank) * 4
+        slots = (ctypes.c_void_p * self.world)(*[p + slot_off for p in self.record_ptrs])
+        flags = (ctypes.c_void_p * self.world)(*[p + flag_off for p in self.flag_ptrs])
+        rc = _lib.lib().rt_splitkv_push_record(self.records[par, self.rank].data_ptr(), slots, flags, self.world,
+                                               self.rows, self.dim, self.epoch, _stream_ptr())
+        _lib.check(rc, "rt_splitkv_push_record")
+
+    def merge(self, out_dtype=None, wait_clocks: int = 0):
+        import torch
+        from . import _lib
+        from .gqa import _stream_ptr
+        par = self.epoch & 1
+        out_dtype = out_dtype or torch.bfloat16
+        out = torch.empty((self.rows, self.dim), dtype=out_dtype, device=self.records.device)
+        lse = torch.empty((self.rows,), dtype=torch.float32, device=self.records.device)
+        rc = _lib.lib().rt_attn_merge_records_after(self.records[par].data_ptr(), self.flags[par].data_ptr(), self.epoch,
+                                                    wait_clocks, self.world, self.rows, self.dim,
+                                                    out.data_ptr() if out_dtype == torch.bfloat16 else None,
+                                                    out.data_ptr() if out_dtype == torch.float32 else None,
+                                                    lse.data_ptr(), _stream_ptr())
+        _lib.check(rc, "rt_attn_merge_records_after")
+        return out, lse

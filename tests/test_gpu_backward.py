@@ -100,3 +100,48 @@ def test_backward_linearity_and_full_size_property(oracle):
     for x, y, z in zip(a, b, c):
         assert (x + 2 * y - z).abs().max().item() < 2e-4 * max(1.0, z.abs().max().item())
     assert (a[2].sum(dim=2) - d1.sum(dim=2)).abs().max().item() < 1e-2
+
+
+def _rel_l2(got, ref):
+    return float(np.sqrt(((got.astype(np.float64) - ref) ** 2).sum()) / max(1e-30, np.sqrt((ref.astype(np.float64) ** 2).sum())))
+
+
+@pytest.mark.parametrize("shape", [(1, 2, 64, 64), (2, 2, 200, 64), (1, 3, 257, 128), (2, 1, 512, 128), (1, 1, 1, 64)])
+@pytest.mark.parametrize("causal", [False, True])
+def test_backward_bf16_tensor_core_matches_oracle(oracle, shape, causal):
+    """bf16 operands, P and dS rounded to bf16 inside the kernel (as the forward rounds P), delta from the bf16
+    forward output: gradients within 2e-2 of the largest reference entry and 1e-2 in relative L2."""
+    import torch
+    import rustorch_b200 as rt
+    q, k, v, do_ = (util.normal_bf16(oracle, shape, s) for s in (util.SEED_Q, util.SEED_K, util.SEED_V, 0xD0))
+    rc, rq, rk, rv = oracle.flash_backward(q, k, v, do_, causal=causal)
+    assert rc == 0
+    dq_, dk_, dv_, ddo = (util.to_cuda_bf16(x) for x in (q, k, v, do_))
+    out, lse = rt.prefill_bf16(dq_, dk_, dv_, causal=causal)
+    gq, gk, gv = rt.backward_bf16(dq_, dk_, dv_, out, ddo, lse, causal=causal)
+    torch.cuda.synchronize()
+    for name, got, ref in (("dq", gq, rq), ("dk", gk, rk), ("dv", gv, rv)):
+        got = util.to_np(got)
+        assert np.all(np.isfinite(got)), name
+        lim = 2e-2 * max(1.0, float(np.abs(ref).max()))
+        assert np.abs(got - ref).max() <= lim, f"{name} {shape} causal={causal}: {np.abs(got - ref).max():.3e} > {lim:.3e}"
+        if shape[2] > 1:
+            assert _rel_l2(got, ref) <= 1e-2, f"{name} {shape} causal={causal}: rel L2 {_rel_l2(got, ref):.3e}"
+
+
+def test_backward_bf16_agrees_with_f32_kernel_at_size(oracle):
+    """At a size beyond the O(N^2)-memory oracle the two CUDA backward kernels (f32 CUDA cores, bf16 tensor
+    cores) are compared with each other on the same bf16-representable inputs."""
+    import torch
+    import rustorch_b200 as rt
+    B, H, N, D = 1, 2, 1536, 128
+    g = torch.Generator(device="cuda").manual_seed(9)
+    q, k, v, do_ = (torch.randn((B, H, N, D), device="cuda", generator=g).to(torch.bfloat16) for _ in range(4))
+    out, lse = rt.prefill_bf16(q, k, v, causal=True)
+    a = rt.backward_bf16(q, k, v, out, do_, lse, causal=True)
+    of, lf = rt.prefill_f32(q.float(), k.float(), v.float(), causal=True)
+    b = rt.backward_f32(q.float(), k.float(), v.float(), of, do_.float(), lf, causal=True)
+    torch.cuda.synchronize()
+    for x, y in zip(a, b):
+        rel = ((x - y).double().norm() / y.double().norm()).item()
+        assert rel < 1e-2, rel

@@ -255,3 +255,56 @@ def test_rope_kv_append_then_decode(oracle, style, code):
     out, _ = rt.gqa_decode(dq, dk, dv, kv_lens=util.to_cuda(lens + 1))
     _, ref, _ = oracle.gqa_decode_cache(util.to_np(dq), kc, vc, lens + 1)
     util.check_output(util.to_np(out), ref, label="rope + append + decode")
+
+
+def test_peer_exchange_push_and_merge_on_one_device(oracle):
+    """The split-KV exchange over peer stores (rt_splitkv_push_record + rt_attn_merge_records_after), with the
+    "peers" being buffers of one device: every emulated rank decodes its KV shard into its own slot, pushes it
+    to all ranks, and every rank's merge equals the merge of the gathered records, twice in a row (the two
+    slot sets alternate)."""
+    import torch
+    import rustorch_b200 as rt
+    from rustorch_b200 import _lib, sharding
+    B, Hq, Hkv, D, S, world = 1, 32, 8, 128, 3000, 3
+    q, k, v, lens = _problem(oracle, B, Hq, Hkv, D, S, [2900])
+    dk, dv, dl = util.to_cuda_bf16(k), util.to_cuda_bf16(v), util.to_cuda(lens)
+    ranks = sharding.PeerRecordExchange.local_pair(world, B * Hq, D)
+    for step in range(2):
+        qs = util.normal_bf16(oracle, (B, Hq, D), 77 + step)
+        dq = util.to_cuda_bf16(qs)
+        recs = []
+        for r, ex in enumerate(ranks):
+            b0, b1 = sharding.kv_shard(2900, world, r, align=16)
+            recs.append(rt.gqa_decode_record(dq, dk, dv, kv_lens=dl, kv_begin=b0, kv_end=b1, record=ex.next_epoch()))
+        for ex in ranks:
+            ex.push()
+        want, want_lse = rt.merge_records(torch.stack([r.clone() for r in recs]), out_dtype=torch.float32)
+        for ex in ranks:
+            got, got_lse = ex.merge(out_dtype=torch.float32)
+            assert torch.equal(got, want) and torch.equal(got_lse, want_lse)
+        torch.cuda.synchronize()
+        assert _lib.device_status() == 0
+        _, ref, ref_lse = oracle.gqa_decode_cache(qs, k, v, lens)
+        util.check_output(util.to_np(want).reshape(B, Hq, D), ref, bf16_out=False, label=f"exchange step {step}")
+        util.check_lse(util.to_np(want_lse).reshape(B, Hq), ref_lse)
+
+
+def test_peer_exchange_wait_runs_out_and_reports(oracle):
+    """A record that never arrives: the merge's bounded wait (here ~10 ms) expires, the kernel leaves the outputs
+    alone, the status word reports code 301, and the context stays usable."""
+    import torch
+    import rustorch_b200 as rt
+    from rustorch_b200 import _lib, sharding
+    ranks = sharding.PeerRecordExchange.local_pair(2, 32, 128)
+    ranks[0].next_epoch().fill_(1.0)
+    ranks[0].push()              # rank 1 never pushes: flag 1 on rank 0 stays 0
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    out, lse = ranks[0].merge(out_dtype=torch.float32, wait_clocks=20_000_000)
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 301
+    assert _lib.device_status() == 0  # reading clears it
+    # the device still works
+    o, l = rt.merge_records(torch.ones((2, 32, 129), dtype=torch.float32, device="cuda"), out_dtype=torch.float32)
+    torch.cuda.synchronize()
+    assert torch.allclose(o, torch.ones_like(o))
