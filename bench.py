@@ -366,34 +366,39 @@ def main():
         del k1, v1
         torch.cuda.empty_cache()
 
-    # ---------------------------------------------------------------- f32 backward (CUDA cores; auxiliary line)
+    # ---------------------------------------------------------------- backward (auxiliary line)
     backward = None
     if "backward" in legs and n_gpus == 1:
-        Bb, Hb, Nb, Db = 4, 16, 2048, 64
         g = torch.Generator(device="cuda").manual_seed(0xBAC0 + rank)
-        qb, kb, vb, dob = (torch.randn((Bb, Hb, Nb, Db), device="cuda", generator=g) for _ in range(4))
-        ob, lseb = rt.prefill_f32(qb, kb, vb, causal=True)
+        qb, kb, vb, dob = (torch.randn((B, H, N, D), device="cuda", generator=g).to(torch.bfloat16) for _ in range(4))
+        ob, lseb = rt.prefill_bf16(qb, kb, vb, causal=True)
 
         def step_backward():
-            rt.backward_f32(qb, kb, vb, ob, dob, lseb, causal=True)
+            rt.backward_bf16(qb, kb, vb, ob, dob, lseb, causal=True)
 
-        bsteps = max(3, min(args.steps, 10))
+        bsteps = max(3, min(args.steps, 20))
         bms = timed(step_backward, bsteps, 3, dist, torch)
         # five N x N x D products (S, dP, dV, dQ, dK) over the unmasked pairs, 2 flops per multiply-add
-        pairs = Bb * Hb * (Nb * (Nb + 1) / 2)
-        btf = 10.0 * Db * pairs / (bms * 1e-3) / 1e12
-        backward = {"metric": "attn_backward_tflops", "value": btf, "unit": "TFLOP/s", "ms_per_step": bms, "dtype": "f32",
+        btf = 2.5 * flops / (bms * 1e-3) / 1e12
+        # the exact f32 companion on a smaller shape (CUDA cores)
+        Bf, Hf, Nf, Df = 2, 8, 2048, 64
+        qf, kf, vf, dof = (torch.randn((Bf, Hf, Nf, Df), device="cuda", generator=g) for _ in range(4))
+        of, lsef = rt.prefill_f32(qf, kf, vf, causal=True)
+        fms = timed(lambda: rt.backward_f32(qf, kf, vf, of, dof, lsef, causal=True), 3, 2, dist, torch)
+        ftf = 10.0 * Df * Bf * Hf * (Nf * (Nf + 1) / 2) / (fms * 1e-3) / 1e12
+        backward = {"metric": "attn_backward_tflops", "value": btf, "unit": "TFLOP/s", "ms_per_step": bms, "dtype": "bf16",
                     "steps": bsteps,
-                    "config": {"workload": f"causal backward f32 B={Bb} H={Hb} N={Nb} D={Db} (dQ, dK, dV from saved O, LSE)",
+                    "config": {"workload": f"causal backward bf16 B={B} H={H} N={N} D={D} (dQ, dK, dV f32 from saved O, LSE)",
                                "flop_convention": "10*D*unmasked (q,k) pairs; the two-pass kernel executes 14*D (scores "
                                                   "and dP are recomputed in the second pass)",
-                               "l2": "Q,K,V,O,dO,dQ,dK,dV = 268 MB per step, larger than the 126 MB L2"},
-                    "roofline": {"bound": "fp32 CUDA cores", "achieved": btf * 1.4, "peak": 74.4, "unit": "TFLOP/s",
-                                 "frac": btf * 1.4 / 74.4,
-                                 "peak_source": "nominal 148 SM x 128 FMA x 2 x 1.965 GHz (no measured f32 peak on file); "
-                                                "achieved counts the executed 14*D flops"},
+                               "l2": "Q,K,V,O,dO bf16 + dQ,dK,dV f32 = 1 GiB per step, larger than the 126 MB L2"},
+                    "roofline": {"bound": "tensor", "achieved": btf * 1.4, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                                 "frac": btf * 1.4 / peaks["bf16_tflops"], "peak_source": peaks["source"],
+                                 "note": "mma.sync path (no tcgen05 yet); achieved counts the executed 14*D flops"},
+                    "f32_companion": {"value": ftf, "unit": "TFLOP/s", "ms_per_step": fms,
+                                      "workload": f"causal backward f32 B={Bf} H={Hf} N={Nf} D={Df}, CUDA cores"},
                     "gpu_launches": 3 * bsteps}
-        del qb, kb, vb, dob, ob, lseb
+        del qb, kb, vb, dob, ob, lseb, qf, kf, vf, dof, of, lsef
         torch.cuda.empty_cache()
 
     # ---------------------------------------------------------------- CPU baseline (rank 0, N = 1 only)
