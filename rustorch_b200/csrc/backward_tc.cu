@@ -14,7 +14,8 @@
 // for the accumulating ones, and the score accumulators are re-packed in registers as the A operand
 // of the accumulating product.  P and dS are rounded to bf16 for those products, as the forward
 // rounds P.  No atomics; a causal launch skips the tiles beyond the diagonal.
-// Tiles are staged with plain 16-byte loads into 128-byte-swizzled shared memory.
+// The other side's tiles travel global -> 128-byte-swizzled shared memory with cp.async into two
+// stages, so the loads of tile t+1 overlap the MMAs of tile t.
 #include "common.cuh"
 #include "kernels.h"
 
@@ -62,6 +63,27 @@ __device__ __forceinline__ void load_tile(uint8_t* tile, const __nv_bfloat16* sr
     }
 }
 
+// The same through cp.async (no registers held, completion by commit/wait groups); rows >= N are
+// zero-filled by a zero source size (the source address is clamped to a valid row).
+template <int D>
+__device__ __forceinline__ void load_tile_async(uint8_t* tile, const __nv_bfloat16* src, int64_t r0, int64_t n_rows) {
+    constexpr int CH = D / 8;
+    const uint32_t base = smem_u32(tile);
+    for (int i = threadIdx.x; i < kRows * CH; i += blockDim.x) {
+        const int r = i / CH, c = i % CH;
+        const bool in = r0 + r < n_rows;
+        const __nv_bfloat16* g = src + (in ? r0 + r : 0) * D + c * 8;
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(base + tile_off(r, c)), "l"(g),
+                     "r"(in ? 16 : 0)
+                     : "memory");
+    }
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int kPending>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(kPending) : "memory");
+}
+
 }  // namespace
 
 struct BwdTcParams {
@@ -98,10 +120,8 @@ __global__ void __launch_bounds__(128) bwd_tc_kernel(const BwdTcParams p) {
     extern __shared__ __align__(1024) uint8_t smem_bwd[];
     uint8_t* sX1 = smem_bwd;             // own rows: Q (query side) / K (key side)
     uint8_t* sX2 = sX1 + TILE;           // own rows: dO           / V
-    uint8_t* sY1 = sX2 + TILE;           // other tile: K          / Q
-    uint8_t* sY2 = sY1 + TILE;           // other tile: V          / dO
-    float* sLse = reinterpret_cast<float*>(sY2 + TILE);  // [64] statistics of the tile's QUERY rows (log2 units)
-    float* sDelta = sLse + kRows;                        // [64]
+    uint8_t* sY = sX2 + TILE;            // two stages of the other side: [stage][K, V] / [stage][Q, dO]
+    float* sStat = reinterpret_cast<float*>(sY + 4 * TILE);  // [2 stages][lse (natural log) | delta][64] of QUERY rows
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
@@ -115,11 +135,15 @@ __global__ void __launch_bounds__(128) bwd_tc_kernel(const BwdTcParams p) {
 
     load_tile<D>(sX1, X1, own0, N);
     load_tile<D>(sX2, X2, own0, N);
-    if (!kKeySide && threadIdx.x < kRows) {  // the own rows are the query rows: their statistics never change
-        const int64_t r = own0 + threadIdx.x;
-        sLse[threadIdx.x] = r < N ? p.lse[bh * N + r] * kLog2e : -INFINITY;
-        sDelta[threadIdx.x] = r < N ? p.delta[bh * N + r] : 0.f;
-    }
+    // query statistics: of the own rows (query side, loaded once into stage 0) or of each tile (key side)
+    auto load_stats = [&](int stage, int64_t r0) {
+        if (threadIdx.x < kRows) {
+            const int64_t r = r0 + threadIdx.x;
+            sStat[stage * 2 * kRows + threadIdx.x] = r < N ? p.lse[bh * N + r] : -INFINITY;
+            sStat[stage * 2 * kRows + kRows + threadIdx.x] = r < N ? p.delta[bh * N + r] : 0.f;
+        }
+    };
+    if (!kKeySide) load_stats(0, own0);
 
     // other-side tile range
     int64_t t_lo = 0, t_hi = N;
@@ -139,20 +163,30 @@ __global__ void __launch_bounds__(128) bwd_tc_kernel(const BwdTcParams p) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) z2[j][e] = 0.f;
 
-    const uint32_t x1_a = smem_u32(sX1), x2_a = smem_u32(sX2), y1_a = smem_u32(sY1), y2_a = smem_u32(sY2);
+    const uint32_t x1_a = smem_u32(sX1), x2_a = smem_u32(sX2);
     const int lr = lane & 7, lm = lane >> 3;          // ldmatrix: this lane addresses row lr of matrix lm
     const int a_row = warp * 16 + (lm & 1) * 8 + lr;  // A operand: matrices 0,2 rows 0-7; 1,3 rows 8-15
 
-    for (int64_t t0 = t_lo; t0 < t_hi; t0 += kRows) {
-        __syncthreads();  // the previous tile is no longer read (also orders the X loads before first use)
-        load_tile<D>(sY1, Y1, t0, N);
-        load_tile<D>(sY2, Y2, t0, N);
-        if (kKeySide && threadIdx.x < kRows) {
-            const int64_t r = t0 + threadIdx.x;
-            sLse[threadIdx.x] = r < N ? p.lse[bh * N + r] * kLog2e : -INFINITY;
-            sDelta[threadIdx.x] = r < N ? p.delta[bh * N + r] : 0.f;
+    auto prefetch = [&](int stage, int64_t t0) {
+        load_tile_async<D>(sY + (stage * 2) * TILE, Y1, t0, N);
+        load_tile_async<D>(sY + (stage * 2 + 1) * TILE, Y2, t0, N);
+        if (kKeySide) load_stats(stage, t0);
+        cp_async_commit();
+    };
+    if (t_lo < t_hi) prefetch(0, t_lo);
+    int stage = 0;
+    for (int64_t t0 = t_lo; t0 < t_hi; t0 += kRows, stage ^= 1) {
+        // the other stage was last read in the previous iteration; every warp has passed its barrier below
+        if (t0 + kRows < t_hi) {
+            prefetch(stage ^ 1, t0 + kRows);
+            cp_async_wait<1>();  // this iteration's tile has landed (the prefetch just issued may be in flight)
+        } else {
+            cp_async_wait<0>();
         }
-        __syncthreads();
+        __syncthreads();  // copies and statistics of all threads visible (also orders the X loads before first use)
+        const uint32_t y1_a = smem_u32(sY + (stage * 2) * TILE), y2_a = smem_u32(sY + (stage * 2 + 1) * TILE);
+        const float* sLse = sStat + (kKeySide ? stage * 2 * kRows : 0);
+        const float* sDelta = sLse + kRows;
 
 #pragma unroll
         for (int half = 0; half < 2; ++half) {  // 32 columns of the other tile at a time (register budget)
@@ -198,9 +232,9 @@ __global__ void __launch_bounds__(128) bwd_tc_kernel(const BwdTcParams p) {
                     const int64_t own = own0 + r_own, oth = t0 + c_oth;
                     const int64_t qi = kKeySide ? oth : own, kj = kKeySide ? own : oth;
                     const int stat = kKeySide ? c_oth : r_own;
-                    const float lse2 = sLse[stat];
-                    const bool vis = own < N && oth < N && !(p.causal && kj > qi) && lse2 != -INFINITY;
-                    const float prob = vis ? fast_exp2(t1[j][e] * p.scale_log2 - lse2) : 0.f;
+                    const float lse = sLse[stat];
+                    const bool vis = own < N && oth < N && !(p.causal && kj > qi) && lse != -INFINITY;
+                    const float prob = vis ? fast_exp2(t1[j][e] * p.scale_log2 - lse * kLog2e) : 0.f;
                     pv[e] = prob;
                     dv[e] = prob * (t2[j][e] - sDelta[stat]) * p.scale;
                 }
@@ -233,6 +267,7 @@ __global__ void __launch_bounds__(128) bwd_tc_kernel(const BwdTcParams p) {
                 }
             }
         }
+        __syncthreads();  // every warp is done with this stage before the next iteration refills it
     }
 
     // ---- write the own rows: element e of n-tile j = row g + 8*(e>>1), column j*8 + 2t + (e&1)
@@ -254,7 +289,7 @@ __global__ void __launch_bounds__(128) bwd_tc_kernel(const BwdTcParams p) {
 
 template <int D>
 static cudaError_t launch_bwd_tc(const BwdTcParams& p, int64_t bh, cudaStream_t stream) {
-    const size_t smem = (size_t)4 * kRows * D * 2 + 2 * kRows * sizeof(float);
+    const size_t smem = (size_t)6 * kRows * D * 2 + 4 * kRows * sizeof(float);
     cudaError_t e = cudaFuncSetAttribute(bwd_tc_kernel<D, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e == cudaSuccess)
         e = cudaFuncSetAttribute(bwd_tc_kernel<D, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
