@@ -313,7 +313,7 @@ def main():
                   "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                                "frac": gbs / peaks["hbm_gbs"], "peak_source": peaks["source"],
                                "traffic": traffic.get("gqa_decode_tc_kernel")},
-                  "gpu_launches": 2 * args.steps, "clocks": dclk.summary()}
+                  "gpu_launches": args.steps, "clocks": dclk.summary()}
         del qd, kc, vc
         torch.cuda.empty_cache()
 

@@ -466,7 +466,9 @@ size_t rt_gqa_decode_workspace_bytes(int64_t batch, int64_t n_heads, int64_t n_k
     if (batch <= 0 || n_heads <= 0 || n_kv_heads <= 0 || head_dim <= 0 || max_seq <= 0) return 0;
     const size_t chunks = (size_t)rt::decode_num_chunks(batch, (int)n_kv_heads, max_seq);
     if (chunks <= 1) return 0;
-    return chunks * (size_t)batch * (size_t)n_heads * ((size_t)head_dim + 1) * sizeof(float);
+    // chunk partials (O | LSE) followed by one completion counter per (sequence, KV head)
+    return chunks * (size_t)batch * (size_t)n_heads * ((size_t)head_dim + 1) * sizeof(float) +
+           (((size_t)batch * (size_t)n_kv_heads * sizeof(int) + 15) & ~(size_t)15);
 }
 
 // Shared validation + launch of the decode entries; of_stride / lse_stride are the row pitches (in

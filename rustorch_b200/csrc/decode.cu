@@ -575,11 +575,15 @@ cudaError_t launch_gqa_decode(const void* q, const void* k, const void* v, void*
     p.part_o = (float*)workspace;
     p.part_lse = p.part_o ? p.part_o + (int64_t)decode_num_chunks(batch, n_kv, max_seq) * p.rows * head_dim : nullptr;
     const int group = n_heads / n_kv;
+    // after the partials: one completion counter per (sequence, KV head) for the in-kernel merge
+    int* counters = p.part_lse ? reinterpret_cast<int*>(p.part_lse + (int64_t)decode_num_chunks(batch, n_kv, max_seq) * p.rows)
+                               : nullptr;
+    bool merged = false;
     cudaError_t e = cudaErrorNotSupported;
     if (decode_use_tensor_cores())
         e = launch_gqa_decode_tc(q, k, v, out_bf16, out_f32, lse, batch, n_heads, n_kv, head_dim, max_seq, kv_lens,
-                                 kv_len_uniform, kv_begin, kv_end, scale, p.part_o, p.part_lse, p.chunk, p.n_chunks,
-                                 p.of_stride, p.lse_stride, stream);
+                                 kv_len_uniform, kv_begin, kv_end, scale, p.part_o, p.part_lse, counters, p.chunk,
+                                 p.n_chunks, p.of_stride, p.lse_stride, &merged, stream);
     if (e == cudaErrorNotSupported) {  // head dim 256, or a cache too large for 32-bit TMA row coordinates
         switch (head_dim) {
             case 64: e = launch_decode_d<64>(p, group, batch, stream); break;
@@ -589,7 +593,7 @@ cudaError_t launch_gqa_decode(const void* q, const void* k, const void* v, void*
         }
     }
     if (e != cudaSuccess) return e;
-    if (p.n_chunks > 1) {
+    if (p.n_chunks > 1 && !merged) {
         merge_partials_kernel<<<(unsigned)p.rows, kMergeWarps * 32, merge_smem_bytes(p.n_chunks, head_dim), stream>>>(
             p.part_o, p.part_lse, p.n_chunks, p.rows, head_dim, head_dim, 1, p.out_bf16, p.out_f32, lse, p.of_stride,
             p.lse_stride, MergeWait{nullptr, 0, 0u, 0, nullptr});

@@ -17,6 +17,7 @@
 // the launch has a single chunk.  Rows past the visible range are masked in the scores and
 // zeroed in V (uninitialised cache memory may hold NaN bit patterns).  Waits are bounded.
 #include <cuda.h>
+#include <cstdlib>
 
 #include "kernels.h"
 #include "tc_ptx.cuh"
@@ -42,7 +43,86 @@ struct DecodeTcParams {
     int64_t of_stride, lse_stride;  // floats between consecutive rows of out_f32 / lse
     float scale_log2;
     int* status;
+    int* counters;  // NULL, or [B * Hkv] zeroed before the launch: the last chunk of a group merges its partials
 };
+
+// Called by every CTA of a multi-chunk launch once its partial is written.  The CTA that completes
+// its (sequence, KV head) group combines the group's chunk partials with the (m, l) merge of
+// online_softmax.rs:105-131 and writes the final rows, so no separate merge launch is needed:
+// for short chunks that launch costs as much as the streaming itself.  Partials of other CTAs are
+// read with cache-global loads after a device-scope fence.
+template <int D, int G>
+__device__ __forceinline__ void finish_group(const DecodeTcParams& p, int b, int kvh, int64_t row0, float* scratch) {
+    __shared__ int s_last;
+    __shared__ float s_red[4];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) s_last = (atomicAdd(&p.counters[b * p.n_kv + kvh], 1) == p.n_chunks - 1);
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    float* w_sm = scratch;  // [n_chunks]
+    for (int gg = 0; gg < G; ++gg) {
+        const int64_t row = row0 + gg;
+        float m = -INFINITY;
+        for (int c = tid; c < p.n_chunks; c += 128) {
+            const float x = __ldcg(p.part_lse + (int64_t)c * p.rows + row);
+            w_sm[c] = x;
+            m = fmaxf(m, x);
+        }
+#pragma unroll
+        for (int off = 16; off; off >>= 1) m = fmaxf(m, __shfl_xor_sync(kFullMask, m, off));
+        __syncthreads();  // s_red free (previous row), w_sm written
+        if (lane == 0) s_red[warp] = m;
+        __syncthreads();
+        m = fmaxf(fmaxf(s_red[0], s_red[1]), fmaxf(s_red[2], s_red[3]));
+        float l = 0.f;
+        if (m != -INFINITY) {
+            for (int c = tid; c < p.n_chunks; c += 128) {
+                const float x = w_sm[c];
+                const float w = (x == -INFINITY) ? 0.f : expf(x - m);
+                w_sm[c] = w;
+                l += w;
+            }
+        }
+#pragma unroll
+        for (int off = 16; off; off >>= 1) l += __shfl_xor_sync(kFullMask, l, off);
+        __syncthreads();  // everyone has read s_red (max); weights written
+        if (lane == 0) s_red[warp] = l;
+        __syncthreads();
+        l = (s_red[0] + s_red[1]) + (s_red[2] + s_red[3]);
+        const float inv = (l > 0.f) ? 1.f / l : 0.f;
+        for (int d = tid; d < D; d += 128) {
+            float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+            if (l > 0.f) {
+                const float* src = p.part_o + row * D + d;
+                const int64_t cs = p.rows * D;
+                int c = 0;
+                for (; c + 4 <= p.n_chunks; c += 4) {  // four independent loads in flight; empty chunks may be uninitialised
+                    const float w0 = w_sm[c], w1 = w_sm[c + 1], w2 = w_sm[c + 2], w3 = w_sm[c + 3];
+                    const float x0 = w0 != 0.f ? __ldcg(src + (int64_t)c * cs) : 0.f;
+                    const float x1 = w1 != 0.f ? __ldcg(src + (int64_t)(c + 1) * cs) : 0.f;
+                    const float x2 = w2 != 0.f ? __ldcg(src + (int64_t)(c + 2) * cs) : 0.f;
+                    const float x3 = w3 != 0.f ? __ldcg(src + (int64_t)(c + 3) * cs) : 0.f;
+                    a0 = fmaf(w0, x0, a0);
+                    a1 = fmaf(w1, x1, a1);
+                    a2 = fmaf(w2, x2, a2);
+                    a3 = fmaf(w3, x3, a3);
+                }
+                for (; c < p.n_chunks; ++c) {
+                    const float w0 = w_sm[c];
+                    if (w0 != 0.f) a0 = fmaf(w0, __ldcg(src + (int64_t)c * cs), a0);
+                }
+            }
+            const float outv = ((a0 + a1) + (a2 + a3)) * inv;
+            if (p.out_bf16) p.out_bf16[row * D + d] = __float2bfloat16(outv);
+            if (p.out_f32) p.out_f32[row * p.of_stride + d] = outv;
+        }
+        if (tid == 0 && p.lse) p.lse[row * p.lse_stride] = (l > 0.f) ? m + logf(l) : -INFINITY;
+        __syncthreads();  // w_sm and s_red are reused by the next row
+    }
+}
 
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m, uint64_t* bar, int c0, int c1) {
     asm volatile(
@@ -122,6 +202,7 @@ gqa_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
         } else if (tid < G) {
             p.part_lse[(int64_t)chunk_idx * p.rows + row0 + tid] = -INFINITY;
         }
+        if (!direct && p.counters) finish_group<D, G>(p, b, kvh, row0, reinterpret_cast<float*>(smem));
         return;
     }
 
@@ -313,6 +394,10 @@ gqa_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
             if (d == 0) p.part_lse[(int64_t)chunk_idx * p.rows + row] = lse;
         }
     }
+    if (!direct && p.counters) {
+        __syncthreads();  // the warp-merge scratch at the start of the ring is free again
+        finish_group<D, G>(p, b, kvh, row0, reinterpret_cast<float*>(smem));
+    }
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -361,8 +446,9 @@ static cudaError_t launch_d(const CUtensorMap& mk, const CUtensorMap& mv, const 
 cudaError_t launch_gqa_decode_tc(const void* q, const void* k, const void* v, void* out_bf16, float* out_f32,
                                  float* lse, int64_t batch, int n_heads, int n_kv, int head_dim, int64_t max_seq,
                                  const int32_t* kv_lens, int64_t kv_len_uniform, int64_t kv_begin, int64_t kv_end,
-                                 float scale, float* part_o, float* part_lse, int chunk, int n_chunks,
-                                 int64_t of_stride, int64_t lse_stride, cudaStream_t stream) {
+                                 float scale, float* part_o, float* part_lse, int* counters, int chunk, int n_chunks,
+                                 int64_t of_stride, int64_t lse_stride, bool* merged, cudaStream_t stream) {
+    *merged = false;
     const int64_t cache_rows = batch * n_kv * max_seq;
     if ((head_dim != 64 && head_dim != 128) || cache_rows >= (1ll << 31) - 64) return cudaErrorNotSupported;
     CUtensorMap mk, mv;
@@ -390,6 +476,20 @@ cudaError_t launch_gqa_decode_tc(const void* q, const void* k, const void* v, vo
     p.scale_log2 = scale * kLog2e;
     p.status = device_status_ptr();
     if (!p.status) return cudaErrorInvalidSymbol;
+    // The in-kernel merge is serial per (sequence, KV head): worth it for the few chunks of a batched
+    // decode, not for the hundred-odd chunks of one long sequence, which the merge kernel spreads
+    // over many more threads.
+    constexpr int kMaxFusedChunks = 32;
+    static const bool fused_off = [] {
+        const char* s = getenv("RT_ATTN_DECODE_FUSED_MERGE");
+        return s && s[0] == '0';
+    }();
+    p.counters = (n_chunks > 1 && n_chunks <= kMaxFusedChunks && !fused_off) ? counters : nullptr;
+    if (p.counters) {
+        cudaError_t e = cudaMemsetAsync(p.counters, 0, sizeof(int) * (size_t)batch * n_kv, stream);
+        if (e != cudaSuccess) return e;
+        *merged = true;
+    }
     return head_dim == 128 ? launch_d<128>(mk, mv, p, n_heads / n_kv, batch, stream)
                            : launch_d<64>(mk, mv, p, n_heads / n_kv, batch, stream);
 }

@@ -44,8 +44,8 @@ cudaError_t launch_rope_kv_append(void* q, const void* k_in, const void* v_in, v
 cudaError_t launch_gqa_decode_tc(const void* q, const void* k, const void* v, void* out_bf16, float* out_f32,
                                  float* lse, int64_t batch, int n_heads, int n_kv, int head_dim, int64_t max_seq,
                                  const int32_t* kv_lens, int64_t kv_len_uniform, int64_t kv_begin, int64_t kv_end,
-                                 float scale, float* part_o, float* part_lse, int chunk, int n_chunks,
-                                 int64_t of_stride, int64_t lse_stride, cudaStream_t stream);
+                                 float scale, float* part_o, float* part_lse, int* counters, int chunk, int n_chunks,
+                                 int64_t of_stride, int64_t lse_stride, bool* merged, cudaStream_t stream);
 
 // ---- prefill_simt.cu
 cudaError_t launch_prefill_f32(const float* q, const float* k, const float* v, float* out, float* lse,
