@@ -153,6 +153,33 @@ def cpu_flash_sample(steps: int, warmup: int, target_seconds: float | None):
     return prefill_flops(1, slabs, N, D) / per_step / 1e12, cores, slabs, per_step, len(times)
 
 
+def cpu_decode_sample(n_seq: int = 8, reps: int = 3):
+    """Times the oracle's cache decode (decode_attn_row over (sequence, head), gqa.rs:216-270) on `n_seq`
+    sequences of the config-4 geometry, serial as the reference runs seq_q == 1 (gqa.rs:190-198) and
+    over all host threads.  Bytes are counted as for the GPU (bf16 K and V once per cached token)."""
+    import numpy as np
+    from oracle import oracle as orc
+    orc.set_threads(len(os.sched_getaffinity(0)))
+    cores = orc.get_threads()
+    c = CFG4
+    lens = orc.fill_uniform_int(n_seq, 0x5EED, c["lo"], c["hi"])
+    q = orc.round_to_bf16(orc.fill_normal((n_seq, c["Hq"], c["D"]), 0xC0FFEE))
+    k = orc.round_to_bf16(orc.fill_normal((n_seq, c["Hkv"], c["S"], c["D"]), 0xBADBEEF))
+    v = orc.round_to_bf16(orc.fill_normal((n_seq, c["Hkv"], c["S"], c["D"]), 0xCAFE00))
+    kv_bytes = 2.0 * c["Hkv"] * c["D"] * 2 * float(lens.sum())
+    out = {}
+    for label, par in (("all_cores", True), ("serial_as_written", False)):
+        orc.gqa_decode_cache(q, k, v, lens, parallel=par)
+        ts = []
+        for _ in range(reps):
+            t0 = time.perf_counter()
+            rc, _, _ = orc.gqa_decode_cache(q, k, v, lens, parallel=par)
+            ts.append(time.perf_counter() - t0)
+            assert rc == 0
+        out[label] = kv_bytes / float(np.median(ts)) / 1e9
+    return out, cores, n_seq
+
+
 def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -314,6 +341,13 @@ def main():
                                "frac": gbs / peaks["hbm_gbs"], "peak_source": peaks["source"],
                                "traffic": traffic.get("gqa_decode_tc_kernel")},
                   "gpu_launches": args.steps, "clocks": dclk.summary()}
+        if rank == 0 and n_gpus == 1 and not args.skip_cpu:
+            gb, cores_d, nseq = cpu_decode_sample()
+            decode["cpu_baseline"] = {"value": gb["all_cores"], "unit": "GB/s", "cores": cores_d, "kind": "port",
+                                      "serial_as_written": gb["serial_as_written"],
+                                      "sample": f"{nseq} of 64 sequences of the workload, median of 3; C restatement of "
+                                                f"decode_attn_row over (sequence, head), f32 caches read by the CPU, "
+                                                f"bytes counted as bf16 K and V once per cached token"}
         del qd, kc, vc
         torch.cuda.empty_cache()
 
