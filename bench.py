@@ -234,7 +234,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-cpu", action="store_true", help="skip the cpu_baseline leg (profiling runs)")
-    ap.add_argument("--only", default="", help="comma list of legs: prefill,e2e,decode,splitkv,backward (default all)")
+    ap.add_argument("--only", default="", help="comma list of legs: prefill,e2e,decode,splitkv,backward,published (default all)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -255,7 +255,7 @@ def main():
         dist_mod.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
         dist = dist_mod
     n_gpus = world
-    legs = set(args.only.split(",")) if args.only else {"prefill", "e2e", "decode", "splitkv", "backward"}
+    legs = set(args.only.split(",")) if args.only else {"prefill", "e2e", "decode", "splitkv", "backward", "published"}
     peaks = load_peaks()
     traffic = load_traffic()
     lib = _lib.lib()
@@ -435,6 +435,50 @@ def main():
         del qb, kb, vb, dob, ob, lseb, qf, kf, vf, dof, of, lsef
         torch.cuda.empty_cache()
 
+    # ---------------------------------------------------------------- the shapes the reference publishes numbers for
+    published = None
+    if "published" in legs and n_gpus == 1:
+        g = torch.Generator(device="cuda").manual_seed(0x9B)
+        rows = []
+
+        def graph_ms(fn, iters=50):
+            """The same call captured once into a CUDA graph and replayed: device-side time without the
+            Python/ctypes cost of each enqueue.  None if the capture is refused."""
+            try:
+                fn()
+                torch.cuda.synchronize()
+                cg = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(cg):
+                    fn()
+                return timed(cg.replay, iters, 5, dist, torch)
+            except Exception:
+                return None
+
+        # flash forward, unmasked, flops = 4*B*H*N^2*D (bench-vs-pytorch/benches/compare.rs:191); M4 Max CPU best runs
+        for (Bp, Hp, Np, Dp, ref_ms) in ((2, 4, 2048, 64, 13.09), (1, 4, 1024, 64, 3.40), (1, 1, 512, 64, 0.783)):
+            qf, kf, vf = (torch.randn((Bp, Hp, Np, Dp), device="cuda", generator=g) for _ in range(3))
+            qh, kh, vh = (t.to(torch.bfloat16) for t in (qf, kf, vf))
+            t16 = timed(lambda: rt.prefill_bf16(qh, kh, vh, causal=False), 20, 5, dist, torch)
+            g16 = graph_ms(lambda: rt.prefill_bf16(qh, kh, vh, causal=False))
+            t32 = timed(lambda: rt.prefill_f32(qf, kf, vf, causal=False), 5, 2, dist, torch)
+            fl = 4.0 * Bp * Hp * Np * Np * Dp
+            rows.append({"workload": f"flash forward B={Bp} H={Hp} N={Np} D={Dp}, no mask", "reference_ms": ref_ms,
+                         "reference_hw": "Apple M4 Max CPU (published)", "bf16_tcgen05_ms": t16, "bf16_tcgen05_graph_replay_ms": g16,
+                         "bf16_gflops": fl / t16 / 1e6, "f32_cuda_core_ms": t32})
+        # Metal decode microbenchmarks: Hq=16 Hkv=2 D=256 f32 on the M4 Max GPU (rustorch-metal/src/kernels.rs:14314-14319)
+        for kv, ref_us in ((64, 18.5), (256, 62.0), (1024, 238.0), (4096, 1474.0)):
+            qd1 = torch.randn((1, 16, 256), device="cuda", generator=g).to(torch.bfloat16)
+            kc1 = torch.randn((1, 2, 4096, 256), device="cuda", generator=g).to(torch.bfloat16)
+            vc1 = torch.randn((1, 2, 4096, 256), device="cuda", generator=g).to(torch.bfloat16)
+            td = timed(lambda: rt.gqa_decode(qd1, kc1, vc1, kv_len=kv), 50, 5, dist, torch)
+            gd = graph_ms(lambda: rt.gqa_decode(qd1, kc1, vc1, kv_len=kv))
+            rows.append({"workload": f"GQA decode Hq=16 Hkv=2 D=256 kv_len={kv}, batch 1", "reference_us": ref_us,
+                         "reference_hw": "Apple M4 Max GPU, Metal NSG2 kernel (published)", "bf16_us": td * 1e3,
+                         "bf16_graph_replay_us": None if gd is None else gd * 1e3,
+                         "note": "bf16_us includes the Python/ctypes cost of each enqueue; graph replay is the same call "
+                                 "captured once"})
+        published = rows
+
     # ---------------------------------------------------------------- CPU baseline (rank 0, N = 1 only)
     cpu = None
     if rank == 0 and n_gpus == 1 and not args.skip_cpu:
@@ -458,6 +502,7 @@ def main():
                          "traffic": traffic.get("prefill_tc_kernel")},
             "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": args.steps, "clocks": clocks,
             "decode": decode, "decode_splitkv": splitkv, "backward": backward,
+            "published_shapes": published,
         }
         print(json.dumps(out_line), flush=True)
     if dist is not None:

@@ -130,20 +130,32 @@ def gqa_decode_online_bf16_static(stream, q: int, k_cache: int, v_cache: int, ou
 _default_ws = {}
 
 
+_ws_bytes_cache: dict = {}
+
+
 def gqa_decode(q, k_cache, v_cache, kv_lens=None, kv_len: Optional[int] = None, kv_begin: int = 0, kv_end: int = -1,
-               scale: Optional[float] = None, out_dtype=None, return_lse: bool = True, workspace=None):
+               scale: Optional[float] = None, out_dtype=None, return_lse: bool = True, workspace=None, out=None,
+               lse=None):
     """Batched single-token GQA decode via ``rt_gqa_decode_bf16``.
 
     q [B,Hq,D] bf16, caches [B,Hkv,max_seq,D] bf16 (CUDA, contiguous); kv_lens int32 CUDA [B] or a
     uniform ``kv_len``.  Returns (out [B,Hq,D] in ``out_dtype`` (bf16 default, or float32), lse or None).
+    ``out`` / ``lse`` may be passed in (a decode loop reuses them: nothing is allocated per step).
     """
     import torch
     B, Hq, D = q.shape
     _, Hkv, max_seq, _ = k_cache.shape
-    out_dtype = out_dtype or torch.bfloat16
-    out = torch.empty((B, Hq, D), dtype=out_dtype, device=q.device)
-    lse = torch.empty((B, Hq), dtype=torch.float32, device=q.device) if return_lse else None
-    need = decode_workspace_bytes(B, Hq, Hkv, D, max_seq)
+    if out is None:
+        out_dtype = out_dtype or torch.bfloat16
+        out = torch.empty((B, Hq, D), dtype=out_dtype, device=q.device)
+    else:
+        out_dtype = out.dtype
+    if lse is None and return_lse:
+        lse = torch.empty((B, Hq), dtype=torch.float32, device=q.device)
+    key = (B, Hq, Hkv, D, max_seq)
+    need = _ws_bytes_cache.get(key)
+    if need is None:
+        need = _ws_bytes_cache[key] = decode_workspace_bytes(B, Hq, Hkv, D, max_seq)
     if workspace is None and need:
         key = (q.device.index, need)
         workspace = _default_ws.get(key)
