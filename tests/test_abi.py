@@ -71,9 +71,10 @@ def test_validation_happens_before_any_device_work(lib):
     assert d(p, p, p, None, None, None, 1, 4, 2, 128, 64, None, 3, 0, -1, -1.0, None, 0, None) == L.RT_ERR_NULL_POINTER
     assert d(p, p, p, p, None, None, 1, 4, 2, 128, 4096, None, 3, 0, -1, -1.0, None, 0, None) == L.RT_ERR_WORKSPACE
     assert lib.rt_gqa_decode_workspace_bytes(1, 4, 2, 128, 64) == 0
-    ws = lib.rt_gqa_decode_workspace_bytes(2, 32, 8, 128, 8192)  # n_chunks records of B*Hq rows x (D+1) floats
+    # n_chunks records of B*Hq rows x (D+1) floats, then one int32 completion counter per (sequence, KV head)
+    ws = lib.rt_gqa_decode_workspace_bytes(2, 32, 8, 128, 8192) - 2 * 8 * 4
     assert ws > 0 and ws % (2 * 32 * 129 * 4) == 0 and 8 <= ws // (2 * 32 * 129 * 4) <= 64
-    assert lib.rt_gqa_decode_workspace_bytes(64, 32, 8, 128, 8192) == 8 * 64 * 32 * 129 * 4  # 1024-token chunks
+    assert lib.rt_gqa_decode_workspace_bytes(64, 32, 8, 128, 8192) == 8 * 64 * 32 * 129 * 4 + 64 * 8 * 4  # 1024-token chunks
     assert lib.rt_attn_merge_partials(p, p, 2, 4, 0, p, None, None, None) == L.RT_ERR_ZERO_DIM
     assert lib.rt_attn_merge_partials(p, p, 2, 4, 8, None, None, None, None) == L.RT_ERR_NULL_POINTER
     assert lib.rt_kv_append_bf16(p, p, p, p, 1, 2, 128, 64, 64, None, None) == L.RT_ERR_BAD_LENGTH
