@@ -71,6 +71,7 @@ struct TcParams {
     int64_t o_stride_b, o_stride_h, o_stride_row;  // element strides of the output (inner dim contiguous)
     int n_qb;          // 256-row blocks per head
     int slots_per_head, n_slots, paired;  // static schedule, see tc_item
+    int single_tile;   // items are 128-row blocks handled by Q tile 1 alone (small launches, see tc_item)
 #ifdef RT_TC_TIMELINE
     long long* timeline;  // profiling builds only, see TL_* below
 #endif
@@ -163,7 +164,9 @@ struct TcItem {
 // Static schedule.  The (batch, head)-major slot list is dealt round-robin to the CTAs, so the
 // CTAs running at one time work on a few neighbouring heads and share their K/V in L2.  In
 // paired mode a slot holds the 256-row blocks r and n_qb-1-r of one head, heavy one first: under
-// a causal mask every slot then costs the same, and the CTAs finish together.
+// a causal mask every slot then costs the same, and the CTAs finish together.  A launch with fewer
+// 256-row blocks than 3/4 of the SMs uses 128-row items instead (single_tile): twice the CTAs, each with
+// one Q tile, which shortens the critical path of a small problem.
 template <bool kCausal>
 __device__ __forceinline__ TcItem tc_item(int j, const TcParams& p) {
     TcItem it;
@@ -182,7 +185,9 @@ __device__ __forceinline__ TcItem tc_item(int j, const TcParams& p) {
     it.b = it.bh / p.heads;
     it.h = it.bh % p.heads;
     it.h_kv = it.h / (p.heads / p.heads_kv);
-    it.q0 = qb * 256;
+    // Single-tile items: block qb covers rows [128 qb, 128 qb + 128) and is given to Q tile 1, so the
+    // item's origin lies 128 rows earlier and Q tile 0 takes no part (its rows belong to another item).
+    it.q0 = p.single_tile ? qb * 128 - 128 : qb * 256;
     it.kv_hi = p.seq_kv;
     if (p.kv_lens) {
         const int l = p.kv_lens[it.b];
@@ -191,7 +196,7 @@ __device__ __forceinline__ TcItem tc_item(int j, const TcParams& p) {
     it.q_off = p.q_offsets ? p.q_offsets[it.b] : 0;  // query row i sits at key position i + q_off
     const int n_steps = (it.kv_hi + 63) / 64;        // 64-key steps that hold a visible key
     const int last0 = it.q0 + 127 + it.q_off, last1 = last0 + 128;  // last key each tile's last row may see
-    it.U0 = !kCausal ? n_steps : (last0 < 0 ? 0 : min(n_steps, last0 / 64 + 1));
+    it.U0 = p.single_tile ? 0 : (!kCausal ? n_steps : (last0 < 0 ? 0 : min(n_steps, last0 / 64 + 1)));
     it.U1 = !kCausal ? n_steps : (last1 < 0 ? 0 : min(n_steps, last1 / 64 + 1));
     it.n_tiles = (it.U1 + 1) / 2;
     return it;
@@ -520,7 +525,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             if (w == 0) TL_ITEM(j, 0, tl_globaltimer());
 
             if (n_iter == 0) {  // the tile sees no key: NaN rows, LSE = -inf (cpu_forward.rs:411-420)
-                if (row < N) {
+                if (row < N && !(p.single_tile && w == 0)) {
                     uint4* dst = reinterpret_cast<uint4*>(p.out + it.b * p.o_stride_b + it.h * p.o_stride_h +
                                                           (int64_t)row * p.o_stride_row);
 #pragma unroll
@@ -826,15 +831,20 @@ cudaError_t launch_prefill_tc(const void* q, const void* k, const void* v, void*
     // item.  Other launches (uniform items, or lengths only the device knows) use one CTA per item
     // and leave the balancing to the hardware scheduler.  RT_ATTN_PREFILL_SCHED=persistent|percta
     // overrides the choice.
-    const int64_t n_qb = (seq + 255) / 256;
-    const int64_t n_items = bh * n_qb;
-    if (n_items > 0x3fffffff) return cudaErrorInvalidValue;
     int dev = 0, n_sm = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e == cudaSuccess) e = cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
     if (e != cudaSuccess) return e;
+    p.single_tile = (seq > 128 && bh * ((seq + 255) / 256) * 4 < 3 * (int64_t)n_sm) ? 1 : 0;
+    if (const char* s = getenv("RT_ATTN_PREFILL_TILES")) {
+        if (s[0] == '1') p.single_tile = 1;
+        if (s[0] == '2') p.single_tile = 0;
+    }
+    const int64_t n_qb = p.single_tile ? (seq + 127) / 128 : (seq + 255) / 256;
+    const int64_t n_items = bh * n_qb;
+    if (n_items > 0x3fffffff) return cudaErrorInvalidValue;
     p.n_qb = (int)n_qb;
-    bool persistent = causal && kv_lens == nullptr && n_items >= 2 * (int64_t)n_sm;
+    bool persistent = causal && kv_lens == nullptr && n_items >= 2 * (int64_t)n_sm && !p.single_tile;
     if (const char* s = getenv("RT_ATTN_PREFILL_SCHED")) {
         if (!strcmp(s, "persistent")) persistent = true;
         if (!strcmp(s, "percta")) persistent = false;

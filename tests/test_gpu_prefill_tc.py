@@ -388,3 +388,16 @@ def test_prefill_schedules_agree(oracle, monkeypatch, sched, case):
     _, ref, ref_lse = oracle.attention_general(q, k, v, **okw)
     util.check_output(out, ref, label=f"{case} {sched}")
     util.check_lse(lse, ref_lse)
+
+
+@pytest.mark.parametrize("tiles", ["1", "2"])
+@pytest.mark.parametrize("D,N,causal", [(64, 2048, True), (128, 300, False), (128, 129, True)])
+def test_prefill_single_and_double_tile_items(oracle, monkeypatch, tiles, D, N, causal):
+    """Small launches hand each CTA one 128-row Q tile instead of two (more CTAs for the same rows); both item
+    sizes give the same numbers."""
+    monkeypatch.setenv("RT_ATTN_PREFILL_TILES", tiles)
+    q, k, v = _qkv(oracle, (1, 3, N, D))
+    out, lse = _run_tc(q, k, v, causal=causal)
+    _, ref, ref_lse = oracle.flash_forward_ext(q, k, v, causal=causal)
+    util.check_output(out, ref, label=f"tiles={tiles} N{N} D{D}")
+    util.check_lse(lse, ref_lse)
