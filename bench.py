@@ -477,6 +477,18 @@ def main():
                          "bf16_graph_replay_us": None if gd is None else gd * 1e3,
                          "note": "bf16_us includes the Python/ctypes cost of each enqueue; graph replay is the same call "
                                  "captured once"})
+        # the reference model's own decode call (LlamaModelCuda::decode_step, batch 1): no published number exists
+        qd2 = torch.randn((1, 32, 128), device="cuda", generator=g).to(torch.bfloat16)
+        kc2 = torch.randn((1, 8, 8192, 128), device="cuda", generator=g).to(torch.bfloat16)
+        vc2 = torch.randn((1, 8, 8192, 128), device="cuda", generator=g).to(torch.bfloat16)
+        od2 = torch.empty((1, 32, 128), device="cuda", dtype=torch.bfloat16)
+        for kv in (1024, 4096, 8192):
+            td = timed(lambda: rt.gqa_decode(qd2, kc2, vc2, kv_len=kv, out=od2, return_lse=False), 50, 5, dist, torch)
+            gd = graph_ms(lambda: rt.gqa_decode(qd2, kc2, vc2, kv_len=kv, out=od2, return_lse=False))
+            rows.append({"workload": f"GQA decode Hq=32 Hkv=8 D=128 kv_len={kv}, batch 1 (the reference model's call shape)",
+                         "reference_us": None, "reference_hw": "not published", "bf16_us": td * 1e3,
+                         "bf16_graph_replay_us": None if gd is None else gd * 1e3,
+                         "kv_gbs_graph_replay": None if gd is None else 2.0 * 8 * 128 * 2 * kv / (gd * 1e-3) / 1e9})
         published = rows
 
     # ---------------------------------------------------------------- CPU baseline (rank 0, N = 1 only)

@@ -477,14 +477,18 @@ cudaError_t launch_gqa_decode_tc(const void* q, const void* k, const void* v, vo
     p.status = device_status_ptr();
     if (!p.status) return cudaErrorInvalidSymbol;
     // The in-kernel merge is serial per (sequence, KV head): worth it for the few chunks of a batched
-    // decode, not for the hundred-odd chunks of one long sequence, which the merge kernel spreads
-    // over many more threads.
-    constexpr int kMaxFusedChunks = 32;
+    // decode (config 4 has at most 8), not for the dozens of chunks of one long sequence, which the
+    // merge kernel spreads over many more threads (batch 1, kv_len 4096 = 32 chunks: 20.5 us fused,
+    // 14.4 us with the merge kernel).
+    constexpr int kMaxFusedChunks = 8;
     static const bool fused_off = [] {
         const char* s = getenv("RT_ATTN_DECODE_FUSED_MERGE");
         return s && s[0] == '0';
     }();
-    p.counters = (n_chunks > 1 && n_chunks <= kMaxFusedChunks && !fused_off) ? counters : nullptr;
+    // ... and only for grids of several waves: a small launch (batch 1) is latency-bound, and there the
+    // memset node plus the serial tail cost more than the second launch (14.4 us against 10.3 us).
+    const bool many_ctas = batch * n_kv * (int64_t)n_chunks >= 4 * 148;
+    p.counters = (n_chunks > 1 && n_chunks <= kMaxFusedChunks && many_ctas && !fused_off) ? counters : nullptr;
     if (p.counters) {
         cudaError_t e = cudaMemsetAsync(p.counters, 0, sizeof(int) * (size_t)batch * n_kv, stream);
         if (e != cudaSuccess) return e;
