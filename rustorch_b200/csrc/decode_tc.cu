@@ -422,7 +422,7 @@ template <int D, int G>
 static cudaError_t launch_dg(const CUtensorMap& mk, const CUtensorMap& mv, const DecodeTcParams& p, int64_t batch,
                              cudaStream_t stream) {
     auto kern = gqa_decode_tc_kernel<D, G>;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, DecodeTcCfg<D>::SMEM_BYTES);
+    cudaError_t e = set_max_dynamic_smem_once<gqa_decode_tc_kernel<D, G>>(DecodeTcCfg<D>::SMEM_BYTES);
     if (e != cudaSuccess) return e;
     dim3 grid(p.n_chunks, p.n_kv, (unsigned)batch);
     kern<<<grid, 128, DecodeTcCfg<D>::SMEM_BYTES, stream>>>(mk, mv, p);

@@ -56,6 +56,20 @@ cudaError_t launch_prefill_f32(const float* q, const float* k, const float* v, f
 cudaError_t launch_f32_to_bf16(const float* src, void* dst, int64_t n, cudaStream_t stream);
 cudaError_t launch_bf16_to_f32(const void* src, float* dst, int64_t n, cudaStream_t stream);
 
+// Raises a kernel's dynamic shared-memory limit once per device instead of on every launch (the value
+// per kernel never changes; a race between two first launches sets the same value twice).
+template <auto Kern>
+inline cudaError_t set_max_dynamic_smem_once(int bytes) {
+    static bool done[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev >= 0 && dev < 64 && done[dev]) return cudaSuccess;
+    e = cudaFuncSetAttribute(Kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e == cudaSuccess && dev >= 0 && dev < 64) done[dev] = true;
+    return e;
+}
+
 // ---- backward_simt.cu
 cudaError_t launch_backward_f32(const float* q, const float* k, const float* v, const float* out, const float* d_out,
                                 const float* lse, float* dq, float* dk, float* dv, float* delta_ws, int64_t batch,

@@ -782,7 +782,7 @@ template <int D, bool kCausal, bool kKeep>
 static cudaError_t launch_tc(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mo,
                              const TcParams& p, int64_t n_ctas, cudaStream_t stream) {
     auto kern = prefill_tc_kernel<D, kCausal, kKeep>;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TcCfg<D>::SMEM_BYTES);
+    cudaError_t e = set_max_dynamic_smem_once<prefill_tc_kernel<D, kCausal, kKeep>>(TcCfg<D>::SMEM_BYTES);
     if (e != cudaSuccess) return e;
     kern<<<(unsigned)n_ctas, 384, TcCfg<D>::SMEM_BYTES, stream>>>(mq, mk, mv, mo, p);
     return cudaGetLastError();
