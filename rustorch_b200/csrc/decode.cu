@@ -584,7 +584,7 @@ cudaError_t launch_gqa_decode(const void* q, const void* k, const void* v, void*
         e = launch_gqa_decode_tc(q, k, v, out_bf16, out_f32, lse, batch, n_heads, n_kv, head_dim, max_seq, kv_lens,
                                  kv_len_uniform, kv_begin, kv_end, scale, p.part_o, p.part_lse, counters, p.chunk,
                                  p.n_chunks, p.of_stride, p.lse_stride, &merged, stream);
-    if (e == cudaErrorNotSupported) {  // head dim 256, or a cache too large for 32-bit TMA row coordinates
+    if (e == cudaErrorNotSupported) {  // a cache too large for 32-bit TMA row coordinates, or RT_ATTN_DECODE_IMPL=simt
         switch (head_dim) {
             case 64: e = launch_decode_d<64>(p, group, batch, stream); break;
             case 128: e = launch_decode_d<128>(p, group, batch, stream); break;

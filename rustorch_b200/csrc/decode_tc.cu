@@ -1,4 +1,4 @@
-// Split-KV GQA decode, TMA-staged and tensor-core assisted (head dim 64 or 128).
+// Split-KV GQA decode, TMA-staged and tensor-core assisted (head dim 64, 128 or 256).
 //
 // Same contract and partial format as gqa_decode_splitkv_kernel (decode.cu) — it replaces the
 // reference's per-head scalar decode kernels (crates/rustorch-cuda/src/llm_kernels.rs:376-536)
@@ -450,7 +450,8 @@ cudaError_t launch_gqa_decode_tc(const void* q, const void* k, const void* v, vo
                                  int64_t of_stride, int64_t lse_stride, bool* merged, cudaStream_t stream) {
     *merged = false;
     const int64_t cache_rows = batch * n_kv * max_seq;
-    if ((head_dim != 64 && head_dim != 128) || cache_rows >= (1ll << 31) - 64) return cudaErrorNotSupported;
+    if ((head_dim != 64 && head_dim != 128 && head_dim != 256) || cache_rows >= (1ll << 31) - 64)
+        return cudaErrorNotSupported;
     CUtensorMap mk, mv;
     if (!make_cache_map(&mk, k, cache_rows, head_dim) || !make_cache_map(&mv, v, cache_rows, head_dim))
         return cudaErrorNotSupported;
@@ -494,8 +495,9 @@ cudaError_t launch_gqa_decode_tc(const void* q, const void* k, const void* v, vo
         if (e != cudaSuccess) return e;
         *merged = true;
     }
-    return head_dim == 128 ? launch_d<128>(mk, mv, p, n_heads / n_kv, batch, stream)
-                           : launch_d<64>(mk, mv, p, n_heads / n_kv, batch, stream);
+    return head_dim == 256   ? launch_d<256>(mk, mv, p, n_heads / n_kv, batch, stream)
+           : head_dim == 128 ? launch_d<128>(mk, mv, p, n_heads / n_kv, batch, stream)
+                             : launch_d<64>(mk, mv, p, n_heads / n_kv, batch, stream);
 }
 
 }  // namespace rt
