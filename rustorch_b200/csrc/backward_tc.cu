@@ -18,30 +18,13 @@
 // stages, so the loads of tile t+1 overlap the MMAs of tile t.
 #include "common.cuh"
 #include "kernels.h"
+#include "mma_sync.cuh"
 
 namespace rt {
 
 namespace {
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
-                 : "r"(addr));
-}
-__device__ __forceinline__ void ldsm_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
-                 : "r"(addr));
-}
-// D = A(16x16, row) * B(16x8, col) + D, bf16 inputs, f32 accumulate.
-__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
 
 constexpr int kRows = 64;  // rows per tile (own side and other side)
 
@@ -203,17 +186,17 @@ __global__ void __launch_bounds__(128) bwd_tc_kernel(const BwdTcParams p) {
 #pragma unroll
                 for (int s = 0; s < 2; ++s) {
                     const int chunk = (kp * 2 + s) * 2 + (lm >> 1);
-                    ldsm_x4(x1_a + tile_off(a_row, chunk), a1[s][0], a1[s][1], a1[s][2], a1[s][3]);
-                    ldsm_x4(x2_a + tile_off(a_row, chunk), a2[s][0], a2[s][1], a2[s][2], a2[s][3]);
+                    ldmatrix_x4(x1_a + tile_off(a_row, chunk), a1[s][0], a1[s][1], a1[s][2], a1[s][3]);
+                    ldmatrix_x4(x2_a + tile_off(a_row, chunk), a2[s][0], a2[s][1], a2[s][2], a2[s][3]);
                 }
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const int n_row = half * 32 + j * 8 + lr;
                     uint32_t b0, b1, b2, b3;
-                    ldsm_x4(y1_a + tile_off(n_row, kp * 4 + lm), b0, b1, b2, b3);
+                    ldmatrix_x4(y1_a + tile_off(n_row, kp * 4 + lm), b0, b1, b2, b3);
                     mma_bf16(t1[j], a1[0], b0, b1);
                     mma_bf16(t1[j], a1[1], b2, b3);
-                    ldsm_x4(y2_a + tile_off(n_row, kp * 4 + lm), b0, b1, b2, b3);
+                    ldmatrix_x4(y2_a + tile_off(n_row, kp * 4 + lm), b0, b1, b2, b3);
                     mma_bf16(t2[j], a2[0], b0, b1);
                     mma_bf16(t2[j], a2[1], b2, b3);
                 }
@@ -256,11 +239,11 @@ __global__ void __launch_bounds__(128) bwd_tc_kernel(const BwdTcParams p) {
                 for (int jp = 0; jp < NT_D / 2; ++jp) {  // two n-tiles of the head dim per ldmatrix.trans
                     const int chunk = jp * 2 + (lm >> 1);
                     uint32_t b0, b1, b2, b3;
-                    ldsm_x4_trans(y1_a + tile_off(k_row, chunk), b0, b1, b2, b3);
+                    ldmatrix_x4_trans(y1_a + tile_off(k_row, chunk), b0, b1, b2, b3);
                     mma_bf16(z1[2 * jp], wd[s], b0, b1);
                     mma_bf16(z1[2 * jp + 1], wd[s], b2, b3);
                     if (kKeySide) {
-                        ldsm_x4_trans(y2_a + tile_off(k_row, chunk), b0, b1, b2, b3);
+                        ldmatrix_x4_trans(y2_a + tile_off(k_row, chunk), b0, b1, b2, b3);
                         mma_bf16(z2[2 * jp], wp[s], b0, b1);
                         mma_bf16(z2[2 * jp + 1], wp[s], b2, b3);
                     }

@@ -54,27 +54,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // Bounded wait: gives up after ~2^31 SM clocks (about a second), records `code` in the
 // device status word and returns false.  Callers then skip their remaining work and fall
 // through to the common teardown so the context stays usable.
-// try_wait with a suspend-time hint: the thread may sleep in hardware for up to `ns` nanoseconds
-// (it is woken when the phase completes), which keeps a polling warp out of the issue slots.
-__device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parity, uint32_t ns) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity), "r"(ns)
-        : "memory");
-    return ok != 0;
-}
-
-#ifndef RT_WAIT_HINT_NS
-#define RT_WAIT_HINT_NS 0
-#endif
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
-    while (!(RT_WAIT_HINT_NS ? mbar_try_wait_hint(bar, parity, RT_WAIT_HINT_NS) : mbar_try_wait(bar, parity))) {
+    while (!mbar_try_wait(bar, parity)) {
         if (clock64() - t0 > (1ll << 31)) {
             report_timeout(status, code);
             return false;
@@ -116,17 +99,6 @@ __device__ __forceinline__ void tma_store_4d(const CUtensorMap* m, const void* s
     asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
                  ::"l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(smem_src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
                  : "memory");
-}
-
-// 3-D tiled store shared -> global (bulk async-group completion); rows outside the tensor are clipped.
-__device__ __forceinline__ void tma_store_3d(const CUtensorMap* m, const void* smem_src, int c0, int c1, int c2) {
-    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
-                 ::"l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(smem_src)), "r"(c0), "r"(c1), "r"(c2)
-                 : "memory");
-}
-__device__ __forceinline__ void tma_store_commit_and_wait() {
-    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
 }
 
 // Waits only until the staged source has been read; the global writes complete on their own.
@@ -237,11 +209,6 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
         "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
         "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
         : "memory");
-}
-
-// Named barrier among `nthreads` threads (ids 1..15; 0 is __syncthreads).
-__device__ __forceinline__ void named_barrier_sync(int id, int nthreads) {
-    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 
 }  // namespace ptx
