@@ -52,6 +52,14 @@ def test_oracle_reproduces_golden_decode(oracle):
     assert _same(mo.reshape(B, Hq, D), g["out"], 1e-5) and _same(ml.reshape(B, Hq), g["lse"], 1e-5)
 
 
+def test_oracle_reproduces_golden_backward(oracle):
+    g = _load("backward_causal_d64", oracle)
+    do_ = oracle.bf16_bits_to_f32(g["d_out"])
+    rc, dq, dk, dv, lse = oracle.flash_backward(g["q"], g["k"], g["v"], do_, causal=True, with_lse=True)
+    assert rc == 0
+    assert _same(dq, g["dq"]) and _same(dk, g["dk"]) and _same(dv, g["dv"]) and _same(lse, g["lse"], 1e-5)
+
+
 def test_reference_kats_on_the_oracle(oracle):
     kats = json.load(open(os.path.join(GOLD, "reference_kats.json")))
     for name in ("scaling_factor_is_one_over_sqrt_d", "causal_first_query_only_attends_to_self",
@@ -135,3 +143,26 @@ def test_gpu_reference_kats_through_the_host_mirror():
         out = np.zeros_like(q)
         rt.flash_forward_masked(rt.AttentionShape.new(*c["shape"]), q, k, v, mask, out)
         _check_kat(c, out)
+
+
+@pytest.mark.gpu
+def test_gpu_backward_matches_golden(oracle):
+    """Both CUDA backward kernels against the committed gradients: f32 at 2e-4, bf16 tensor cores at 2e-2 of the
+    largest entry."""
+    import torch
+    import rustorch_b200 as rt
+    g = _load("backward_causal_d64", oracle)
+    do_ = oracle.bf16_bits_to_f32(g["d_out"])
+    q, k, v, d = (torch.from_numpy(x).cuda() for x in (g["q"], g["k"], g["v"], do_))
+    out, lse = rt.prefill_f32(q, k, v, causal=True)
+    got = rt.backward_f32(q, k, v, out, d, lse, causal=True)
+    qh, kh, vh, dh = (x.to(torch.bfloat16) for x in (q, k, v, d))
+    outh, lseh = rt.prefill_bf16(qh, kh, vh, causal=True)
+    goth = rt.backward_bf16(qh, kh, vh, outh, dh, lseh, causal=True)
+    torch.cuda.synchronize()
+    assert np.abs(lse.cpu().numpy() - g["lse"]).max() < 1e-4
+    for name, a, b in zip(("dq", "dk", "dv"), got, goth):
+        ref = g[name]
+        scale = max(1.0, float(np.abs(ref).max()))
+        assert np.abs(a.cpu().numpy() - ref).max() <= 2e-4 * scale, name
+        assert np.abs(b.cpu().numpy() - ref).max() <= 2e-2 * scale, name
