@@ -86,8 +86,9 @@ const char* rt_attn_error_string(int status);
 
 /*
  * Reads (and clears) the device-side status word of the current device: 0 = clean,
- * otherwise a code identifying which bounded wait inside a kernel gave up.  Synchronises
- * the device.  Returns RT_OK, a cudaError_t, or RT_ERR_DEVICE_TIMEOUT when *status != 0.
+ * otherwise a code identifying which bounded wait inside a kernel gave up (101-113: a barrier of
+ * the prefill kernel, 301: a TMA stage of the decode kernel, 401: a peer's record in
+ * rt_attn_merge_records_after).  Synchronises the device.  Returns RT_OK, a cudaError_t, or RT_ERR_DEVICE_TIMEOUT when *status != 0.
  */
 int rt_attn_device_status(int* status);
 
@@ -355,7 +356,7 @@ int rt_attn_merge_records(const float* records, int64_t n_parts, int64_t rows, i
  *       the copy).  Never waits.  rows * (D+1) must be a multiple of 4.
  *   rt_attn_merge_records_after : rt_attn_merge_records on the local slots once flags[r] >= epoch
  *       for every r < n_parts.  The wait is bounded by wait_clocks SM clocks (<= 0: 2^31, about a
- *       second); on expiry the kernel writes nothing and rt_attn_device_status reports 301.
+ *       second); on expiry the kernel writes nothing and rt_attn_device_status reports 401.
  * Epochs must increase by one per exchange; with two slot sets used alternately a rank can never
  * overwrite a record that a slower peer is still merging.
  */

@@ -277,7 +277,7 @@ __global__ void __launch_bounds__(128) gqa_decode_splitkv_kernel(const DecodePar
 // loads in flight per lane, so a row with hundreds of partials (long-context split-KV) costs a few
 // memory latencies instead of one per partial.  Each lane owns dims lane, lane+32, ...
 // A partial with LSE_r = -inf gets weight 0 and its O is never read (it may be uninitialised).
-constexpr int kToPeerFlag = 301;  // device status code: a peer's record did not arrive in time
+constexpr int kToPeerFlag = 401;  // device status code: a peer's record did not arrive in time
 
 __device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
     uint32_t v;

@@ -291,7 +291,7 @@ def test_peer_exchange_push_and_merge_on_one_device(oracle):
 
 def test_peer_exchange_wait_runs_out_and_reports(oracle):
     """A record that never arrives: the merge's bounded wait (here ~10 ms) expires, the kernel leaves the outputs
-    alone, the status word reports code 301, and the context stays usable."""
+    alone, the status word reports code 401, and the context stays usable."""
     import torch
     import rustorch_b200 as rt
     from rustorch_b200 import _lib, sharding
@@ -302,7 +302,7 @@ def test_peer_exchange_wait_runs_out_and_reports(oracle):
     assert _lib.device_status() == 0
     out, lse = ranks[0].merge(out_dtype=torch.float32, wait_clocks=20_000_000)
     torch.cuda.synchronize()
-    assert _lib.device_status() == 301
+    assert _lib.device_status() == 401
     assert _lib.device_status() == 0  # reading clears it
     # the device still works
     o, l = rt.merge_records(torch.ones((2, 32, 129), dtype=torch.float32, device="cuda"), out_dtype=torch.float32)
