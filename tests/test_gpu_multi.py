@@ -52,6 +52,7 @@ def _worker(rank, world, port, tmpdir):
         dist.destroy_process_group()
 
 
+@pytest.mark.timeout(300)
 def test_split_kv_exchange_over_two_gpus(tmp_path):
     import torch
     if torch.cuda.device_count() < 2:
