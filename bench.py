@@ -370,15 +370,14 @@ def main():
 
         # The same exchange over peer memory: the record is decoded straight into this rank's slot, pushed
         # to every peer with NVLink stores + a flag, and the merge kernel waits (bounded) for all flags.
-        exchange, exchange_note = None, "peer stores over NVLink (symmetric memory) + flag, merge waits in-kernel"
+        exchange, exchange_note = None, "peer stores over NVLink (symmetric memory) from the kernel that produces the record, flag, merge waits in-kernel"
         try:
             exchange = sharding.PeerRecordExchange.create(Hq, Dd)
         except Exception as exc:  # symmetric memory not available: keep the NCCL form, and say so
             exchange_note = f"NCCL all-gather (peer exchange unavailable: {type(exc).__name__}: {exc})"[:200]
 
         def step_splitkv_p2p():
-            rt.gqa_decode_record(q1, k1, v1, kv_len=T, workspace=ws, record=exchange.next_epoch())
-            exchange.push()
+            exchange.decode_push(q1, k1, v1, kv_len=T, workspace=ws)  # the merge kernel stores the record on every peer
             return exchange.merge()
 
         nccl_ms = timed(step_splitkv_nccl, args.steps, args.warmup, dist, torch)

@@ -367,6 +367,24 @@ int rt_attn_merge_records_after(const float* records, const uint32_t* flags, uin
                                 void* out_bf16, float* out_f32, float* lse, void* stream);
 
 /*
+ * rt_gqa_decode_record_bf16 and rt_splitkv_push_record in one call: the kernel that merges the
+ * chunk partials of this rank's KV shard into its record also stores every row into the slot each
+ * peer keeps for this rank, and the CTA that finishes last sets the peers' flags to `epoch`, so the
+ * record crosses NVLink while the remaining rows are still being merged and no separate copy
+ * kernel runs.  `record` is this rank's own slot; peer_slots / peer_flags as in
+ * rt_splitkv_push_record; done_counter is a device int32 that is zero between calls (the kernel
+ * resets it).  A launch whose record comes straight from the decode kernel (a single chunk, or
+ * chunks merged in-kernel) falls back to the copy kernel; the effect is the same.
+ */
+int rt_gqa_decode_record_push_bf16(const void* q, const void* k_cache, const void* v_cache,
+                                   float* record, void* const* peer_slots, void* const* peer_flags,
+                                   int world, uint32_t epoch, int* done_counter, int64_t batch,
+                                   int64_t n_heads, int64_t n_kv_heads, int head_dim, int64_t max_seq,
+                                   const int32_t* kv_lens, int64_t kv_len_uniform, int64_t kv_begin,
+                                   int64_t kv_end, float scale, void* workspace,
+                                   size_t workspace_bytes, void* stream);
+
+/*
  * Host-slice mirror of
  *   gqa_forward_f32(q,k,v,out, batch,n_heads,n_kv_heads,seq_q,seq_kv,head_dim) -> Result<(),GQAError>
  * (gqa.rs:94-105), f32 arithmetic.  seq_q == seq_kv runs the unmasked prefill without

@@ -75,6 +75,10 @@ PROTOTYPES = {
                                           c_int64, c_void_p, c_int64, c_int64, c_int64, c_float, c_void_p, c_size_t,
                                           c_void_p]),
     "rt_splitkv_push_record": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int, ctypes.c_uint32, c_void_p]),
+    "rt_gqa_decode_record_push_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                               ctypes.c_uint32, c_void_p, c_int64, c_int64, c_int64, c_int, c_int64,
+                                               c_void_p, c_int64, c_int64, c_int64, c_float, c_void_p, c_size_t,
+                                               c_void_p]),
     "rt_attn_merge_records_after": (c_int, [c_void_p, c_void_p, ctypes.c_uint32, c_int64, c_int64, c_int64, c_int,
                                             c_void_p, c_void_p, c_void_p, c_void_p]),
     "rt_attn_merge_records": (c_int, [c_void_p, c_int64, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),

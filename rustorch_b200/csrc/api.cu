@@ -477,7 +477,9 @@ static int decode_common(const void* q, const void* k_cache, const void* v_cache
                          float* lse, int64_t of_stride, int64_t lse_stride, int64_t batch, int64_t n_heads,
                          int64_t n_kv_heads, int head_dim, int64_t max_seq, const int32_t* kv_lens,
                          int64_t kv_len_uniform, int64_t kv_begin, int64_t kv_end, float scale, void* workspace,
-                         size_t workspace_bytes, void* stream) {
+                         size_t workspace_bytes, void* stream, const rt::MergePush* push = nullptr,
+                         bool* pushed = nullptr) {
+    if (pushed) *pushed = false;
     if (n_kv_heads <= 0 || n_heads <= 0 || n_heads % n_kv_heads != 0) return RT_ERR_HEAD_COUNT;  // gqa.rs:106-111
     if (head_dim == 0) return RT_ERR_ZERO_DIM;
     if (batch < 0 || max_seq <= 0 || kv_begin < 0 || head_dim < 0) return RT_ERR_BAD_LENGTH;
@@ -494,7 +496,7 @@ static int decode_common(const void* q, const void* k_cache, const void* v_cache
     RT_CUDA(rt::launch_gqa_decode(q, k_cache, v_cache, out_bf16, out_f32, lse, batch, (int)n_heads, (int)n_kv_heads,
                                   head_dim, max_seq, kv_lens, kv_len_uniform, kv_begin, kv_end,
                                   default_scale(scale, head_dim), need ? workspace : nullptr, of_stride, lse_stride,
-                                  as_stream(stream)));
+                                  as_stream(stream), push, pushed));
     return RT_OK;
 }
 
@@ -514,6 +516,34 @@ int rt_gqa_decode_record_bf16(const void* q, const void* k_cache, const void* v_
     return decode_common(q, k_cache, v_cache, nullptr, record, record ? record + head_dim : nullptr, head_dim + 1,
                          head_dim + 1, batch, n_heads, n_kv_heads, head_dim, max_seq, kv_lens, kv_len_uniform, kv_begin,
                          kv_end, scale, workspace, workspace_bytes, stream);
+}
+
+int rt_gqa_decode_record_push_bf16(const void* q, const void* k_cache, const void* v_cache, float* record,
+                                   void* const* peer_slots, void* const* peer_flags, int world, uint32_t epoch,
+                                   int* done_counter, int64_t batch, int64_t n_heads, int64_t n_kv_heads, int head_dim,
+                                   int64_t max_seq, const int32_t* kv_lens, int64_t kv_len_uniform, int64_t kv_begin,
+                                   int64_t kv_end, float scale, void* workspace, size_t workspace_bytes, void* stream) {
+    if (world <= 0) return RT_ERR_BAD_LENGTH;
+    if (world > rt::kMaxPeers) return RT_ERR_UNSUPPORTED;
+    if ((batch > 0 && !record) || !peer_slots || !peer_flags || !done_counter) return RT_ERR_NULL_POINTER;
+    rt::MergePush push{};
+    for (int r = 0; r < world; ++r) {
+        if (!peer_slots[r] || !peer_flags[r]) return RT_ERR_NULL_POINTER;
+        if (!aligned16(peer_slots[r])) return RT_ERR_ALIGNMENT;
+        push.dst[r] = static_cast<float*>(peer_slots[r]);
+        push.flag[r] = static_cast<uint32_t*>(peer_flags[r]);
+    }
+    push.world = world;
+    push.epoch = epoch;
+    push.done_counter = done_counter;
+    bool pushed = false;
+    const int rc = decode_common(q, k_cache, v_cache, nullptr, record, record ? record + head_dim : nullptr,
+                                 head_dim + 1, head_dim + 1, batch, n_heads, n_kv_heads, head_dim, max_seq, kv_lens,
+                                 kv_len_uniform, kv_begin, kv_end, scale, workspace, workspace_bytes, stream, &push,
+                                 &pushed);
+    if (rc != RT_OK || pushed || batch == 0) return rc;
+    // the record came straight out of the decode kernel (one chunk, or chunks merged in-kernel): copy it over
+    return rt_splitkv_push_record(record, peer_slots, peer_flags, world, batch * n_heads, head_dim, epoch, stream);
 }
 
 int rt_gqa_decode_online_bf16(const void* q, const void* k_cache, const void* v_cache, void* out, int n_heads,

@@ -294,9 +294,25 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_partials_kernel(const 
                                                                          int64_t in_row_stride, int64_t in_lse_stride,
                                                                          __nv_bfloat16* out_bf16, float* out_f32,
                                                                          float* lse_out, int64_t of_stride,
-                                                                         int64_t lse_stride, MergeWait wait) {
+                                                                         int64_t lse_stride, MergeWait wait,
+                                                                         MergePush push) {
     const int64_t row = blockIdx.x;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    // Delivery of this row to the peers (record layout: out_f32 rows of of_stride floats, LSE at column dim).
+    auto push_row_value = [&](int d, float x) {
+        for (int r = 0; r < push.world; ++r)
+            if (push.dst[r] != out_f32) push.dst[r][row * of_stride + d] = x;
+    };
+    auto push_done = [&]() {  // every thread of the CTA calls this once its stores are issued
+        __threadfence_system();
+        __syncthreads();
+        if (tid == 0 && atomicAdd(push.done_counter, 1) == (int)rows - 1) {
+            *push.done_counter = 0;  // ready for the next launch
+            __threadfence_system();  // all rows of all CTAs are ordered before the flags
+            for (int r = 0; r < push.world; ++r)
+                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(push.flag[r]), "r"(push.epoch) : "memory");
+        }
+    };
     if (wait.flags) {
         // Part r of this merge is written into local memory by rank r (push_records_kernel on that GPU),
         // which then raises flags[r] to the epoch with a system-scope release.  The wait is bounded: on
@@ -345,8 +361,13 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_partials_kernel(const 
         for (int d = tid; d < dim; d += kMergeWarps * 32) {
             if (out_bf16) out_bf16[row * dim + d] = __float2bfloat16(0.f);
             if (out_f32) out_f32[row * of_stride + d] = 0.f;
+            if (push.world) push_row_value(d, 0.f);
         }
         if (tid == 0 && lse_out) lse_out[row * lse_stride] = -INFINITY;
+        if (push.world) {
+            if (tid == 0) push_row_value(dim, -INFINITY);
+            push_done();
+        }
         return;
     }
 
@@ -405,8 +426,13 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_partials_kernel(const 
         o *= inv;
         if (out_bf16) out_bf16[row * dim + d] = __float2bfloat16(o);
         if (out_f32) out_f32[row * of_stride + d] = o;
+        if (push.world) push_row_value(d, o);
     }
     if (tid == 0 && lse_out) lse_out[row * lse_stride] = m + logf(s_l);
+    if (push.world) {
+        if (tid == 0) push_row_value(dim, m + logf(s_l));
+        push_done();
+    }
 }
 
 static size_t merge_smem_bytes(int64_t n_parts, int dim) {
@@ -546,7 +572,9 @@ cudaError_t launch_gqa_decode(const void* q, const void* k, const void* v, void*
                               float* lse, int64_t batch, int n_heads, int n_kv, int head_dim,
                               int64_t max_seq, const int32_t* kv_lens, int64_t kv_len_uniform,
                               int64_t kv_begin, int64_t kv_end, float scale, void* workspace,
-                              int64_t of_stride, int64_t lse_stride, cudaStream_t stream) {
+                              int64_t of_stride, int64_t lse_stride, cudaStream_t stream, const MergePush* push,
+                              bool* pushed) {
+    if (pushed) *pushed = false;
     DecodeParams p;
     p.q = (const __nv_bfloat16*)q;
     p.k = (const __nv_bfloat16*)k;
@@ -596,7 +624,8 @@ cudaError_t launch_gqa_decode(const void* q, const void* k, const void* v, void*
     if (p.n_chunks > 1 && !merged) {
         merge_partials_kernel<<<(unsigned)p.rows, kMergeWarps * 32, merge_smem_bytes(p.n_chunks, head_dim), stream>>>(
             p.part_o, p.part_lse, p.n_chunks, p.rows, head_dim, head_dim, 1, p.out_bf16, p.out_f32, lse, p.of_stride,
-            p.lse_stride, MergeWait{nullptr, 0, 0u, 0, nullptr});
+            p.lse_stride, MergeWait{nullptr, 0, 0u, 0, nullptr}, push ? *push : MergePush{});
+        if (push && pushed) *pushed = true;
         e = cudaGetLastError();
     }
     return e;
@@ -604,13 +633,14 @@ cudaError_t launch_gqa_decode(const void* q, const void* k, const void* v, void*
 
 cudaError_t launch_merge_partials(const float* o_parts, const float* lse_parts, int64_t n_parts, int64_t rows,
                                   int dim, int64_t in_row_stride, int64_t in_lse_stride, void* out_bf16,
-                                  float* out_f32, float* lse, cudaStream_t stream, const MergeWait* wait) {
+                                  float* out_f32, float* lse, cudaStream_t stream, const MergeWait* wait,
+                                  const MergePush* push) {
     if (rows == 0) return cudaSuccess;
     if (dim > 32 * kMergeMaxDimPerLane || merge_smem_bytes(n_parts, dim) > 48 * 1024) return cudaErrorInvalidValue;
     if (wait && wait->n_flags > kMergeWarps * 32) return cudaErrorInvalidValue;
     merge_partials_kernel<<<(unsigned)rows, kMergeWarps * 32, merge_smem_bytes(n_parts, dim), stream>>>(
         o_parts, lse_parts, (int)n_parts, rows, dim, in_row_stride, in_lse_stride, (__nv_bfloat16*)out_bf16, out_f32, lse,
-        dim, 1, wait ? *wait : MergeWait{nullptr, 0, 0u, 0, nullptr});
+        dim, 1, wait ? *wait : MergeWait{nullptr, 0, 0u, 0, nullptr}, push ? *push : MergePush{});
     return cudaGetLastError();
 }
 

@@ -9,13 +9,15 @@ namespace rt {
 int* device_status_ptr();
 
 // ---- decode.cu
+struct MergePush;
 int decode_chunk_tokens(int64_t batch, int n_kv, int64_t max_seq);
 int decode_num_chunks(int64_t batch, int n_kv, int64_t max_seq);
 cudaError_t launch_gqa_decode(const void* q, const void* k, const void* v, void* out_bf16, float* out_f32,
                               float* lse, int64_t batch, int n_heads, int n_kv, int head_dim,
                               int64_t max_seq, const int32_t* kv_lens, int64_t kv_len_uniform,
                               int64_t kv_begin, int64_t kv_end, float scale, void* workspace,
-                              int64_t of_stride, int64_t lse_stride, cudaStream_t stream);
+                              int64_t of_stride, int64_t lse_stride, cudaStream_t stream,
+                              const struct MergePush* push = nullptr, bool* pushed = nullptr);
 // o_parts rows are in_row_stride floats apart, lse_parts entries in_lse_stride floats apart
 // Optional bounded wait in front of a merge: flags[r] >= epoch means part r has arrived.
 struct MergeWait {
@@ -26,9 +28,20 @@ struct MergeWait {
     int* status;
 };
 constexpr int kMaxPeers = 16;
+// Optional delivery of a merge's output record ([rows, dim + 1] f32: O | LSE) to the peers of a split-KV
+// decode: every row is also stored into dst[r] (r < world, entries equal to the local record are skipped);
+// the CTA that finishes last (done_counter, zero between launches) then sets *flag[r] = epoch.
+struct MergePush {
+    float* dst[kMaxPeers];
+    uint32_t* flag[kMaxPeers];
+    int world;
+    uint32_t epoch;
+    int* done_counter;
+};
 cudaError_t launch_merge_partials(const float* o_parts, const float* lse_parts, int64_t n_parts, int64_t rows,
                                   int dim, int64_t in_row_stride, int64_t in_lse_stride, void* out_bf16,
-                                  float* out_f32, float* lse, cudaStream_t stream, const MergeWait* wait = nullptr);
+                                  float* out_f32, float* lse, cudaStream_t stream, const MergeWait* wait = nullptr,
+                                  const MergePush* push = nullptr);
 cudaError_t launch_push_records(const float* record, void* const* peer_slots, void* const* peer_flags, int world,
                                 int64_t record_floats, uint32_t epoch, cudaStream_t stream);
 cudaError_t launch_kv_append(void* k_cache, void* v_cache, const void* k_in, const void* v_in, int64_t batch,

@@ -96,6 +96,7 @@ class PeerRecordExchange:
         self.record_ptrs = list(record_ptrs)  # base address of every rank's `records`
         self.flag_ptrs = list(flag_ptrs)      # base address of every rank's `flags`
         self.epoch = 0
+        self._done = None  # device int32, zero between calls (used by decode_push)
         if (rows * (dim + 1)) % 4:
             raise ValueError("rows * (dim + 1) must be a multiple of 4 (16-byte copies)")
 
@@ -133,6 +134,43 @@ class PeerRecordExchange:
         decode kernel should write its record into for this exchange."""
         self.epoch += 1
         return self.records[self.epoch & 1, self.rank]
+
+    def _peer_ptrs(self):
+        import ctypes
+        par = self.epoch & 1
+        rec_bytes = self.rows * (self.dim + 1) * 4
+        slot_off = (par * self.world + self.rank) * rec_bytes
+        flag_off = (par * self.world + self.rank) * 4
+        slots = (ctypes.c_void_p * self.world)(*[p + slot_off for p in self.record_ptrs])
+        flags = (ctypes.c_void_p * self.world)(*[p + flag_off for p in self.flag_ptrs])
+        return slots, flags
+
+    def decode_push(self, q, k_cache, v_cache, kv_lens=None, kv_len=None, kv_begin: int = 0, kv_end: int = -1,
+                    scale=None, workspace=None):
+        """Advances the epoch, decodes this rank's KV shard into its slot and delivers the record to every peer
+        from inside the merge kernel (``rt_gqa_decode_record_push_bf16``).  Follow with ``merge()``."""
+        import torch
+        from . import _lib
+        from .gqa import _stream_ptr, decode_workspace_bytes
+        B, Hq, D = q.shape
+        _, Hkv, max_seq, _ = k_cache.shape
+        if self._done is None:
+            self._done = torch.zeros(1, dtype=torch.int32, device=self.records.device)
+        need = decode_workspace_bytes(B, Hq, Hkv, D, max_seq)
+        if workspace is None and need:
+            workspace = getattr(self, "_ws", None)
+            if workspace is None or workspace.numel() < need:
+                workspace = self._ws = torch.empty(need, dtype=torch.uint8, device=q.device)
+        record = self.next_epoch()
+        slots, flags = self._peer_ptrs()
+        rc = _lib.lib().rt_gqa_decode_record_push_bf16(
+            q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), record.data_ptr(), slots, flags, self.world,
+            self.epoch, self._done.data_ptr(), B, Hq, Hkv, D, max_seq,
+            kv_lens.data_ptr() if kv_lens is not None else None, 0 if kv_len is None else int(kv_len), kv_begin, kv_end,
+            -1.0 if scale is None else float(scale), workspace.data_ptr() if workspace is not None else None,
+            workspace.numel() if workspace is not None else 0, _stream_ptr())
+        _lib.check(rc, "rt_gqa_decode_record_push_bf16")
+        return record
 
     def push(self):
         import ctypes

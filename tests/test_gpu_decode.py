@@ -308,3 +308,35 @@ def test_peer_exchange_wait_runs_out_and_reports(oracle):
     o, l = rt.merge_records(torch.ones((2, 32, 129), dtype=torch.float32, device="cuda"), out_dtype=torch.float32)
     torch.cuda.synchronize()
     assert torch.allclose(o, torch.ones_like(o))
+
+
+@pytest.mark.parametrize("kv_total,S", [(2900, 3000), (40000, 40960), (100, 128)])
+def test_peer_exchange_fused_decode_push_on_one_device(oracle, kv_total, S):
+    """rt_gqa_decode_record_push_bf16: the merge kernel of each emulated rank delivers its record to all ranks
+    itself (many chunks), or the copy kernel does (a single chunk); either way every rank's merge equals the merge
+    of the gathered records."""
+    import torch
+    import rustorch_b200 as rt
+    from rustorch_b200 import _lib, sharding
+    B, Hq, Hkv, D, world = 1, 32, 8, 128, 3
+    g = torch.Generator(device="cuda").manual_seed(11)
+    k = torch.randn((B, Hkv, S, D), device="cuda", generator=g).to(torch.bfloat16)
+    v = torch.randn((B, Hkv, S, D), device="cuda", generator=g).to(torch.bfloat16)
+    ranks = sharding.PeerRecordExchange.local_pair(world, B * Hq, D)
+    for step in range(3):
+        q = torch.randn((B, Hq, D), device="cuda", generator=g).to(torch.bfloat16)
+        recs = []
+        for r, ex in enumerate(ranks):
+            b0, b1 = sharding.kv_shard(kv_total, world, r, align=16)
+            recs.append(rt.gqa_decode_record(q, k, v, kv_len=kv_total, kv_begin=b0, kv_end=b1))
+            got = ex.decode_push(q, k, v, kv_len=kv_total, kv_begin=b0, kv_end=b1)
+            assert torch.equal(got, recs[-1])
+        want, want_lse = rt.merge_records(torch.stack(recs), out_dtype=torch.float32)
+        for ex in ranks:
+            out, lse = ex.merge(out_dtype=torch.float32)
+            assert torch.equal(out, want) and torch.equal(lse, want_lse)
+        torch.cuda.synchronize()
+        assert _lib.device_status() == 0
+        assert all(int(ex._done.item()) == 0 for ex in ranks)
+    full, full_lse = rt.gqa_decode(q, k, v, kv_len=kv_total, out_dtype=torch.float32)
+    assert (want - full.reshape(B * Hq, D)).abs().max().item() < 1e-3

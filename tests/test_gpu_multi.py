@@ -44,6 +44,12 @@ def _worker(rank, world, port, tmpdir):
             torch.cuda.synchronize()
             assert _lib.device_status() == 0
             assert torch.equal(got, want) and torch.equal(got_lse, want_lse)
+            # the same with the record delivered from inside the merge kernel
+            ex.decode_push(q, k, v, kv_len=T, kv_begin=lo, kv_end=hi)
+            got2, got2_lse = ex.merge(out_dtype=torch.float32)
+            torch.cuda.synchronize()
+            assert _lib.device_status() == 0
+            assert torch.equal(got2, want) and torch.equal(got2_lse, want_lse)
             assert (got - full.reshape(Hq, D)).abs().max().item() < 1e-3
             assert (got_lse - full_lse.reshape(Hq)).abs().max().item() < 1e-4
         dist.barrier()
