@@ -370,13 +370,18 @@ def main():
 
         # The same exchange over peer memory: the record is decoded straight into this rank's slot, pushed
         # to every peer with NVLink stores + a flag, and the merge kernel waits (bounded) for all flags.
-        exchange, exchange_note = None, "peer stores over NVLink (symmetric memory) from the kernel that produces the record, flag, merge waits in-kernel"
+        exchange, exchange_note = None, "peer stores over NVLink (symmetric memory) + flag, merge waits in-kernel; value = the faster of the copy-kernel and fused-in-merge forms"
         try:
             exchange = sharding.PeerRecordExchange.create(Hq, Dd)
         except Exception as exc:  # symmetric memory not available: keep the NCCL form, and say so
             exchange_note = f"NCCL all-gather (peer exchange unavailable: {type(exc).__name__}: {exc})"[:200]
 
         def step_splitkv_p2p():
+            rt.gqa_decode_record(q1, k1, v1, kv_len=T, workspace=ws, record=exchange.next_epoch())
+            exchange.push()   # copy kernel: 16-byte peer stores, then the flags
+            return exchange.merge()
+
+        def step_splitkv_p2p_fused():
             exchange.decode_push(q1, k1, v1, kv_len=T, workspace=ws)  # the merge kernel stores the record on every peer
             return exchange.merge()
 
@@ -386,7 +391,12 @@ def main():
             a, b = step_splitkv_nccl(), step_splitkv_p2p()
             torch.cuda.synchronize()
             assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1]), "peer exchange and NCCL exchange disagree"
-            sms = timed(step_splitkv_p2p, args.steps, args.warmup, dist, torch)
+            c = step_splitkv_p2p_fused()
+            torch.cuda.synchronize()
+            assert torch.equal(a[0], c[0]) and torch.equal(a[1], c[1]), "fused peer exchange and NCCL exchange disagree"
+            sms_copy = timed(step_splitkv_p2p, args.steps, args.warmup, dist, torch)
+            sms_fused = timed(step_splitkv_p2p_fused, args.steps, args.warmup, dist, torch)
+            sms = min(sms_copy, sms_fused)
             from rustorch_b200 import _lib
             assert _lib.device_status() == 0, "a bounded wait of the peer exchange expired"
         total_bytes = 2.0 * Hkv * Dd * 2 * T * world
@@ -395,7 +405,9 @@ def main():
                                           f"(BASELINE config 5 sharding), exchange of (O,LSE) records + merge",
                               "kv_len_total": T * world, "exchange": exchange_note},
                    "per_gpu_gbs": total_bytes / world / (sms * 1e-3) / 1e9,
-                   "nccl_all_gather_ms_per_step": nccl_ms}
+                   "nccl_all_gather_ms_per_step": nccl_ms,
+                   "peer_copy_kernel_ms_per_step": sms_copy if exchange is not None else None,
+                   "peer_fused_in_merge_ms_per_step": sms_fused if exchange is not None else None}
         del k1, v1
         torch.cuda.empty_cache()
 
