@@ -44,6 +44,10 @@
 #include <stdint.h>
 #include <stdlib.h>
 #include <string.h>
+#include <time.h>
+#if defined(__x86_64__)
+#include <immintrin.h>
+#endif
 #ifdef _OPENMP
 #include <omp.h>
 #endif
@@ -118,6 +122,202 @@ static void sgemm_value_accumulate(int m, int n, int kd, const float* p, int ldp
     }
 }
 
+
+/* ---------------------------------------------------------------- register-blocked tile GEMMs
+ *
+ * The reference does not run the loop nests above: its two tile products go through the `gemm`
+ * crate 0.18.2 (cpu_forward.rs:487-507, :564-584), a packed, register-blocked FMA micro-kernel
+ * with run-time ISA dispatch.  The loop nests stay the parity oracle (one obvious summation
+ * order); the kernels below stand in for that crate when the CPU path is TIMED, so that the CPU
+ * baseline is not slower than the reference would be on the same cores.  Both compute the same
+ * products; only the summation order differs (tests hold the two to 1e-4 of each other, the gate
+ * the reference's own flash-vs-naive tests use).
+ *
+ *   C[m x n] = alpha * A[m x k] * B[k x n] (+ C),  A row-major (lda), B row-major (ldb), n % NR == 0
+ *
+ * One kernel serves both products: for O += P V, B is the V tile as it lies in memory; for
+ * S = scale Q K^T, B is the K tile transposed once per (b,h) slab into [D][bc] panels (the crate
+ * packs its right-hand side as well).  AVX2: 6 x 16 block (12 accumulators); AVX-512: 4 x 64 (16 accumulators; the shape that measured best).
+ * orc_set_gemm_kernel(0) = loop nests, 1 = micro-kernels (best ISA the CPU has), chosen per call.
+ */
+static int g_gemm_kernel = 0;
+void orc_set_gemm_kernel(int k) { g_gemm_kernel = k; }
+int orc_get_gemm_kernel(void) { return g_gemm_kernel; }
+
+#if defined(__x86_64__)
+#define ORC_MICRO_ROWS(MR, NV, VEC, SETZERO, LOADU, STOREU, BCAST, FMADD, MUL, ADD)                       \
+    do {                                                                                                \
+        for (int c0 = 0; c0 < n; c0 += (NV) * (int)(sizeof(VEC) / 4)) {                                  \
+            VEC acc[MR][NV];                                                                            \
+            for (int i = 0; i < MR; ++i)                                                                \
+                for (int j = 0; j < NV; ++j) acc[i][j] = SETZERO();                                     \
+            for (int kk = 0; kk < k; ++kk) {                                                            \
+                VEC bv[NV];                                                                             \
+                for (int j = 0; j < NV; ++j) bv[j] = LOADU(b + (size_t)kk * ldb + c0 + j * (int)(sizeof(VEC) / 4)); \
+                for (int i = 0; i < MR; ++i) {                                                          \
+                    const VEC av = BCAST(a[(size_t)(r0 + i) * lda + kk]);                               \
+                    for (int j = 0; j < NV; ++j) acc[i][j] = FMADD(av, bv[j], acc[i][j]);               \
+                }                                                                                       \
+            }                                                                                           \
+            const VEC al = BCAST(alpha);                                                                \
+            for (int i = 0; i < MR; ++i)                                                                \
+                for (int j = 0; j < NV; ++j) {                                                          \
+                    float* dst = c + (size_t)(r0 + i) * ldc + c0 + j * (int)(sizeof(VEC) / 4);          \
+                    VEC x = MUL(acc[i][j], al);                                                         \
+                    if (accumulate) x = ADD(x, LOADU(dst));                                             \
+                    STOREU(dst, x);                                                                     \
+                }                                                                                       \
+        }                                                                                               \
+    } while (0)
+
+#define ORC_AVX2_ROWS(MR) \
+    ORC_MICRO_ROWS(MR, 2, __m256, _mm256_setzero_ps, _mm256_loadu_ps, _mm256_storeu_ps, _mm256_set1_ps, \
+                   _mm256_fmadd_ps, _mm256_mul_ps, _mm256_add_ps)
+#define ORC_AVX512_ROWS(MR) \
+    ORC_MICRO_ROWS(MR, 4, __m512, _mm512_setzero_ps, _mm512_loadu_ps, _mm512_storeu_ps, _mm512_set1_ps, \
+                   _mm512_fmadd_ps, _mm512_mul_ps, _mm512_add_ps)
+
+/* n must be a multiple of 16 */
+__attribute__((target("avx2,fma")))
+static void gemm_nn_avx2(int m, int n, int k, float alpha, const float* a, int lda, const float* b, int ldb,
+                         float* c, int ldc, int accumulate) {
+    int r0 = 0;
+    for (; r0 + 6 <= m; r0 += 6) ORC_AVX2_ROWS(6);
+    for (; r0 + 2 <= m; r0 += 2) ORC_AVX2_ROWS(2);
+    for (; r0 < m; ++r0) ORC_AVX2_ROWS(1);
+}
+
+/* n must be a multiple of 64 */
+__attribute__((target("avx512f")))
+static void gemm_nn_avx512(int m, int n, int k, float alpha, const float* a, int lda, const float* b, int ldb,
+                           float* c, int ldc, int accumulate) {
+    int r0 = 0;
+    for (; r0 + 4 <= m; r0 += 4) ORC_AVX512_ROWS(4);
+    for (; r0 + 2 <= m; r0 += 2) ORC_AVX512_ROWS(2);
+    for (; r0 < m; ++r0) ORC_AVX512_ROWS(1);
+}
+
+/* 2 = AVX-512F, 1 = AVX2 + FMA, 0 = neither (the loop nests are used) */
+int orc_micro_isa(void) {
+    static int isa = -1;
+    if (isa < 0) {
+        __builtin_cpu_init();
+        isa = __builtin_cpu_supports("avx512f") ? 2 : (__builtin_cpu_supports("avx2") && __builtin_cpu_supports("fma")) ? 1 : 0;
+    }
+    return isa;
+}
+
+/* One core's FMA throughput measured with independent accumulator chains (GFLOP/s, f32, the
+ * widest ISA the micro-kernels use): the denominator for "fraction of FMA peak". */
+__attribute__((target("avx2,fma")))
+static double fma_peak_avx2(long iters) {
+    __m256 a0 = _mm256_set1_ps(1.0f), a1 = a0, a2 = a0, a3 = a0, a4 = a0, a5 = a0, a6 = a0, a7 = a0, a8 = a0, a9 = a0;
+    const __m256 x = _mm256_set1_ps(0.999999f), y = _mm256_set1_ps(1e-9f);
+    for (long i = 0; i < iters; ++i) {
+        a0 = _mm256_fmadd_ps(a0, x, y); a1 = _mm256_fmadd_ps(a1, x, y); a2 = _mm256_fmadd_ps(a2, x, y);
+        a3 = _mm256_fmadd_ps(a3, x, y); a4 = _mm256_fmadd_ps(a4, x, y); a5 = _mm256_fmadd_ps(a5, x, y);
+        a6 = _mm256_fmadd_ps(a6, x, y); a7 = _mm256_fmadd_ps(a7, x, y); a8 = _mm256_fmadd_ps(a8, x, y);
+        a9 = _mm256_fmadd_ps(a9, x, y);
+    }
+    a0 = _mm256_add_ps(_mm256_add_ps(_mm256_add_ps(a0, a1), _mm256_add_ps(a2, a3)),
+                       _mm256_add_ps(_mm256_add_ps(a4, a5), _mm256_add_ps(_mm256_add_ps(a6, a7), _mm256_add_ps(a8, a9))));
+    float t[8];
+    _mm256_storeu_ps(t, a0);
+    return (double)t[0];
+}
+__attribute__((target("avx512f")))
+static double fma_peak_avx512(long iters) {
+    __m512 a0 = _mm512_set1_ps(1.0f), a1 = a0, a2 = a0, a3 = a0, a4 = a0, a5 = a0, a6 = a0, a7 = a0, a8 = a0, a9 = a0;
+    const __m512 x = _mm512_set1_ps(0.999999f), y = _mm512_set1_ps(1e-9f);
+    for (long i = 0; i < iters; ++i) {
+        a0 = _mm512_fmadd_ps(a0, x, y); a1 = _mm512_fmadd_ps(a1, x, y); a2 = _mm512_fmadd_ps(a2, x, y);
+        a3 = _mm512_fmadd_ps(a3, x, y); a4 = _mm512_fmadd_ps(a4, x, y); a5 = _mm512_fmadd_ps(a5, x, y);
+        a6 = _mm512_fmadd_ps(a6, x, y); a7 = _mm512_fmadd_ps(a7, x, y); a8 = _mm512_fmadd_ps(a8, x, y);
+        a9 = _mm512_fmadd_ps(a9, x, y);
+    }
+    a0 = _mm512_add_ps(_mm512_add_ps(_mm512_add_ps(a0, a1), _mm512_add_ps(a2, a3)),
+                       _mm512_add_ps(_mm512_add_ps(a4, a5), _mm512_add_ps(_mm512_add_ps(a6, a7), _mm512_add_ps(a8, a9))));
+    float t[16];
+    _mm512_storeu_ps(t, a0);
+    return (double)t[0];
+}
+double orc_fma_peak_gflops(void) {
+    const int isa = orc_micro_isa();
+    if (isa == 0) return 0.0;
+    const long iters = 20000000L;
+    struct timespec t0, t1;
+    volatile double sink;
+    sink = isa == 2 ? fma_peak_avx512(1000) : fma_peak_avx2(1000); /* warm the clock */
+    clock_gettime(CLOCK_MONOTONIC, &t0);
+    sink = isa == 2 ? fma_peak_avx512(iters) : fma_peak_avx2(iters);
+    clock_gettime(CLOCK_MONOTONIC, &t1);
+    (void)sink;
+    const double s = (double)(t1.tv_sec - t0.tv_sec) + 1e-9 * (double)(t1.tv_nsec - t0.tv_nsec);
+    return (double)iters * 10.0 * (isa == 2 ? 16.0 : 8.0) * 2.0 / s / 1e9;
+}
+#else
+int orc_micro_isa(void) { return 0; }
+double orc_fma_peak_gflops(void) { return 0.0; }
+#endif
+
+/* C = alpha A B (+ C) through the best micro-kernel; returns 0 if none applies (caller falls back). */
+static int gemm_nn_fast(int m, int n, int k, float alpha, const float* a, int lda, const float* b, int ldb,
+                        float* c, int ldc, int accumulate) {
+#if defined(__x86_64__)
+    const int isa = orc_micro_isa();
+    if (isa == 2 && n % 64 == 0) { gemm_nn_avx512(m, n, k, alpha, a, lda, b, ldb, c, ldc, accumulate); return 1; }
+    if (isa >= 1 && n % 16 == 0) { gemm_nn_avx2(m, n, k, alpha, a, lda, b, ldb, c, ldc, accumulate); return 1; }
+#endif
+    (void)m; (void)n; (void)k; (void)alpha; (void)a; (void)lda; (void)b; (void)ldb; (void)c; (void)ldc; (void)accumulate;
+    return 0;
+}
+
+/* Throughput of the tile products alone on one core (GFLOP/s): the 64 x 64 x dim score tile and the
+ * 64 x dim x 64 value tile back to back, operands resident in L1/L2 as inside the tile loop. */
+double orc_tile_gemm_gflops(int dim, int reps) {
+    const int br = 64, bc = 64;
+    float* q = (float*)malloc(sizeof(float) * br * dim);
+    float* kt = (float*)malloc(sizeof(float) * dim * bc);
+    float* vv = (float*)malloc(sizeof(float) * bc * dim);
+    float* sb = (float*)malloc(sizeof(float) * br * bc);
+    float* ob = (float*)malloc(sizeof(float) * br * dim);
+    if (!q || !kt || !vv || !sb || !ob) { free(q); free(kt); free(vv); free(sb); free(ob); return 0.0; }
+    for (int i = 0; i < br * dim; ++i) { q[i] = 0.001f * (float)(i % 97); ob[i] = 0.0f; }
+    for (int i = 0; i < dim * bc; ++i) { kt[i] = 0.002f * (float)(i % 89); vv[i] = 0.003f * (float)(i % 83); }
+    struct timespec t0, t1;
+    clock_gettime(CLOCK_MONOTONIC, &t0);
+    int used = 1;
+    for (int r = 0; r < reps && used; ++r) {
+        used = gemm_nn_fast(br, bc, dim, 0.088f, q, dim, kt, bc, sb, bc, 0);
+        used = used && gemm_nn_fast(br, dim, bc, 1.0f, sb, bc, vv, dim, ob, dim, 1);
+    }
+    clock_gettime(CLOCK_MONOTONIC, &t1);
+    volatile float sink = ob[5];
+    (void)sink;
+    free(q); free(kt); free(vv); free(sb); free(ob);
+    if (!used) return 0.0;
+    const double s = (double)(t1.tv_sec - t0.tv_sec) + 1e-9 * (double)(t1.tv_nsec - t0.tv_nsec);
+    return 4.0 * br * bc * dim * (double)reps / s / 1e9;
+}
+
+/* K[seq x dim] -> per-tile transposed panels: tile t (keys [t*bc, t*bc+bc)) at kt + t*dim*bc as
+ * [dim][bc], keys past seq zero-filled. */
+static void pack_k_transposed(const float* k, int64_t seq, int dim, int bc, float* kt) {
+    const int64_t n_tiles = (seq + bc - 1) / bc;
+    for (int64_t t = 0; t < n_tiles; ++t) {
+        float* panel = kt + (size_t)t * dim * bc;
+        for (int c = 0; c < bc; ++c) {
+            const int64_t key = t * bc + c;
+            if (key < seq) {
+                const float* kr = k + (size_t)key * dim;
+                for (int d = 0; d < dim; ++d) panel[(size_t)d * bc + c] = kr[d];
+            } else {
+                for (int d = 0; d < dim; ++d) panel[(size_t)d * bc + c] = 0.0f;
+            }
+        }
+    }
+}
+
 /* ---------------------------------------------------------------- tiled forward */
 
 /* cpu_forward.rs:268-425 for one (b,h) slab.  Every KV tile is visited, masked or
@@ -135,6 +335,17 @@ static int flash_forward_bh(const float* q, const float* k, const float* v, floa
         return ORC_ERR_ALLOC;
     }
     const int none = mask_is_none(mask);
+    /* timed-baseline mode: K transposed once per slab, tile products on the micro-kernels */
+    float* kt = NULL;
+    const int fast = g_gemm_kernel && orc_micro_isa() > 0 && bc % 16 == 0 && dim % 16 == 0;
+    if (fast) {
+        kt = (float*)malloc(sizeof(float) * (size_t)((seq + bc - 1) / bc) * dim * bc);
+        if (!kt) {
+            free(s_buf); free(p_buf); free(o_buf); free(m_buf); free(l_buf);
+            return ORC_ERR_ALLOC;
+        }
+        pack_k_transposed(k, seq, dim, bc, kt);
+    }
     for (int64_t qi = 0; qi < seq; qi += br) {
         const int br_used = (int)((qi + br < seq ? qi + br : seq) - qi);
         for (int r = 0; r < br_used; ++r) { /* :303-309 */
@@ -144,15 +355,22 @@ static int flash_forward_bh(const float* q, const float* k, const float* v, floa
         }
         for (int64_t kj = 0; kj < seq; kj += bc) { /* :312-403 */
             const int bc_used = (int)((kj + bc < seq ? kj + bc : seq) - kj);
-            sgemm_score_tile(br_used, bc_used, dim, scale, q + (size_t)qi * dim, dim,
-                             k + (size_t)kj * dim, dim, s_buf, bc_used);
+            /* in fast mode the score tile is computed bc wide (padded keys give 0 and are masked by
+             * bc_used below); rows of s_buf / p_buf are then bc apart */
+            const int lds = fast ? bc : bc_used;
+            if (fast)
+                gemm_nn_fast(br_used, bc, dim, scale, q + (size_t)qi * dim, dim, kt + (size_t)(kj / bc) * dim * bc,
+                             bc, s_buf, bc, 0);
+            else
+                sgemm_score_tile(br_used, bc_used, dim, scale, q + (size_t)qi * dim, dim,
+                                 k + (size_t)kj * dim, dim, s_buf, bc_used);
             if (!none) { /* :342-352 */
                 for (int r = 0; r < br_used; ++r)
                     for (int c = 0; c < bc_used; ++c)
-                        if (is_masked(mask, qi + r, kj + c)) s_buf[(size_t)r * bc_used + c] = -INFINITY;
+                        if (is_masked(mask, qi + r, kj + c)) s_buf[(size_t)r * lds + c] = -INFINITY;
             }
             for (int r = 0; r < br_used; ++r) { /* :355-386 */
-                const float* s_row = s_buf + (size_t)r * bc_used;
+                const float* s_row = s_buf + (size_t)r * lds;
                 float m_tile = -INFINITY;
                 for (int c = 0; c < bc_used; ++c)
                     if (s_row[c] > m_tile) m_tile = s_row[c];
@@ -163,7 +381,7 @@ static int flash_forward_bh(const float* q, const float* k, const float* v, floa
                     l_buf[r] *= alpha;
                     for (int d = 0; d < dim; ++d) o_buf[(size_t)r * dim + d] *= alpha;
                 }
-                float* p_row = p_buf + (size_t)r * bc_used;
+                float* p_row = p_buf + (size_t)r * lds;
                 float tile_l = 0.0f;
                 if (fix_leading_masked_tile && m_new == -INFINITY) {
                     for (int c = 0; c < bc_used; ++c) p_row[c] = 0.0f;
@@ -177,8 +395,11 @@ static int flash_forward_bh(const float* q, const float* k, const float* v, floa
                 l_buf[r] += tile_l;
                 m_buf[r] = m_new;
             }
-            sgemm_value_accumulate(br_used, dim, bc_used, p_buf, bc_used, v + (size_t)kj * dim, dim,
-                                   o_buf, dim);
+            if (fast)
+                gemm_nn_fast(br_used, dim, bc_used, 1.0f, p_buf, lds, v + (size_t)kj * dim, dim, o_buf, dim, 1);
+            else
+                sgemm_value_accumulate(br_used, dim, bc_used, p_buf, bc_used, v + (size_t)kj * dim, dim,
+                                       o_buf, dim);
         }
         for (int r = 0; r < br_used; ++r) { /* :406-421 */
             float* dst = out + (size_t)(qi + r) * dim;
@@ -192,7 +413,7 @@ static int flash_forward_bh(const float* q, const float* k, const float* v, floa
             if (lse) lse[qi + r] = (l > 0.0f) ? m_buf[r] + logf(l) : (l == 0.0f ? -INFINITY : NAN);
         }
     }
-    free(s_buf); free(p_buf); free(o_buf); free(m_buf); free(l_buf);
+    free(s_buf); free(p_buf); free(o_buf); free(m_buf); free(l_buf); free(kt);
     return ORC_OK;
 }
 

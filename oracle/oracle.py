@@ -69,6 +69,12 @@ def lib() -> ctypes.CDLL:
         _lib.orc_fill_uniform_int.argtypes = [i32p, c_int64, c_uint64, c_int32, c_int32]
         _lib.orc_fill_lcg.argtypes = [fp, c_int64, c_uint32, c_float]
         _lib.orc_set_threads.argtypes = [c_int]
+        _lib.orc_set_gemm_kernel.argtypes = [c_int]
+        _lib.orc_get_gemm_kernel.restype = c_int
+        _lib.orc_micro_isa.restype = c_int
+        _lib.orc_fma_peak_gflops.restype = ctypes.c_double
+        _lib.orc_tile_gemm_gflops.restype = ctypes.c_double
+        _lib.orc_tile_gemm_gflops.argtypes = [c_int, c_int]
         _lib.orc_get_threads.restype = c_int
     return _lib
 
@@ -88,6 +94,30 @@ def set_threads(n: int) -> None:
 
 def get_threads() -> int:
     return int(lib().orc_get_threads())
+
+
+def set_gemm_kernel(kind: int) -> None:
+    """0: the tile products run as plain loop nests (the parity oracle).  1: they run on the register-blocked
+    FMA micro-kernels that stand in for the reference's `gemm` crate when the CPU path is timed."""
+    lib().orc_set_gemm_kernel(int(kind))
+
+
+def get_gemm_kernel() -> int:
+    return int(lib().orc_get_gemm_kernel())
+
+
+def micro_isa() -> str:
+    return {0: "none", 1: "avx2+fma", 2: "avx512f"}[int(lib().orc_micro_isa())]
+
+
+def fma_peak_gflops() -> float:
+    """One core's measured f32 FMA throughput on the ISA the micro-kernels use (GFLOP/s)."""
+    return float(lib().orc_fma_peak_gflops())
+
+
+def tile_gemm_gflops(dim: int, reps: int = 20000) -> float:
+    """Throughput of the two tile products alone (64x64xdim and 64xdimx64) on one core (GFLOP/s)."""
+    return float(lib().orc_tile_gemm_gflops(int(dim), int(reps)))
 
 
 # ----------------------------------------------------------------- inputs

@@ -1,6 +1,7 @@
 // extern "C" boundary of the attention library: argument validation (mirroring the reference's
 // validate() / Mask::validate / gqa_forward_f32 checks) and dispatch to the sm_100a kernels.
 // Nothing here computes attention on the host: without a CUDA device every compute entry fails.
+#include <atomic>
 #include <cmath>
 #include <cstdlib>
 #include <mutex>
@@ -13,15 +14,29 @@ namespace rt {
 __device__ int g_device_status = 0;
 
 int* device_status_ptr() {
-    static int* cache[64] = {nullptr};
+    static std::atomic<int*> cache[64];
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
-    if (!cache[dev]) {
-        void* p = nullptr;
-        if (cudaGetSymbolAddress(&p, g_device_status) != cudaSuccess) return nullptr;
-        cache[dev] = static_cast<int*>(p);
+    int* p = cache[dev].load(std::memory_order_acquire);
+    if (!p) {  // two first callers may both look the address up; they store the same value
+        void* q = nullptr;
+        if (cudaGetSymbolAddress(&q, g_device_status) != cudaSuccess) return nullptr;
+        p = static_cast<int*>(q);
+        cache[dev].store(p, std::memory_order_release);
     }
-    return cache[dev];
+    return p;
+}
+
+int sm_count() {
+    static std::atomic<int> cache[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    int n = cache[dev].load(std::memory_order_relaxed);
+    if (n <= 0) {
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) return 148;
+        cache[dev].store(n, std::memory_order_relaxed);
+    }
+    return n;
 }
 }  // namespace rt
 

@@ -506,7 +506,7 @@ cudaError_t launch_rope_kv_append(void* q, const void* k_in, const void* v_in, v
 
 // Tokens per KV chunk (one CTA per chunk).  Large chunks amortise the per-CTA prologue and the
 // partial traffic (1024 tokens measured best on the ragged batched workload); the choice walks
-// down from 1024 until the grid both covers the 148 SMs x 2 resident CTAs and fills its last wave
+// down from 1024 until the grid both covers the SMs x 2 resident CTAs and fills its last wave
 // to at least 95 % (a long single sequence otherwise loses up to a quarter of a wave).  It depends
 // only on (batch, n_kv, max_seq) so that rt_gqa_decode_workspace_bytes can size the scratch.
 // RT_ATTN_DECODE_CHUNK=<multiple of 64> overrides it.
@@ -518,7 +518,7 @@ int decode_chunk_tokens(int64_t batch, int n_kv, int64_t max_seq) {
     }();
     if (forced) return forced;
     const int64_t base = (batch > 0 ? batch : 1) * (int64_t)(n_kv > 0 ? n_kv : 1);
-    const int64_t slots = 148 * 2;
+    const int64_t slots = (int64_t)sm_count() * 2;
     int best = 128;
     double best_eff = -1.0;
     for (int c = 1024; c >= 128; c -= 64) {

@@ -22,6 +22,7 @@
 #include "kernels.h"
 #include "mma_sync.cuh"
 #include "tc_ptx.cuh"
+#include "tensor_map.h"
 
 namespace rt {
 
@@ -229,8 +230,12 @@ gqa_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
             tma_load_2d(dst + C::KV_BYTES + s * C::BOX_BYTES, &tm_v, &full[st], s * 64, (int)(cache_row0 + t0));
         }
     };
+    int issued_upto = -1;  // lane 0: highest iteration whose loads have been issued
     if (lane == 0)
-        for (int it = 0; it < STAGES && it < n_my; ++it) issue(it);
+        for (int it = 0; it < STAGES && it < n_my; ++it) {
+            issue(it);
+            issued_upto = it;
+        }
 
     float m_run = -INFINITY, l_part = 0.f;  // state of head g (all four lanes of a group agree on m_run)
     float o[NT][4];
@@ -322,13 +327,20 @@ gqa_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
         if (lane == 0 && it + STAGES < n_my) {
             fence_proxy_async();  // order this warp's reads of the stage before the refill
             issue(it + STAGES);
+            issued_upto = it + STAGES;
         }
     }
     if (!ok && lane == 0) {
-        // Drain: the copies this warp issued must land before the CTA may exit.
+        // Drain: every copy this warp issued must land before the ring is reused below and before the
+        // CTA may exit.  The last load into stage s was iteration `last`; it completes phase last/STAGES
+        // of that stage's barrier, so that parity (and no other) is what to wait for, bounded.
+        const int issued = issued_upto + 1;  // iterations 0 .. issued-1 have loads in flight or landed
         for (int s = 0; s < STAGES; ++s) {
-            long long t0 = clock64();
-            while (!mbar_try_wait(&full[s], 0) && !mbar_try_wait(&full[s], 1) && clock64() - t0 < (1ll << 28)) {
+            if (issued <= s) continue;  // this stage was never loaded
+            const int last = s + ((issued - 1 - s) / STAGES) * STAGES;
+            const uint32_t par = (uint32_t)(last / STAGES) & 1u;
+            const long long t0 = clock64();
+            while (!mbar_try_wait(&full[s], par) && clock64() - t0 < (1ll << 28)) {
             }
         }
     }
@@ -382,22 +394,12 @@ gqa_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
     }
 }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-EncodeTiledFn tensor_map_encoder();  // prefill_tc.cu
-
 // The cache viewed as a 2-D bf16 tensor [rows = B*Hkv*max_seq, D]; box = 16 rows x 64 columns.
 static bool make_cache_map(CUtensorMap* map, const void* base, int64_t rows, int dim) {
-    EncodeTiledFn enc = tensor_map_encoder();
-    if (!enc) return false;
-    cuuint64_t dims[2] = {(cuuint64_t)dim, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)dim * 2};
-    cuuint32_t box[2] = {64, 16};
-    cuuint32_t estr[2] = {1, 1};
-    return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    const uint64_t dims[2] = {(uint64_t)dim, (uint64_t)rows};
+    const uint64_t strides[1] = {(uint64_t)dim * 2};
+    const uint32_t box[2] = {64, 16};
+    return encode_bf16_map_cached(map, 2, base, dims, strides, box);
 }
 
 template <int D, int G>
@@ -470,7 +472,7 @@ cudaError_t launch_gqa_decode_tc(const void* q, const void* k, const void* v, vo
     }();
     // ... and only for grids of several waves: a small launch (batch 1) is latency-bound, and there the
     // memset node plus the serial tail cost more than the second launch (14.4 us against 10.3 us).
-    const bool many_ctas = batch * n_kv * (int64_t)n_chunks >= 4 * 148;
+    const bool many_ctas = batch * n_kv * (int64_t)n_chunks >= 4 * (int64_t)sm_count();
     p.counters = (n_chunks > 1 && n_chunks <= kMaxFusedChunks && many_ctas && !fused_off) ? counters : nullptr;
     if (p.counters) {
         cudaError_t e = cudaMemsetAsync(p.counters, 0, sizeof(int) * (size_t)batch * n_kv, stream);

@@ -7,6 +7,9 @@ namespace rt {
 
 // ---- api.cu: device address of the status word of the current device (NULL on failure)
 int* device_status_ptr();
+// Multiprocessors of the current device, queried once per device; 148 (B200) when no device answers,
+// so that the size queries that need no GPU (workspace bytes) stay deterministic.
+int sm_count();
 
 // ---- decode.cu
 struct MergePush;

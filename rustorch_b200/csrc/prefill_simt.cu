@@ -162,7 +162,8 @@ __global__ void bf16_to_f32_kernel(const __nv_bfloat16* __restrict__ src, float*
 
 static unsigned grid_for(int64_t n) {
     int64_t g = (n + 255) / 256;
-    return (unsigned)(g > 148 * 16 ? 148 * 16 : (g < 1 ? 1 : g));
+    const int64_t cap = (int64_t)sm_count() * 16;
+    return (unsigned)(g > cap ? cap : (g < 1 ? 1 : g));
 }
 
 cudaError_t launch_f32_to_bf16(const float* src, void* dst, int64_t n, cudaStream_t stream) {

@@ -35,6 +35,7 @@
 
 #include "kernels.h"
 #include "tc_ptx.cuh"
+#include "tensor_map.h"
 
 namespace rt {
 
@@ -72,54 +73,8 @@ struct TcParams {
     int n_qb;          // 256-row blocks per head
     int slots_per_head, n_slots, paired;  // static schedule, see tc_item
     int single_tile;   // items are 128-row blocks handled by Q tile 1 alone (small launches, see tc_item)
-#ifdef RT_TC_TIMELINE
-    long long* timeline;  // profiling builds only, see TL_* below
-#endif
 };
 
-#ifdef RT_TC_TIMELINE
-// Profiling aid, compiled only with -DRT_TC_TIMELINE.  Per CTA 64 entries: {start ns, end ns, SM id,
-// items}, then per item j < 15 {softmax of tile 0 reaches the item, its steps are done, its
-// epilogue is done, steps}.
-__device__ __forceinline__ long long tl_globaltimer() {
-    long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
-}
-__device__ __forceinline__ int tl_smid() {
-    int s;
-    asm volatile("mov.u32 %0, %smid;" : "=r"(s));
-    return s;
-}
-#define TL_CTA_BEGIN() const long long tl_t0 = tl_globaltimer(), tl_c0 = clock64()
-#define TL_CTA_END(items)                                                       \
-    do {                                                                        \
-        if (p.timeline && threadIdx.x == 0) {                                   \
-            long long* e = p.timeline + (long long)blockIdx.x * 64;             \
-            e[0] = tl_t0; e[1] = tl_globaltimer(); e[2] = tl_smid(); e[3] = (items); \
-            e[62] = tl_c0; e[63] = clock64();                                   \
-        }                                                                       \
-    } while (0)
-#define TL_ITEM(j, slot, val)                                                   \
-    do {                                                                        \
-        if (p.timeline && threadIdx.x == 0 && (j) < 15)                         \
-            p.timeline[(long long)blockIdx.x * 64 + 4 + (j) * 4 + (slot)] = (val); \
-    } while (0)
-// After the CTA log (gridDim.x * 64 entries): clock64 stamps of the first item of CTA 0,
-// [role 0..3][step][8] (role 0/1 = softmax of Q tile 0/1, role 2/3 = MMA issuer of Q tile 0/1).
-#define TL_STAMP(role, step, slot)                                                                     \
-    do {                                                                                               \
-        if (p.timeline && blockIdx.x == 0 && j == 0 && (step) < 256)                                   \
-            p.timeline[(long long)gridDim.x * 64 + (((role) * 256) + (step)) * 8 + (slot)] = clock64(); \
-    } while (0)
-static long long* g_tc_timeline = nullptr;
-extern "C" void rt_debug_set_tc_timeline(void* ptr) { g_tc_timeline = (long long*)ptr; }
-#else
-#define TL_CTA_BEGIN() do { } while (0)
-#define TL_CTA_END(items) do { } while (0)
-#define TL_ITEM(j, slot, val) do { } while (0)
-#define TL_STAMP(role, step, slot) do { } while (0)
-#endif
 
 // Timeout codes written to the device status word (100 + site).
 enum { kToQ = 101, kToKFull, kToKEmpty, kToVFull, kToVEmpty, kToSFull, kToPFull, kToOFull, kToDone, kToDrain,
@@ -217,7 +172,6 @@ __global__ void __launch_bounds__(384, 1)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                   const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
                   const TcParams p) {
-    TL_CTA_BEGIN();
     using C = TcCfg<D>;
     constexpr int KS = C::KS, VS = C::VS, TILE = C::TILE_BYTES, SUB = C::SUB_BYTES, HALF = C::HALF_BYTES;
 
@@ -308,7 +262,6 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    int n_items_done = 0;
 
     // The register hand-over sits inside each role's own branch: the compiler budgets the code
     // that follows a setmaxnreg only when no path with a different budget merges into it.
@@ -455,9 +408,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                             if (!wait(&v_full[(vg + vt) % VS], (uint32_t)((vg + vt) / VS) & 1u, kToVFull)) { ok = false; break; }
                             v_waited = vt;
                         }
-                        TL_STAMP(2 + w, u, 0);
                         if (!wait(&p_full[w * 2 + (u & 1)], (uint32_t)(((u & 1) ? cp1 : cp0) + (u >> 1)) & 1u, kToPFull)) { ok = false; break; }
-                        TL_STAMP(2 + w, u, 1);
                         // the previous item's epilogue must have read O_w before it is overwritten
                         if (u == 0 && na > 0 && !wait(&o_free[w], (uint32_t)(na - 1) & 1u, kToOFree)) { ok = false; break; }
                         tc_fence_after();
@@ -472,12 +423,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                                 k_waited = kt;
                                 tc_fence_after();
                             }
-                            TL_STAMP(2 + w, u, 2);
                             issue_S(u + 2);
                             commit(&s_full[w * 2 + (u & 1)]);
                             if (last_use(u + 2)) commit(&ke[(kg + kt) % KS]);
                         }
-                        TL_STAMP(2 + w, u, 3);
                     }
                     ++na;
                     cp0 += (n_u + 1) / 2;
@@ -517,12 +466,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             const TcItem it = tc_item<kCausal>(j, p);
             if (it.end) break;
             if (!it.valid) continue;
-            ++n_items_done;
             const int n_iter = it.steps(w);
             const int bh = it.bh, kv_hi = it.kv_hi, q_off = it.q_off;
             const int row = it.q0 + w * 128 + row_in_tile;  // query index within the sequence
             const uint8_t* keep = kKeep ? p.key_keep + (int64_t)it.b * p.keep_batch_stride : nullptr;
-            if (w == 0) TL_ITEM(j, 0, tl_globaltimer());
 
             if (n_iter == 0) {  // the tile sees no key: NaN rows, LSE = -inf (cpu_forward.rs:411-420)
                 if (row < N && !(p.single_tile && w == 0)) {
@@ -540,14 +487,12 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             bool seen = false;  // the row has met a score that no mask hides
             for (int u = 0; u < n_iter; ++u) {
                 const int buf = u & 1;
-                if ((warp & 3) == 0 && lane == 0) TL_STAMP(w, u, 0);
                 if (!__all_sync(kFullMask, mbar_wait(&s_full[w * 2 + buf], (uint32_t)((buf ? cs1 : cs0) + (u >> 1)) & 1u,
                                                      p.status, kToSFull))) {
                     ok = false;
                     break;
                 }
                 tc_fence_after();
-                if ((warp & 3) == 0 && lane == 0) TL_STAMP(w, u, 1);
 
                 uint32_t s[64];
                 {
@@ -557,7 +502,6 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                     tmem_ld32(tS + buf * 64 + 32, s1);
                     tc_wait_ld();
                 }
-                if ((warp & 3) == 0 && lane == 0) TL_STAMP(w, u, 2);
 
                 // ---- masks: keys beyond kv_hi, causal diagonal, keep flags
                 const int col0 = u * 64;
@@ -616,7 +560,6 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                         tc_wait_st();
                     }
                 }
-                if ((warp & 3) == 0 && lane == 0) TL_STAMP(w, u, 3);
 
                 // ---- P = exp2(s*c - m*c), row sum, bf16 pack, store to TMEM over S (packed f32x2 math)
                 const float mc = (m_ref == -INFINITY) ? 0.f : m_ref * c;
@@ -644,14 +587,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                     tmem_st16(tS + buf * 64 + ch * 16, pk);
                 }
                 l += (sum_a.x + sum_a.y) + (sum_b.x + sum_b.y);
-                if ((warp & 3) == 0 && lane == 0) TL_STAMP(w, u, 4);
                 tc_wait_st();
                 tc_fence_before();
                 mbar_arrive(&p_full[w * 2 + buf]);
-                if ((warp & 3) == 0 && lane == 0) TL_STAMP(w, u, 5);
             }
             if (!ok) break;
-            if (w == 0) TL_ITEM(j, 1, tl_globaltimer());
 
             // ---- epilogue: O / l -> bf16 into the (now idle) shared-memory tile of Q_w in the swizzled
             // layout of the output tensor map, then one TMA store per 64-column half: 16-byte shared
@@ -708,8 +648,6 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 }
             }
             ok = __all_sync(kFullMask, ok);
-            if (w == 0) TL_ITEM(j, 2, tl_globaltimer());
-            if (w == 0) TL_ITEM(j, 3, (long long)(it.U0 + it.U1));
             ++na;
             cs0 += (n_iter + 1) / 2;
             cs1 += n_iter / 2;
@@ -724,7 +662,6 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         tc_fence_after();
         tmem_dealloc(tmem_base, C::TMEM_COLS);
     }
-    TL_CTA_END(n_items_done);
 }
 
 // ---------------------------------------------------------------------- host side
@@ -746,7 +683,54 @@ static EncodeTiledFn get_encode_fn() {
     return fn;
 }
 
-EncodeTiledFn tensor_map_encoder() { return get_encode_fn(); }
+bool encode_bf16_map_cached(CUtensorMap* out, int rank, const void* base, const uint64_t* dims,
+                            const uint64_t* strides_bytes, const uint32_t* box) {
+    struct Key {
+        const void* base;
+        uint64_t dims[4], strides[3];
+        uint32_t box[4];
+        int rank;
+    };
+    constexpr int kEntries = 32;
+    struct Cache {
+        Key key[kEntries];
+        CUtensorMap map[kEntries];
+        int used = 0, next = 0;
+    };
+    thread_local Cache cache;
+    if (rank < 1 || rank > 4) return false;
+    Key k;
+    memset(&k, 0, sizeof(k));
+    k.base = base;
+    k.rank = rank;
+    for (int i = 0; i < rank; ++i) {
+        k.dims[i] = dims[i];
+        k.box[i] = box[i];
+        if (i + 1 < rank) k.strides[i] = strides_bytes[i];
+    }
+    for (int i = 0; i < cache.used; ++i)
+        if (memcmp(&cache.key[i], &k, sizeof(Key)) == 0) {
+            *out = cache.map[i];
+            return true;
+        }
+    EncodeTiledFn enc = get_encode_fn();
+    if (!enc) return false;
+    cuuint64_t d[4], st[3];
+    cuuint32_t bx[4], estr[4] = {1, 1, 1, 1};
+    for (int i = 0; i < rank; ++i) {
+        d[i] = dims[i];
+        bx[i] = box[i];
+        if (i + 1 < rank) st[i] = strides_bytes[i];
+    }
+    if (enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank, const_cast<void*>(base), d, st, bx, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return false;
+    const int slot = cache.used < kEntries ? cache.used++ : (cache.next = (cache.next + 1) % kEntries);
+    cache.key[slot] = k;
+    cache.map[slot] = *out;
+    return true;
+}
 
 // View of a [B, H, N, D] bf16 tensor with arbitrary batch / head / row strides (inner dim contiguous)
 // as a 4-D TMA tensor (d, row, head, batch); box = 64 columns x 128 rows of one (b,h), 128-byte
@@ -754,28 +738,18 @@ EncodeTiledFn tensor_map_encoder() { return get_encode_fn(); }
 // neighbouring head.  Strides are in elements and must be multiples of 8 (16 bytes).
 bool make_tensor_map_bf16_4d(CUtensorMap* map, const void* base, int64_t batch, int64_t heads, int64_t seq, int dim,
                              int64_t stride_b, int64_t stride_h, int64_t stride_row) {
-    EncodeTiledFn enc = get_encode_fn();
-    if (!enc) return false;
-    cuuint64_t dims[4] = {(cuuint64_t)dim, (cuuint64_t)seq, (cuuint64_t)heads, (cuuint64_t)batch};
-    cuuint64_t strides[3] = {(cuuint64_t)stride_row * 2, (cuuint64_t)stride_h * 2, (cuuint64_t)stride_b * 2};
-    cuuint32_t box[4] = {64, 128, 1, 1};
-    cuuint32_t estr[4] = {1, 1, 1, 1};
-    return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
-               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    const uint64_t dims[4] = {(uint64_t)dim, (uint64_t)seq, (uint64_t)heads, (uint64_t)batch};
+    const uint64_t strides[3] = {(uint64_t)stride_row * 2, (uint64_t)stride_h * 2, (uint64_t)stride_b * 2};
+    const uint32_t box[4] = {64, 128, 1, 1};
+    return encode_bf16_map_cached(map, 4, base, dims, strides, box);
 }
 
 // The contiguous [B*H, N, D] view used by the self-test kernel.
 bool make_tensor_map_bf16_3d(CUtensorMap* map, const void* base, int64_t bh, int64_t seq, int dim) {
-    EncodeTiledFn enc = get_encode_fn();
-    if (!enc) return false;
-    cuuint64_t dims[3] = {(cuuint64_t)dim, (cuuint64_t)seq, (cuuint64_t)bh};
-    cuuint64_t strides[2] = {(cuuint64_t)dim * 2, (cuuint64_t)seq * dim * 2};
-    cuuint32_t box[3] = {64, 128, 1};
-    cuuint32_t estr[3] = {1, 1, 1};
-    return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
-               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    const uint64_t dims[3] = {(uint64_t)dim, (uint64_t)seq, (uint64_t)bh};
+    const uint64_t strides[2] = {(uint64_t)dim * 2, (uint64_t)seq * dim * 2};
+    const uint32_t box[3] = {64, 128, 1};
+    return encode_bf16_map_cached(map, 3, base, dims, strides, box);
 }
 
 template <int D, bool kCausal, bool kKeep>
@@ -822,33 +796,33 @@ cudaError_t launch_prefill_tc(const void* q, const void* k, const void* v, void*
     p.scale_log2 = scale * kLog2e;
     p.status = device_status_ptr();
     if (!p.status) return cudaErrorInvalidSymbol;
-#ifdef RT_TC_TIMELINE
-    p.timeline = g_tc_timeline;
-#endif
     // Schedule (tc_item).  A causal launch without per-batch lengths has a known cost per item, so
     // it runs one CTA per SM over a static list in which the 256-row blocks of a head are paired
     // heavy + light: every CTA gets the same work and the per-item set-up overlaps the previous
     // item.  Other launches (uniform items, or lengths only the device knows) use one CTA per item
     // and leave the balancing to the hardware scheduler.  RT_ATTN_PREFILL_SCHED=persistent|percta
     // overrides the choice.
-    int dev = 0, n_sm = 0;
-    cudaError_t e = cudaGetDevice(&dev);
-    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
-    if (e != cudaSuccess) return e;
+    const int n_sm = sm_count();
+    // RT_ATTN_PREFILL_TILES=1|2 and RT_ATTN_PREFILL_SCHED=persistent|percta override the choices below
+    // (read once per process).
+    static const int env_tiles = [] {
+        const char* s = getenv("RT_ATTN_PREFILL_TILES");
+        return (s && s[0] == '1') ? 1 : (s && s[0] == '2') ? 2 : 0;
+    }();
+    static const int env_sched = [] {
+        const char* s = getenv("RT_ATTN_PREFILL_SCHED");
+        return (s && !strcmp(s, "persistent")) ? 1 : (s && !strcmp(s, "percta")) ? 2 : 0;
+    }();
     p.single_tile = (seq > 128 && bh * ((seq + 255) / 256) * 4 < 3 * (int64_t)n_sm) ? 1 : 0;
-    if (const char* s = getenv("RT_ATTN_PREFILL_TILES")) {
-        if (s[0] == '1') p.single_tile = 1;
-        if (s[0] == '2') p.single_tile = 0;
-    }
+    if (env_tiles == 1) p.single_tile = 1;
+    if (env_tiles == 2) p.single_tile = 0;
     const int64_t n_qb = p.single_tile ? (seq + 127) / 128 : (seq + 255) / 256;
     const int64_t n_items = bh * n_qb;
     if (n_items > 0x3fffffff) return cudaErrorInvalidValue;
     p.n_qb = (int)n_qb;
     bool persistent = causal && kv_lens == nullptr && n_items >= 2 * (int64_t)n_sm && !p.single_tile;
-    if (const char* s = getenv("RT_ATTN_PREFILL_SCHED")) {
-        if (!strcmp(s, "persistent")) persistent = true;
-        if (!strcmp(s, "percta")) persistent = false;
-    }
+    if (env_sched == 1) persistent = true;
+    if (env_sched == 2) persistent = false;
     p.paired = (persistent && n_items >= 2 * (int64_t)n_sm) ? 1 : 0;
     p.slots_per_head = p.paired ? (int)((n_qb + 1) / 2) : (int)n_qb;
     p.n_slots = (int)(bh * p.slots_per_head);

@@ -340,3 +340,42 @@ def test_peer_exchange_fused_decode_push_on_one_device(oracle, kv_total, S):
         assert all(int(ex._done.item()) == 0 for ex in ranks)
     full, full_lse = rt.gqa_decode(q, k, v, kv_len=kv_total, out_dtype=torch.float32)
     assert (want - full.reshape(B * Hq, D)).abs().max().item() < 1e-3
+
+
+def test_decode_long_context_shard_at_full_size(oracle):
+    """One GPU's share of the long-context split-KV workload at its real size: B=1, Hq=32, Hkv=8, D=128,
+    131072 cached positions (0.5 GiB of K and V on the device, 147 chunks into the chunk-merge kernel),
+    against the oracle's decode_attn_row restatement, through rt_gqa_decode_record_bf16 +
+    rt_attn_merge_records; then the same range cut into 8 shards by 8 emulated ranks on this device
+    (peer exchange with the peers being local buffers), every rank's merge against the oracle."""
+    import torch
+    import rustorch_b200 as rt
+    from rustorch_b200 import _lib, sharding
+    B, Hq, Hkv, D, T = 1, 32, 8, 128, 131072
+    q, k, v, lens = _problem(oracle, B, Hq, Hkv, D, T, [T])
+    rc, ref, ref_lse = oracle.gqa_decode_cache(q, k, v, lens)
+    assert rc == 0
+    dq, dk, dv = util.to_cuda_bf16(q), util.to_cuda_bf16(k), util.to_cuda_bf16(v)
+
+    rec = rt.gqa_decode_record(dq, dk, dv, kv_len=T)
+    out, lse = rt.merge_records(rec.unsqueeze(0), out_dtype=torch.float32)
+    out16, _ = rt.gqa_decode(dq, dk, dv, kv_len=T)
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    util.check_output(util.to_np(out).reshape(B, Hq, D), ref, bf16_out=False, label="131072-position shard, f32 record")
+    util.check_lse(util.to_np(lse).reshape(B, Hq), ref_lse)
+    util.check_output(util.to_np(out16), ref, label="131072-position shard, bf16 out")
+
+    world = 8
+    ranks = sharding.PeerRecordExchange.local_pair(world, B * Hq, D)
+    for r, ex in enumerate(ranks):
+        b0, b1 = sharding.kv_shard(T, world, r, align=16)
+        rt.gqa_decode_record(dq, dk, dv, kv_len=T, kv_begin=b0, kv_end=b1, record=ex.next_epoch())
+    for ex in ranks:
+        ex.push()
+    for ex in ranks:
+        got, got_lse = ex.merge(out_dtype=torch.float32)
+        torch.cuda.synchronize()
+        util.check_output(util.to_np(got).reshape(B, Hq, D), ref, bf16_out=False, label="8 emulated shards")
+        util.check_lse(util.to_np(got_lse).reshape(B, Hq), ref_lse)
+    assert _lib.device_status() == 0

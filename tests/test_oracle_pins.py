@@ -271,3 +271,42 @@ def test_gqa_decode_row_equals_naive_attention(oracle):
             w = np.exp(s - s.max())
             ref = (w / w.sum()) @ v[b, h // 4].astype(np.float64)
             assert np.abs(out[b, h] - ref).max() < 1e-5
+
+
+# ---- the timed CPU arm: register-blocked tile GEMMs standing in for the `gemm` crate
+@pytest.mark.parametrize("shape", SHAPES_20)
+def test_micro_kernel_path_matches_loop_nests(oracle, shape):
+    """The micro-kernel path of the timed baseline computes what the loop-nest oracle computes (1e-4, the
+    reference's own flash-vs-naive gate), on the reference's 20-shape matrix; shapes whose dims the
+    micro-kernels do not cover fall back to the loop nests and agree exactly."""
+    q, k, v = _buffers(oracle, shape, 2.0)
+    assert oracle.get_gemm_kernel() == 0
+    _, a = oracle.flash_forward_masked(q, k, v)
+    oracle.set_gemm_kernel(1)
+    try:
+        _, b = oracle.flash_forward_masked(q, k, v)
+        _, c = oracle.flash_forward_masked(q, k, v, mask_kind=1)
+    finally:
+        oracle.set_gemm_kernel(0)
+    _, c0 = oracle.flash_forward_masked(q, k, v, mask_kind=1)
+    assert np.abs(a - b).max() < 1e-4 and np.abs(c - c0).max() < 1e-4
+    _, n = oracle.naive_forward_masked(q, k, v)
+    assert np.abs(b - n).max() < 1e-4
+
+
+def test_micro_kernel_path_ragged_and_masked(oracle):
+    """Sequence lengths that leave partial row and key tiles, causal + kv_len, LSE: both GEMM modes agree."""
+    for (B, H, N, D) in ((1, 2, 200, 64), (2, 1, 129, 128), (1, 1, 70, 32)):
+        q, k, v = (oracle.round_to_bf16(oracle.fill_normal((B, H, N, D), s)) for s in (5, 6, 7))
+        lens = np.array([N - 3] * B, dtype=np.int32)
+        _, a, la = oracle.flash_forward_ext(q, k, v, causal=True, kv_lens=lens)
+        oracle.set_gemm_kernel(1)
+        try:
+            _, b, lb = oracle.flash_forward_ext(q, k, v, causal=True, kv_lens=lens)
+        finally:
+            oracle.set_gemm_kernel(0)
+        assert np.array_equal(np.isnan(a), np.isnan(b))
+        ok = ~np.isnan(a)
+        assert np.abs(a[ok] - b[ok]).max() < 1e-4 and np.abs(la - lb).max() < 1e-4
+    if oracle.micro_isa() != "none":
+        assert oracle.tile_gemm_gflops(64, 200) > 0.0 and oracle.fma_peak_gflops() > 0.0
