@@ -215,66 +215,6 @@ int rt_attn_prefill_f32(const float* q, const float* k, const float* v, float* o
     return RT_OK;
 }
 
-int rt_flash_forward_f32_host(const float* q, size_t q_len, const float* k, size_t k_len, const float* v,
-                              size_t v_len, float* out, size_t out_len, int64_t batch, int64_t heads, int64_t seq,
-                              int64_t dim, int mask_kind, const uint8_t* keep, size_t keep_len, int precision) {
-    // validate(): cpu_forward.rs:142-169
-    if (dim == 0) return RT_ERR_ZERO_DIM;
-    if (batch < 0 || heads < 0 || seq < 0 || dim < 0) return RT_ERR_BAD_LENGTH;
-    const size_t expected = (size_t)batch * (size_t)heads * (size_t)seq * (size_t)dim;
-    if (q_len != expected || k_len != expected || v_len != expected) return RT_ERR_BUFFER_SHAPE;
-    if (out_len != expected) return RT_ERR_OUTPUT_SHAPE;
-    // Mask::validate: mask.rs:51-65
-    if (mask_kind < RT_MASKKIND_NONE || mask_kind > RT_MASKKIND_PADDING) return RT_ERR_UNSUPPORTED;
-    if (mask_kind == RT_MASKKIND_PADDING && keep_len != (size_t)seq) return RT_ERR_MASK_LEN;
-    if (seq == 0 || expected == 0) return RT_OK;
-    if (!q || !k || !v || !out) return RT_ERR_NULL_POINTER;
-    if (mask_kind == RT_MASKKIND_PADDING && !keep) return RT_ERR_NULL_POINTER;
-    if (precision != RT_PRECISION_F32 && precision != RT_PRECISION_BF16) return RT_ERR_UNSUPPORTED;
-    if (precision == RT_PRECISION_BF16 && dim != 64 && dim != 128) return RT_ERR_UNSUPPORTED;
-    if (precision == RT_PRECISION_F32 && dim > 256) return RT_ERR_UNSUPPORTED;
-
-    const size_t bytes = expected * sizeof(float);
-    std::lock_guard<std::mutex> lock(g_staging.mu);
-    DevBuf dq(0), dk(1), dv(2), dout(3), dkeep(4);
-    RT_CUDA(dq.alloc(bytes));
-    RT_CUDA(dk.alloc(bytes));
-    RT_CUDA(dv.alloc(bytes));
-    RT_CUDA(dout.alloc(bytes));
-    RT_CUDA(cudaMemcpy(dq.p, q, bytes, cudaMemcpyHostToDevice));
-    RT_CUDA(cudaMemcpy(dk.p, k, bytes, cudaMemcpyHostToDevice));
-    RT_CUDA(cudaMemcpy(dv.p, v, bytes, cudaMemcpyHostToDevice));
-    const uint8_t* keep_dev = nullptr;
-    if (mask_kind == RT_MASKKIND_PADDING) {
-        RT_CUDA(dkeep.alloc(keep_len));
-        RT_CUDA(cudaMemcpy(dkeep.p, keep, keep_len, cudaMemcpyHostToDevice));
-        keep_dev = dkeep.as<uint8_t>();
-    }
-    const int flags = (mask_kind == RT_MASKKIND_CAUSAL) ? RT_MASK_CAUSAL : RT_MASK_NONE;
-    if (precision == RT_PRECISION_F32) {
-        int rc = rt_attn_prefill_f32(dq.as<float>(), dk.as<float>(), dv.as<float>(), dout.as<float>(), nullptr,
-                                     batch, heads, heads, seq, seq, (int)dim, flags, nullptr, nullptr, keep_dev, 0,
-                                     -1.f, nullptr);
-        if (rc != RT_OK) return rc;
-    } else {
-        DevBuf bq(5), bk(6), bv(7), bo(8);
-        RT_CUDA(bq.alloc(expected * 2));
-        RT_CUDA(bk.alloc(expected * 2));
-        RT_CUDA(bv.alloc(expected * 2));
-        RT_CUDA(bo.alloc(expected * 2));
-        RT_CUDA(rt::launch_f32_to_bf16(dq.as<float>(), bq.p, (int64_t)expected, nullptr));
-        RT_CUDA(rt::launch_f32_to_bf16(dk.as<float>(), bk.p, (int64_t)expected, nullptr));
-        RT_CUDA(rt::launch_f32_to_bf16(dv.as<float>(), bv.p, (int64_t)expected, nullptr));
-        int rc = rt_attn_prefill_bf16(bq.p, bk.p, bv.p, bo.p, nullptr, batch, heads, seq, (int)dim, flags, nullptr,
-                                      keep_dev, 0, -1.f, nullptr);
-        if (rc != RT_OK) return rc;
-        RT_CUDA(rt::launch_bf16_to_f32(bo.p, dout.as<float>(), (int64_t)expected, nullptr));
-        RT_CUDA(cudaDeviceSynchronize());
-    }
-    RT_CUDA(cudaMemcpy(out, dout.p, bytes, cudaMemcpyDeviceToHost));
-    return RT_OK;
-}
-
 // Streams and events of the pipelined host entry, created once per device.
 namespace {
 struct HostPipeline {
@@ -298,6 +238,106 @@ struct HostPipeline {
 };
 HostPipeline g_pipe;
 }  // namespace
+
+// flash_forward / flash_forward_masked on host f32 slices (cpu_forward.rs:175-242).  The (batch, head
+// range) chunks run through three streams: upload of chunk c+1, conversion + kernel of chunk c and
+// download of chunk c-1 overlap (fully with pinned host memory; with pageable memory the driver
+// stages the copies, and the kernels still overlap them).
+int rt_flash_forward_f32_host(const float* q, size_t q_len, const float* k, size_t k_len, const float* v,
+                              size_t v_len, float* out, size_t out_len, int64_t batch, int64_t heads, int64_t seq,
+                              int64_t dim, int mask_kind, const uint8_t* keep, size_t keep_len, int precision) {
+    // validate(): cpu_forward.rs:142-169
+    if (dim == 0) return RT_ERR_ZERO_DIM;
+    if (batch < 0 || heads < 0 || seq < 0 || dim < 0) return RT_ERR_BAD_LENGTH;
+    const size_t expected = (size_t)batch * (size_t)heads * (size_t)seq * (size_t)dim;
+    if (q_len != expected || k_len != expected || v_len != expected) return RT_ERR_BUFFER_SHAPE;
+    if (out_len != expected) return RT_ERR_OUTPUT_SHAPE;
+    // Mask::validate: mask.rs:51-65
+    if (mask_kind < RT_MASKKIND_NONE || mask_kind > RT_MASKKIND_PADDING) return RT_ERR_UNSUPPORTED;
+    if (mask_kind == RT_MASKKIND_PADDING && keep_len != (size_t)seq) return RT_ERR_MASK_LEN;
+    if (seq == 0 || expected == 0) return RT_OK;
+    if (!q || !k || !v || !out) return RT_ERR_NULL_POINTER;
+    if (mask_kind == RT_MASKKIND_PADDING && !keep) return RT_ERR_NULL_POINTER;
+    if (precision != RT_PRECISION_F32 && precision != RT_PRECISION_BF16) return RT_ERR_UNSUPPORTED;
+    if (precision == RT_PRECISION_BF16 && dim != 64 && dim != 128) return RT_ERR_UNSUPPORTED;
+    if (precision == RT_PRECISION_F32 && dim > 256) return RT_ERR_UNSUPPORTED;
+
+    const size_t bytes = expected * sizeof(float);
+    std::lock_guard<std::mutex> lock(g_staging.mu);
+    int dev = 0;
+    RT_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return RT_ERR_UNSUPPORTED;
+    RT_CUDA(g_pipe.init(dev));
+    cudaStream_t s_in = g_pipe.in[dev], s_comp = g_pipe.comp[dev], s_out = g_pipe.out[dev];
+    DevBuf dq(0), dk(1), dv(2), dout(3), dkeep(4), bq(5), bk(6), bv(7), bo(8);
+    RT_CUDA(dq.alloc(bytes));
+    RT_CUDA(dk.alloc(bytes));
+    RT_CUDA(dv.alloc(bytes));
+    RT_CUDA(dout.alloc(bytes));
+    const bool bf16 = precision == RT_PRECISION_BF16;
+    if (bf16) {
+        RT_CUDA(bq.alloc(expected * 2));
+        RT_CUDA(bk.alloc(expected * 2));
+        RT_CUDA(bv.alloc(expected * 2));
+        RT_CUDA(bo.alloc(expected * 2));
+    }
+    const uint8_t* keep_dev = nullptr;
+    if (mask_kind == RT_MASKKIND_PADDING) {
+        RT_CUDA(dkeep.alloc(keep_len));
+        RT_CUDA(cudaMemcpyAsync(dkeep.p, keep, keep_len, cudaMemcpyHostToDevice, s_in));
+        keep_dev = dkeep.as<uint8_t>();
+    }
+    const int flags = (mask_kind == RT_MASKKIND_CAUSAL) ? RT_MASK_CAUSAL : RT_MASK_NONE;
+    // chunking: (batch element, head range) pieces, at least 4 when the shape allows, at most kMaxChunks
+    int64_t per_batch = (4 + batch - 1) / batch;
+    if (per_batch > heads) per_batch = heads;
+    int64_t batch_step = 1;  // batch elements per chunk
+    if (batch * per_batch > HostPipeline::kMaxChunks) {
+        per_batch = 1;
+        batch_step = (batch + HostPipeline::kMaxChunks - 1) / HostPipeline::kMaxChunks;
+    }
+    const size_t slab = (size_t)seq * (size_t)dim;  // elements of one (b,h)
+    int c = 0;
+    for (int64_t b0 = 0; b0 < batch; b0 += batch_step) {
+        const int64_t nb = (b0 + batch_step <= batch) ? batch_step : batch - b0;
+        for (int64_t part = 0; part < per_batch; ++part, ++c) {
+            const int64_t h0 = heads * part / per_batch, h1 = heads * (part + 1) / per_batch;
+            // with batch_step > 1 a chunk holds whole batch elements (per_batch == 1, h0 = 0, h1 = heads)
+            const size_t off = ((size_t)b0 * heads + h0) * slab, cnt = (size_t)nb * (size_t)(h1 - h0) * slab;
+            RT_CUDA(cudaMemcpyAsync(dq.as<float>() + off, q + off, cnt * 4, cudaMemcpyHostToDevice, s_in));
+            RT_CUDA(cudaMemcpyAsync(dk.as<float>() + off, k + off, cnt * 4, cudaMemcpyHostToDevice, s_in));
+            RT_CUDA(cudaMemcpyAsync(dv.as<float>() + off, v + off, cnt * 4, cudaMemcpyHostToDevice, s_in));
+            RT_CUDA(cudaEventRecord(g_pipe.ev_in[dev][c], s_in));
+            RT_CUDA(cudaStreamWaitEvent(s_comp, g_pipe.ev_in[dev][c], 0));
+            int rc;
+            if (bf16) {
+                RT_CUDA(rt::launch_f32_to_bf16(dq.as<float>() + off, bq.as<char>() + off * 2, (int64_t)cnt, s_comp));
+                RT_CUDA(rt::launch_f32_to_bf16(dk.as<float>() + off, bk.as<char>() + off * 2, (int64_t)cnt, s_comp));
+                RT_CUDA(rt::launch_f32_to_bf16(dv.as<float>() + off, bv.as<char>() + off * 2, (int64_t)cnt, s_comp));
+                rc = rt_attn_prefill_bf16(bq.as<char>() + off * 2, bk.as<char>() + off * 2, bv.as<char>() + off * 2,
+                                          bo.as<char>() + off * 2, nullptr, nb, h1 - h0, seq, (int)dim, flags, nullptr,
+                                          keep_dev, 0, -1.f, s_comp);
+                if (rc == RT_OK)
+                    RT_CUDA(rt::launch_bf16_to_f32(bo.as<char>() + off * 2, dout.as<float>() + off, (int64_t)cnt, s_comp));
+            } else {
+                rc = rt_attn_prefill_f32(dq.as<float>() + off, dk.as<float>() + off, dv.as<float>() + off,
+                                         dout.as<float>() + off, nullptr, nb, h1 - h0, h1 - h0, seq, seq, (int)dim, flags,
+                                         nullptr, nullptr, keep_dev, 0, -1.f, s_comp);
+            }
+            if (rc != RT_OK) {
+                cudaDeviceSynchronize();
+                return rc;
+            }
+            RT_CUDA(cudaEventRecord(g_pipe.ev_comp[dev][c], s_comp));
+            RT_CUDA(cudaStreamWaitEvent(s_out, g_pipe.ev_comp[dev][c], 0));
+            RT_CUDA(cudaMemcpyAsync(out + off, dout.as<float>() + off, cnt * 4, cudaMemcpyDeviceToHost, s_out));
+        }
+    }
+    RT_CUDA(cudaStreamSynchronize(s_out));
+    RT_CUDA(cudaStreamSynchronize(s_comp));
+    RT_CUDA(cudaStreamSynchronize(s_in));
+    return RT_OK;
+}
 
 // The (b, head-range) chunks run through three streams (copy in, kernel, copy out), so the upload
 // of chunk c+1, the kernel of chunk c and the download of chunk c-1 overlap; with pinned host
@@ -508,6 +548,11 @@ static int decode_common(const void* q, const void* k_cache, const void* v_cache
     if (!aligned16(q) || !aligned16(k_cache) || !aligned16(v_cache)) return RT_ERR_ALIGNMENT;
     const size_t need = rt_gqa_decode_workspace_bytes(batch, n_heads, n_kv_heads, head_dim, max_seq);
     if (need > 0 && (!workspace || workspace_bytes < need)) return RT_ERR_WORKSPACE;
+    // Everything that could fail after the decode kernel is enqueued is checked here instead: the chunk merge
+    // keeps one weight per chunk in shared memory, and a record delivered to peers travels in 16-byte pieces.
+    if (!rt::merge_fits((int64_t)rt::decode_num_chunks(batch, (int)n_kv_heads, max_seq), head_dim))
+        return RT_ERR_UNSUPPORTED;
+    if (push && ((batch * n_heads * ((int64_t)head_dim + 1)) & 3)) return RT_ERR_ALIGNMENT;
     RT_CUDA(rt::launch_gqa_decode(q, k_cache, v_cache, out_bf16, out_f32, lse, batch, (int)n_heads, (int)n_kv_heads,
                                   head_dim, max_seq, kv_lens, kv_len_uniform, kv_begin, kv_end,
                                   default_scale(scale, head_dim), need ? workspace : nullptr, of_stride, lse_stride,

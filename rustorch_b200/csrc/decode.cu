@@ -439,6 +439,10 @@ static size_t merge_smem_bytes(int64_t n_parts, int dim) {
     return sizeof(float) * ((size_t)kMergeWarps * dim + (size_t)n_parts);
 }
 
+bool merge_fits(int64_t n_parts, int dim) {
+    return dim <= 32 * kMergeMaxDimPerLane && merge_smem_bytes(n_parts, dim) <= 48 * 1024;
+}
+
 // Writes one token's K and V rows into the caches (llm_kernels.rs:345-373, batched).
 __global__ void kv_append_kernel(__nv_bfloat16* k_cache, __nv_bfloat16* v_cache,
                                  const __nv_bfloat16* k_in, const __nv_bfloat16* v_in, int n_kv,
@@ -636,7 +640,7 @@ cudaError_t launch_merge_partials(const float* o_parts, const float* lse_parts, 
                                   float* out_f32, float* lse, cudaStream_t stream, const MergeWait* wait,
                                   const MergePush* push) {
     if (rows == 0) return cudaSuccess;
-    if (dim > 32 * kMergeMaxDimPerLane || merge_smem_bytes(n_parts, dim) > 48 * 1024) return cudaErrorInvalidValue;
+    if (!merge_fits(n_parts, dim)) return cudaErrorInvalidValue;
     if (wait && wait->n_flags > kMergeWarps * 32) return cudaErrorInvalidValue;
     merge_partials_kernel<<<(unsigned)rows, kMergeWarps * 32, merge_smem_bytes(n_parts, dim), stream>>>(
         o_parts, lse_parts, (int)n_parts, rows, dim, in_row_stride, in_lse_stride, (__nv_bfloat16*)out_bf16, out_f32, lse,

@@ -1,6 +1,6 @@
 // Single-sequence GQA decode that never allocates: the split-KV scratch lives inside the library.
 //
-// Who needs this.  The decode kernel writes one partial result per 512-token chunk and merges
+// Who needs this.  The decode kernel writes one partial result per chunk of 128 to 1024 tokens and merges
 // them, so it needs scratch memory.  The library's other decode entries take that scratch from
 // the caller.  Two kinds of caller cannot supply it:
 //   * a caller bound to the reference's ten-argument

@@ -15,6 +15,9 @@ int sm_count();
 struct MergePush;
 int decode_chunk_tokens(int64_t batch, int n_kv, int64_t max_seq);
 int decode_num_chunks(int64_t batch, int n_kv, int64_t max_seq);
+// Whether merge_partials_kernel can combine n_parts partials of this head dim (its weights live in
+// shared memory).
+bool merge_fits(int64_t n_parts, int dim);
 cudaError_t launch_gqa_decode(const void* q, const void* k, const void* v, void* out_bf16, float* out_f32,
                               float* lse, int64_t batch, int n_heads, int n_kv, int head_dim,
                               int64_t max_seq, const int32_t* kv_lens, int64_t kv_len_uniform,

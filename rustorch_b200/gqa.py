@@ -58,8 +58,8 @@ def gqa_forward_f32(q, k, v, out, batch: int, n_heads: int, n_kv_heads: int, seq
                                             head_dim)
     if rc == _lib.RT_ERR_HEAD_COUNT:
         raise HeadCountMismatch(n_heads, n_kv_heads)
-    if rc == _lib.RT_ERR_WRONG_INPUT_LEN:
-        raise WrongInputLen("buffer", 0, 0)
+    if rc == _lib.RT_ERR_WRONG_INPUT_LEN:  # unreachable after the checks above; keep the variant's fields meaningful
+        raise WrongInputLen("q", q_len, q.size)
     _lib.check(rc, "rt_gqa_forward_f32_host")
 
 
@@ -67,6 +67,43 @@ def _stream_ptr(stream=None):
     import torch
     s = stream if stream is not None else torch.cuda.current_stream()
     return ctypes.c_void_p(s.cuda_stream)
+
+
+def _guard(name: str, t, dtype, like=None, shape=None):
+    """Refuses, before anything is launched, a tensor the kernels would misread: they take raw device
+    pointers, so a CPU tensor would hand them a host address (an illegal-address fault on the GPU), and a
+    tensor of another dtype or with gaps would silently be read as dense data of the expected type."""
+    import torch
+    if not isinstance(t, torch.Tensor):
+        raise TypeError(f"{name} must be a torch.Tensor, got {type(t).__name__}")
+    if not t.is_cuda:
+        raise TypeError(f"{name} must be a CUDA tensor (got device {t.device})")
+    if like is not None and t.device != like.device:
+        raise TypeError(f"{name} is on {t.device}, expected {like.device}")
+    if t.dtype != dtype:
+        raise TypeError(f"{name} must be {dtype}, got {t.dtype}")
+    if not t.is_contiguous():
+        raise TypeError(f"{name} must be contiguous")
+    if shape is not None and tuple(t.shape) != tuple(shape):
+        raise TypeError(f"{name} must have shape {tuple(shape)}, got {tuple(t.shape)}")
+
+
+def _guard_decode_args(q, k_cache, v_cache, kv_lens=None, workspace=None):
+    """Shape / dtype / device checks shared by the decode wrappers; returns (B, Hq, Hkv, D, max_seq)."""
+    import torch
+    _guard("q", q, torch.bfloat16)
+    if q.dim() != 3:
+        raise TypeError(f"q must be [B, Hq, D], got {tuple(q.shape)}")
+    B, Hq, D = q.shape
+    _guard("k_cache", k_cache, torch.bfloat16, like=q)
+    if k_cache.dim() != 4 or k_cache.shape[0] != B or k_cache.shape[3] != D:
+        raise TypeError(f"k_cache must be [B={B}, Hkv, max_seq, D={D}], got {tuple(k_cache.shape)}")
+    _guard("v_cache", v_cache, torch.bfloat16, like=q, shape=k_cache.shape)
+    if kv_lens is not None:
+        _guard("kv_lens", kv_lens, torch.int32, like=q, shape=(B,))
+    if workspace is not None:
+        _guard("workspace", workspace, torch.uint8, like=q)
+    return B, Hq, k_cache.shape[1], D, k_cache.shape[2]
 
 
 def decode_workspace_bytes(batch: int, n_heads: int, n_kv_heads: int, head_dim: int, max_seq: int) -> int:
@@ -128,9 +165,19 @@ def gqa_decode_online_bf16_static(stream, q: int, k_cache: int, v_cache: int, ou
 
 
 _default_ws = {}
-
-
 _ws_bytes_cache: dict = {}
+
+
+def _implicit_workspace(device, nbytes: int):
+    """The split-KV scratch used when the caller passes no ``workspace=``: one buffer per (device, CUDA
+    stream, size).  Two decodes of equal shape on different streams therefore never share chunk partials
+    and completion counters; calls on ONE stream run in order and may share them."""
+    import torch
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream, nbytes)
+    ws = _default_ws.get(key)
+    if ws is None:
+        ws = _default_ws[key] = torch.empty(nbytes, dtype=torch.uint8, device=device)
+    return ws
 
 
 def gqa_decode(q, k_cache, v_cache, kv_lens=None, kv_len: Optional[int] = None, kv_begin: int = 0, kv_end: int = -1,
@@ -143,24 +190,25 @@ def gqa_decode(q, k_cache, v_cache, kv_lens=None, kv_len: Optional[int] = None, 
     ``out`` / ``lse`` may be passed in (a decode loop reuses them: nothing is allocated per step).
     """
     import torch
-    B, Hq, D = q.shape
-    _, Hkv, max_seq, _ = k_cache.shape
+    B, Hq, Hkv, D, max_seq = _guard_decode_args(q, k_cache, v_cache, kv_lens, workspace)
     if out is None:
         out_dtype = out_dtype or torch.bfloat16
         out = torch.empty((B, Hq, D), dtype=out_dtype, device=q.device)
     else:
         out_dtype = out.dtype
+        if out_dtype not in (torch.bfloat16, torch.float32):
+            raise TypeError(f"out must be bfloat16 or float32, got {out_dtype}")
+        _guard("out", out, out_dtype, like=q, shape=(B, Hq, D))
     if lse is None and return_lse:
         lse = torch.empty((B, Hq), dtype=torch.float32, device=q.device)
+    elif lse is not None:
+        _guard("lse", lse, torch.float32, like=q, shape=(B, Hq))
     key = (B, Hq, Hkv, D, max_seq)
     need = _ws_bytes_cache.get(key)
     if need is None:
         need = _ws_bytes_cache[key] = decode_workspace_bytes(B, Hq, Hkv, D, max_seq)
     if workspace is None and need:
-        key = (q.device.index, need)
-        workspace = _default_ws.get(key)
-        if workspace is None:
-            workspace = _default_ws[key] = torch.empty(need, dtype=torch.uint8, device=q.device)
+        workspace = _implicit_workspace(q.device, need)
     rc = _lib.lib().rt_gqa_decode_bf16(
         q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
         out.data_ptr() if out_dtype == torch.bfloat16 else None,
@@ -180,16 +228,14 @@ def gqa_decode_record(q, k_cache, v_cache, kv_lens=None, kv_len: Optional[int] =
     """Decode one KV shard into a packed partial record f32 [B*Hq, D+1] (O | LSE) via
     ``rt_gqa_decode_record_bf16`` — the unit the ranks of a split-KV decode all-gather."""
     import torch
-    B, Hq, D = q.shape
-    _, Hkv, max_seq, _ = k_cache.shape
+    B, Hq, Hkv, D, max_seq = _guard_decode_args(q, k_cache, v_cache, kv_lens, workspace)
     if record is None:
         record = torch.empty((B * Hq, D + 1), dtype=torch.float32, device=q.device)
+    else:
+        _guard("record", record, torch.float32, like=q, shape=(B * Hq, D + 1))
     need = decode_workspace_bytes(B, Hq, Hkv, D, max_seq)
     if workspace is None and need:
-        key = (q.device.index, need)
-        workspace = _default_ws.get(key)
-        if workspace is None:
-            workspace = _default_ws[key] = torch.empty(need, dtype=torch.uint8, device=q.device)
+        workspace = _implicit_workspace(q.device, need)
     rc = _lib.lib().rt_gqa_decode_record_bf16(
         q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), record.data_ptr(), B, Hq, Hkv, D, max_seq,
         kv_lens.data_ptr() if kv_lens is not None else None, 0 if kv_len is None else int(kv_len), kv_begin, kv_end,
@@ -204,6 +250,9 @@ def gqa_decode_record(q, k_cache, v_cache, kv_lens=None, kv_len: Optional[int] =
 def merge_records(records, out_dtype=None):
     """records f32 [R, rows, D+1] (CUDA) -> (out [rows, D], lse [rows]) via ``rt_attn_merge_records``."""
     import torch
+    _guard("records", records, torch.float32)
+    if records.dim() != 3:
+        raise TypeError(f"records must be [R, rows, D+1], got {tuple(records.shape)}")
     R, rows, D1 = records.shape
     D = D1 - 1
     out_dtype = out_dtype or torch.bfloat16
@@ -220,7 +269,11 @@ def merge_records(records, out_dtype=None):
 def merge_partials(o_parts, lse_parts, out_dtype=None):
     """o_parts f32 [R,rows,D], lse_parts f32 [R,rows] (CUDA) -> (out [rows,D], lse [rows])."""
     import torch
+    _guard("o_parts", o_parts, torch.float32)
+    if o_parts.dim() != 3:
+        raise TypeError(f"o_parts must be [R, rows, D], got {tuple(o_parts.shape)}")
     R, rows, D = o_parts.shape
+    _guard("lse_parts", lse_parts, torch.float32, like=o_parts, shape=(R, rows))
     out_dtype = out_dtype or torch.bfloat16
     out = torch.empty((rows, D), dtype=out_dtype, device=o_parts.device)
     lse = torch.empty((rows,), dtype=torch.float32, device=o_parts.device)
@@ -234,7 +287,16 @@ def merge_partials(o_parts, lse_parts, out_dtype=None):
 
 def kv_append(k_cache, v_cache, k_in, v_in, pos=None, positions=None) -> None:
     """Batched kv_append via ``rt_kv_append_bf16``: k_in/v_in [B,Hkv,D] -> caches [B,Hkv,max_seq,D]."""
+    import torch
+    _guard("k_cache", k_cache, torch.bfloat16)
+    if k_cache.dim() != 4:
+        raise TypeError(f"k_cache must be [B, Hkv, max_seq, D], got {tuple(k_cache.shape)}")
     B, Hkv, max_seq, D = k_cache.shape
+    _guard("v_cache", v_cache, torch.bfloat16, like=k_cache, shape=k_cache.shape)
+    _guard("k_in", k_in, torch.bfloat16, like=k_cache, shape=(B, Hkv, D))
+    _guard("v_in", v_in, torch.bfloat16, like=k_cache, shape=(B, Hkv, D))
+    if positions is not None:
+        _guard("positions", positions, torch.int32, like=k_cache, shape=(B,))
     rc = _lib.lib().rt_kv_append_bf16(k_cache.data_ptr(), v_cache.data_ptr(), k_in.data_ptr(), v_in.data_ptr(), B, Hkv,
                                       D, max_seq, 0 if pos is None else int(pos),
                                       positions.data_ptr() if positions is not None else None, _stream_ptr())
@@ -251,8 +313,13 @@ def rope_inv_freq(head_dim: int, base: float = 10000.0, device="cuda"):
 def rope_kv_append(q, k_in, v_in, k_cache, v_cache, inv_freq, pos=None, positions=None, style: str = "half_split") -> None:
     """Rotary embedding of q (in place) and of the new K row + append of K, V at each sequence's position, one
     launch (``rt_rope_kv_append_bf16``).  q [B,Hq,D], k_in/v_in [B,Hkv,D], caches [B,Hkv,max_seq,D]."""
-    B, Hq, D = q.shape
-    _, Hkv, max_seq, _ = k_cache.shape
+    import torch
+    B, Hq, Hkv, D, max_seq = _guard_decode_args(q, k_cache, v_cache)
+    _guard("k_in", k_in, torch.bfloat16, like=q, shape=(B, Hkv, D))
+    _guard("v_in", v_in, torch.bfloat16, like=q, shape=(B, Hkv, D))
+    _guard("inv_freq", inv_freq, torch.float32, like=q, shape=(D // 2,))
+    if positions is not None:
+        _guard("positions", positions, torch.int32, like=q, shape=(B,))
     rc = _lib.lib().rt_rope_kv_append_bf16(q.data_ptr(), k_in.data_ptr(), v_in.data_ptr(), k_cache.data_ptr(),
                                            v_cache.data_ptr(), inv_freq.data_ptr(), B, Hq, Hkv, D, max_seq,
                                            0 if pos is None else int(pos),

@@ -151,9 +151,8 @@ class PeerRecordExchange:
         from inside the merge kernel (``rt_gqa_decode_record_push_bf16``).  Follow with ``merge()``."""
         import torch
         from . import _lib
-        from .gqa import _stream_ptr, decode_workspace_bytes
-        B, Hq, D = q.shape
-        _, Hkv, max_seq, _ = k_cache.shape
+        from .gqa import _guard_decode_args, _stream_ptr, decode_workspace_bytes
+        B, Hq, Hkv, D, max_seq = _guard_decode_args(q, k_cache, v_cache, kv_lens, workspace)
         if self._done is None:
             self._done = torch.zeros(1, dtype=torch.int32, device=self.records.device)
         need = decode_workspace_bytes(B, Hq, Hkv, D, max_seq)

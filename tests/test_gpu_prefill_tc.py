@@ -416,3 +416,27 @@ def test_prefill_is_deterministic_across_launches():
     torch.cuda.synchronize()
     assert torch.equal(out, ref) and torch.equal(lse, ref_lse)
     _clean_status()
+
+
+def test_prefill_tc_random_shapes(oracle):
+    """Randomised shapes on the tensor-core path (the reference randomises its CPU path the same way,
+    cpu_forward.rs:1045-1087): 40 seeded cases over B, H, N in [1, 700], D in {64, 128}, causal or not,
+    with and without per-batch kv_len, against the oracle at the bf16 tolerances."""
+    import torch
+    rng = np.random.default_rng(0xB200)
+    for i in range(40):
+        B, H = int(rng.integers(1, 4)), int(rng.integers(1, 5))
+        N = int(rng.integers(1, 700))
+        D = (64, 128)[int(rng.integers(0, 2))]
+        causal = bool(rng.integers(0, 2))
+        q, k, v = (util.normal_bf16(oracle, (B, H, N, D), 5000 + 3 * i + j) for j in range(3))
+        lens = None
+        if rng.integers(0, 2):
+            lens = rng.integers(1, N + 1, B).astype(np.int32)
+        kw = dict(causal=causal)
+        if lens is not None:
+            kw["kv_lens"] = util.to_cuda(lens)
+        out, lse = _run_tc(q, k, v, **kw)
+        _, ref, ref_lse = oracle.flash_forward_ext(q, k, v, causal=causal, kv_lens=lens)
+        util.check_output(out, ref, label=f"case {i}: B{B} H{H} N{N} D{D} causal={causal} lens={lens}")
+        util.check_lse(lse, ref_lse)
