@@ -166,3 +166,47 @@ def test_gpu_backward_matches_golden(oracle):
         scale = max(1.0, float(np.abs(ref).max()))
         assert np.abs(a.cpu().numpy() - ref).max() <= 2e-4 * scale, name
         assert np.abs(b.cpu().numpy() - ref).max() <= 2e-2 * scale, name
+
+
+# ---- outputs of the reference's own CUDA decode kernel (see tests/golden/make_ref_decode_golden.py)
+def _ref_decode_fixture():
+    import importlib.util
+    path = os.path.join(GOLD, "decode_ref_kernel.npz")
+    if not os.path.exists(path):
+        pytest.skip("decode_ref_kernel.npz not generated yet (needs one GPU run of make_ref_decode_golden.py)")
+    spec = importlib.util.spec_from_file_location("make_ref_decode_golden",
+                                                  os.path.join(GOLD, "make_ref_decode_golden.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return np.load(path), mod
+
+
+def _bf16_bits_to_f32(bits):
+    return (bits.astype(np.uint32) << 16).view(np.float32)
+
+
+def test_oracle_decode_matches_reference_kernel_outputs(oracle):
+    """The oracle's decode_attn_row restatement against what the reference's CUDA kernel itself returned
+    (bf16 outputs, fast-math exp): max-abs 1e-2 (+ half a bf16 ulp where |o| >= 4), relative L2 5e-3."""
+    data, mod = _ref_decode_fixture()
+    for i, case in enumerate(data["cases"].tolist()):
+        q, k, v = mod.inputs(oracle, case)
+        rc, out, _ = oracle.gqa_decode_cache(q[None], k[None], v[None], np.array([case[4]], dtype=np.int32))
+        assert rc == 0
+        util.check_output(_bf16_bits_to_f32(data[f"out_{i}"]), out[0], label=f"reference kernel case {case}")
+
+
+@pytest.mark.gpu
+def test_dropin_decode_matches_reference_kernel_outputs(oracle):
+    import torch
+    import rustorch_b200 as rt
+    data, mod = _ref_decode_fixture()
+    for i, case in enumerate(data["cases"].tolist()):
+        Hq, Hkv, D, S, L, _ = case
+        q, k, v = mod.inputs(oracle, case)
+        dq, dk, dv = (util.to_cuda_bf16(x) for x in (q, k, v))
+        out = torch.empty((Hq, D), dtype=torch.bfloat16, device="cuda")
+        rt.LlmKernels().gqa_decode_online_bf16(torch.cuda.current_stream(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+                                               out.data_ptr(), Hq, Hkv, L, D, S)
+        torch.cuda.synchronize()
+        util.check_output(util.to_np(out), _bf16_bits_to_f32(data[f"out_{i}"]), label=f"drop-in vs reference {case}")
