@@ -725,8 +725,8 @@ def main():
 
         # The same exchange over peer memory: the record is decoded straight into this rank's slot, pushed
         # to every peer with NVLink stores + a flag, and the merge kernel waits (bounded) for all flags.
-        exchange, exchange_note = None, ("peer stores over NVLink (symmetric memory) + flag, merge waits in-kernel; "
-                                         "value = the faster of the copy-kernel and fused-in-merge forms")
+        exchange, exchange_note = None, ("peer stores over NVLink (symmetric memory) + flags, the merge waits in-kernel; "
+                                         "value = the fastest of the three forms timed below")
         try:
             exchange = sharding.PeerRecordExchange.create(Hq, Dd)
         except Exception as exc:  # symmetric memory not available: keep the NCCL form, and say so
@@ -741,6 +741,10 @@ def main():
             exchange.decode_push(q1, k1, v1, kv_len=T, workspace=ws)  # the merge kernel stores the record on every peer
             return exchange.merge()
 
+        def step_splitkv_rows():
+            # decode kernel, then ONE kernel: chunk merge, row delivery, per-row wait, cross-rank merge
+            return exchange.decode_exchange(q1, k1, v1, kv_len=T, workspace=ws)
+
         # Verification over real peer memory, before anything is timed: every rank holds the SAME small cache
         # (4096 positions per rank), decodes only its own KV range, exchanges, and compares the merged result
         # with its own single-GPU decode of the whole range.
@@ -753,13 +757,17 @@ def main():
             whole, whole_lse = rt.gqa_decode(q1, kv_, vv_, kv_len=Tv, out_dtype=torch.float32)
             b0, b1 = sharding.kv_shard(Tv, world, rank, align=16)
             errs = []
-            for form in ("copy", "fused"):
+            for form in ("copy", "fused", "rows"):
                 if form == "copy":
                     rt.gqa_decode_record(q1, kv_, vv_, kv_len=Tv, kv_begin=b0, kv_end=b1, record=exchange.next_epoch())
                     exchange.push()
-                else:
+                elif form == "fused":
                     exchange.decode_push(q1, kv_, vv_, kv_len=Tv, kv_begin=b0, kv_end=b1)
-                got, got_lse = exchange.merge(out_dtype=torch.float32)
+                if form == "rows":
+                    got, got_lse = exchange.decode_exchange(q1, kv_, vv_, kv_len=Tv, kv_begin=b0, kv_end=b1,
+                                                            out_dtype=torch.float32)
+                else:
+                    got, got_lse = exchange.merge(out_dtype=torch.float32)
                 torch.cuda.synchronize()
                 errs.append(max((got - whole.reshape(Hq, Dd)).abs().max().item(),
                                 (got_lse - whole_lse.reshape(Hq)).abs().max().item()))
@@ -771,17 +779,23 @@ def main():
 
         nccl_ms = timed(step_splitkv_nccl, args.steps, args.warmup, dist, torch)
         sms = nccl_ms
-        sms_copy = sms_fused = None
+        sms_copy = sms_fused = sms_rows = None
         if exchange is not None:
             a, b = step_splitkv_nccl(), step_splitkv_p2p()
             torch.cuda.synchronize()
             assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1]), "peer exchange and NCCL exchange disagree"
-            cc = step_splitkv_p2p_fused()
+            cc = step_splitkv_p2p_fused()  # chunks merged inside the decode kernel: another summation order
             torch.cuda.synchronize()
-            assert torch.equal(a[0], cc[0]) and torch.equal(a[1], cc[1]), "fused peer exchange and NCCL exchange disagree"
+            assert (a[0].float() - cc[0].float()).abs().max().item() <= 2e-2 and (a[1] - cc[1]).abs().max().item() <= 1e-5, \
+                "fused peer exchange and NCCL exchange disagree"
             sms_copy = timed(step_splitkv_p2p, args.steps, args.warmup, dist, torch)
             sms_fused = timed(step_splitkv_p2p_fused, args.steps, args.warmup, dist, torch)
-            sms = min(sms_copy, sms_fused)
+            dd = step_splitkv_rows()
+            torch.cuda.synchronize()
+            assert (a[0].float() - dd[0].float()).abs().max().item() <= 2e-2 and (a[1] - dd[1]).abs().max().item() <= 1e-5, \
+                "row exchange and NCCL exchange disagree"
+            sms_rows = timed(step_splitkv_rows, args.steps, args.warmup, dist, torch)
+            sms = min(sms_copy, sms_fused, sms_rows)
             assert _lib.device_status() == 0, "a bounded wait of the peer exchange expired"
         total_bytes = shard_bytes * world
         splitkv = {"metric": "kv_read_gbs", "value": total_bytes / (sms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": sms,
@@ -791,7 +805,7 @@ def main():
                    "per_gpu_gbs": total_bytes / world / (sms * 1e-3) / 1e9,
                    "frac_of_hbm_per_gpu": total_bytes / world / (sms * 1e-3) / 1e9 / peaks["hbm_gbs"],
                    "nccl_all_gather_ms_per_step": nccl_ms, "peer_copy_kernel_ms_per_step": sms_copy,
-                   "peer_fused_in_merge_ms_per_step": sms_fused,
+                   "peer_fused_in_merge_ms_per_step": sms_fused, "peer_row_exchange_one_kernel_ms_per_step": sms_rows,
                    "splitkv_verified": verified, "splitkv_verify_max_err": verify_err,
                    "splitkv_verify": "every rank decodes its range of a shared 4096*N-position cache, exchanges over real "
                                      "peer memory (both forms) and compares with its own single-GPU decode (max |diff| "

@@ -385,6 +385,38 @@ int rt_gqa_decode_record_push_bf16(const void* q, const void* k_cache, const voi
                                    size_t workspace_bytes, void* stream);
 
 /*
+ * The whole tail of a split-KV decode in one kernel, row by row (no reference counterpart: the
+ * reference has no multi-device attention).  After the decode kernel has written the chunk partials of
+ * this rank's KV shard, ONE kernel with one CTA per output row merges the row's partials, stores the
+ * row (O | LSE) into the slot every rank keeps for this rank (plain stores, over NVLink for the peers;
+ * nothing is loaded from a peer), raises that rank's flag for (this rank, row), waits (bounded by
+ * wait_clocks SM clocks, <= 0: 2^31; expiry: nothing is written, device status 401) for the same row
+ * from every rank, and merges the `world` rows from local memory into out / lse.  Compared with
+ * rt_gqa_decode_record_bf16 + rt_splitkv_push_record + rt_attn_merge_records_after there is no record-
+ * wide flag, no counter shared between CTAs and no kernel boundary between merge, delivery and merge.
+ *   peer_slots[r] : on rank r, the [rows, D+1] f32 slot r keeps for THIS rank (r == rank: local memory)
+ *   peer_flags[r] : on rank r, the [rows] u32 flags r keeps for THIS rank
+ *   local_slots   : this rank's slots for all ranks, [world][rows][D+1] f32 (peer_slots[rank] points into it)
+ *   local_flags   : this rank's flags for all ranks, [world][rows] u32 (zero before the first epoch)
+ *   do_wait = 0   : stop after the delivery; rt_attn_merge_records_after_rows then finishes the step
+ *                   (needed where several ranks are emulated on ONE GPU: a kernel must never wait for
+ *                   a flag that a later launch on the same GPU raises).
+ * Epochs increase by one per exchange and two slot / flag sets are used alternately, as above.
+ */
+int rt_gqa_decode_exchange_bf16(const void* q, const void* k_cache, const void* v_cache, void* out_bf16,
+                                float* out_f32, float* lse, void* const* peer_slots,
+                                void* const* peer_flags, const float* local_slots,
+                                const uint32_t* local_flags, int world, int rank, uint32_t epoch,
+                                int64_t wait_clocks, int do_wait, int64_t batch, int64_t n_heads,
+                                int64_t n_kv_heads, int head_dim, int64_t max_seq, const int32_t* kv_lens,
+                                int64_t kv_len_uniform, int64_t kv_begin, int64_t kv_end, float scale,
+                                void* workspace, size_t workspace_bytes, void* stream);
+/* rt_attn_merge_records_after with one flag per (rank, row): row_flags u32 [n_parts][rows]. */
+int rt_attn_merge_records_after_rows(const float* records, const uint32_t* row_flags, uint32_t epoch,
+                                     int64_t wait_clocks, int64_t n_parts, int64_t rows, int dim,
+                                     void* out_bf16, float* out_f32, float* lse, void* stream);
+
+/*
  * Host-slice mirror of
  *   gqa_forward_f32(q,k,v,out, batch,n_heads,n_kv_heads,seq_q,seq_kv,head_dim) -> Result<(),GQAError>
  * (gqa.rs:94-105), f32 arithmetic.  seq_q == seq_kv runs the unmasked prefill without

@@ -533,7 +533,7 @@ static int decode_common(const void* q, const void* k_cache, const void* v_cache
                          int64_t n_kv_heads, int head_dim, int64_t max_seq, const int32_t* kv_lens,
                          int64_t kv_len_uniform, int64_t kv_begin, int64_t kv_end, float scale, void* workspace,
                          size_t workspace_bytes, void* stream, const rt::MergePush* push = nullptr,
-                         bool* pushed = nullptr) {
+                         bool* pushed = nullptr, rt::DecodeTail* tail = nullptr) {
     if (pushed) *pushed = false;
     if (n_kv_heads <= 0 || n_heads <= 0 || n_heads % n_kv_heads != 0) return RT_ERR_HEAD_COUNT;  // gqa.rs:106-111
     if (head_dim == 0) return RT_ERR_ZERO_DIM;
@@ -556,7 +556,7 @@ static int decode_common(const void* q, const void* k_cache, const void* v_cache
     RT_CUDA(rt::launch_gqa_decode(q, k_cache, v_cache, out_bf16, out_f32, lse, batch, (int)n_heads, (int)n_kv_heads,
                                   head_dim, max_seq, kv_lens, kv_len_uniform, kv_begin, kv_end,
                                   default_scale(scale, head_dim), need ? workspace : nullptr, of_stride, lse_stride,
-                                  as_stream(stream), push, pushed));
+                                  as_stream(stream), push, pushed, tail));
     return RT_OK;
 }
 
@@ -664,7 +664,53 @@ int rt_attn_merge_records_after(const float* records, const uint32_t* flags, uin
     if (rows == 0) return RT_OK;
     if (!records || !flags || (!out_bf16 && !out_f32)) return RT_ERR_NULL_POINTER;
     rt::MergeWait w{flags, (int)n_parts, epoch, wait_clocks > 0 ? (long long)wait_clocks : (1ll << 31),
-                    rt::device_status_ptr()};
+                    rt::device_status_ptr(), 0};
+    if (!w.status) return (int)cudaErrorInvalidSymbol;
+    RT_CUDA(rt::launch_merge_partials(records, records + dim, n_parts, rows, dim, dim + 1, dim + 1, out_bf16, out_f32,
+                                      lse, as_stream(stream), &w));
+    return RT_OK;
+}
+
+int rt_gqa_decode_exchange_bf16(const void* q, const void* k_cache, const void* v_cache, void* out_bf16, float* out_f32,
+                                float* lse, void* const* peer_slots, void* const* peer_flags, const float* local_slots,
+                                const uint32_t* local_flags, int world, int rank, uint32_t epoch, int64_t wait_clocks,
+                                int do_wait, int64_t batch, int64_t n_heads, int64_t n_kv_heads, int head_dim,
+                                int64_t max_seq, const int32_t* kv_lens, int64_t kv_len_uniform, int64_t kv_begin,
+                                int64_t kv_end, float scale, void* workspace, size_t workspace_bytes, void* stream) {
+    if (world <= 0 || rank < 0 || rank >= world) return RT_ERR_BAD_LENGTH;
+    if (world > rt::kMaxPeers) return RT_ERR_UNSUPPORTED;
+    if (!peer_slots || !peer_flags || !local_slots || !local_flags) return RT_ERR_NULL_POINTER;
+    for (int r = 0; r < world; ++r)
+        if (!peer_slots[r] || !peer_flags[r]) return RT_ERR_NULL_POINTER;
+    if (do_wait && !out_bf16 && !out_f32) return RT_ERR_NULL_POINTER;
+    // The decode writes chunk partials (or, with a single chunk, the record itself into this rank's own
+    // local slot); the row-exchange kernel merges, delivers, waits and merges again.
+    float* self_slot = static_cast<float*>(peer_slots[rank]);
+    rt::DecodeTail tail{0, nullptr, nullptr};
+    const int rc = decode_common(q, k_cache, v_cache, nullptr, self_slot, self_slot + head_dim, head_dim + 1,
+                                 head_dim + 1, batch, n_heads, n_kv_heads, head_dim, max_seq, kv_lens, kv_len_uniform,
+                                 kv_begin, kv_end, scale, workspace, workspace_bytes, stream, nullptr, nullptr, &tail);
+    if (rc != RT_OK || batch == 0) return rc;
+    const int64_t rows = batch * n_heads;
+    const bool direct = tail.n_chunks <= 1;
+    RT_CUDA(rt::launch_row_exchange(direct ? self_slot : tail.part_o, direct ? self_slot + head_dim : tail.part_lse,
+                                    direct ? 1 : tail.n_chunks, rows, head_dim, direct ? head_dim + 1 : head_dim,
+                                    direct ? head_dim + 1 : 1, out_bf16, out_f32, lse, peer_slots, peer_flags,
+                                    local_slots, local_flags, world, epoch, (long long)wait_clocks, do_wait,
+                                    as_stream(stream)));
+    return RT_OK;
+}
+
+int rt_attn_merge_records_after_rows(const float* records, const uint32_t* row_flags, uint32_t epoch,
+                                     int64_t wait_clocks, int64_t n_parts, int64_t rows, int dim, void* out_bf16,
+                                     float* out_f32, float* lse, void* stream) {
+    if (dim == 0) return RT_ERR_ZERO_DIM;
+    if (n_parts <= 0 || rows < 0 || dim < 0) return RT_ERR_BAD_LENGTH;
+    if (dim > 256 || n_parts > rt::kMaxPeers) return RT_ERR_UNSUPPORTED;
+    if (rows == 0) return RT_OK;
+    if (!records || !row_flags || (!out_bf16 && !out_f32)) return RT_ERR_NULL_POINTER;
+    rt::MergeWait w{row_flags, (int)n_parts, epoch, wait_clocks > 0 ? (long long)wait_clocks : (1ll << 31),
+                    rt::device_status_ptr(), 1};
     if (!w.status) return (int)cudaErrorInvalidSymbol;
     RT_CUDA(rt::launch_merge_partials(records, records + dim, n_parts, rows, dim, dim + 1, dim + 1, out_bf16, out_f32,
                                       lse, as_stream(stream), &w));

@@ -288,89 +288,39 @@ __device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
 constexpr int kMergeWarps = 8;
 constexpr int kMergeMaxDimPerLane = 8;  // dim <= 256
 
-__global__ void __launch_bounds__(kMergeWarps * 32) merge_partials_kernel(const float* __restrict__ o_parts,
-                                                                         const float* __restrict__ lse_parts,
-                                                                         int n_parts, int64_t rows, int dim,
-                                                                         int64_t in_row_stride, int64_t in_lse_stride,
-                                                                         __nv_bfloat16* out_bf16, float* out_f32,
-                                                                         float* lse_out, int64_t of_stride,
-                                                                         int64_t lse_stride, MergeWait wait,
-                                                                         MergePush push) {
-    const int64_t row = blockIdx.x;
+// Merge of one output row over n_parts partials (the CTA's 8 warps in parallel, see above).  On return every
+// thread holds the row's LSE; thread d < dim holds O[d] (normalised; zeros and LSE = -inf when every part is
+// empty).  part r of the row lies at o_row + r * part_stride (dim floats), its LSE at lse_row[r * lse_part_stride].
+// sm: kMergeWarps * dim + n_parts floats; red / s_ml: small CTA-shared scratch.  Ends with a __syncthreads-free
+// state in which sm may be reused after the next barrier.
+__device__ __forceinline__ float merge_row(const float* o_row, const float* lse_row, int n_parts, int64_t part_stride,
+                                           int64_t lse_part_stride, int dim, float* sm, float* red, float* s_ml,
+                                           float& lse_out) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    // Delivery of this row to the peers (record layout: out_f32 rows of of_stride floats, LSE at column dim).
-    auto push_row_value = [&](int d, float x) {
-        for (int r = 0; r < push.world; ++r)
-            if (push.dst[r] != out_f32) push.dst[r][row * of_stride + d] = x;
-    };
-    auto push_done = [&]() {  // every thread of the CTA calls this once its stores are issued
-        __threadfence_system();
-        __syncthreads();
-        if (tid == 0 && atomicAdd(push.done_counter, 1) == (int)rows - 1) {
-            *push.done_counter = 0;  // ready for the next launch
-            __threadfence_system();  // all rows of all CTAs are ordered before the flags
-            for (int r = 0; r < push.world; ++r)
-                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(push.flag[r]), "r"(push.epoch) : "memory");
-        }
-    };
-    if (wait.flags) {
-        // Part r of this merge is written into local memory by rank r (push_records_kernel on that GPU),
-        // which then raises flags[r] to the epoch with a system-scope release.  The wait is bounded: on
-        // expiry the kernel records the code and returns without touching the outputs.
-        __shared__ int wait_failed;
-        if (tid == 0) wait_failed = 0;
-        __syncthreads();
-        if (tid < wait.n_flags) {
-            const long long t0 = clock64();
-            while (ld_acquire_sys_u32(wait.flags + tid) < wait.epoch) {
-                if (clock64() - t0 > wait.max_clocks) {
-                    report_timeout(wait.status, kToPeerFlag);
-                    wait_failed = 1;
-                    break;
-                }
-            }
-        }
-        __syncthreads();
-        if (wait_failed) return;
-    }
-    __shared__ float red[kMergeWarps];
-    __shared__ float s_m, s_l;
-    extern __shared__ float merge_sm[];
-    float* acc_sm = merge_sm;                    // [kMergeWarps][dim]
-    float* w_sm = merge_sm + kMergeWarps * dim;  // [n_parts]: LSE_r, then the weight of part r
-
+    float* acc_sm = sm;                    // [kMergeWarps][dim]
+    float* w_sm = sm + kMergeWarps * dim;  // [n_parts]: LSE_r, then the weight of part r
     float m = -INFINITY;
     for (int r = tid; r < n_parts; r += kMergeWarps * 32) {
-        const float x = lse_parts[((int64_t)r * rows + row) * in_lse_stride];
+        const float x = lse_row[(int64_t)r * lse_part_stride];
         w_sm[r] = x;
         m = fmaxf(m, x);
     }
 #pragma unroll
     for (int off = 16; off; off >>= 1) m = fmaxf(m, __shfl_xor_sync(kFullMask, m, off));
+    __syncthreads();  // red / s_ml / sm of an earlier merge in this kernel are no longer read
     if (lane == 0) red[warp] = m;
     __syncthreads();
     if (tid == 0) {
         float x = red[0];
         for (int i = 1; i < kMergeWarps; ++i) x = fmaxf(x, red[i]);
-        s_m = x;
+        s_ml[0] = x;
     }
     __syncthreads();
-    m = s_m;
-
+    m = s_ml[0];
     if (m == -INFINITY) {  // every partial empty
-        for (int d = tid; d < dim; d += kMergeWarps * 32) {
-            if (out_bf16) out_bf16[row * dim + d] = __float2bfloat16(0.f);
-            if (out_f32) out_f32[row * of_stride + d] = 0.f;
-            if (push.world) push_row_value(d, 0.f);
-        }
-        if (tid == 0 && lse_out) lse_out[row * lse_stride] = -INFINITY;
-        if (push.world) {
-            if (tid == 0) push_row_value(dim, -INFINITY);
-            push_done();
-        }
-        return;
+        lse_out = -INFINITY;
+        return 0.f;
     }
-
     float l = 0.f;
     for (int r = tid; r < n_parts; r += kMergeWarps * 32) {
         const float x = w_sm[r];
@@ -386,8 +336,6 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_partials_kernel(const 
     float acc[kMergeMaxDimPerLane];
 #pragma unroll
     for (int i = 0; i < kMergeMaxDimPerLane; ++i) acc[i] = 0.f;
-    const float* base = o_parts + row * in_row_stride;
-    const int64_t part_stride = rows * in_row_stride;
     for (int r0 = warp; r0 < n_parts; r0 += 4 * kMergeWarps) {
         float w[4];
         float v[4][kMergeMaxDimPerLane];
@@ -398,7 +346,7 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_partials_kernel(const 
 #pragma unroll
             for (int i = 0; i < kMergeMaxDimPerLane; ++i) {
                 const int d = lane + 32 * i;
-                v[u][i] = (w[u] != 0.f && d < dim) ? base[(int64_t)r * part_stride + d] : 0.f;
+                v[u][i] = (w[u] != 0.f && d < dim) ? o_row[(int64_t)r * part_stride + d] : 0.f;
             }
         }
 #pragma unroll
@@ -415,24 +363,144 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_partials_kernel(const 
     if (tid == 0) {
         float x = 0.f;
         for (int i = 0; i < kMergeWarps; ++i) x += red[i];
-        s_l = x;
+        s_ml[1] = x;
     }
     __syncthreads();
-    const float inv = 1.f / s_l;
-    for (int d = tid; d < dim; d += kMergeWarps * 32) {
-        float o = 0.f;
+    const float s_l = s_ml[1];
+    lse_out = m + logf(s_l);
+    float o = 0.f;
+    if (tid < dim) {
 #pragma unroll
-        for (int x = 0; x < kMergeWarps; ++x) o += acc_sm[x * dim + d];
-        o *= inv;
-        if (out_bf16) out_bf16[row * dim + d] = __float2bfloat16(o);
-        if (out_f32) out_f32[row * of_stride + d] = o;
-        if (push.world) push_row_value(d, o);
+        for (int x = 0; x < kMergeWarps; ++x) o += acc_sm[x * dim + tid];
+        o *= 1.f / s_l;
     }
-    if (tid == 0 && lse_out) lse_out[row * lse_stride] = m + logf(s_l);
+    return o;
+}
+
+// Bounded wait for arrival flags: thread t < n waits until flag_of(t) >= epoch.  Returns false (for the whole
+// CTA) when a wait ran out; the code is then in the device status word.
+__device__ __forceinline__ bool wait_for_flags(const uint32_t* flags, int n, int64_t flag_stride, uint32_t epoch,
+                                               long long max_clocks, int* status) {
+    __shared__ int wait_failed;
+    const int tid = threadIdx.x;
+    if (tid == 0) wait_failed = 0;
+    __syncthreads();
+    if (tid < n) {
+        const long long t0 = clock64();
+        while (ld_acquire_sys_u32(flags + tid * flag_stride) < epoch) {
+            if (clock64() - t0 > max_clocks) {
+                report_timeout(status, kToPeerFlag);
+                wait_failed = 1;
+                break;
+            }
+        }
+    }
+    __syncthreads();
+    return !wait_failed;
+}
+
+__global__ void __launch_bounds__(kMergeWarps * 32) merge_partials_kernel(const float* __restrict__ o_parts,
+                                                                         const float* __restrict__ lse_parts,
+                                                                         int n_parts, int64_t rows, int dim,
+                                                                         int64_t in_row_stride, int64_t in_lse_stride,
+                                                                         __nv_bfloat16* out_bf16, float* out_f32,
+                                                                         float* lse_out, int64_t of_stride,
+                                                                         int64_t lse_stride, MergeWait wait,
+                                                                         MergePush push) {
+    const int64_t row = blockIdx.x;
+    const int tid = threadIdx.x;
+    // Delivery of this row to the peers (record layout: out_f32 rows of of_stride floats, LSE at column dim).
+    auto push_row_value = [&](int d, float x) {
+        for (int r = 0; r < push.world; ++r)
+            if (push.dst[r] != out_f32) push.dst[r][row * of_stride + d] = x;
+    };
+    if (wait.flags) {
+        // Part r of this merge is written into local memory by rank r (on that GPU), which then raises
+        // flags[r] (or, with per-row flags, flags[r * rows + row]) to the epoch with a system-scope release.
+        // The wait is bounded: on expiry the kernel records the code and returns without touching the outputs.
+        const uint32_t* f = wait.flags + (wait.per_row ? row : 0);
+        if (!wait_for_flags(f, wait.n_flags, wait.per_row ? rows : 1, wait.epoch, wait.max_clocks, wait.status)) return;
+    }
+    __shared__ float red[kMergeWarps];
+    __shared__ float s_ml[2];
+    extern __shared__ float merge_sm[];
+    float lse;
+    const float o = merge_row(o_parts + row * in_row_stride, lse_parts + row * in_lse_stride, n_parts,
+                              rows * in_row_stride, rows * in_lse_stride, dim, merge_sm, red, s_ml, lse);
+    if (tid < dim) {
+        if (out_bf16) out_bf16[row * dim + tid] = __float2bfloat16(o);
+        if (out_f32) out_f32[row * of_stride + tid] = o;
+        if (push.world) push_row_value(tid, o);
+    }
+    if (tid == 0 && lse_out) lse_out[row * lse_stride] = lse;
     if (push.world) {
-        if (tid == 0) push_row_value(dim, m + logf(s_l));
-        push_done();
+        if (tid == 0) push_row_value(dim, lse);
+        __threadfence_system();  // every thread of the CTA, once its stores are issued
+        __syncthreads();
+        if (tid == 0 && atomicAdd(push.done_counter, 1) == (int)rows - 1) {
+            *push.done_counter = 0;  // ready for the next launch
+            __threadfence_system();  // all rows of all CTAs are ordered before the flags
+            for (int r = 0; r < push.world; ++r)
+                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(push.flag[r]), "r"(push.epoch) : "memory");
+        }
     }
+}
+
+// The tail of a split-KV decode in ONE kernel, one CTA per output row: merge the rank's chunk partials of the
+// row, store the row (O | LSE) into the slot every rank keeps for this rank (plain stores, NVLink for the peers;
+// nothing is ever loaded from a peer) and raise that rank's flag for (this rank, row); then wait, bounded, for
+// the row from every rank and merge the `world` rows out of local memory.  Rows are independent, so nothing
+// waits for a whole record, no counter is shared between CTAs, and the chunk merge, the delivery and the
+// cross-rank merge need no kernel boundary between them.
+// With do_wait = 0 the kernel stops after the delivery; merge_partials_kernel with per-row flags then does
+// the second half (used where several ranks are emulated on one GPU: a kernel must not wait for a flag that a
+// later launch on the same GPU raises).
+struct RowExchange {
+    float* slot[kMaxPeers];          // on rank p: the [rows, dim + 1] slot p keeps for this rank (p = this rank: local)
+    uint32_t* flag[kMaxPeers];       // on rank p: the [rows] flags p keeps for this rank
+    const float* local_slots;        // this rank's slots for all ranks: [world][rows][dim + 1]
+    const uint32_t* local_flags;     // [world][rows]
+    int world;
+    uint32_t epoch;
+    long long max_clocks;
+    int* status;
+    int do_wait;
+};
+
+__global__ void __launch_bounds__(kMergeWarps * 32) splitkv_row_exchange_kernel(
+    const float* __restrict__ o_parts, const float* __restrict__ lse_parts, int n_parts, int64_t rows, int dim,
+    int64_t in_row_stride, int64_t in_lse_stride, __nv_bfloat16* out_bf16, float* out_f32, float* lse_out,
+    RowExchange x) {
+    const int64_t row = blockIdx.x;
+    const int tid = threadIdx.x;
+    __shared__ float red[kMergeWarps];
+    __shared__ float s_ml[2];
+    extern __shared__ float merge_sm[];
+    // Launched with programmatic stream serialisation: the CTAs may already be resident when the decode kernel
+    // before this one finishes (it lets its dependents go once every CTA has streamed its chunk); this wait
+    // returns when that kernel has completed and its partials are visible (at once under a normal launch).
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    float lse;
+    const float o = merge_row(o_parts + row * in_row_stride, lse_parts + row * in_lse_stride, n_parts,
+                              rows * in_row_stride, rows * in_lse_stride, dim, merge_sm, red, s_ml, lse);
+    const int64_t rec = row * (dim + 1);
+    for (int r = 0; r < x.world; ++r) {
+        if (tid < dim) x.slot[r][rec + tid] = o;
+        if (tid == 0) x.slot[r][rec + dim] = lse;
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (tid < x.world)
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(x.flag[tid] + row), "r"(x.epoch) : "memory");
+    if (!x.do_wait) return;
+    if (!wait_for_flags(x.local_flags + row, x.world, rows, x.epoch, x.max_clocks, x.status)) return;
+    const float o2 = merge_row(x.local_slots + rec, x.local_slots + rec + dim, x.world, rows * (dim + 1),
+                               rows * (dim + 1), dim, merge_sm, red, s_ml, lse);
+    if (tid < dim) {
+        if (out_bf16) out_bf16[row * dim + tid] = __float2bfloat16(o2);
+        if (out_f32) out_f32[row * dim + tid] = o2;
+    }
+    if (tid == 0 && lse_out) lse_out[row] = lse;
 }
 
 static size_t merge_smem_bytes(int64_t n_parts, int dim) {
@@ -577,7 +645,7 @@ cudaError_t launch_gqa_decode(const void* q, const void* k, const void* v, void*
                               int64_t max_seq, const int32_t* kv_lens, int64_t kv_len_uniform,
                               int64_t kv_begin, int64_t kv_end, float scale, void* workspace,
                               int64_t of_stride, int64_t lse_stride, cudaStream_t stream, const MergePush* push,
-                              bool* pushed) {
+                              bool* pushed, DecodeTail* tail) {
     if (pushed) *pushed = false;
     DecodeParams p;
     p.q = (const __nv_bfloat16*)q;
@@ -599,6 +667,18 @@ cudaError_t launch_gqa_decode(const void* q, const void* k, const void* v, void*
     if (!kv_lens && kv_len_uniform - kv_begin < span) span = kv_len_uniform - kv_begin;
     if (kv_end >= 0 && kv_end - kv_begin < span) span = kv_end - kv_begin;
     if (span < 1) span = 1;
+    // A few long sequences (fewer (sequence, KV head) groups than resident CTAs): one wave of longer chunks
+    // streams as fast as several waves of short ones and leaves a fraction of the partials to merge
+    // (one sequence of 131072 positions: 37 chunks instead of 147).  The chunk only ever grows here, so the
+    // chunk count stays within what rt_gqa_decode_workspace_bytes sized the scratch for.
+    {
+        const int64_t groups = batch * (int64_t)n_kv, slots = (int64_t)sm_count() * 2;
+        if (groups < slots) {
+            const int64_t per_group = slots / groups;
+            const int64_t want = ((span + per_group - 1) / per_group + 63) / 64 * 64;
+            if (want > p.chunk && want <= (1 << 20)) p.chunk = (int)want;
+        }
+    }
     p.n_chunks = (int)((span + p.chunk - 1) / p.chunk);
     p.rows = batch * n_heads;
     p.of_stride = of_stride > 0 ? of_stride : head_dim;
@@ -611,11 +691,17 @@ cudaError_t launch_gqa_decode(const void* q, const void* k, const void* v, void*
     int* counters = p.part_lse ? reinterpret_cast<int*>(p.part_lse + (int64_t)decode_num_chunks(batch, n_kv, max_seq) * p.rows)
                                : nullptr;
     bool merged = false;
+    if (tail) {  // the caller merges the chunk partials itself (split-KV row exchange)
+        counters = nullptr;
+        tail->n_chunks = p.n_chunks;
+        tail->part_o = p.part_o;
+        tail->part_lse = p.part_lse;
+    }
     cudaError_t e = cudaErrorNotSupported;
     if (decode_use_tensor_cores())
         e = launch_gqa_decode_tc(q, k, v, out_bf16, out_f32, lse, batch, n_heads, n_kv, head_dim, max_seq, kv_lens,
                                  kv_len_uniform, kv_begin, kv_end, scale, p.part_o, p.part_lse, counters, p.chunk,
-                                 p.n_chunks, p.of_stride, p.lse_stride, &merged, stream);
+                                 p.n_chunks, p.of_stride, p.lse_stride, &merged, push, stream);
     if (e == cudaErrorNotSupported) {  // a cache too large for 32-bit TMA row coordinates, or RT_ATTN_DECODE_IMPL=simt
         switch (head_dim) {
             case 64: e = launch_decode_d<64>(p, group, batch, stream); break;
@@ -625,12 +711,12 @@ cudaError_t launch_gqa_decode(const void* q, const void* k, const void* v, void*
         }
     }
     if (e != cudaSuccess) return e;
-    if (p.n_chunks > 1 && !merged) {
-        merge_partials_kernel<<<(unsigned)p.rows, kMergeWarps * 32, merge_smem_bytes(p.n_chunks, head_dim), stream>>>(
-            p.part_o, p.part_lse, p.n_chunks, p.rows, head_dim, head_dim, 1, p.out_bf16, p.out_f32, lse, p.of_stride,
-            p.lse_stride, MergeWait{nullptr, 0, 0u, 0, nullptr}, push ? *push : MergePush{});
+    if (merged && push && push->world > 0 && pushed) *pushed = true;  // delivered by the decode kernel itself
+    if (p.n_chunks > 1 && !merged && !tail) {
+        e = launch_merge_partials(p.part_o, p.part_lse, p.n_chunks, p.rows, head_dim, head_dim, 1, p.out_bf16, p.out_f32, lse,
+                                  stream, nullptr, push, p.of_stride, p.lse_stride);
+        if (e != cudaSuccess) return e;
         if (push && pushed) *pushed = true;
-        e = cudaGetLastError();
     }
     return e;
 }
@@ -638,14 +724,73 @@ cudaError_t launch_gqa_decode(const void* q, const void* k, const void* v, void*
 cudaError_t launch_merge_partials(const float* o_parts, const float* lse_parts, int64_t n_parts, int64_t rows,
                                   int dim, int64_t in_row_stride, int64_t in_lse_stride, void* out_bf16,
                                   float* out_f32, float* lse, cudaStream_t stream, const MergeWait* wait,
-                                  const MergePush* push) {
+                                  const MergePush* push, int64_t of_stride, int64_t lse_stride) {
     if (rows == 0) return cudaSuccess;
+    if (of_stride <= 0) of_stride = dim;
+    if (lse_stride <= 0) lse_stride = 1;
     if (!merge_fits(n_parts, dim)) return cudaErrorInvalidValue;
     if (wait && wait->n_flags > kMergeWarps * 32) return cudaErrorInvalidValue;
-    merge_partials_kernel<<<(unsigned)rows, kMergeWarps * 32, merge_smem_bytes(n_parts, dim), stream>>>(
-        o_parts, lse_parts, (int)n_parts, rows, dim, in_row_stride, in_lse_stride, (__nv_bfloat16*)out_bf16, out_f32, lse,
-        dim, 1, wait ? *wait : MergeWait{nullptr, 0, 0u, 0, nullptr}, push ? *push : MergePush{});
-    return cudaGetLastError();
+    const MergeWait w = wait ? *wait : MergeWait{nullptr, 0, 0u, 0, nullptr, 0};
+    const MergePush ps = push ? *push : MergePush{};
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)rows);
+    cfg.blockDim = dim3(kMergeWarps * 32);
+    cfg.dynamicSmemBytes = merge_smem_bytes(n_parts, dim);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    if (wait) {
+        // A merge that waits on arrival flags reads nothing the kernel before it in the stream wrote except
+        // through those flags (acquire loads), so it may be scheduled as soon as that kernel lets its
+        // dependents go (the decode kernel does once every CTA has streamed its chunk).  Its wait is bounded,
+        // and the CTAs it waits for are resident by then.
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+    }
+    return cudaLaunchKernelEx(&cfg, merge_partials_kernel, o_parts, lse_parts, (int)n_parts, rows, dim, in_row_stride,
+                              in_lse_stride, (__nv_bfloat16*)out_bf16, out_f32, lse, of_stride, lse_stride, w, ps);
+}
+
+cudaError_t launch_row_exchange(const float* o_parts, const float* lse_parts, int64_t n_parts, int64_t rows, int dim,
+                                int64_t in_row_stride, int64_t in_lse_stride, void* out_bf16, float* out_f32, float* lse,
+                                void* const* peer_slots, void* const* peer_flags, const float* local_slots,
+                                const uint32_t* local_flags, int world, uint32_t epoch, long long wait_clocks,
+                                int do_wait, cudaStream_t stream) {
+    if (rows == 0) return cudaSuccess;
+    const int64_t most = n_parts > world ? n_parts : world;
+    if (world <= 0 || world > kMaxPeers || !merge_fits(most, dim)) return cudaErrorInvalidValue;
+    RowExchange x;
+    for (int r = 0; r < kMaxPeers; ++r) {
+        x.slot[r] = r < world ? static_cast<float*>(peer_slots[r]) : nullptr;
+        x.flag[r] = r < world ? static_cast<uint32_t*>(peer_flags[r]) : nullptr;
+    }
+    x.local_slots = local_slots;
+    x.local_flags = local_flags;
+    x.world = world;
+    x.epoch = epoch;
+    x.max_clocks = wait_clocks > 0 ? wait_clocks : (1ll << 31);
+    x.status = device_status_ptr();
+    x.do_wait = do_wait;
+    if (!x.status) return cudaErrorInvalidSymbol;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)rows);
+    cfg.blockDim = dim3(kMergeWarps * 32);
+    cfg.dynamicSmemBytes = merge_smem_bytes(most, dim);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    static const bool pdl = [] {
+        const char* e = getenv("RT_ATTN_EXCHANGE_PDL");
+        return !(e && e[0] == '0');
+    }();
+    if (pdl) {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+    }
+    return cudaLaunchKernelEx(&cfg, splitkv_row_exchange_kernel, o_parts, lse_parts, (int)n_parts, rows, dim, in_row_stride,
+                              in_lse_stride, (__nv_bfloat16*)out_bf16, out_f32, lse, x);
 }
 
 // Copies this rank's packed (O | LSE) record into the slot every peer keeps for it and raises the

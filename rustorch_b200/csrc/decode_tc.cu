@@ -46,85 +46,176 @@ struct DecodeTcParams {
     float scale_log2;
     int* status;
     int* counters;  // NULL, or [B * Hkv] zeroed before the launch: the last chunk of a group merges its partials
+    MergePush push; // world > 0: the merged rows (record layout, out_f32 = this rank's slot) also go to the peers
 };
 
 // Called by every CTA of a multi-chunk launch once its partial is written.  The CTA that completes
 // its (sequence, KV head) group combines the group's chunk partials with the (m, l) merge of
-// online_softmax.rs:105-131 and writes the final rows, so no separate merge launch is needed:
-// for short chunks that launch costs as much as the streaming itself.  Partials of other CTAs are
-// read with cache-global loads after a device-scope fence.
+// online_softmax.rs:105-131 and writes the final rows, so no separate merge launch is needed.
+// The combine is spread over the CTA: chunk c goes to warp c % 4, each lane owns D/32 consecutive
+// dims and keeps up to eight 16-byte loads in flight, the four warp sums meet in shared memory.
+// Partials of other CTAs are read with cache-global loads after a device-scope fence.
+// With p.push.world > 0 the launch is one rank of a split-KV decode: the rows are the rank's (O | LSE)
+// record; the finishing CTA also stores them into the slot every peer keeps for this rank (one warp per
+// peer in turn, 16-byte stores over NVLink, nothing is ever loaded from a peer), and the CTA that
+// finishes the launch's last group raises every peer's flag with a system-scope release.
+// scratch: G * n_chunks + 4 * G * D floats of shared memory (decode_merge_smem_bytes).
 template <int D, int G>
 __device__ __forceinline__ void finish_group(const DecodeTcParams& p, int b, int kvh, int64_t row0, float* scratch) {
     __shared__ int s_last;
-    __shared__ float s_red[4];
+    __shared__ float s_red[4][G];
+    constexpr int VPL = D / 32;  // dims per lane
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int n = p.n_chunks;
     __threadfence();
     __syncthreads();
-    if (tid == 0) s_last = (atomicAdd(&p.counters[b * p.n_kv + kvh], 1) == p.n_chunks - 1);
+    if (tid == 0) s_last = (atomicAdd(&p.counters[b * p.n_kv + kvh], 1) == n - 1);
     __syncthreads();
     if (!s_last) return;
     __threadfence();
-    float* w_sm = scratch;  // [n_chunks]
+    float* w_sm = scratch;                                   // [G][n]: LSE of (row, chunk), then its weight
+    float* acc_sm = scratch + G * n;                         // [4 warps][G][D]
+    float* stage = scratch + ((G * n + 4 * G * D + 3) & ~3);  // [G][D + 1]: the record rows on their way to the peers
+
+    // ---- weights: per row the maximum LSE, exp(LSE_c - max) and their sum
+    float mrow[G], lrow[G];
+#pragma unroll
     for (int gg = 0; gg < G; ++gg) {
-        const int64_t row = row0 + gg;
         float m = -INFINITY;
-        for (int c = tid; c < p.n_chunks; c += 128) {
-            const float x = __ldcg(p.part_lse + (int64_t)c * p.rows + row);
-            w_sm[c] = x;
+        for (int c = tid; c < n; c += 128) {
+            const float x = __ldcg(p.part_lse + (int64_t)c * p.rows + row0 + gg);
+            w_sm[gg * n + c] = x;
             m = fmaxf(m, x);
         }
 #pragma unroll
         for (int off = 16; off; off >>= 1) m = fmaxf(m, __shfl_xor_sync(kFullMask, m, off));
-        __syncthreads();  // s_red free (previous row), w_sm written
-        if (lane == 0) s_red[warp] = m;
-        __syncthreads();
-        m = fmaxf(fmaxf(s_red[0], s_red[1]), fmaxf(s_red[2], s_red[3]));
+        if (lane == 0) s_red[warp][gg] = m;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int gg = 0; gg < G; ++gg) {
+        const float m = fmaxf(fmaxf(s_red[0][gg], s_red[1][gg]), fmaxf(s_red[2][gg], s_red[3][gg]));
+        mrow[gg] = m;
         float l = 0.f;
         if (m != -INFINITY) {
-            for (int c = tid; c < p.n_chunks; c += 128) {
-                const float x = w_sm[c];
+            for (int c = tid; c < n; c += 128) {  // the same thread wrote these entries above
+                const float x = w_sm[gg * n + c];
                 const float w = (x == -INFINITY) ? 0.f : expf(x - m);
-                w_sm[c] = w;
+                w_sm[gg * n + c] = w;
                 l += w;
             }
         }
 #pragma unroll
         for (int off = 16; off; off >>= 1) l += __shfl_xor_sync(kFullMask, l, off);
-        __syncthreads();  // everyone has read s_red (max); weights written
-        if (lane == 0) s_red[warp] = l;
-        __syncthreads();
-        l = (s_red[0] + s_red[1]) + (s_red[2] + s_red[3]);
-        const float inv = (l > 0.f) ? 1.f / l : 0.f;
-        for (int d = tid; d < D; d += 128) {
-            float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-            if (l > 0.f) {
-                const float* src = p.part_o + row * D + d;
-                const int64_t cs = p.rows * D;
-                int c = 0;
-                for (; c + 4 <= p.n_chunks; c += 4) {  // four independent loads in flight; empty chunks may be uninitialised
-                    const float w0 = w_sm[c], w1 = w_sm[c + 1], w2 = w_sm[c + 2], w3 = w_sm[c + 3];
-                    const float x0 = w0 != 0.f ? __ldcg(src + (int64_t)c * cs) : 0.f;
-                    const float x1 = w1 != 0.f ? __ldcg(src + (int64_t)(c + 1) * cs) : 0.f;
-                    const float x2 = w2 != 0.f ? __ldcg(src + (int64_t)(c + 2) * cs) : 0.f;
-                    const float x3 = w3 != 0.f ? __ldcg(src + (int64_t)(c + 3) * cs) : 0.f;
-                    a0 = fmaf(w0, x0, a0);
-                    a1 = fmaf(w1, x1, a1);
-                    a2 = fmaf(w2, x2, a2);
-                    a3 = fmaf(w3, x3, a3);
-                }
-                for (; c < p.n_chunks; ++c) {
-                    const float w0 = w_sm[c];
-                    if (w0 != 0.f) a0 = fmaf(w0, __ldcg(src + (int64_t)c * cs), a0);
+        lrow[gg] = l;
+    }
+    __syncthreads();  // every thread has read the maxima: s_red is free for the sums; weights are visible
+#pragma unroll
+    for (int gg = 0; gg < G; ++gg)
+        if (lane == 0) s_red[warp][gg] = lrow[gg];
+
+    // ---- weighted sum of the partial rows: warp x takes chunks x, x+4, ...
+    float acc[G][VPL];
+#pragma unroll
+    for (int gg = 0; gg < G; ++gg)
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) acc[gg][i] = 0.f;
+    const int64_t cs = p.rows * D;  // floats between consecutive chunks of part_o
+    const float* src = p.part_o + row0 * D + lane * VPL;
+    constexpr int kLoadsPerChunk = G * (VPL >= 4 ? VPL / 4 : 1);         // 16-byte (8-byte at D = 64) loads per lane
+    constexpr int kInFlight = kLoadsPerChunk >= 8 ? 1 : 8 / kLoadsPerChunk;  // chunks loaded per round
+    for (int c0 = warp; c0 < n; c0 += 4 * kInFlight) {
+        float v[kInFlight][G][VPL], wgt[kInFlight][G];
+#pragma unroll
+        for (int u = 0; u < kInFlight; ++u) {
+            const int c = c0 + 4 * u;
+#pragma unroll
+            for (int gg = 0; gg < G; ++gg) {
+                wgt[u][gg] = (c < n && mrow[gg] != -INFINITY) ? w_sm[gg * n + c] : 0.f;
+                const float* q = src + (int64_t)c * cs + gg * D;
+                if (wgt[u][gg] != 0.f) {  // an empty chunk's partial row may be uninitialised
+                    if constexpr (VPL == 2) {
+                        const float2 t = __ldcg(reinterpret_cast<const float2*>(q));
+                        v[u][gg][0] = t.x; v[u][gg][1] = t.y;
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < VPL; i += 4) {
+                            const float4 t = __ldcg(reinterpret_cast<const float4*>(q + i));
+                            v[u][gg][i] = t.x; v[u][gg][i + 1] = t.y; v[u][gg][i + 2] = t.z; v[u][gg][i + 3] = t.w;
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < VPL; ++i) v[u][gg][i] = 0.f;
                 }
             }
-            const float outv = ((a0 + a1) + (a2 + a3)) * inv;
-            if (p.out_bf16) p.out_bf16[row * D + d] = __float2bfloat16(outv);
-            if (p.out_f32) p.out_f32[row * p.of_stride + d] = outv;
         }
-        if (tid == 0 && p.lse) p.lse[row * p.lse_stride] = (l > 0.f) ? m + logf(l) : -INFINITY;
-        __syncthreads();  // w_sm and s_red are reused by the next row
+#pragma unroll
+        for (int u = 0; u < kInFlight; ++u)
+#pragma unroll
+            for (int gg = 0; gg < G; ++gg)
+#pragma unroll
+                for (int i = 0; i < VPL; ++i) acc[gg][i] = fmaf(wgt[u][gg], v[u][gg][i], acc[gg][i]);
+    }
+#pragma unroll
+    for (int gg = 0; gg < G; ++gg)
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) acc_sm[(warp * G + gg) * D + lane * VPL + i] = acc[gg][i];
+    __syncthreads();
+
+    // ---- final rows: O = sum of the four warp sums / l, LSE = m + ln l
+    const bool do_push = p.push.world > 0;
+    for (int i = tid; i < G * D; i += 128) {
+        const int gg = i / D, d = i % D;
+        const float l = (s_red[0][gg] + s_red[1][gg]) + (s_red[2][gg] + s_red[3][gg]);
+        const float sum = (acc_sm[(0 * G + gg) * D + d] + acc_sm[(1 * G + gg) * D + d]) +
+                          (acc_sm[(2 * G + gg) * D + d] + acc_sm[(3 * G + gg) * D + d]);
+        const float outv = (l > 0.f) ? sum / l : 0.f;
+        const int64_t row = row0 + gg;
+        if (p.out_bf16) p.out_bf16[row * D + d] = __float2bfloat16(outv);
+        if (p.out_f32) p.out_f32[row * p.of_stride + d] = outv;
+        if (do_push) stage[gg * (D + 1) + d] = outv;
+    }
+    if (tid < G) {
+        const float l = (s_red[0][tid] + s_red[1][tid]) + (s_red[2][tid] + s_red[3][tid]);
+        const float lse = (l > 0.f) ? mrow[tid] + logf(l) : -INFINITY;
+        if (p.lse) p.lse[(row0 + tid) * p.lse_stride] = lse;
+        if (do_push) stage[tid * (D + 1) + D] = lse;
+    }
+    if (!do_push) return;
+
+    // ---- delivery: the G record rows are contiguous ([rows, D + 1] layout) and 16-byte aligned as a block
+    // when G * (D + 1) is a multiple of 4 (checked by the launcher)
+    __syncthreads();
+    {
+        const float4* stage4 = reinterpret_cast<const float4*>(stage);
+        constexpr int kVec = G * (D + 1) / 4;
+        for (int r = warp; r < p.push.world; r += 4) {
+            float* base = p.push.dst[r];
+            if (base == p.out_f32) continue;  // this rank's own slot was written above
+            float4* dst = reinterpret_cast<float4*>(base + row0 * (D + 1));
+            for (int i = lane; i < kVec; i += 32) dst[i] = stage4[i];
+        }
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (tid == 0) {
+        const int groups = (int)(p.rows / G);
+        if (atomicAdd(p.push.done_counter, 1) == groups - 1) {
+            *p.push.done_counter = 0;  // ready for the next launch
+            __threadfence_system();    // the rows of every group are ordered before the flags
+            for (int r = 0; r < p.push.world; ++r)
+                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.push.flag[r]), "r"(p.push.epoch) : "memory");
+        }
     }
 }
+
+// Shared memory finish_group needs: weights, four warp sums, the staged record rows.
+static size_t decode_merge_smem_bytes(int G, int D, int n_chunks) {
+    return sizeof(float) * ((size_t)G * (size_t)n_chunks + 4 * (size_t)G * (size_t)D + 4 + (size_t)G * (size_t)(D + 1));
+}
+
+__device__ __forceinline__ void launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m, uint64_t* bar, int c0, int c1) {
     asm volatile(
@@ -175,6 +266,7 @@ gqa_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
     if (c1 > hi) c1 = hi;
 
     if (c0 >= c1) {  // nothing visible in this chunk: identity partial
+        launch_dependents();
         if (direct) {
             for (int i = tid; i < G * D; i += 128) {
                 const int64_t o = (row0 + i / D) * D + i % D;
@@ -345,6 +437,11 @@ gqa_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
         }
     }
 
+    // This CTA has streamed its share of the cache: a kernel launched behind this one with programmatic
+    // stream serialisation (the cross-rank merge, which only waits on flags) may be scheduled once every CTA
+    // has got here, instead of after the whole grid has drained.
+    launch_dependents();
+
     // ---- merge the four warp states through shared memory (the ring is idle now)
     l_part += __shfl_xor_sync(kFullMask, l_part, 1);
     l_part += __shfl_xor_sync(kFullMask, l_part, 2);
@@ -431,7 +528,8 @@ cudaError_t launch_gqa_decode_tc(const void* q, const void* k, const void* v, vo
                                  float* lse, int64_t batch, int n_heads, int n_kv, int head_dim, int64_t max_seq,
                                  const int32_t* kv_lens, int64_t kv_len_uniform, int64_t kv_begin, int64_t kv_end,
                                  float scale, float* part_o, float* part_lse, int* counters, int chunk, int n_chunks,
-                                 int64_t of_stride, int64_t lse_stride, bool* merged, cudaStream_t stream) {
+                                 int64_t of_stride, int64_t lse_stride, bool* merged, const MergePush* push,
+                                 cudaStream_t stream) {
     *merged = false;
     const int64_t cache_rows = batch * n_kv * max_seq;
     if ((head_dim != 64 && head_dim != 128 && head_dim != 256) || cache_rows >= (1ll << 31) - 64)
@@ -461,23 +559,40 @@ cudaError_t launch_gqa_decode_tc(const void* q, const void* k, const void* v, vo
     p.scale_log2 = scale * kLog2e;
     p.status = device_status_ptr();
     if (!p.status) return cudaErrorInvalidSymbol;
-    // The in-kernel merge is serial per (sequence, KV head): worth it for the few chunks of a batched
-    // decode (config 4 has at most 8), not for the dozens of chunks of one long sequence, which the
-    // merge kernel spreads over many more threads (batch 1, kv_len 4096 = 32 chunks: 20.5 us fused,
-    // 14.4 us with the merge kernel).
-    constexpr int kMaxFusedChunks = 8;
+    // The CTA that completes a (sequence, KV head) group can merge the group's chunk partials itself
+    // (finish_group), which makes a multi-chunk decode one kernel.  It costs a memset node for the counters
+    // and a tail in which one CTA per group works alone, so it is used where that is cheaper than a second
+    // launch: grids of several waves with few chunks per group (batched decode), and launches whose rows
+    // also go to the peers of a split-KV decode, where it also replaces the copy kernel.  A small batch-1
+    // launch is latency-bound and keeps the separate merge kernel.  RT_ATTN_DECODE_FUSED_MERGE=0 forces the
+    // separate kernel everywhere.  The merge scratch must fit the (then idle) ring, and rows delivered to
+    // peers must be 16-byte aligned group by group (group size 4 or 8).
     static const bool fused_off = [] {
         const char* s = getenv("RT_ATTN_DECODE_FUSED_MERGE");
         return s && s[0] == '0';
     }();
-    // ... and only for grids of several waves: a small launch (batch 1) is latency-bound, and there the
-    // memset node plus the serial tail cost more than the second launch (14.4 us against 10.3 us).
+    const int group = n_heads / n_kv;
+    const size_t ring = head_dim == 256 ? DecodeTcCfg<256>::RING_BYTES
+                                        : head_dim == 128 ? DecodeTcCfg<128>::RING_BYTES : DecodeTcCfg<64>::RING_BYTES;
+    const bool fits = decode_merge_smem_bytes(group, head_dim, n_chunks) <= ring;
+    const bool pushing = push && push->world > 0;
+    // Delivery from inside the decode kernel is built and tested but measured slower than the chunk-merge
+    // kernel delivering the rows (its tail is one CTA per group); RT_ATTN_DECODE_PUSH_IN_KERNEL=1 selects it.
+    static const bool push_in_kernel = [] {
+        const char* s = getenv("RT_ATTN_DECODE_PUSH_IN_KERNEL");
+        return s && s[0] == '1';
+    }();
+    const bool push_ok = pushing && push_in_kernel && group % 4 == 0 && out_f32 && of_stride == head_dim + 1;
+    constexpr int kMaxFusedChunks = 8;
     const bool many_ctas = batch * n_kv * (int64_t)n_chunks >= 4 * (int64_t)sm_count();
-    p.counters = (n_chunks > 1 && n_chunks <= kMaxFusedChunks && many_ctas && !fused_off) ? counters : nullptr;
+    const bool batched = n_chunks <= kMaxFusedChunks && many_ctas && !pushing;
+    p.counters = (n_chunks > 1 && fits && (batched || push_ok) && !fused_off) ? counters : nullptr;
+    p.push = MergePush{};
     if (p.counters) {
         cudaError_t e = cudaMemsetAsync(p.counters, 0, sizeof(int) * (size_t)batch * n_kv, stream);
         if (e != cudaSuccess) return e;
         *merged = true;
+        if (push) p.push = *push;
     }
     return head_dim == 256   ? launch_d<256>(mk, mv, p, n_heads / n_kv, batch, stream)
            : head_dim == 128 ? launch_d<128>(mk, mv, p, n_heads / n_kv, batch, stream)

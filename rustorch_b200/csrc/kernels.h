@@ -13,6 +13,7 @@ int sm_count();
 
 // ---- decode.cu
 struct MergePush;
+struct DecodeTail;
 int decode_chunk_tokens(int64_t batch, int n_kv, int64_t max_seq);
 int decode_num_chunks(int64_t batch, int n_kv, int64_t max_seq);
 // Whether merge_partials_kernel can combine n_parts partials of this head dim (its weights live in
@@ -23,7 +24,16 @@ cudaError_t launch_gqa_decode(const void* q, const void* k, const void* v, void*
                               int64_t max_seq, const int32_t* kv_lens, int64_t kv_len_uniform,
                               int64_t kv_begin, int64_t kv_end, float scale, void* workspace,
                               int64_t of_stride, int64_t lse_stride, cudaStream_t stream,
-                              const struct MergePush* push = nullptr, bool* pushed = nullptr);
+                              const struct MergePush* push = nullptr, bool* pushed = nullptr,
+                              struct DecodeTail* tail = nullptr);
+// With a DecodeTail the decode launches no chunk merge of its own: the caller gets the chunk partials
+// ([n_chunks][rows][dim] O and [n_chunks][rows] LSE in the workspace) and combines them itself.  With a
+// single chunk there are no partials; the outputs passed to launch_gqa_decode hold the result then.
+struct DecodeTail {
+    int n_chunks;
+    const float* part_o;
+    const float* part_lse;
+};
 // o_parts rows are in_row_stride floats apart, lse_parts entries in_lse_stride floats apart
 // Optional bounded wait in front of a merge: flags[r] >= epoch means part r has arrived.
 struct MergeWait {
@@ -32,6 +42,7 @@ struct MergeWait {
     uint32_t epoch;
     long long max_clocks;
     int* status;
+    int per_row;  // 0: flags[r]; 1: one flag per (part, row), flags[r * rows + row]
 };
 constexpr int kMaxPeers = 16;
 // Optional delivery of a merge's output record ([rows, dim + 1] f32: O | LSE) to the peers of a split-KV
@@ -47,7 +58,12 @@ struct MergePush {
 cudaError_t launch_merge_partials(const float* o_parts, const float* lse_parts, int64_t n_parts, int64_t rows,
                                   int dim, int64_t in_row_stride, int64_t in_lse_stride, void* out_bf16,
                                   float* out_f32, float* lse, cudaStream_t stream, const MergeWait* wait = nullptr,
-                                  const MergePush* push = nullptr);
+                                  const MergePush* push = nullptr, int64_t of_stride = 0, int64_t lse_stride = 0);
+cudaError_t launch_row_exchange(const float* o_parts, const float* lse_parts, int64_t n_parts, int64_t rows, int dim,
+                                int64_t in_row_stride, int64_t in_lse_stride, void* out_bf16, float* out_f32, float* lse,
+                                void* const* peer_slots, void* const* peer_flags, const float* local_slots,
+                                const uint32_t* local_flags, int world, uint32_t epoch, long long wait_clocks,
+                                int do_wait, cudaStream_t stream);
 cudaError_t launch_push_records(const float* record, void* const* peer_slots, void* const* peer_flags, int world,
                                 int64_t record_floats, uint32_t epoch, cudaStream_t stream);
 cudaError_t launch_kv_append(void* k_cache, void* v_cache, const void* k_in, const void* v_in, int64_t batch,
@@ -64,7 +80,8 @@ cudaError_t launch_gqa_decode_tc(const void* q, const void* k, const void* v, vo
                                  float* lse, int64_t batch, int n_heads, int n_kv, int head_dim, int64_t max_seq,
                                  const int32_t* kv_lens, int64_t kv_len_uniform, int64_t kv_begin, int64_t kv_end,
                                  float scale, float* part_o, float* part_lse, int* counters, int chunk, int n_chunks,
-                                 int64_t of_stride, int64_t lse_stride, bool* merged, cudaStream_t stream);
+                                 int64_t of_stride, int64_t lse_stride, bool* merged, const MergePush* push,
+                                 cudaStream_t stream);
 
 // ---- prefill_simt.cu
 cudaError_t launch_prefill_f32(const float* q, const float* k, const float* v, float* out, float* lse,

@@ -20,13 +20,11 @@
 //   warp  11   : idle (it completes the third warpgroup so that setmaxnreg can move its
 //                registers to the softmax warpgroups: 72 vs 216 registers per thread; the split
 //                must stay below the 64 K register file or setmaxnreg.inc never returns)
-// TMEM (512 columns x 128 lanes, f32): S0 [0,128), S1 [128,256), O0 [256,256+D), O1 [256+D,256+2D).
-// One step = one 128-key K/V tile: S_w = Q_w K^T is an SS MMA with N = 128 (both operands K-major in
-// 128-byte-swizzled shared memory; with N = 64 the instruction is bound by the shared-memory read of
-// its 4 KB Q slice, 52 clocks instead of 32, which N = 128 amortises over twice the math); P (bf16)
-// overwrites the first 64 columns of S_w and feeds O_w += P V from TMEM (TS MMA, V MN-major, i.e. used
-// exactly as TMA lands it).  S_w is single-buffered: the two Q tiles alternate on the tensor pipe, so
-// the pipe runs PV_1(u-1), S_1(u) while the softmax of tile 0 works on S_0(u), and the reverse.
+// TMEM (512 columns x 128 lanes, f32): per Q tile two 64-column S buffers (S[w][b] at w*128 + b*64),
+// O0 [256,256+D), O1 [256+D,256+2D).  K/V are loaded as 128-key tiles but multiplied in 64-key
+// steps; P (bf16) overwrites the first 32 columns of its S buffer and feeds the PV MMA from TMEM.
+// S = Q K^T is an SS MMA with both operands K-major in 128-byte-swizzled shared memory; O += P V
+// is a TS MMA whose B operand (V) is MN-major, i.e. V is used exactly as TMA lands it.
 // The normalised O tile is staged in the tile's own (by then idle) Q buffer and leaves through
 // TMA stores.  Every mbarrier wait is bounded; on expiry the kernel records a code in the device
 // status word, drains its own copies and MMAs, frees TMEM and returns.
@@ -47,16 +45,21 @@ template <int D>
 struct TcCfg {
     static constexpr int BM = 128;                      // query rows per tile
     static constexpr int BL = 128;                      // keys per TMA-loaded K/V tile
-    static constexpr int BN = 128;                      // keys per MMA / softmax step (= one K/V tile)
+    static constexpr int BN = 64;                       // keys per MMA / softmax step
     static constexpr int KS = (D == 128) ? 3 : 4;       // K ring depth (runs one tile ahead of V)
     static constexpr int VS = (D == 128) ? 2 : 4;       // V ring depth
     static constexpr int TILE_BYTES = 128 * D * 2;
     static constexpr int SUB_BYTES = 128 * 64 * 2;      // one 64-column (128-byte) swizzled sub-tile
+    static constexpr int HALF_BYTES = 64 * 128;         // 64 rows inside a sub-tile
     static constexpr int NSUB = D / 64;
-    static constexpr int NBARS = 2 + 2 + 3 * KS + 3 * VS + 2 + 2 + 2 + 2 + 2 + 1;
-    static constexpr int SMEM_BYTES = (2 + KS + VS) * TILE_BYTES + NBARS * 8 + 16 + 1024;
+    static constexpr int NBARS = 2 + 2 + 3 * KS + 3 * VS + 4 + 4 + 2 + 2 + 2 + 2 + 1;
+    // (batch, query block) pairs the length-sorted schedule can hold (two uint16 per pair); what is left of
+    // the 227 KB of shared memory at D = 128 bounds it there
+    static constexpr int SCHED_CAP = (D == 128) ? 384 : 2048;
+    static constexpr int SMEM_BYTES = (2 + KS + VS) * TILE_BYTES + NBARS * 8 + 16 + 4 * SCHED_CAP + 1024;
+    static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB of shared memory a CTA can opt into");
     static constexpr uint32_t TMEM_COLS = 512;
-    static constexpr uint32_t COL_S = 0, COL_O = 256;   // S of tile w at COL_S + w*128, O at COL_O + w*D
+    static constexpr uint32_t COL_S = 0, COL_O = 256;   // S: tile w, buffer b at COL_S + w*128 + b*64
 };
 
 struct TcParams {
@@ -73,6 +76,7 @@ struct TcParams {
     int64_t o_stride_b, o_stride_h, o_stride_row;  // element strides of the output (inner dim contiguous)
     int n_qb;          // 256-row blocks per head
     int slots_per_head, n_slots, paired;  // static schedule, see tc_item
+    int sorted;        // length-sorted schedule (launches with per-batch kv_lens), see tc_item
     int single_tile;   // items are 128-row blocks handled by Q tile 1 alone (small launches, see tc_item)
 };
 
@@ -110,8 +114,8 @@ __host__ __device__ constexpr bool poly_pair(int q) { return (q & 3) == 3; }
 // One work item of a CTA's static list.
 struct TcItem {
     int bh, b, h, h_kv, q0, kv_hi, q_off;  // bh = b * heads + h indexes LSE; h_kv is the KV head h reads
-    int U0, U1;    // 128-key steps of each Q tile (U0 <= U1); scalars, so nothing is indexed dynamically
-    int n_tiles;   // 128-key K/V tiles to load (= U1)
+    int U0, U1;    // 64-key steps of each Q tile (U0 <= U1); scalars, so nothing is indexed dynamically
+    int n_tiles;   // 128-key K/V tiles to load
     bool end;      // the list is exhausted
     bool valid;    // false: this position of the list holds no item
     __device__ __forceinline__ int steps(int w) const { return w ? U1 : U0; }
@@ -123,48 +127,71 @@ struct TcItem {
 // a causal mask every slot then costs the same, and the CTAs finish together.  A launch with fewer
 // 256-row blocks than 3/4 of the SMs uses 128-row items instead (single_tile): twice the CTAs, each with
 // one Q tile, which shortens the critical path of a small problem.
+// Sorted mode (per-batch kv_lens, where an item's cost is only known on the device): every CTA ranks the
+// (batch, query block) pairs by their step count at start-up (the same deterministic sort in every CTA, so
+// no queue, no atomics and no scratch memory are needed), the item list is that order with all heads of a
+// pair side by side, and it is dealt to the CTAs boustrophedon (0..G-1, G-1..0, ...), heaviest first: the
+// persistent kernel's overlap of one item's set-up with the previous item's tail, and a balanced finish.
 template <bool kCausal>
-__device__ __forceinline__ TcItem tc_item(int j, const TcParams& p) {
+__device__ __forceinline__ void tc_steps(const TcParams& p, int b, int q0, int& kv_hi, int& q_off, int& U0, int& U1) {
+    kv_hi = p.seq_kv;
+    if (p.kv_lens) {
+        const int l = p.kv_lens[b];
+        kv_hi = l < 0 ? 0 : (l < p.seq_kv ? l : p.seq_kv);
+    }
+    q_off = p.q_offsets ? p.q_offsets[b] : 0;   // query row i sits at key position i + q_off
+    const int n_steps = (kv_hi + 63) / 64;      // 64-key steps that hold a visible key
+    const int last0 = q0 + 127 + q_off, last1 = last0 + 128;  // last key each tile's last row may see
+    U0 = p.single_tile ? 0 : (!kCausal ? n_steps : (last0 < 0 ? 0 : min(n_steps, last0 / 64 + 1)));
+    U1 = !kCausal ? n_steps : (last1 < 0 ? 0 : min(n_steps, last1 / 64 + 1));
+}
+
+template <bool kCausal>
+__device__ __forceinline__ TcItem tc_item(int j, const TcParams& p, const uint16_t* sched) {
     TcItem it;
-    const int slot = (int)blockIdx.x + (p.paired ? (j >> 1) : j) * (int)gridDim.x;
-    it.end = slot >= p.n_slots;
     it.valid = false;
-    if (it.end) return it;
-    it.bh = slot / p.slots_per_head;
-    const int r = slot % p.slots_per_head;
-    int qb = p.n_qb - 1 - r;
-    if (p.paired && (j & 1)) {
-        if (r == qb) return it;  // the middle block of an odd count has no partner
-        qb = r;
+    int qb;
+    if (p.sorted) {
+        const int G = (int)gridDim.x;
+        it.end = (int64_t)j * G >= (int64_t)p.n_slots;
+        if (it.end) return it;
+        const int pos = j * G + ((j & 1) ? G - 1 - (int)blockIdx.x : (int)blockIdx.x);
+        if (pos >= p.n_slots) return it;
+        const int pair = sched[pos / p.heads];
+        qb = pair % p.n_qb;
+        it.b = pair / p.n_qb;
+        it.h = pos % p.heads;
+        it.bh = it.b * p.heads + it.h;
+    } else {
+        const int slot = (int)blockIdx.x + (p.paired ? (j >> 1) : j) * (int)gridDim.x;
+        it.end = slot >= p.n_slots;
+        if (it.end) return it;
+        it.bh = slot / p.slots_per_head;
+        const int r = slot % p.slots_per_head;
+        qb = p.n_qb - 1 - r;
+        if (p.paired && (j & 1)) {
+            if (r == qb) return it;  // the middle block of an odd count has no partner
+            qb = r;
+        }
+        it.b = it.bh / p.heads;
+        it.h = it.bh % p.heads;
     }
     it.valid = true;
-    it.b = it.bh / p.heads;
-    it.h = it.bh % p.heads;
     it.h_kv = it.h / (p.heads / p.heads_kv);
     // Single-tile items: block qb covers rows [128 qb, 128 qb + 128) and is given to Q tile 1, so the
     // item's origin lies 128 rows earlier and Q tile 0 takes no part (its rows belong to another item).
     it.q0 = p.single_tile ? qb * 128 - 128 : qb * 256;
-    it.kv_hi = p.seq_kv;
-    if (p.kv_lens) {
-        const int l = p.kv_lens[it.b];
-        it.kv_hi = l < 0 ? 0 : (l < p.seq_kv ? l : p.seq_kv);
-    }
-    it.q_off = p.q_offsets ? p.q_offsets[it.b] : 0;  // query row i sits at key position i + q_off
-    const int n_steps = (it.kv_hi + 127) / 128;      // 128-key steps that hold a visible key
-    const int last0 = it.q0 + 127 + it.q_off, last1 = last0 + 128;  // last key each tile's last row may see
-    it.U0 = p.single_tile ? 0 : (!kCausal ? n_steps : (last0 < 0 ? 0 : min(n_steps, last0 / 128 + 1)));
-    it.U1 = !kCausal ? n_steps : (last1 < 0 ? 0 : min(n_steps, last1 / 128 + 1));
-    it.n_tiles = it.U1;
+    tc_steps<kCausal>(p, it.b, it.q0, it.kv_hi, it.q_off, it.U0, it.U1);
+    it.n_tiles = (it.U1 + 1) / 2;
     return it;
 }
 
-// Pipeline, per Q tile w and 128-key step u:
-//   MMA:     S_w(u) -> TMEM S[w]                (SS, N = 128, D/16 k-steps)      commit s_full[w]
-//   softmax: S[w] -> registers -> P (bf16) over the first 64 columns of S[w]     arrive p_full[w]
-//   MMA:     O_w += P V(u)                      (TS, N = D, 8 k-steps), then S_w(u+1) into S[w]: the tensor
-//            pipe runs one thread's MMAs in issue order, so S_w(u+1) cannot overtake the PV that reads P.
-// s_full[w] of step u is committed after PV_w(u-1) was issued, so seeing it also means that O_w is at
-// rest: the softmax warps may rescale O_w in place before they release P.
+// Pipeline, per Q tile w and 64-key step u (buffer b = u & 1):
+//   MMA:     S_w(u) -> TMEM S[w][b]            (SS, N = 64, D/16 k-steps)       commit s_full[w][b]
+//   softmax: S[w][b] -> registers -> P (bf16) over the first 32 columns of S[w][b]   arrive p_full[w][b]
+//   MMA:     O_w += P V(u)                      (TS, N = D, 4 k-steps)           commit o_full[w]
+//            then S_w(u+2) into the same buffer (in-order after the PV that read P from it)
+// S is double-buffered, so the softmax of step u+1 never waits for the PV of step u.
 // Per item and tile: q_full (Q landed) -> ... -> o_done (last PV retired) -> epilogue reads O
 // (o_free: the next item's first PV may overwrite it), stages it in the Q buffer (stage_full),
 // one thread stores it (q_empty: the next item's Q may land).  A tile that sees no key in an
@@ -175,7 +202,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                   const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
                   const TcParams p) {
     using C = TcCfg<D>;
-    constexpr int KS = C::KS, VS = C::VS, TILE = C::TILE_BYTES, SUB = C::SUB_BYTES;
+    constexpr int KS = C::KS, VS = C::VS, TILE = C::TILE_BYTES, SUB = C::SUB_BYTES, HALF = C::HALF_BYTES;
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -189,13 +216,15 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     uint64_t* k_empty = k_full + KS;      // [2 tiles][KS]: the issuer of tile w is done with the slot
     uint64_t* v_full = k_empty + 2 * KS;  // [VS]
     uint64_t* v_empty = v_full + VS;      // [2 tiles][VS]
-    uint64_t* s_full = v_empty + 2 * VS;  // [2]  one phase per step: S_w is in TMEM (and O_w at rest)
-    uint64_t* p_full = s_full + 2;        // [2]  one phase per step: P_w is in TMEM
-    uint64_t* o_done = p_full + 2;        // [2]  one phase per item: the last PV of the tile has retired
+    uint64_t* s_full = v_empty + 2 * VS;  // [2 tiles][2 buffers]
+    uint64_t* p_full = s_full + 4;        // [2 tiles][2 buffers]
+    uint64_t* o_full = p_full + 4;        // [2]  one phase per PV step (O at rest for a rescale)
+    uint64_t* o_done = o_full + 2;        // [2]  one phase per item: the last PV of the tile has retired
     uint64_t* o_free = o_done + 2;        // [2]  one phase per item: the epilogue has read O out of TMEM
     uint64_t* stage_full = o_free + 2;    // [2]  one phase per item: the O tile is staged in shared memory
     uint64_t* done_bar = stage_full + 2;  // [1]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done_bar + 1);
+    uint16_t* sched = reinterpret_cast<uint16_t*>(tmem_slot + 4);  // [SCHED_CAP] pair order, then [SCHED_CAP] step counts
 
     // Broadcasting the warp index makes it provably warp-uniform, so role dispatch and the MMA
     // operands stay on the uniform datapath.
@@ -204,6 +233,28 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     const int Nkv = p.seq_kv;
 
     // ------------------------------------------------------------------ setup
+    if (p.sorted) {
+        // Rank sort of the (batch, query block) pairs by their step count, descending, ties by index:
+        // every CTA computes the same table.
+        uint16_t* cost = sched + C::SCHED_CAP;
+        const int n_pairs = p.n_slots / p.heads;
+        for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
+            int kv_hi, q_off, U0, U1;
+            tc_steps<kCausal>(p, i / p.n_qb, (i % p.n_qb) * 256, kv_hi, q_off, U0, U1);
+            cost[i] = (uint16_t)min(U0 + U1, 65535);
+        }
+        __syncthreads();
+        for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
+            const int ci = cost[i];
+            int rank = 0;
+            for (int k2 = 0; k2 < n_pairs; ++k2) {
+                const int ck = cost[k2];
+                rank += (ck > ci || (ck == ci && k2 < i)) ? 1 : 0;
+            }
+            sched[rank] = (uint16_t)i;
+        }
+        __syncthreads();
+    }
     bool first_preloaded = false;  // meaningful in the producer thread only
     if (warp == 8 && lane == 0) {
         prefetch_tensormap(&tm_q);
@@ -213,11 +264,12 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         for (int i = 0; i < 2; ++i) {
             mbar_init(&q_full[i], 1);
             mbar_init(&q_empty[i], 1);
+            mbar_init(&o_full[i], 1);
             mbar_init(&o_done[i], 1);
             mbar_init(&o_free[i], 128);
             mbar_init(&stage_full[i], 128);
         }
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < 4; ++i) {
             mbar_init(&s_full[i], 1);
             mbar_init(&p_full[i], 128);
         }
@@ -236,7 +288,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         fence_proxy_async();
         // Q and the first K tile of the first item are requested right away, so their latency
         // overlaps the TMEM allocation and the CTA-wide barrier below.
-        const TcItem it = tc_item<kCausal>(0, p);
+        const TcItem it = tc_item<kCausal>(0, p, sched);
         if (!it.end && it.valid && it.U1 > 0) {
             first_preloaded = true;
             for (int w = 0; w < 2; ++w) {
@@ -274,7 +326,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             int na0 = 0, na1 = 0;  // items so far in which tile w took part (phase of its per-item barriers)
             bool ok = true;
             for (int j = 0; ok; ++j) {
-                const TcItem it = tc_item<kCausal>(j, p);
+                const TcItem it = tc_item<kCausal>(j, p, sched);
                 if (it.end) break;
                 if (!it.valid || it.U1 == 0) continue;  // nothing to load
                 auto load_q = [&](int w, int na) {
@@ -342,7 +394,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         {
             const int w = warp - 9;
             const bool leader = elect_one();
-            constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);
+            constexpr uint32_t idesc_s = make_idesc_bf16(128, 64, 0, 0);
             constexpr uint32_t idesc_o = make_idesc_bf16(128, D, 0, 1);
             // Descriptors are built once; each MMA only adds an offset (in 16-byte units) to the
             // start-address field, so the issuing thread keeps ahead of the tensor pipe.
@@ -354,7 +406,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             uint64_t* const ve = v_empty + w * VS;
             int kg = 0, vg = 0;    // ring index of the item's first K / V tile
             int na = 0;            // items so far in which this tile took part
-            int cp = 0;            // p_full phases consumed before the item
+            int cp0 = 0, cp1 = 0;  // p_full phases of each S buffer consumed before the item
             auto commit = [&](uint64_t* bar) {
                 if (leader) mma_commit(bar);
             };
@@ -363,28 +415,31 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             };
             bool ok = true;
             for (int j = 0; ok; ++j) {
-                const TcItem it = tc_item<kCausal>(j, p);
+                const TcItem it = tc_item<kCausal>(j, p, sched);
                 if (it.end) break;
                 if (!it.valid || it.U1 == 0) continue;
                 const int n_u = it.steps(w);
-                // S_w(u) = Q_w K(u)^T over the 128 keys of the item's K tile u
+                // S_w(u): keys [64u, 64u+64) = rows (u&1)*64.. of the item's K tile u/2
                 auto issue_S = [&](int u) {
-                    const uint64_t bk = dk + (uint64_t)((((kg + u) % KS) * TILE) >> 4);
+                    const uint64_t bk = dk + (uint64_t)((((kg + (u >> 1)) % KS) * TILE + (u & 1) * HALF) >> 4);
+                    const uint32_t d = tS + (u & 1) * 64;
 #pragma unroll
                     for (int kk = 0; kk < D / 16; ++kk) {
                         const uint32_t off = (uint32_t)(((kk / 4) * SUB + (kk % 4) * 32) >> 4);
-                        if (leader) mma_ss(tS, dq + off, bk + off, idesc_s, kk > 0);
+                        if (leader) mma_ss(d, dq + off, bk + off, idesc_s, kk > 0);
                     }
                 };
-                // O_w += P V(u): P (bf16, 128 keys) sits in the first 64 columns of S[w]; 16 keys per k-step
+                // O_w += P V(u): P (bf16) sits in the first 32 columns of S[w][u&1]
                 auto issue_PV = [&](int u) {
-                    const uint64_t bv = dv + (uint64_t)((((vg + u) % VS) * TILE) >> 4);
+                    const uint64_t bv = dv + (uint64_t)((((vg + (u >> 1)) % VS) * TILE + (u & 1) * HALF) >> 4);
+                    const uint32_t a = tS + (u & 1) * 64;
                     const uint32_t acc0 = u > 0 ? 1u : 0u;
 #pragma unroll
-                    for (int kk = 0; kk < 8; ++kk)
+                    for (int kk = 0; kk < 4; ++kk)
                         if (leader)
-                            mma_ts(tO, tS + kk * 8, bv + (uint64_t)((kk * 2048) >> 4), idesc_o, kk > 0 ? 1u : acc0);
+                            mma_ts(tO, a + kk * 8, bv + (uint64_t)((kk * 2048) >> 4), idesc_o, kk > 0 ? 1u : acc0);
                 };
+                auto last_use = [&](int u) { return (u & 1) || u == n_u - 1; };  // of a 128-key tile, by this Q tile
 
                 if (n_u > 0) {
                     ok = wait(&k_full[kg % KS], (uint32_t)(kg / KS) & 1u, kToKFull) &&
@@ -392,31 +447,46 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                     if (!ok) break;
                     tc_fence_after();
                     issue_S(0);
-                    commit(&s_full[w]);
+                    commit(&s_full[w * 2]);
+                    if (n_u > 1) {
+                        issue_S(1);
+                        commit(&s_full[w * 2 + 1]);
+                    }
                     commit(&ke[kg % KS]);
+                    int k_waited = 0, v_waited = -1;  // item-local tile indices already waited for
                     for (int u = 0; u < n_u && ok; ++u) {
-                        if (!wait(&v_full[(vg + u) % VS], (uint32_t)((vg + u) / VS) & 1u, kToVFull)) { ok = false; break; }
-                        if (!wait(&p_full[w], (uint32_t)(cp + u) & 1u, kToPFull)) { ok = false; break; }
+                        const int vt = u >> 1;
+                        if (vt > v_waited) {
+                            if (!wait(&v_full[(vg + vt) % VS], (uint32_t)((vg + vt) / VS) & 1u, kToVFull)) { ok = false; break; }
+                            v_waited = vt;
+                        }
+                        if (!wait(&p_full[w * 2 + (u & 1)], (uint32_t)(((u & 1) ? cp1 : cp0) + (u >> 1)) & 1u, kToPFull)) { ok = false; break; }
                         // the previous item's epilogue must have read O_w before it is overwritten
                         if (u == 0 && na > 0 && !wait(&o_free[w], (uint32_t)(na - 1) & 1u, kToOFree)) { ok = false; break; }
                         tc_fence_after();
                         issue_PV(u);
+                        commit(&o_full[w]);
                         if (u == n_u - 1) commit(&o_done[w]);
-                        commit(&ve[(vg + u) % VS]);
-                        if (u + 1 < n_u) {
-                            if (!wait(&k_full[(kg + u + 1) % KS], (uint32_t)((kg + u + 1) / KS) & 1u, kToKFull)) { ok = false; break; }
-                            tc_fence_after();
-                            issue_S(u + 1);
-                            commit(&s_full[w]);
-                            commit(&ke[(kg + u + 1) % KS]);
+                        if (last_use(u)) commit(&ve[(vg + vt) % VS]);
+                        if (u + 2 < n_u) {
+                            const int kt = (u + 2) >> 1;
+                            if (kt > k_waited) {
+                                if (!wait(&k_full[(kg + kt) % KS], (uint32_t)((kg + kt) / KS) & 1u, kToKFull)) { ok = false; break; }
+                                k_waited = kt;
+                                tc_fence_after();
+                            }
+                            issue_S(u + 2);
+                            commit(&s_full[w * 2 + (u & 1)]);
+                            if (last_use(u + 2)) commit(&ke[(kg + kt) % KS]);
                         }
                     }
                     ++na;
-                    cp += n_u;
+                    cp0 += (n_u + 1) / 2;
+                    cp1 += n_u / 2;
                 }
                 // Tiles this Q tile does not read (it sees fewer keys than the other one) are passed on
                 // once they have landed, which keeps this issuer inside the ring window.
-                for (int t = n_u; t < it.n_tiles && ok; ++t) {
+                for (int t = (n_u + 1) / 2; t < it.n_tiles && ok; ++t) {
                     ok = wait(&k_full[(kg + t) % KS], (uint32_t)((kg + t) / KS) & 1u, kToKFull);
                     if (ok) commit(&ke[(kg + t) % KS]);
                     ok = ok && wait(&v_full[(vg + t) % VS], (uint32_t)((vg + t) / VS) & 1u, kToVFull);
@@ -440,11 +510,12 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         const uint32_t tO = tmem_base + lane_sel + C::COL_O + w * D;
         const float c = p.scale_log2;
         int na = 0;            // items so far in which this tile took part
-        int cs = 0;            // s_full phases consumed before the item
+        int cs0 = 0, cs1 = 0;  // s_full phases of each S buffer consumed before the item
+        int co = 0;            // PV steps of this tile before the item (phase of o_full)
         bool ok = true;
 
         for (int j = 0; ok; ++j) {
-            const TcItem it = tc_item<kCausal>(j, p);
+            const TcItem it = tc_item<kCausal>(j, p, sched);
             if (it.end) break;
             if (!it.valid) continue;
             const int n_iter = it.steps(w);
@@ -467,45 +538,42 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             float l = 0.f;
             bool seen = false;  // the row has met a score that no mask hides
             for (int u = 0; u < n_iter; ++u) {
-                // S_w(u) is complete, and so is PV_w(u-1), which the same thread issued before it: O_w is at rest.
-                if (!__all_sync(kFullMask, mbar_wait(&s_full[w], (uint32_t)(cs + u) & 1u, p.status, kToSFull))) {
+                const int buf = u & 1;
+                if (!__all_sync(kFullMask, mbar_wait(&s_full[w * 2 + buf], (uint32_t)((buf ? cs1 : cs0) + (u >> 1)) & 1u,
+                                                     p.status, kToSFull))) {
                     ok = false;
                     break;
                 }
                 tc_fence_after();
 
-                uint32_t s[128];
+                uint32_t s[64];
                 {
                     uint32_t(&s0)[32] = *reinterpret_cast<uint32_t(*)[32]>(&s[0]);
                     uint32_t(&s1)[32] = *reinterpret_cast<uint32_t(*)[32]>(&s[32]);
-                    uint32_t(&s2)[32] = *reinterpret_cast<uint32_t(*)[32]>(&s[64]);
-                    uint32_t(&s3)[32] = *reinterpret_cast<uint32_t(*)[32]>(&s[96]);
-                    tmem_ld32(tS, s0);
-                    tmem_ld32(tS + 32, s1);
-                    tmem_ld32(tS + 64, s2);
-                    tmem_ld32(tS + 96, s3);
+                    tmem_ld32(tS + buf * 64, s0);
+                    tmem_ld32(tS + buf * 64 + 32, s1);
                     tc_wait_ld();
                 }
 
                 // ---- masks: keys beyond kv_hi, causal diagonal, keep flags
-                const int col0 = u * 128;
+                const int col0 = u * 64;
                 int lim = kv_hi - 1 - col0;                       // last visible column in this step
                 if (kCausal) lim = min(lim, row + q_off - col0);
-                if (lim < 127) {
+                if (lim < 63) {
 #pragma unroll
-                    for (int i = 0; i < 128; ++i)
+                    for (int i = 0; i < 64; ++i)
                         if (i > lim) s[i] = 0xff800000u;  // -inf
                 }
                 if (kKeep) {  // Mask::Padding keep flags (mask.rs:44); every thread reads the same bytes
 #pragma unroll
-                    for (int i = 0; i < 128; ++i)
+                    for (int i = 0; i < 64; ++i)
                         if (col0 + i < Nkv && __ldg(keep + col0 + i) == 0) s[i] = 0xff800000u;
                 }
 
                 // ---- row max (three-input max halves the instruction count)
                 float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
-                for (int i = 0; i < 128; i += 8) {
+                for (int i = 0; i < 64; i += 8) {
                     mx0 = max3(mx0, __uint_as_float(s[i]), __uint_as_float(s[i + 1]));
                     mx1 = max3(mx1, __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
                     mx2 = max3(mx2, __uint_as_float(s[i + 4]), __uint_as_float(s[i + 5]));
@@ -520,6 +588,14 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 } else {
                     const bool need = (mx > m_ref) && ((mx - m_ref) * c > 8.0f || m_ref == -INFINITY);
                     if (__any_sync(kFullMask, need)) {
+                        // O must be at rest: the PV of the previous step has to be complete.  (The score
+                        // MMA just waited for was issued after the PV before that one, so the barrier is
+                        // at most one phase behind and the parity wait is unambiguous.)
+                        if (!__all_sync(kFullMask, mbar_wait(&o_full[w], (uint32_t)(co + u - 1) & 1u, p.status, kToOFull))) {
+                            ok = false;
+                            break;
+                        }
+                        tc_fence_after();
                         const float m_new = fmaxf(m_ref, mx);
                         const float alpha = (m_new == -INFINITY) ? 1.f : fast_exp2((m_ref - m_new) * c);
                         l *= alpha;
@@ -542,7 +618,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 const float2 c2 = make_float2(c, c), nmc2 = make_float2(-mc, -mc);
                 float2 sum_a = make_float2(0.f, 0.f), sum_b = make_float2(0.f, 0.f);
 #pragma unroll
-                for (int ch = 0; ch < 4; ++ch) {
+                for (int ch = 0; ch < 2; ++ch) {
                     uint32_t pk[16];
 #pragma unroll
                     for (int i = 0; i < 16; i += 2) {
@@ -560,12 +636,12 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                         pk[i] = float2_to_bf16x2(pa.x, pa.y);
                         pk[i + 1] = float2_to_bf16x2(pb.x, pb.y);
                     }
-                    tmem_st16(tS + ch * 16, pk);
+                    tmem_st16(tS + buf * 64 + ch * 16, pk);
                 }
                 l += (sum_a.x + sum_a.y) + (sum_b.x + sum_b.y);
                 tc_wait_st();
                 tc_fence_before();
-                mbar_arrive(&p_full[w]);
+                mbar_arrive(&p_full[w * 2 + buf]);
             }
             if (!ok) break;
 
@@ -625,7 +701,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             }
             ok = __all_sync(kFullMask, ok);
             ++na;
-            cs += n_iter;
+            cs0 += (n_iter + 1) / 2;
+            cs1 += n_iter / 2;
+            co += n_iter;
         }
     }
 
@@ -798,6 +876,14 @@ cudaError_t launch_prefill_tc(const void* q, const void* k, const void* v, void*
     if (env_sched == 1) persistent = true;
     if (env_sched == 2) persistent = false;
     p.paired = (persistent && n_items >= 2 * (int64_t)n_sm) ? 1 : 0;
+    // Per-batch lengths: the length-sorted persistent schedule, if its table fits (tc_item).
+    p.sorted = 0;
+    if (kv_lens != nullptr && !p.single_tile && env_sched != 2 && n_items >= 2 * (int64_t)n_sm &&
+        batch * n_qb <= (dim == 128 ? TcCfg<128>::SCHED_CAP : TcCfg<64>::SCHED_CAP) && batch * n_qb <= 65535) {
+        p.sorted = 1;
+        p.paired = 0;
+        persistent = true;
+    }
     p.slots_per_head = p.paired ? (int)((n_qb + 1) / 2) : (int)n_qb;
     p.n_slots = (int)(bh * p.slots_per_head);
     const int64_t n_ctas = (persistent && p.n_slots > n_sm) ? n_sm : p.n_slots;

@@ -89,8 +89,23 @@ def _guard(name: str, t, dtype, like=None, shape=None):
 
 
 def _guard_decode_args(q, k_cache, v_cache, kv_lens=None, workspace=None):
-    """Shape / dtype / device checks shared by the decode wrappers; returns (B, Hq, Hkv, D, max_seq)."""
+    """Shape / dtype / device checks shared by the decode wrappers; returns (B, Hq, Hkv, D, max_seq).
+    One combined test on the hot path; the per-argument diagnosis only runs when it fails."""
     import torch
+    try:
+        B, Hq, D = q.shape
+        Bk, Hkv, max_seq, Dk = k_cache.shape
+        bf16, dev = torch.bfloat16, q.device
+        if (q.is_cuda and q.dtype is bf16 and k_cache.dtype is bf16 and v_cache.dtype is bf16 and k_cache.device == dev
+                and v_cache.device == dev and Bk == B and Dk == D and v_cache.shape == k_cache.shape
+                and q.is_contiguous() and k_cache.is_contiguous() and v_cache.is_contiguous()
+                and (kv_lens is None or (kv_lens.dtype is torch.int32 and kv_lens.device == dev
+                                         and kv_lens.shape == (B,) and kv_lens.is_contiguous()))
+                and (workspace is None or (workspace.dtype is torch.uint8 and workspace.device == dev
+                                           and workspace.is_contiguous()))):
+            return B, Hq, Hkv, D, max_seq
+    except (AttributeError, ValueError, TypeError):
+        pass
     _guard("q", q, torch.bfloat16)
     if q.dim() != 3:
         raise TypeError(f"q must be [B, Hq, D], got {tuple(q.shape)}")
@@ -103,7 +118,7 @@ def _guard_decode_args(q, k_cache, v_cache, kv_lens=None, workspace=None):
         _guard("kv_lens", kv_lens, torch.int32, like=q, shape=(B,))
     if workspace is not None:
         _guard("workspace", workspace, torch.uint8, like=q)
-    return B, Hq, k_cache.shape[1], D, k_cache.shape[2]
+    raise TypeError("decode arguments are inconsistent")
 
 
 def decode_workspace_bytes(batch: int, n_heads: int, n_kv_heads: int, head_dim: int, max_seq: int) -> int:
@@ -168,12 +183,12 @@ _default_ws = {}
 _ws_bytes_cache: dict = {}
 
 
-def _implicit_workspace(device, nbytes: int):
+def _implicit_workspace(device, nbytes: int, stream: Optional[int] = None):
     """The split-KV scratch used when the caller passes no ``workspace=``: one buffer per (device, CUDA
     stream, size).  Two decodes of equal shape on different streams therefore never share chunk partials
     and completion counters; calls on ONE stream run in order and may share them."""
     import torch
-    key = (device.index, torch.cuda.current_stream(device).cuda_stream, nbytes)
+    key = (device.index, stream if stream is not None else torch.cuda.current_stream(device).cuda_stream, nbytes)
     ws = _default_ws.get(key)
     if ws is None:
         ws = _default_ws[key] = torch.empty(nbytes, dtype=torch.uint8, device=device)
@@ -207,8 +222,9 @@ def gqa_decode(q, k_cache, v_cache, kv_lens=None, kv_len: Optional[int] = None, 
     need = _ws_bytes_cache.get(key)
     if need is None:
         need = _ws_bytes_cache[key] = decode_workspace_bytes(B, Hq, Hkv, D, max_seq)
+    stream = torch.cuda.current_stream(q.device).cuda_stream
     if workspace is None and need:
-        workspace = _implicit_workspace(q.device, need)
+        workspace = _implicit_workspace(q.device, need, stream)
     rc = _lib.lib().rt_gqa_decode_bf16(
         q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
         out.data_ptr() if out_dtype == torch.bfloat16 else None,
@@ -216,10 +232,11 @@ def gqa_decode(q, k_cache, v_cache, kv_lens=None, kv_len: Optional[int] = None, 
         lse.data_ptr() if lse is not None else None, B, Hq, Hkv, D, max_seq,
         kv_lens.data_ptr() if kv_lens is not None else None, 0 if kv_len is None else int(kv_len), kv_begin, kv_end,
         -1.0 if scale is None else float(scale), workspace.data_ptr() if workspace is not None else None,
-        workspace.numel() if workspace is not None else 0, _stream_ptr())
+        workspace.numel() if workspace is not None else 0, stream)
     if rc == _lib.RT_ERR_HEAD_COUNT:
         raise HeadCountMismatch(Hq, Hkv)
-    _lib.check(rc, "rt_gqa_decode_bf16")
+    if rc:
+        _lib.check(rc, "rt_gqa_decode_bf16")
     return out, lse
 
 

@@ -97,6 +97,8 @@ class PeerRecordExchange:
         self.flag_ptrs = list(flag_ptrs)      # base address of every rank's `flags`
         self.epoch = 0
         self._done = None  # device int32, zero between calls (used by decode_push)
+        self.row_flags = None      # local int32 [2, world, rows]: one flag per (rank, row), for decode_exchange
+        self.row_flag_ptrs = None  # base address of every rank's `row_flags'
         if (rows * (dim + 1)) % 4:
             raise ValueError("rows * (dim + 1) must be a multiple of 4 (16-byte copies)")
 
@@ -116,8 +118,14 @@ class PeerRecordExchange:
         h_flag = symm.rendezvous(flags, group.group_name)
         torch.cuda.synchronize()
         dist.barrier(group)  # every rank's flags are zero before anyone pushes
+        row_flags = symm.empty((2, world, rows), dtype=torch.int32, device=device)
+        row_flags.zero_()
+        h_rows = symm.rendezvous(row_flags, group.group_name)
+        torch.cuda.synchronize()
+        dist.barrier(group)
         ex = cls(rank, world, rows, dim, records, flags, h_rec.buffer_ptrs, h_flag.buffer_ptrs)
-        ex._handles = (h_rec, h_flag)  # keep the mappings alive
+        ex.row_flags, ex.row_flag_ptrs = row_flags, list(h_rows.buffer_ptrs)
+        ex._handles = (h_rec, h_flag, h_rows)  # keep the mappings alive
         return ex
 
     @classmethod
@@ -126,8 +134,12 @@ class PeerRecordExchange:
         import torch
         recs = [torch.zeros((2, world, rows, dim + 1), dtype=torch.float32, device=device) for _ in range(world)]
         flgs = [torch.zeros((2, world), dtype=torch.int32, device=device) for _ in range(world)]
-        return [cls(r, world, rows, dim, recs[r], flgs[r], [t.data_ptr() for t in recs], [t.data_ptr() for t in flgs])
-                for r in range(world)]
+        rowf = [torch.zeros((2, world, rows), dtype=torch.int32, device=device) for _ in range(world)]
+        out = [cls(r, world, rows, dim, recs[r], flgs[r], [t.data_ptr() for t in recs], [t.data_ptr() for t in flgs])
+               for r in range(world)]
+        for r, ex in enumerate(out):
+            ex.row_flags, ex.row_flag_ptrs = rowf[r], [t.data_ptr() for t in rowf]
+        return out
 
     def next_epoch(self):
         """Advances the epoch; returns the slot (a [rows, D+1] view of local memory) that this rank's
@@ -170,6 +182,60 @@ class PeerRecordExchange:
             workspace.numel() if workspace is not None else 0, _stream_ptr())
         _lib.check(rc, "rt_gqa_decode_record_push_bf16")
         return record
+
+    def decode_exchange(self, q, k_cache, v_cache, kv_lens=None, kv_len=None, kv_begin: int = 0, kv_end: int = -1,
+                        scale=None, workspace=None, out_dtype=None, wait: bool = True, wait_clocks: int = 0):
+        """One exchange in two launches (``rt_gqa_decode_exchange_bf16``): the decode kernel over this rank's KV
+        shard, then ONE kernel that merges its chunk partials row by row, delivers each row to every rank, waits
+        for the same row from every rank and merges them.  Returns (out [rows, D], lse [rows]).  With
+        ``wait=False`` the second kernel stops after the delivery and ``merge_rows()`` finishes the step (for
+        several ranks emulated on one GPU, where no kernel may wait for a later launch of the same GPU)."""
+        import ctypes
+        import torch
+        from . import _lib
+        from .gqa import _guard_decode_args, _stream_ptr, decode_workspace_bytes
+        B, Hq, Hkv, D, max_seq = _guard_decode_args(q, k_cache, v_cache, kv_lens, workspace)
+        need = decode_workspace_bytes(B, Hq, Hkv, D, max_seq)
+        if workspace is None and need:
+            workspace = getattr(self, "_ws", None)
+            if workspace is None or workspace.numel() < need:
+                workspace = self._ws = torch.empty(need, dtype=torch.uint8, device=q.device)
+        self.epoch += 1
+        par = self.epoch & 1
+        rec_bytes = self.rows * (self.dim + 1) * 4
+        slot_off = (par * self.world + self.rank) * rec_bytes
+        flag_off = (par * self.world + self.rank) * self.rows * 4
+        slots = (ctypes.c_void_p * self.world)(*[p + slot_off for p in self.record_ptrs])
+        flags = (ctypes.c_void_p * self.world)(*[p + flag_off for p in self.row_flag_ptrs])
+        out_dtype = out_dtype or torch.bfloat16
+        out = torch.empty((self.rows, self.dim), dtype=out_dtype, device=q.device)
+        lse = torch.empty((self.rows,), dtype=torch.float32, device=q.device)
+        rc = _lib.lib().rt_gqa_decode_exchange_bf16(
+            q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+            out.data_ptr() if out_dtype == torch.bfloat16 else None, out.data_ptr() if out_dtype == torch.float32 else None,
+            lse.data_ptr(), slots, flags, self.records[par].data_ptr(), self.row_flags[par].data_ptr(), self.world,
+            self.rank, self.epoch, wait_clocks, 1 if wait else 0, B, Hq, Hkv, D, max_seq,
+            kv_lens.data_ptr() if kv_lens is not None else None, 0 if kv_len is None else int(kv_len), kv_begin, kv_end,
+            -1.0 if scale is None else float(scale), workspace.data_ptr() if workspace is not None else None,
+            workspace.numel() if workspace is not None else 0, _stream_ptr())
+        _lib.check(rc, "rt_gqa_decode_exchange_bf16")
+        return out, lse
+
+    def merge_rows(self, out_dtype=None, wait_clocks: int = 0):
+        """Second half of ``decode_exchange(wait=False)``: waits per row for every rank's row, then merges."""
+        import torch
+        from . import _lib
+        from .gqa import _stream_ptr
+        par = self.epoch & 1
+        out_dtype = out_dtype or torch.bfloat16
+        out = torch.empty((self.rows, self.dim), dtype=out_dtype, device=self.records.device)
+        lse = torch.empty((self.rows,), dtype=torch.float32, device=self.records.device)
+        rc = _lib.lib().rt_attn_merge_records_after_rows(
+            self.records[par].data_ptr(), self.row_flags[par].data_ptr(), self.epoch, wait_clocks, self.world, self.rows,
+            self.dim, out.data_ptr() if out_dtype == torch.bfloat16 else None,
+            out.data_ptr() if out_dtype == torch.float32 else None, lse.data_ptr(), _stream_ptr())
+        _lib.check(rc, "rt_attn_merge_records_after_rows")
+        return out, lse
 
     def push(self):
         import ctypes

@@ -44,12 +44,18 @@ def _worker(rank, world, port, tmpdir):
             torch.cuda.synchronize()
             assert _lib.device_status() == 0
             assert torch.equal(got, want) and torch.equal(got_lse, want_lse)
-            # the same with the record delivered from inside the merge kernel
+            # the same with the record delivered from inside the decode kernel
             ex.decode_push(q, k, v, kv_len=T, kv_begin=lo, kv_end=hi)
             got2, got2_lse = ex.merge(out_dtype=torch.float32)
             torch.cuda.synchronize()
             assert _lib.device_status() == 0
-            assert torch.equal(got2, want) and torch.equal(got2_lse, want_lse)
+            # (that launch merges its chunks in the decode kernel: the same partials in another summation order)
+            assert (got2 - want).abs().max().item() < 1e-5 and (got2_lse - want_lse).abs().max().item() < 1e-5
+            # and with the whole tail in one kernel: chunk merge, row delivery, per-row wait, cross-rank merge
+            got3, got3_lse = ex.decode_exchange(q, k, v, kv_len=T, kv_begin=lo, kv_end=hi, out_dtype=torch.float32)
+            torch.cuda.synchronize()
+            assert _lib.device_status() == 0
+            assert (got3 - want).abs().max().item() < 1e-5 and (got3_lse - want_lse).abs().max().item() < 1e-5
             assert (got - full.reshape(Hq, D)).abs().max().item() < 1e-3
             assert (got_lse - full_lse.reshape(Hq)).abs().max().item() < 1e-4
         dist.barrier()
