@@ -16,7 +16,7 @@ import sys
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_PATH = os.path.join(PKG_DIR, "librustorch_attn.so")
-SOURCES = ["api.cu", "decode.cu", "decode_tc.cu", "prefill_simt.cu", "prefill_tc.cu", "tc_selftest.cu", "decode_static.cu", "backward_simt.cu", "backward_tc.cu"]
+SOURCES = ["api.cu", "decode.cu", "decode_tc.cu", "prefill_simt.cu", "prefill_tc.cu", "tc_selftest.cu", "decode_static.cu", "backward_simt.cu", "backward_tc.cu", "backward_tcgen05.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

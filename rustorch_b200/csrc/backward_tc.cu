@@ -16,6 +16,8 @@
 // rounds P.  No atomics; a causal launch skips the tiles beyond the diagonal.
 // The other side's tiles travel global -> 128-byte-swizzled shared memory with cp.async into two
 // stages, so the loads of tile t+1 overlap the MMAs of tile t.
+#include <cstdlib>
+
 #include "common.cuh"
 #include "kernels.h"
 #include "mma_sync.cuh"
@@ -294,6 +296,16 @@ cudaError_t launch_backward_bf16(const void* q, const void* k, const void* v, co
                                                                           (const __nv_bfloat16*)d_out, delta_ws, rows, dim);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
+    // The tcgen05 / TMEM / TMA kernel (backward_tcgen05.cu) is the path; RT_ATTN_BACKWARD_IMPL=mma_sync keeps
+    // this file's mma.sync kernel for comparisons, and it also serves shapes the other one does not cover.
+    static const bool legacy = [] {
+        const char* s = getenv("RT_ATTN_BACKWARD_IMPL");
+        return s && s[0] == 'm';
+    }();
+    if (!legacy) {
+        e = launch_backward_tcgen05(q, k, v, d_out, lse, delta_ws, dq, dk, dv, batch, heads, seq, dim, causal, scale, stream);
+        if (e != cudaErrorNotSupported) return e;
+    }
     BwdTcParams p{(const __nv_bfloat16*)q, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v,
                   (const __nv_bfloat16*)d_out, lse, delta_ws, dq, dk, dv, seq, causal, scale, scale * kLog2e};
     if (dim == 128) return launch_bwd_tc<128>(p, bh, stream);

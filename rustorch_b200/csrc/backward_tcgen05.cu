@@ -1,0 +1,378 @@
+// bf16 flash-attention backward on the Blackwell tensor cores (tcgen05 + TMEM + TMA).
+//
+// Same math as rustorch_attention::flash_backward (crates/rustorch-attention/src/cpu_backward.rs:16-27,
+// 96-189) with the saved row statistics in place of the N x N probability matrix:
+//   P = exp(scale * Q K^T - LSE),  dP = dO V^T,  dS = P o (dP - delta),  delta_i = dO_i . O_i,
+//   dV = P^T dO,  dQ = scale * dS K,  dK = scale * dS^T Q.
+// Two deterministic passes (no atomics, fixed summation order) share one kernel template.  A CTA owns
+// 128 rows of one side, keeps them in shared memory, and walks the 128-row tiles of the other side that
+// TMA streams through a two-stage ring:
+//   query side: own X1 = Q_i, X2 = dO_i;  per key tile (Y1 = K_j, Y2 = V_j)
+//               T1 = Q K^T, T2 = dO V^T (SS MMAs into TMEM) -> dS (bf16, back into TMEM) -> dQ += dS K_j (TS MMA)
+//   key side:   own X1 = K_j, X2 = V_j;   per query tile (Y1 = Q_i, Y2 = dO_i)
+//               T1 = K Q^T = S^T, T2 = V dO^T = dP^T -> P^T, dS^T (bf16, into TMEM)
+//               -> dV += P^T dO_i, dK += dS^T Q_i (TS MMAs)
+// Every product is "own rows x other tile": the score-like ones take both operands K-major from
+// 128-byte-swizzled shared memory, the accumulating ones take A from TMEM and the other tile MN-major,
+// exactly as TMA lands it (the forward's P V product has the same shape).  The thread that owns TMEM lane
+// r owns own-row r: on the query side the statistics (LSE_i, delta_i) are per thread, on the key side
+// they belong to the columns and are staged in shared memory per tile.  P and dS are rounded to bf16 for
+// the accumulating products, as the forward rounds P.  A causal launch skips the tiles beyond the diagonal.
+// TMEM (512 columns): T1 [0,128), T2 [128,256), accumulators from 256 (dQ, or dV then dK), D columns each;
+// P^T / dS overwrite the first 64 columns of T1 / T2.  192 threads: warps 0-3 element-wise work and the
+// final read-out (one thread per own row), warp 4 TMA producer, warp 5 TMEM allocation and MMA issue.
+// Every mbarrier wait is bounded; on expiry the kernel records a code in the device status word and
+// leaves through the common teardown.
+#include <cuda.h>
+
+#include "kernels.h"
+#include "tc_ptx.cuh"
+
+namespace rt {
+
+using namespace ptx;
+
+bool make_tensor_map_bf16_4d(CUtensorMap* map, const void* base, int64_t batch, int64_t heads, int64_t seq, int dim,
+                             int64_t stride_b, int64_t stride_h, int64_t stride_row);  // prefill_tc.cu
+
+namespace {
+
+enum { kToBwdX = 201, kToBwdYFull, kToBwdYEmpty, kToBwdT, kToBwdA, kToBwdAcc, kToBwdDrain, kToBwdStat };
+
+template <int D>
+struct BwdCfg {
+    static constexpr int TILE_BYTES = 128 * D * 2;
+    static constexpr int SUB_BYTES = 128 * 64 * 2;  // one 64-column (128-byte) swizzled sub-tile
+    static constexpr int NSUB = D / 64;
+    static constexpr int STAGES = 2;
+    static constexpr int NBARS = 1 + 2 * STAGES + 4;
+    static constexpr int STAT_BYTES = STAGES * 2 * 128 * 4;  // per stage: LSE * log2(e) and delta of the other tile
+    static constexpr int SMEM_BYTES = (2 + 2 * STAGES) * TILE_BYTES + STAT_BYTES + NBARS * 8 + 16 + 1024;
+    static constexpr uint32_t COL_T1 = 0, COL_T2 = 128, COL_ACC = 256;
+};
+
+struct Bwd5Params {
+    const float* lse;    // [B*H, N]
+    const float* delta;  // [B*H, N]
+    float* out1;         // query side: dQ; key side: dV   ([B*H, N, D] f32)
+    float* out2;         // key side: dK
+    int seq, heads;
+    int causal;
+    float scale, scale_log2;
+    int* status;
+};
+
+template <int D, bool kKeySide>
+__global__ void __launch_bounds__(192, 1)
+bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_constant__ CUtensorMap tm_x2,
+                   const __grid_constant__ CUtensorMap tm_y1, const __grid_constant__ CUtensorMap tm_y2,
+                   const Bwd5Params p) {
+    using C = BwdCfg<D>;
+    constexpr int TILE = C::TILE_BYTES, SUB = C::SUB_BYTES, STAGES = C::STAGES;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* sX1 = smem;
+    uint8_t* sX2 = sX1 + TILE;
+    uint8_t* sY = sX2 + TILE;  // [STAGES][Y1 | Y2]
+    float* stat = reinterpret_cast<float*>(sY + STAGES * 2 * TILE);  // [STAGES][lse2[128] | delta[128]]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(stat) + C::STAT_BYTES);
+    uint64_t* x_full = bars;                // [1]
+    uint64_t* y_full = x_full + 1;          // [STAGES]
+    uint64_t* y_empty = y_full + STAGES;    // [STAGES]
+    uint64_t* t_full = y_empty + STAGES;    // [1] one phase per step: T1, T2 are in TMEM
+    uint64_t* a_full = t_full + 1;          // [1] one phase per step: the bf16 A operands are in TMEM
+    uint64_t* acc_done = a_full + 1;        // [1] the last accumulating MMA has retired
+    uint64_t* stat_bar = acc_done + 1;      // [1] one phase per step: the column statistics are in shared memory
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(stat_bar + 1);
+
+    const int warp = __shfl_sync(kFullMask, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
+    const int N = p.seq;
+    const int n_tiles = (N + 127) / 128;
+    // heaviest tiles first: under a causal mask the query side's last tiles and the key side's first tiles
+    // walk the most other-side tiles
+    const int own = kKeySide ? (int)blockIdx.x : (p.causal ? n_tiles - 1 - (int)blockIdx.x : (int)blockIdx.x);
+    const int bh = blockIdx.y, b = bh / p.heads, h = bh % p.heads;
+    const int own0 = own * 128;
+    // other-side tiles [t_lo, t_hi)
+    const int t_lo = (kKeySide && p.causal) ? own : 0;
+    const int t_hi = (!kKeySide && p.causal) ? own + 1 : n_tiles;
+    const int n_steps = t_hi - t_lo;
+
+    if (warp == 4 && lane == 0) {
+        prefetch_tensormap(&tm_x1);
+        prefetch_tensormap(&tm_x2);
+        prefetch_tensormap(&tm_y1);
+        prefetch_tensormap(&tm_y2);
+        mbar_init(x_full, 1);
+        for (int i = 0; i < STAGES; ++i) {
+            mbar_init(&y_full[i], 1);
+            mbar_init(&y_empty[i], 1);
+        }
+        mbar_init(t_full, 1);
+        mbar_init(a_full, 128);
+        mbar_init(acc_done, 1);
+        mbar_init(stat_bar, 128);
+        fence_barrier_init();
+        fence_proxy_async();
+    }
+    if (warp == 5) {
+        tmem_alloc(tmem_slot, 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 4) {
+        // ============================================================== TMA producer
+        if (lane == 0) {
+            mbar_arrive_expect_tx(x_full, 2 * TILE);
+#pragma unroll
+            for (int s = 0; s < C::NSUB; ++s) {
+                tma_load_4d(sX1 + s * SUB, &tm_x1, x_full, s * 64, own0, h, b);
+                tma_load_4d(sX2 + s * SUB, &tm_x2, x_full, s * 64, own0, h, b);
+            }
+            int issued = 0;
+            for (int t = 0; t < n_steps; ++t) {
+                const int st = t % STAGES;
+                if (t >= STAGES && !mbar_wait(&y_empty[st], (uint32_t)(t / STAGES - 1) & 1u, p.status, kToBwdYEmpty)) break;
+                mbar_arrive_expect_tx(&y_full[st], 2 * TILE);
+                uint8_t* dst = sY + st * 2 * TILE;
+                const int r0 = (t_lo + t) * 128;
+#pragma unroll
+                for (int s = 0; s < C::NSUB; ++s) {
+                    tma_load_4d(dst + s * SUB, &tm_y1, &y_full[st], s * 64, r0, h, b);
+                    tma_load_4d(dst + TILE + s * SUB, &tm_y2, &y_full[st], s * 64, r0, h, b);
+                }
+                issued = t + 1;
+            }
+            // Drain: every copy this thread issued must have landed before the CTA may exit.
+            mbar_wait(x_full, 0, p.status, kToBwdDrain);
+            for (int t = max(0, issued - STAGES); t < issued; ++t)
+                mbar_wait(&y_full[t % STAGES], (uint32_t)(t / STAGES) & 1u, p.status, kToBwdDrain);
+        }
+    } else if (warp == 5) {
+        // ============================================================== MMA issuer
+        const bool leader = elect_one();
+        constexpr uint32_t idesc_t = make_idesc_bf16(128, 128, 0, 0);
+        constexpr uint32_t idesc_a = make_idesc_bf16(128, D, 0, 1);
+        const uint64_t dx1 = make_smem_desc_sw128(smem_u32(sX1), 16, 1024);
+        const uint64_t dx2 = make_smem_desc_sw128(smem_u32(sX2), 16, 1024);
+        const uint64_t dy_k = make_smem_desc_sw128(smem_u32(sY), 16, 1024);    // other tile as a K-major operand
+        const uint64_t dy_mn = make_smem_desc_sw128(smem_u32(sY), SUB, 1024);  // the same tile as an MN-major operand
+        const uint32_t tT1 = tmem_base + C::COL_T1, tT2 = tmem_base + C::COL_T2, tAcc = tmem_base + C::COL_ACC;
+        auto commit = [&](uint64_t* bar) {
+            if (leader) mma_commit(bar);
+        };
+        auto wait = [&](uint64_t* bar, uint32_t parity, int code) {
+            return __all_sync(kFullMask, mbar_wait(bar, parity, p.status, code));
+        };
+        bool ok = wait(x_full, 0, kToBwdX);
+        for (int t = 0; t < n_steps && ok; ++t) {
+            const int st = t % STAGES;
+            if (!wait(&y_full[st], (uint32_t)(t / STAGES) & 1u, kToBwdYFull)) break;
+            tc_fence_after();
+            const uint64_t y1_k = dy_k + (uint64_t)((st * 2 * TILE) >> 4), y2_k = y1_k + (uint64_t)(TILE >> 4);
+            const uint64_t y1_mn = dy_mn + (uint64_t)((st * 2 * TILE) >> 4), y2_mn = y1_mn + (uint64_t)(TILE >> 4);
+            // T1 = X1 Y1^T, T2 = X2 Y2^T (these overwrite last step's A operands: the pipe runs this thread's
+            // MMAs in issue order, after the accumulating MMAs that read them)
+#pragma unroll
+            for (int kk = 0; kk < D / 16; ++kk) {
+                const uint32_t off = (uint32_t)(((kk / 4) * SUB + (kk % 4) * 32) >> 4);
+                if (leader) mma_ss(tT1, dx1 + off, y1_k + off, idesc_t, kk > 0);
+            }
+#pragma unroll
+            for (int kk = 0; kk < D / 16; ++kk) {
+                const uint32_t off = (uint32_t)(((kk / 4) * SUB + (kk % 4) * 32) >> 4);
+                if (leader) mma_ss(tT2, dx2 + off, y2_k + off, idesc_t, kk > 0);
+            }
+            commit(t_full);
+            if (!wait(a_full, (uint32_t)t & 1u, kToBwdA)) break;
+            tc_fence_after();
+            const uint32_t acc0 = t > 0 ? 1u : 0u;
+            if (kKeySide) {
+                // dV += P^T dO (A = P^T in the first 64 columns of T1, B = Y2 = dO), dK += dS^T Q (A in T2, B = Y1 = Q)
+#pragma unroll
+                for (int kk = 0; kk < 8; ++kk)
+                    if (leader) mma_ts(tAcc, tT1 + kk * 8, y2_mn + (uint64_t)((kk * 2048) >> 4), idesc_a, kk > 0 ? 1u : acc0);
+#pragma unroll
+                for (int kk = 0; kk < 8; ++kk)
+                    if (leader) mma_ts(tAcc + D, tT2 + kk * 8, y1_mn + (uint64_t)((kk * 2048) >> 4), idesc_a, kk > 0 ? 1u : acc0);
+            } else {
+                // dQ += dS K (A = dS in the first 64 columns of T2, B = Y1 = K)
+#pragma unroll
+                for (int kk = 0; kk < 8; ++kk)
+                    if (leader) mma_ts(tAcc, tT2 + kk * 8, y1_mn + (uint64_t)((kk * 2048) >> 4), idesc_a, kk > 0 ? 1u : acc0);
+            }
+            commit(&y_empty[st]);
+            if (t == n_steps - 1) commit(acc_done);
+        }
+        // every MMA issued above must retire before TMEM is freed: acc_done (or, after a failed wait, a fresh
+        // commit) covers them
+        if (n_steps == 0) commit(acc_done);
+    } else {
+        // ============================================================== element-wise warps (one thread per own row)
+        const int r = warp * 32 + lane;
+        const int own_row = own0 + r;
+        const uint32_t lane_sel = (uint32_t)(warp * 32) << 16;
+        const uint32_t tT1 = tmem_base + lane_sel + C::COL_T1, tT2 = tmem_base + lane_sel + C::COL_T2;
+        const uint32_t tAcc = tmem_base + lane_sel + C::COL_ACC;
+        const float c = p.scale_log2;
+        const int64_t stat_base = (int64_t)bh * N;
+        float my_lse2 = 0.f, my_delta = 0.f;  // query side: this row's statistics
+        if (!kKeySide && own_row < N) {
+            my_lse2 = p.lse[stat_base + own_row] * kLog2e;
+            my_delta = p.delta[stat_base + own_row];
+        }
+        bool ok = true;
+        for (int t = 0; t < n_steps && ok; ++t) {
+            const int st = t % STAGES;
+            const int other0 = (t_lo + t) * 128;
+            float* s_lse2 = stat + st * 256;
+            float* s_delta = s_lse2 + 128;
+            if (kKeySide) {
+                // the statistics of this step's query tile (columns); the slot was last read two steps ago, and
+                // every thread has passed the a_full arrival of that step's successor by now
+                const int qi = other0 + r;
+                s_lse2[r] = qi < N ? p.lse[stat_base + qi] * kLog2e : INFINITY;  // +inf -> P = 0
+                s_delta[r] = qi < N ? p.delta[stat_base + qi] : 0.f;
+                mbar_arrive(stat_bar);  // an mbarrier rather than bar.sync, so that this wait is bounded as well
+                if (!__all_sync(kFullMask, mbar_wait(stat_bar, (uint32_t)t & 1u, p.status, kToBwdStat))) {
+                    ok = false;
+                    break;
+                }
+            }
+            if (!__all_sync(kFullMask, mbar_wait(t_full, (uint32_t)t & 1u, p.status, kToBwdT))) {
+                ok = false;
+                break;
+            }
+            tc_fence_after();
+            // Is any (own row, other index) pair of this tile masked?  Only the diagonal tile of a causal
+            // launch and the last tile of a ragged sequence are.
+            const bool diag = p.causal && other0 == own0;
+            const bool ragged = other0 + 128 > N;
+#pragma unroll
+            for (int ch = 0; ch < 4; ++ch) {
+                uint32_t a1[32], a2[32];
+                tmem_ld32(tT1 + ch * 32, a1);
+                tmem_ld32(tT2 + ch * 32, a2);
+                tc_wait_ld();
+                uint32_t pk_p[16], pk_ds[16];
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    float pv[2], dsv[2];
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const int col = ch * 32 + i + e;
+                        const float lse2 = kKeySide ? s_lse2[col] : my_lse2;
+                        const float dl = kKeySide ? s_delta[col] : my_delta;
+                        float pe = fast_exp2(fmaf(__uint_as_float(a1[i + e]), c, -lse2));
+                        if (diag || ragged) {
+                            const int other = other0 + col;
+                            const bool hidden = other >= N || (p.causal && (kKeySide ? own_row > other : other > own_row));
+                            if (hidden) pe = 0.f;
+                        }
+                        if (!(lse2 < INFINITY) || !(lse2 > -INFINITY)) pe = 0.f;  // rows without any visible key
+                        pv[e] = pe;
+                        dsv[e] = pe * (__uint_as_float(a2[i + e]) - dl);
+                    }
+                    pk_p[i / 2] = float2_to_bf16x2(pv[0], pv[1]);
+                    pk_ds[i / 2] = float2_to_bf16x2(dsv[0], dsv[1]);
+                }
+                // chunk ch's bf16 values land in columns [16 ch, 16 ch + 16), which chunks 0 .. ch/2 covered: loaded already
+                if (kKeySide) tmem_st16(tT1 + ch * 16, pk_p);
+                tmem_st16(tT2 + ch * 16, pk_ds);
+            }
+            tc_wait_st();
+            tc_fence_before();
+            mbar_arrive(a_full);
+        }
+        // ---- read-out: accumulators -> f32 global (scale folded into dQ and dK)
+        if (ok && __all_sync(kFullMask, mbar_wait(acc_done, 0, p.status, kToBwdAcc))) {
+            tc_fence_after();
+            constexpr int kOuts = kKeySide ? 2 : 1;
+#pragma unroll
+            for (int o = 0; o < kOuts; ++o) {
+                float* dst = (o == 0 ? p.out1 : p.out2) + ((int64_t)bh * N + own_row) * D;
+                const float mul = (kKeySide && o == 0) ? 1.f : p.scale;  // dV is not scaled
+#pragma unroll
+                for (int ch = 0; ch < D / 32; ++ch) {
+                    uint32_t a[32];
+                    if (n_steps > 0) {
+                        tmem_ld32(tAcc + o * D + ch * 32, a);
+                        tc_wait_ld();
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) a[i] = 0u;
+                    }
+                    if (own_row < N) {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 4)
+                            *reinterpret_cast<float4*>(dst + ch * 32 + i) =
+                                make_float4(__uint_as_float(a[i]) * mul, __uint_as_float(a[i + 1]) * mul,
+                                            __uint_as_float(a[i + 2]) * mul, __uint_as_float(a[i + 3]) * mul);
+                    }
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 5) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+template <int D, bool kKeySide>
+cudaError_t launch_side(const CUtensorMap& x1, const CUtensorMap& x2, const CUtensorMap& y1, const CUtensorMap& y2,
+                        const Bwd5Params& p, int64_t bh, cudaStream_t stream) {
+    cudaError_t e = set_max_dynamic_smem_once<bwd_tcgen05_kernel<D, kKeySide>>(BwdCfg<D>::SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    dim3 grid((unsigned)((p.seq + 127) / 128), (unsigned)bh);
+    bwd_tcgen05_kernel<D, kKeySide><<<grid, 192, BwdCfg<D>::SMEM_BYTES, stream>>>(x1, x2, y1, y2, p);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+// Returns cudaErrorNotSupported when this kernel does not cover the shape (the caller then uses the
+// mma.sync kernel).
+cudaError_t launch_backward_tcgen05(const void* q, const void* k, const void* v, const void* d_out, const float* lse,
+                                    const float* delta, float* dq, float* dk, float* dv, int64_t batch, int64_t heads,
+                                    int64_t seq, int dim, int causal, float scale, cudaStream_t stream) {
+    const int64_t bh = batch * heads;
+    if ((dim != 64 && dim != 128) || bh > 65535 || seq > (1 << 30)) return cudaErrorNotSupported;
+    CUtensorMap mq, mk, mv, mdo;
+    const TensorStrides s = TensorStrides::contiguous(heads, seq, dim);
+    if (!make_tensor_map_bf16_4d(&mq, q, batch, heads, seq, dim, s.batch, s.head, s.row) ||
+        !make_tensor_map_bf16_4d(&mk, k, batch, heads, seq, dim, s.batch, s.head, s.row) ||
+        !make_tensor_map_bf16_4d(&mv, v, batch, heads, seq, dim, s.batch, s.head, s.row) ||
+        !make_tensor_map_bf16_4d(&mdo, d_out, batch, heads, seq, dim, s.batch, s.head, s.row))
+        return cudaErrorNotSupported;
+    Bwd5Params p;
+    p.lse = lse;
+    p.delta = delta;
+    p.seq = (int)seq;
+    p.heads = (int)heads;
+    p.causal = causal;
+    p.scale = scale;
+    p.scale_log2 = scale * kLog2e;
+    p.status = device_status_ptr();
+    if (!p.status) return cudaErrorInvalidSymbol;
+    // query side: own (Q, dO), other (K, V) -> dQ
+    p.out1 = dq;
+    p.out2 = nullptr;
+    cudaError_t e = dim == 128 ? launch_side<128, false>(mq, mdo, mk, mv, p, bh, stream)
+                               : launch_side<64, false>(mq, mdo, mk, mv, p, bh, stream);
+    if (e != cudaSuccess) return e;
+    // key side: own (K, V), other (Q, dO) -> dV, dK
+    p.out1 = dv;
+    p.out2 = dk;
+    return dim == 128 ? launch_side<128, true>(mk, mv, mq, mdo, p, bh, stream)
+                      : launch_side<64, true>(mk, mv, mq, mdo, p, bh, stream);
+}
+
+}  // namespace rt

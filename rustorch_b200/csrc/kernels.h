@@ -116,6 +116,11 @@ cudaError_t launch_backward_bf16(const void* q, const void* k, const void* v, co
                                  const float* lse, float* dq, float* dk, float* dv, float* delta_ws, int64_t batch,
                                  int64_t heads, int64_t seq, int dim, int causal, float scale, cudaStream_t stream);
 
+// ---- backward_tcgen05.cu (tcgen05 / TMEM / TMA); cudaErrorNotSupported = shape not covered
+cudaError_t launch_backward_tcgen05(const void* q, const void* k, const void* v, const void* d_out, const float* lse,
+                                    const float* delta, float* dq, float* dk, float* dv, int64_t batch, int64_t heads,
+                                    int64_t seq, int dim, int causal, float scale, cudaStream_t stream);
+
 // ---- prefill_tc.cu (tcgen05 / TMEM / TMA)
 // Element strides of a [B, H, N, D] view whose inner dim is contiguous.
 struct TensorStrides {
