@@ -18,9 +18,13 @@
 // r owns own-row r: on the query side the statistics (LSE_i, delta_i) are per thread, on the key side
 // they belong to the columns and are staged in shared memory per tile.  P and dS are rounded to bf16 for
 // the accumulating products, as the forward rounds P.  A causal launch skips the tiles beyond the diagonal.
-// TMEM (512 columns): T1 [0,128), T2 [128,256), accumulators from 256 (dQ, or dV then dK), D columns each;
-// P^T / dS overwrite the first 64 columns of T1 / T2.  192 threads: warps 0-3 element-wise work and the
-// final read-out (one thread per own row), warp 4 TMA producer, warp 5 TMEM allocation and MMA issue.
+// An other-side tile is consumed in two 64-row steps, and the score-like results are double-buffered in
+// TMEM, so the element-wise work of step u+1 runs while the accumulating MMAs of step u and the score
+// MMAs of step u+2 occupy the tensor pipe (the forward kernel pipelines S and P the same way).
+// TMEM (512 columns): buffer b of step u (b = u & 1) holds T1 at [128 b, 128 b + 64) and T2 at
+// [128 b + 64, 128 b + 128); accumulators from 256 (dQ, or dV then dK), D columns each; P^T / dS (bf16)
+// overwrite the first 32 columns of T1 / T2.  192 threads: warps 0-3 element-wise work and the final
+// read-out (one thread per own row), warp 4 TMA producer, warp 5 TMEM allocation and MMA issue.
 // Every mbarrier wait is bounded; on expiry the kernel records a code in the device status word and
 // leaves through the common teardown.
 #include <cuda.h>
@@ -45,10 +49,10 @@ struct BwdCfg {
     static constexpr int SUB_BYTES = 128 * 64 * 2;  // one 64-column (128-byte) swizzled sub-tile
     static constexpr int NSUB = D / 64;
     static constexpr int STAGES = 2;
-    static constexpr int NBARS = 1 + 2 * STAGES + 4;
+    static constexpr int NBARS = 1 + 2 * STAGES + 6;
     static constexpr int STAT_BYTES = STAGES * 2 * 128 * 4;  // per stage: LSE * log2(e) and delta of the other tile
     static constexpr int SMEM_BYTES = (2 + 2 * STAGES) * TILE_BYTES + STAT_BYTES + NBARS * 8 + 16 + 1024;
-    static constexpr uint32_t COL_T1 = 0, COL_T2 = 128, COL_ACC = 256;
+    static constexpr uint32_t COL_T = 0, COL_ACC = 256;  // T1 of buffer b at COL_T + 128 b, T2 64 columns further
 };
 
 struct Bwd5Params {
@@ -79,9 +83,9 @@ bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
     uint64_t* x_full = bars;                // [1]
     uint64_t* y_full = x_full + 1;          // [STAGES]
     uint64_t* y_empty = y_full + STAGES;    // [STAGES]
-    uint64_t* t_full = y_empty + STAGES;    // [1] one phase per step: T1, T2 are in TMEM
-    uint64_t* a_full = t_full + 1;          // [1] one phase per step: the bf16 A operands are in TMEM
-    uint64_t* acc_done = a_full + 1;        // [1] the last accumulating MMA has retired
+    uint64_t* t_full = y_empty + STAGES;    // [2] per buffer, one phase per use: T1, T2 are in TMEM
+    uint64_t* a_full = t_full + 2;          // [2] per buffer, one phase per use: the bf16 A operands are in TMEM
+    uint64_t* acc_done = a_full + 2;        // [1] the last accumulating MMA has retired
     uint64_t* stat_bar = acc_done + 1;      // [1] one phase per step: the column statistics are in shared memory
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(stat_bar + 1);
 
@@ -96,7 +100,8 @@ bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
     // other-side tiles [t_lo, t_hi)
     const int t_lo = (kKeySide && p.causal) ? own : 0;
     const int t_hi = (!kKeySide && p.causal) ? own + 1 : n_tiles;
-    const int n_steps = t_hi - t_lo;
+    const int n_steps = t_hi - t_lo;  // other-side tiles; each is two 64-row steps
+    const int n_u = 2 * n_steps;
 
     if (warp == 4 && lane == 0) {
         prefetch_tensormap(&tm_x1);
@@ -108,8 +113,10 @@ bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
             mbar_init(&y_full[i], 1);
             mbar_init(&y_empty[i], 1);
         }
-        mbar_init(t_full, 1);
-        mbar_init(a_full, 128);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&t_full[i], 1);
+            mbar_init(&a_full[i], 128);
+        }
         mbar_init(acc_done, 1);
         mbar_init(stat_bar, 128);
         fence_barrier_init();
@@ -155,87 +162,117 @@ bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
     } else if (warp == 5) {
         // ============================================================== MMA issuer
         const bool leader = elect_one();
-        constexpr uint32_t idesc_t = make_idesc_bf16(128, 128, 0, 0);
+        constexpr uint32_t idesc_t = make_idesc_bf16(128, 64, 0, 0);
         constexpr uint32_t idesc_a = make_idesc_bf16(128, D, 0, 1);
+        constexpr int HALF = 64 * 128;  // 64 rows inside a 64-column sub-tile
         const uint64_t dx1 = make_smem_desc_sw128(smem_u32(sX1), 16, 1024);
         const uint64_t dx2 = make_smem_desc_sw128(smem_u32(sX2), 16, 1024);
         const uint64_t dy_k = make_smem_desc_sw128(smem_u32(sY), 16, 1024);    // other tile as a K-major operand
         const uint64_t dy_mn = make_smem_desc_sw128(smem_u32(sY), SUB, 1024);  // the same tile as an MN-major operand
-        const uint32_t tT1 = tmem_base + C::COL_T1, tT2 = tmem_base + C::COL_T2, tAcc = tmem_base + C::COL_ACC;
+        const uint32_t tT = tmem_base + C::COL_T, tAcc = tmem_base + C::COL_ACC;
         auto commit = [&](uint64_t* bar) {
             if (leader) mma_commit(bar);
         };
         auto wait = [&](uint64_t* bar, uint32_t parity, int code) {
             return __all_sync(kFullMask, mbar_wait(bar, parity, p.status, code));
         };
+        // T1 = X1 Y1^T, T2 = X2 Y2^T over the 64 other-side rows of step u, into buffer u & 1 (they overwrite
+        // the A operands of step u - 2: the pipe runs this thread's MMAs in issue order, after the accumulating
+        // MMAs of that step)
+        auto issue_T = [&](int u) {
+            const int st = (u >> 1) % STAGES;
+            const uint64_t y1 = dy_k + (uint64_t)((st * 2 * TILE + (u & 1) * HALF) >> 4), y2 = y1 + (uint64_t)(TILE >> 4);
+            const uint32_t t1 = tT + (u & 1) * 128, t2 = t1 + 64;
+#pragma unroll
+            for (int kk = 0; kk < D / 16; ++kk) {
+                const uint32_t off = (uint32_t)(((kk / 4) * SUB + (kk % 4) * 32) >> 4);
+                if (leader) mma_ss(t1, dx1 + off, y1 + off, idesc_t, kk > 0);
+            }
+#pragma unroll
+            for (int kk = 0; kk < D / 16; ++kk) {
+                const uint32_t off = (uint32_t)(((kk / 4) * SUB + (kk % 4) * 32) >> 4);
+                if (leader) mma_ss(t2, dx2 + off, y2 + off, idesc_t, kk > 0);
+            }
+        };
         bool ok = wait(x_full, 0, kToBwdX);
-        for (int t = 0; t < n_steps && ok; ++t) {
-            const int st = t % STAGES;
-            if (!wait(&y_full[st], (uint32_t)(t / STAGES) & 1u, kToBwdYFull)) break;
+        int y_waited = -1;  // other-side tiles already waited for
+        auto wait_tile = [&](int t) {
+            if (t <= y_waited) return true;
+            y_waited = t;
+            const bool got = wait(&y_full[t % STAGES], (uint32_t)(t / STAGES) & 1u, kToBwdYFull);
             tc_fence_after();
-            const uint64_t y1_k = dy_k + (uint64_t)((st * 2 * TILE) >> 4), y2_k = y1_k + (uint64_t)(TILE >> 4);
-            const uint64_t y1_mn = dy_mn + (uint64_t)((st * 2 * TILE) >> 4), y2_mn = y1_mn + (uint64_t)(TILE >> 4);
-            // T1 = X1 Y1^T, T2 = X2 Y2^T (these overwrite last step's A operands: the pipe runs this thread's
-            // MMAs in issue order, after the accumulating MMAs that read them)
-#pragma unroll
-            for (int kk = 0; kk < D / 16; ++kk) {
-                const uint32_t off = (uint32_t)(((kk / 4) * SUB + (kk % 4) * 32) >> 4);
-                if (leader) mma_ss(tT1, dx1 + off, y1_k + off, idesc_t, kk > 0);
+            return got;
+        };
+        if (ok && n_u > 0) {
+            ok = wait_tile(0);
+            if (ok) {
+                issue_T(0);
+                commit(&t_full[0]);
+                issue_T(1);
+                commit(&t_full[1]);
             }
-#pragma unroll
-            for (int kk = 0; kk < D / 16; ++kk) {
-                const uint32_t off = (uint32_t)(((kk / 4) * SUB + (kk % 4) * 32) >> 4);
-                if (leader) mma_ss(tT2, dx2 + off, y2_k + off, idesc_t, kk > 0);
-            }
-            commit(t_full);
-            if (!wait(a_full, (uint32_t)t & 1u, kToBwdA)) break;
-            tc_fence_after();
-            const uint32_t acc0 = t > 0 ? 1u : 0u;
-            if (kKeySide) {
-                // dV += P^T dO (A = P^T in the first 64 columns of T1, B = Y2 = dO), dK += dS^T Q (A in T2, B = Y1 = Q)
-#pragma unroll
-                for (int kk = 0; kk < 8; ++kk)
-                    if (leader) mma_ts(tAcc, tT1 + kk * 8, y2_mn + (uint64_t)((kk * 2048) >> 4), idesc_a, kk > 0 ? 1u : acc0);
-#pragma unroll
-                for (int kk = 0; kk < 8; ++kk)
-                    if (leader) mma_ts(tAcc + D, tT2 + kk * 8, y1_mn + (uint64_t)((kk * 2048) >> 4), idesc_a, kk > 0 ? 1u : acc0);
-            } else {
-                // dQ += dS K (A = dS in the first 64 columns of T2, B = Y1 = K)
-#pragma unroll
-                for (int kk = 0; kk < 8; ++kk)
-                    if (leader) mma_ts(tAcc, tT2 + kk * 8, y1_mn + (uint64_t)((kk * 2048) >> 4), idesc_a, kk > 0 ? 1u : acc0);
-            }
-            commit(&y_empty[st]);
-            if (t == n_steps - 1) commit(acc_done);
         }
-        // every MMA issued above must retire before TMEM is freed: acc_done (or, after a failed wait, a fresh
-        // commit) covers them
-        if (n_steps == 0) commit(acc_done);
+        for (int u = 0; u < n_u && ok; ++u) {
+            const int st = (u >> 1) % STAGES;
+            if (!wait(&a_full[u & 1], (uint32_t)(u >> 1) & 1u, kToBwdA)) break;
+            tc_fence_after();
+            const uint64_t y1 = dy_mn + (uint64_t)((st * 2 * TILE) >> 4), y2 = y1 + (uint64_t)(TILE >> 4);
+            const uint32_t t1 = tT + (u & 1) * 128, t2 = t1 + 64;
+            const uint32_t acc0 = u > 0 ? 1u : 0u;
+            if (kKeySide) {
+                // dV += P^T dO (A = P^T in the first 32 columns of T1, B = Y2 = dO), dK += dS^T Q (A in T2, B = Y1 = Q)
+#pragma unroll
+                for (int kk = 0; kk < 4; ++kk)
+                    if (leader)
+                        mma_ts(tAcc, t1 + kk * 8, y2 + (uint64_t)((((u & 1) * 4 + kk) * 2048) >> 4), idesc_a, kk > 0 ? 1u : acc0);
+#pragma unroll
+                for (int kk = 0; kk < 4; ++kk)
+                    if (leader)
+                        mma_ts(tAcc + D, t2 + kk * 8, y1 + (uint64_t)((((u & 1) * 4 + kk) * 2048) >> 4), idesc_a, kk > 0 ? 1u : acc0);
+            } else {
+                // dQ += dS K (A = dS in the first 32 columns of T2, B = Y1 = K)
+#pragma unroll
+                for (int kk = 0; kk < 4; ++kk)
+                    if (leader)
+                        mma_ts(tAcc, t2 + kk * 8, y1 + (uint64_t)((((u & 1) * 4 + kk) * 2048) >> 4), idesc_a, kk > 0 ? 1u : acc0);
+            }
+            if (u + 2 < n_u) {
+                if (!wait_tile((u + 2) >> 1)) break;
+                issue_T(u + 2);
+                commit(&t_full[u & 1]);
+            }
+            // the tile's slot is free once its second step's MMAs (and the score MMAs that read it) have retired
+            if (u & 1) commit(&y_empty[st]);
+            if (u == n_u - 1) commit(acc_done);
+        }
+        if (n_u == 0) commit(acc_done);
     } else {
         // ============================================================== element-wise warps (one thread per own row)
         const int r = warp * 32 + lane;
         const int own_row = own0 + r;
         const uint32_t lane_sel = (uint32_t)(warp * 32) << 16;
-        const uint32_t tT1 = tmem_base + lane_sel + C::COL_T1, tT2 = tmem_base + lane_sel + C::COL_T2;
+        const uint32_t tT = tmem_base + lane_sel + C::COL_T;
         const uint32_t tAcc = tmem_base + lane_sel + C::COL_ACC;
         const float c = p.scale_log2;
         const int64_t stat_base = (int64_t)bh * N;
         float my_lse2 = 0.f, my_delta = 0.f;  // query side: this row's statistics
         if (!kKeySide && own_row < N) {
-            my_lse2 = p.lse[stat_base + own_row] * kLog2e;
+            const float x = p.lse[stat_base + own_row];
+            my_lse2 = (x > -INFINITY && x < INFINITY) ? x * kLog2e : INFINITY;  // no visible key (or NaN): P = 0
             my_delta = p.delta[stat_base + own_row];
         }
         bool ok = true;
-        for (int t = 0; t < n_steps && ok; ++t) {
-            const int st = t % STAGES;
-            const int other0 = (t_lo + t) * 128;
+        for (int u = 0; u < n_u && ok; ++u) {
+            const int t = u >> 1, st = t % STAGES, buf = u & 1;
+            const int other0 = (t_lo + t) * 128 + buf * 64;  // first other-side row of this step
             float* s_lse2 = stat + st * 256;
             float* s_delta = s_lse2 + 128;
-            if (kKeySide) {
-                // the statistics of this step's query tile (columns); the slot was last read two steps ago, and
-                // every thread has passed the a_full arrival of that step's successor by now
+            if (kKeySide && buf == 0) {
+                // the statistics of this tile's 128 queries (columns); the slot was last read two tiles ago, and
+                // every thread has passed the a_full arrivals of that tile's successor by now
                 const int qi = other0 + r;
-                s_lse2[r] = qi < N ? p.lse[stat_base + qi] * kLog2e : INFINITY;  // +inf -> P = 0
+                const float x = qi < N ? p.lse[stat_base + qi] : INFINITY;
+                s_lse2[r] = (x > -INFINITY && x < INFINITY) ? x * kLog2e : INFINITY;  // +inf -> P = 0
                 s_delta[r] = qi < N ? p.delta[stat_base + qi] : 0.f;
                 mbar_arrive(stat_bar);  // an mbarrier rather than bar.sync, so that this wait is bounded as well
                 if (!__all_sync(kFullMask, mbar_wait(stat_bar, (uint32_t)t & 1u, p.status, kToBwdStat))) {
@@ -243,50 +280,70 @@ bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
                     break;
                 }
             }
-            if (!__all_sync(kFullMask, mbar_wait(t_full, (uint32_t)t & 1u, p.status, kToBwdT))) {
+            if (!__all_sync(kFullMask, mbar_wait(&t_full[buf], (uint32_t)(u >> 1) & 1u, p.status, kToBwdT))) {
                 ok = false;
                 break;
             }
             tc_fence_after();
-            // Is any (own row, other index) pair of this tile masked?  Only the diagonal tile of a causal
+            // Is any (own row, other index) pair of this step masked?  Only the diagonal tile of a causal
             // launch and the last tile of a ragged sequence are.
-            const bool diag = p.causal && other0 == own0;
-            const bool ragged = other0 + 128 > N;
+            const bool diag = p.causal && (t_lo + t) == own;
+            const bool ragged = other0 + 64 > N;
+            const uint32_t t1 = tT + buf * 128, t2 = t1 + 64;
+            const float2 c2 = make_float2(c, c);
 #pragma unroll
-            for (int ch = 0; ch < 4; ++ch) {
+            for (int ch = 0; ch < 2; ++ch) {
                 uint32_t a1[32], a2[32];
-                tmem_ld32(tT1 + ch * 32, a1);
-                tmem_ld32(tT2 + ch * 32, a2);
+                tmem_ld32(t1 + ch * 32, a1);
+                tmem_ld32(t2 + ch * 32, a2);
                 tc_wait_ld();
                 uint32_t pk_p[16], pk_ds[16];
 #pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    float pv[2], dsv[2];
-#pragma unroll
-                    for (int e = 0; e < 2; ++e) {
-                        const int col = ch * 32 + i + e;
-                        const float lse2 = kKeySide ? s_lse2[col] : my_lse2;
-                        const float dl = kKeySide ? s_delta[col] : my_delta;
-                        float pe = fast_exp2(fmaf(__uint_as_float(a1[i + e]), c, -lse2));
-                        if (diag || ragged) {
-                            const int other = other0 + col;
-                            const bool hidden = other >= N || (p.causal && (kKeySide ? own_row > other : other > own_row));
-                            if (hidden) pe = 0.f;
-                        }
-                        if (!(lse2 < INFINITY) || !(lse2 > -INFINITY)) pe = 0.f;  // rows without any visible key
-                        pv[e] = pe;
-                        dsv[e] = pe * (__uint_as_float(a2[i + e]) - dl);
+                for (int i = 0; i < 32; i += 4) {
+                    // statistics of four columns: the row's own on the query side, one 16-byte broadcast read each
+                    // on the key side (an LSE of +inf makes the probability 0: absent queries, rows without a key)
+                    float4 l4, d4;
+                    if (kKeySide) {
+                        l4 = *reinterpret_cast<const float4*>(s_lse2 + buf * 64 + ch * 32 + i);
+                        d4 = *reinterpret_cast<const float4*>(s_delta + buf * 64 + ch * 32 + i);
+                    } else {
+                        l4 = make_float4(my_lse2, my_lse2, my_lse2, my_lse2);
+                        d4 = make_float4(my_delta, my_delta, my_delta, my_delta);
                     }
-                    pk_p[i / 2] = float2_to_bf16x2(pv[0], pv[1]);
-                    pk_ds[i / 2] = float2_to_bf16x2(dsv[0], dsv[1]);
+                    const float2 xa = __ffma2_rn(make_float2(__uint_as_float(a1[i]), __uint_as_float(a1[i + 1])), c2,
+                                                 make_float2(-l4.x, -l4.y));
+                    const float2 xb = __ffma2_rn(make_float2(__uint_as_float(a1[i + 2]), __uint_as_float(a1[i + 3])), c2,
+                                                 make_float2(-l4.z, -l4.w));
+                    float2 pa = make_float2(fast_exp2(xa.x), fast_exp2(xa.y));
+                    float2 pb = make_float2(fast_exp2(xb.x), fast_exp2(xb.y));
+                    if (diag || ragged) {
+                        const int o0 = other0 + ch * 32 + i;
+                        auto hidden = [&](int other) {
+                            return other >= N || (p.causal && (kKeySide ? own_row > other : other > own_row));
+                        };
+                        if (hidden(o0)) pa.x = 0.f;
+                        if (hidden(o0 + 1)) pa.y = 0.f;
+                        if (hidden(o0 + 2)) pb.x = 0.f;
+                        if (hidden(o0 + 3)) pb.y = 0.f;
+                    }
+                    const float2 ta = __fadd2_rn(make_float2(__uint_as_float(a2[i]), __uint_as_float(a2[i + 1])),
+                                                 make_float2(-d4.x, -d4.y));
+                    const float2 tb = __fadd2_rn(make_float2(__uint_as_float(a2[i + 2]), __uint_as_float(a2[i + 3])),
+                                                 make_float2(-d4.z, -d4.w));
+                    const float2 da = __fmul2_rn(pa, ta), db = __fmul2_rn(pb, tb);
+                    pk_p[i / 2] = float2_to_bf16x2(pa.x, pa.y);
+                    pk_p[i / 2 + 1] = float2_to_bf16x2(pb.x, pb.y);
+                    pk_ds[i / 2] = float2_to_bf16x2(da.x, da.y);
+                    pk_ds[i / 2 + 1] = float2_to_bf16x2(db.x, db.y);
                 }
-                // chunk ch's bf16 values land in columns [16 ch, 16 ch + 16), which chunks 0 .. ch/2 covered: loaded already
-                if (kKeySide) tmem_st16(tT1 + ch * 16, pk_p);
-                tmem_st16(tT2 + ch * 16, pk_ds);
+                // chunk ch's bf16 values land in columns [16 ch, 16 ch + 16) of their buffer, inside the chunk 0
+                // columns, which are in registers by now
+                if (kKeySide) tmem_st16(t1 + ch * 16, pk_p);
+                tmem_st16(t2 + ch * 16, pk_ds);
             }
             tc_wait_st();
             tc_fence_before();
-            mbar_arrive(a_full);
+            mbar_arrive(&a_full[buf]);
         }
         // ---- read-out: accumulators -> f32 global (scale folded into dQ and dK)
         if (ok && __all_sync(kFullMask, mbar_wait(acc_done, 0, p.status, kToBwdAcc))) {
