@@ -5,8 +5,8 @@
 //   P = exp(scale * Q K^T - LSE),  dP = dO V^T,  dS = P o (dP - delta),  delta_i = dO_i . O_i,
 //   dV = P^T dO,  dQ = scale * dS K,  dK = scale * dS^T Q.
 // Two deterministic passes (no atomics, fixed summation order) share one kernel template.  A CTA owns
-// 128 rows of one side, keeps them in shared memory, and walks the 128-row tiles of the other side that
-// TMA streams through a two-stage ring:
+// 128 rows of one side, keeps them in shared memory, and walks the other side in 64-row steps that TMA
+// streams through a four-slot ring:
 //   query side: own X1 = Q_i, X2 = dO_i;  per key tile (Y1 = K_j, Y2 = V_j)
 //               T1 = Q K^T, T2 = dO V^T (SS MMAs into TMEM) -> dS (bf16, back into TMEM) -> dQ += dS K_j (TS MMA)
 //   key side:   own X1 = K_j, X2 = V_j;   per query tile (Y1 = Q_i, Y2 = dO_i)
@@ -37,7 +37,7 @@ namespace rt {
 using namespace ptx;
 
 bool make_tensor_map_bf16_4d(CUtensorMap* map, const void* base, int64_t batch, int64_t heads, int64_t seq, int dim,
-                             int64_t stride_b, int64_t stride_h, int64_t stride_row);  // prefill_tc.cu
+                             int64_t stride_b, int64_t stride_h, int64_t stride_row, int box_rows);  // prefill_tc.cu
 
 namespace {
 
@@ -48,10 +48,12 @@ struct BwdCfg {
     static constexpr int TILE_BYTES = 128 * D * 2;
     static constexpr int SUB_BYTES = 128 * 64 * 2;  // one 64-column (128-byte) swizzled sub-tile
     static constexpr int NSUB = D / 64;
-    static constexpr int STAGES = 2;
+    static constexpr int HALF_BYTES = 64 * D * 2;   // 64 other-side rows: NSUB sub-tiles of 64 rows x 128 bytes
+    static constexpr int HSUB_BYTES = 64 * 64 * 2;
+    static constexpr int STAGES = 4;                // ring slots, each (Y1 | Y2) of one 64-row step
     static constexpr int NBARS = 1 + 2 * STAGES + 6;
-    static constexpr int STAT_BYTES = STAGES * 2 * 128 * 4;  // per stage: LSE * log2(e) and delta of the other tile
-    static constexpr int SMEM_BYTES = (2 + 2 * STAGES) * TILE_BYTES + STAT_BYTES + NBARS * 8 + 16 + 1024;
+    static constexpr int STAT_BYTES = 2 * 2 * 128 * 4;  // two slots of LSE * log2(e) and delta of a 128-row other tile
+    static constexpr int SMEM_BYTES = 2 * TILE_BYTES + STAGES * 2 * HALF_BYTES + STAT_BYTES + NBARS * 8 + 16 + 1024;
     static constexpr uint32_t COL_T = 0, COL_ACC = 256;  // T1 of buffer b at COL_T + 128 b, T2 64 columns further
 };
 
@@ -72,13 +74,13 @@ bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
                    const __grid_constant__ CUtensorMap tm_y1, const __grid_constant__ CUtensorMap tm_y2,
                    const Bwd5Params p) {
     using C = BwdCfg<D>;
-    constexpr int TILE = C::TILE_BYTES, SUB = C::SUB_BYTES, STAGES = C::STAGES;
+    constexpr int TILE = C::TILE_BYTES, SUB = C::SUB_BYTES, STAGES = C::STAGES, HALFT = C::HALF_BYTES, HSUB = C::HSUB_BYTES;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* sX1 = smem;
     uint8_t* sX2 = sX1 + TILE;
-    uint8_t* sY = sX2 + TILE;  // [STAGES][Y1 | Y2]
-    float* stat = reinterpret_cast<float*>(sY + STAGES * 2 * TILE);  // [STAGES][lse2[128] | delta[128]]
+    uint8_t* sY = sX2 + TILE;  // [STAGES][Y1 | Y2], 64 rows each
+    float* stat = reinterpret_cast<float*>(sY + STAGES * 2 * HALFT);  // [2][lse2[128] | delta[128]]
     uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(stat) + C::STAT_BYTES);
     uint64_t* x_full = bars;                // [1]
     uint64_t* y_full = x_full + 1;          // [STAGES]
@@ -141,34 +143,33 @@ bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
                 tma_load_4d(sX2 + s * SUB, &tm_x2, x_full, s * 64, own0, h, b);
             }
             int issued = 0;
-            for (int t = 0; t < n_steps; ++t) {
-                const int st = t % STAGES;
-                if (t >= STAGES && !mbar_wait(&y_empty[st], (uint32_t)(t / STAGES - 1) & 1u, p.status, kToBwdYEmpty)) break;
-                mbar_arrive_expect_tx(&y_full[st], 2 * TILE);
-                uint8_t* dst = sY + st * 2 * TILE;
-                const int r0 = (t_lo + t) * 128;
+            for (int u = 0; u < n_u; ++u) {
+                const int st = u % STAGES;
+                if (u >= STAGES && !mbar_wait(&y_empty[st], (uint32_t)(u / STAGES - 1) & 1u, p.status, kToBwdYEmpty)) break;
+                mbar_arrive_expect_tx(&y_full[st], 2 * HALFT);
+                uint8_t* dst = sY + st * 2 * HALFT;
+                const int r0 = (t_lo + (u >> 1)) * 128 + (u & 1) * 64;
 #pragma unroll
                 for (int s = 0; s < C::NSUB; ++s) {
-                    tma_load_4d(dst + s * SUB, &tm_y1, &y_full[st], s * 64, r0, h, b);
-                    tma_load_4d(dst + TILE + s * SUB, &tm_y2, &y_full[st], s * 64, r0, h, b);
+                    tma_load_4d(dst + s * HSUB, &tm_y1, &y_full[st], s * 64, r0, h, b);
+                    tma_load_4d(dst + HALFT + s * HSUB, &tm_y2, &y_full[st], s * 64, r0, h, b);
                 }
-                issued = t + 1;
+                issued = u + 1;
             }
             // Drain: every copy this thread issued must have landed before the CTA may exit.
             mbar_wait(x_full, 0, p.status, kToBwdDrain);
-            for (int t = max(0, issued - STAGES); t < issued; ++t)
-                mbar_wait(&y_full[t % STAGES], (uint32_t)(t / STAGES) & 1u, p.status, kToBwdDrain);
+            for (int u = max(0, issued - STAGES); u < issued; ++u)
+                mbar_wait(&y_full[u % STAGES], (uint32_t)(u / STAGES) & 1u, p.status, kToBwdDrain);
         }
     } else if (warp == 5) {
         // ============================================================== MMA issuer
         const bool leader = elect_one();
         constexpr uint32_t idesc_t = make_idesc_bf16(128, 64, 0, 0);
         constexpr uint32_t idesc_a = make_idesc_bf16(128, D, 0, 1);
-        constexpr int HALF = 64 * 128;  // 64 rows inside a 64-column sub-tile
         const uint64_t dx1 = make_smem_desc_sw128(smem_u32(sX1), 16, 1024);
         const uint64_t dx2 = make_smem_desc_sw128(smem_u32(sX2), 16, 1024);
         const uint64_t dy_k = make_smem_desc_sw128(smem_u32(sY), 16, 1024);    // other tile as a K-major operand
-        const uint64_t dy_mn = make_smem_desc_sw128(smem_u32(sY), SUB, 1024);  // the same tile as an MN-major operand
+        const uint64_t dy_mn = make_smem_desc_sw128(smem_u32(sY), HSUB, 1024);  // the same rows as an MN-major operand
         const uint32_t tT = tmem_base + C::COL_T, tAcc = tmem_base + C::COL_ACC;
         auto commit = [&](uint64_t* bar) {
             if (leader) mma_commit(bar);
@@ -180,43 +181,45 @@ bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
         // the A operands of step u - 2: the pipe runs this thread's MMAs in issue order, after the accumulating
         // MMAs of that step)
         auto issue_T = [&](int u) {
-            const int st = (u >> 1) % STAGES;
-            const uint64_t y1 = dy_k + (uint64_t)((st * 2 * TILE + (u & 1) * HALF) >> 4), y2 = y1 + (uint64_t)(TILE >> 4);
+            const int st = u % STAGES;
+            const uint64_t y1 = dy_k + (uint64_t)((st * 2 * HALFT) >> 4), y2 = y1 + (uint64_t)(HALFT >> 4);
             const uint32_t t1 = tT + (u & 1) * 128, t2 = t1 + 64;
 #pragma unroll
             for (int kk = 0; kk < D / 16; ++kk) {
-                const uint32_t off = (uint32_t)(((kk / 4) * SUB + (kk % 4) * 32) >> 4);
-                if (leader) mma_ss(t1, dx1 + off, y1 + off, idesc_t, kk > 0);
+                const uint32_t offx = (uint32_t)(((kk / 4) * SUB + (kk % 4) * 32) >> 4);
+                const uint32_t offy = (uint32_t)(((kk / 4) * HSUB + (kk % 4) * 32) >> 4);
+                if (leader) mma_ss(t1, dx1 + offx, y1 + offy, idesc_t, kk > 0);
             }
 #pragma unroll
             for (int kk = 0; kk < D / 16; ++kk) {
-                const uint32_t off = (uint32_t)(((kk / 4) * SUB + (kk % 4) * 32) >> 4);
-                if (leader) mma_ss(t2, dx2 + off, y2 + off, idesc_t, kk > 0);
+                const uint32_t offx = (uint32_t)(((kk / 4) * SUB + (kk % 4) * 32) >> 4);
+                const uint32_t offy = (uint32_t)(((kk / 4) * HSUB + (kk % 4) * 32) >> 4);
+                if (leader) mma_ss(t2, dx2 + offx, y2 + offy, idesc_t, kk > 0);
             }
         };
         bool ok = wait(x_full, 0, kToBwdX);
-        int y_waited = -1;  // other-side tiles already waited for
-        auto wait_tile = [&](int t) {
-            if (t <= y_waited) return true;
-            y_waited = t;
-            const bool got = wait(&y_full[t % STAGES], (uint32_t)(t / STAGES) & 1u, kToBwdYFull);
+        auto wait_rows = [&](int u) {  // the rows of step u have landed
+            const bool got = wait(&y_full[u % STAGES], (uint32_t)(u / STAGES) & 1u, kToBwdYFull);
             tc_fence_after();
             return got;
         };
         if (ok && n_u > 0) {
-            ok = wait_tile(0);
+            ok = wait_rows(0);
             if (ok) {
                 issue_T(0);
                 commit(&t_full[0]);
+                ok = wait_rows(1);
+            }
+            if (ok) {
                 issue_T(1);
                 commit(&t_full[1]);
             }
         }
         for (int u = 0; u < n_u && ok; ++u) {
-            const int st = (u >> 1) % STAGES;
+            const int st = u % STAGES;
             if (!wait(&a_full[u & 1], (uint32_t)(u >> 1) & 1u, kToBwdA)) break;
             tc_fence_after();
-            const uint64_t y1 = dy_mn + (uint64_t)((st * 2 * TILE) >> 4), y2 = y1 + (uint64_t)(TILE >> 4);
+            const uint64_t y1 = dy_mn + (uint64_t)((st * 2 * HALFT) >> 4), y2 = y1 + (uint64_t)(HALFT >> 4);
             const uint32_t t1 = tT + (u & 1) * 128, t2 = t1 + 64;
             const uint32_t acc0 = u > 0 ? 1u : 0u;
             if (kKeySide) {
@@ -224,25 +227,24 @@ bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
 #pragma unroll
                 for (int kk = 0; kk < 4; ++kk)
                     if (leader)
-                        mma_ts(tAcc, t1 + kk * 8, y2 + (uint64_t)((((u & 1) * 4 + kk) * 2048) >> 4), idesc_a, kk > 0 ? 1u : acc0);
+                        mma_ts(tAcc, t1 + kk * 8, y2 + (uint64_t)((kk * 2048) >> 4), idesc_a, kk > 0 ? 1u : acc0);
 #pragma unroll
                 for (int kk = 0; kk < 4; ++kk)
                     if (leader)
-                        mma_ts(tAcc + D, t2 + kk * 8, y1 + (uint64_t)((((u & 1) * 4 + kk) * 2048) >> 4), idesc_a, kk > 0 ? 1u : acc0);
+                        mma_ts(tAcc + D, t2 + kk * 8, y1 + (uint64_t)((kk * 2048) >> 4), idesc_a, kk > 0 ? 1u : acc0);
             } else {
                 // dQ += dS K (A = dS in the first 32 columns of T2, B = Y1 = K)
 #pragma unroll
                 for (int kk = 0; kk < 4; ++kk)
                     if (leader)
-                        mma_ts(tAcc, t2 + kk * 8, y1 + (uint64_t)((((u & 1) * 4 + kk) * 2048) >> 4), idesc_a, kk > 0 ? 1u : acc0);
+                        mma_ts(tAcc, t2 + kk * 8, y1 + (uint64_t)((kk * 2048) >> 4), idesc_a, kk > 0 ? 1u : acc0);
             }
+            commit(&y_empty[st]);  // the step's rows are free once these MMAs (and the score MMAs before them) retire
             if (u + 2 < n_u) {
-                if (!wait_tile((u + 2) >> 1)) break;
+                if (!wait_rows(u + 2)) break;
                 issue_T(u + 2);
                 commit(&t_full[u & 1]);
             }
-            // the tile's slot is free once its second step's MMAs (and the score MMAs that read it) have retired
-            if (u & 1) commit(&y_empty[st]);
             if (u == n_u - 1) commit(acc_done);
         }
         if (n_u == 0) commit(acc_done);
@@ -263,7 +265,7 @@ bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
         }
         bool ok = true;
         for (int u = 0; u < n_u && ok; ++u) {
-            const int t = u >> 1, st = t % STAGES, buf = u & 1;
+            const int t = u >> 1, st = t & 1, buf = u & 1;
             const int other0 = (t_lo + t) * 128 + buf * 64;  // first other-side row of this step
             float* s_lse2 = stat + st * 256;
             float* s_delta = s_lse2 + 128;
@@ -402,13 +404,16 @@ cudaError_t launch_backward_tcgen05(const void* q, const void* k, const void* v,
                                     int64_t seq, int dim, int causal, float scale, cudaStream_t stream) {
     const int64_t bh = batch * heads;
     if ((dim != 64 && dim != 128) || bh > 65535 || seq > (1 << 30)) return cudaErrorNotSupported;
-    CUtensorMap mq, mk, mv, mdo;
+    // own-side tiles are 128-row boxes, other-side steps 64-row boxes of the same tensors
+    CUtensorMap mq, mk, mv, mdo, hq, hk, hv, hdo;
     const TensorStrides s = TensorStrides::contiguous(heads, seq, dim);
-    if (!make_tensor_map_bf16_4d(&mq, q, batch, heads, seq, dim, s.batch, s.head, s.row) ||
-        !make_tensor_map_bf16_4d(&mk, k, batch, heads, seq, dim, s.batch, s.head, s.row) ||
-        !make_tensor_map_bf16_4d(&mv, v, batch, heads, seq, dim, s.batch, s.head, s.row) ||
-        !make_tensor_map_bf16_4d(&mdo, d_out, batch, heads, seq, dim, s.batch, s.head, s.row))
-        return cudaErrorNotSupported;
+    const void* ptrs[4] = {q, k, v, d_out};
+    CUtensorMap* full[4] = {&mq, &mk, &mv, &mdo};
+    CUtensorMap* half[4] = {&hq, &hk, &hv, &hdo};
+    for (int i = 0; i < 4; ++i)
+        if (!make_tensor_map_bf16_4d(full[i], ptrs[i], batch, heads, seq, dim, s.batch, s.head, s.row, 128) ||
+            !make_tensor_map_bf16_4d(half[i], ptrs[i], batch, heads, seq, dim, s.batch, s.head, s.row, 64))
+            return cudaErrorNotSupported;
     Bwd5Params p;
     p.lse = lse;
     p.delta = delta;
@@ -422,14 +427,14 @@ cudaError_t launch_backward_tcgen05(const void* q, const void* k, const void* v,
     // query side: own (Q, dO), other (K, V) -> dQ
     p.out1 = dq;
     p.out2 = nullptr;
-    cudaError_t e = dim == 128 ? launch_side<128, false>(mq, mdo, mk, mv, p, bh, stream)
-                               : launch_side<64, false>(mq, mdo, mk, mv, p, bh, stream);
+    cudaError_t e = dim == 128 ? launch_side<128, false>(mq, mdo, hk, hv, p, bh, stream)
+                               : launch_side<64, false>(mq, mdo, hk, hv, p, bh, stream);
     if (e != cudaSuccess) return e;
     // key side: own (K, V), other (Q, dO) -> dV, dK
     p.out1 = dv;
     p.out2 = dk;
-    return dim == 128 ? launch_side<128, true>(mk, mv, mq, mdo, p, bh, stream)
-                      : launch_side<64, true>(mk, mv, mq, mdo, p, bh, stream);
+    return dim == 128 ? launch_side<128, true>(mk, mv, hq, hdo, p, bh, stream)
+                      : launch_side<64, true>(mk, mv, hq, hdo, p, bh, stream);
 }
 
 }  // namespace rt

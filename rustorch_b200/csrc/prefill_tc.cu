@@ -784,15 +784,18 @@ bool encode_bf16_map_cached(CUtensorMap* out, int rank, const void* base, const 
     return true;
 }
 
+bool make_tensor_map_bf16_4d(CUtensorMap* map, const void* base, int64_t batch, int64_t heads, int64_t seq, int dim,
+                             int64_t stride_b, int64_t stride_h, int64_t stride_row, int box_rows = 128);
+
 // View of a [B, H, N, D] bf16 tensor with arbitrary batch / head / row strides (inner dim contiguous)
-// as a 4-D TMA tensor (d, row, head, batch); box = 64 columns x 128 rows of one (b,h), 128-byte
+// as a 4-D TMA tensor (d, row, head, batch); box = 64 columns x box_rows (128, or 64) rows of one (b,h), 128-byte
 // swizzle.  Rows past N are zero-filled on loads and clipped on stores, so tiles never touch a
 // neighbouring head.  Strides are in elements and must be multiples of 8 (16 bytes).
 bool make_tensor_map_bf16_4d(CUtensorMap* map, const void* base, int64_t batch, int64_t heads, int64_t seq, int dim,
-                             int64_t stride_b, int64_t stride_h, int64_t stride_row) {
+                             int64_t stride_b, int64_t stride_h, int64_t stride_row, int box_rows) {
     const uint64_t dims[4] = {(uint64_t)dim, (uint64_t)seq, (uint64_t)heads, (uint64_t)batch};
     const uint64_t strides[3] = {(uint64_t)stride_row * 2, (uint64_t)stride_h * 2, (uint64_t)stride_b * 2};
-    const uint32_t box[4] = {64, 128, 1, 1};
+    const uint32_t box[4] = {64, (uint32_t)box_rows, 1, 1};
     return encode_bf16_map_cached(map, 4, base, dims, strides, box);
 }
 
