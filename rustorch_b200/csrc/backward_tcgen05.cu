@@ -23,8 +23,11 @@
 // MMAs of step u+2 occupy the tensor pipe (the forward kernel pipelines S and P the same way).
 // TMEM (512 columns): buffer b of step u (b = u & 1) holds T1 at [128 b, 128 b + 64) and T2 at
 // [128 b + 64, 128 b + 128); accumulators from 256 (dQ, or dV then dK), D columns each; P^T / dS (bf16)
-// overwrite the first 32 columns of T1 / T2.  192 threads: warps 0-3 element-wise work and the final
-// read-out (one thread per own row), warp 4 TMA producer, warp 5 TMEM allocation and MMA issue.
+// overwrite 32 of the columns of T1 / T2.  320 threads: warps 0-7 element-wise work and the final read-out,
+// two threads per own row (warp w owns rows 32 (w % 4).. and the 32 score columns of half w / 4; its bf16
+// results go back into the first 16 of its OWN columns, so the two threads of a row never touch each other's
+// inputs, and the accumulating MMAs take K elements 0-31 from columns [0,16) and 32-63 from [32,48));
+// warp 8 TMA producer, warp 9 TMEM allocation and MMA issue.
 // Every mbarrier wait is bounded; on expiry the kernel records a code in the device status word and
 // leaves through the common teardown.
 #include <cuda.h>
@@ -69,7 +72,7 @@ struct Bwd5Params {
 };
 
 template <int D, bool kKeySide>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
 bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_constant__ CUtensorMap tm_x2,
                    const __grid_constant__ CUtensorMap tm_y1, const __grid_constant__ CUtensorMap tm_y2,
                    const Bwd5Params p) {
@@ -105,7 +108,7 @@ bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
     const int n_steps = t_hi - t_lo;  // other-side tiles; each is two 64-row steps
     const int n_u = 2 * n_steps;
 
-    if (warp == 4 && lane == 0) {
+    if (warp == 8 && lane == 0) {
         prefetch_tensormap(&tm_x1);
         prefetch_tensormap(&tm_x2);
         prefetch_tensormap(&tm_y1);
@@ -117,14 +120,14 @@ bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(&t_full[i], 1);
-            mbar_init(&a_full[i], 128);
+            mbar_init(&a_full[i], 256);
         }
         mbar_init(acc_done, 1);
-        mbar_init(stat_bar, 128);
+        mbar_init(stat_bar, 256);
         fence_barrier_init();
         fence_proxy_async();
     }
-    if (warp == 5) {
+    if (warp == 9) {
         tmem_alloc(tmem_slot, 512);
         tmem_relinquish();
     }
@@ -133,7 +136,7 @@ bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    if (warp == 4) {
+    if (warp == 8) {
         // ============================================================== TMA producer
         if (lane == 0) {
             mbar_arrive_expect_tx(x_full, 2 * TILE);
@@ -161,7 +164,7 @@ bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
             for (int u = max(0, issued - STAGES); u < issued; ++u)
                 mbar_wait(&y_full[u % STAGES], (uint32_t)(u / STAGES) & 1u, p.status, kToBwdDrain);
         }
-    } else if (warp == 5) {
+    } else if (warp == 9) {
         // ============================================================== MMA issuer
         const bool leader = elect_one();
         constexpr uint32_t idesc_t = make_idesc_bf16(128, 64, 0, 0);
@@ -227,17 +230,17 @@ bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
 #pragma unroll
                 for (int kk = 0; kk < 4; ++kk)
                     if (leader)
-                        mma_ts(tAcc, t1 + kk * 8, y2 + (uint64_t)((kk * 2048) >> 4), idesc_a, kk > 0 ? 1u : acc0);
+                        mma_ts(tAcc, t1 + kk * 8 + (kk >= 2 ? 16 : 0), y2 + (uint64_t)((kk * 2048) >> 4), idesc_a, kk > 0 ? 1u : acc0);
 #pragma unroll
                 for (int kk = 0; kk < 4; ++kk)
                     if (leader)
-                        mma_ts(tAcc + D, t2 + kk * 8, y1 + (uint64_t)((kk * 2048) >> 4), idesc_a, kk > 0 ? 1u : acc0);
+                        mma_ts(tAcc + D, t2 + kk * 8 + (kk >= 2 ? 16 : 0), y1 + (uint64_t)((kk * 2048) >> 4), idesc_a, kk > 0 ? 1u : acc0);
             } else {
                 // dQ += dS K (A = dS in the first 32 columns of T2, B = Y1 = K)
 #pragma unroll
                 for (int kk = 0; kk < 4; ++kk)
                     if (leader)
-                        mma_ts(tAcc, t2 + kk * 8, y1 + (uint64_t)((kk * 2048) >> 4), idesc_a, kk > 0 ? 1u : acc0);
+                        mma_ts(tAcc, t2 + kk * 8 + (kk >= 2 ? 16 : 0), y1 + (uint64_t)((kk * 2048) >> 4), idesc_a, kk > 0 ? 1u : acc0);
             }
             commit(&y_empty[st]);  // the step's rows are free once these MMAs (and the score MMAs before them) retire
             if (u + 2 < n_u) {
@@ -249,10 +252,11 @@ bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
         }
         if (n_u == 0) commit(acc_done);
     } else {
-        // ============================================================== element-wise warps (one thread per own row)
-        const int r = warp * 32 + lane;
+        // ============================================================== element-wise warps (two threads per own row)
+        const int half = warp >> 2;  // which 32 of a step's 64 score columns
+        const int r = (warp & 3) * 32 + lane;
         const int own_row = own0 + r;
-        const uint32_t lane_sel = (uint32_t)(warp * 32) << 16;
+        const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
         const uint32_t tT = tmem_base + lane_sel + C::COL_T;
         const uint32_t tAcc = tmem_base + lane_sel + C::COL_ACC;
         const float c = p.scale_log2;
@@ -272,10 +276,12 @@ bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
             if (kKeySide && buf == 0) {
                 // the statistics of this tile's 128 queries (columns); the slot was last read two tiles ago, and
                 // every thread has passed the a_full arrivals of that tile's successor by now
-                const int qi = other0 + r;
-                const float x = qi < N ? p.lse[stat_base + qi] : INFINITY;
-                s_lse2[r] = (x > -INFINITY && x < INFINITY) ? x * kLog2e : INFINITY;  // +inf -> P = 0
-                s_delta[r] = qi < N ? p.delta[stat_base + qi] : 0.f;
+                if (half == 0) {
+                    const int qi = other0 + r;
+                    const float x = qi < N ? p.lse[stat_base + qi] : INFINITY;
+                    s_lse2[r] = (x > -INFINITY && x < INFINITY) ? x * kLog2e : INFINITY;  // +inf -> P = 0
+                    s_delta[r] = qi < N ? p.delta[stat_base + qi] : 0.f;
+                }
                 mbar_arrive(stat_bar);  // an mbarrier rather than bar.sync, so that this wait is bounded as well
                 if (!__all_sync(kFullMask, mbar_wait(stat_bar, (uint32_t)t & 1u, p.status, kToBwdStat))) {
                     ok = false;
@@ -293,11 +299,12 @@ bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
             const bool ragged = other0 + 64 > N;
             const uint32_t t1 = tT + buf * 128, t2 = t1 + 64;
             const float2 c2 = make_float2(c, c);
-#pragma unroll
-            for (int ch = 0; ch < 2; ++ch) {
+            {
+                constexpr int ch = 0;  // this thread's single chunk: score columns [32 half, 32 half + 32) of the step
+                const int cbase = half * 32;
                 uint32_t a1[32], a2[32];
-                tmem_ld32(t1 + ch * 32, a1);
-                tmem_ld32(t2 + ch * 32, a2);
+                tmem_ld32(t1 + cbase, a1);
+                tmem_ld32(t2 + cbase, a2);
                 tc_wait_ld();
                 uint32_t pk_p[16], pk_ds[16];
 #pragma unroll
@@ -306,8 +313,8 @@ bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
                     // on the key side (an LSE of +inf makes the probability 0: absent queries, rows without a key)
                     float4 l4, d4;
                     if (kKeySide) {
-                        l4 = *reinterpret_cast<const float4*>(s_lse2 + buf * 64 + ch * 32 + i);
-                        d4 = *reinterpret_cast<const float4*>(s_delta + buf * 64 + ch * 32 + i);
+                        l4 = *reinterpret_cast<const float4*>(s_lse2 + buf * 64 + cbase + i);
+                        d4 = *reinterpret_cast<const float4*>(s_delta + buf * 64 + cbase + i);
                     } else {
                         l4 = make_float4(my_lse2, my_lse2, my_lse2, my_lse2);
                         d4 = make_float4(my_delta, my_delta, my_delta, my_delta);
@@ -319,7 +326,7 @@ bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
                     float2 pa = make_float2(fast_exp2(xa.x), fast_exp2(xa.y));
                     float2 pb = make_float2(fast_exp2(xb.x), fast_exp2(xb.y));
                     if (diag || ragged) {
-                        const int o0 = other0 + ch * 32 + i;
+                        const int o0 = other0 + cbase + i;
                         auto hidden = [&](int other) {
                             return other >= N || (p.causal && (kKeySide ? own_row > other : other > own_row));
                         };
@@ -338,10 +345,10 @@ bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
                     pk_ds[i / 2] = float2_to_bf16x2(da.x, da.y);
                     pk_ds[i / 2 + 1] = float2_to_bf16x2(db.x, db.y);
                 }
-                // chunk ch's bf16 values land in columns [16 ch, 16 ch + 16) of their buffer, inside the chunk 0
-                // columns, which are in registers by now
-                if (kKeySide) tmem_st16(t1 + ch * 16, pk_p);
-                tmem_st16(t2 + ch * 16, pk_ds);
+                // the 32 bf16 values go into the first 16 of this thread's own 32 columns (in registers by now)
+                (void)ch;
+                if (kKeySide) tmem_st16(t1 + cbase, pk_p);
+                tmem_st16(t2 + cbase, pk_ds);
             }
             tc_wait_st();
             tc_fence_before();
@@ -351,20 +358,16 @@ bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
         if (ok && __all_sync(kFullMask, mbar_wait(acc_done, 0, p.status, kToBwdAcc))) {
             tc_fence_after();
             constexpr int kOuts = kKeySide ? 2 : 1;
+            constexpr int OC = D / 2;  // accumulator columns per thread
 #pragma unroll
             for (int o = 0; o < kOuts; ++o) {
-                float* dst = (o == 0 ? p.out1 : p.out2) + ((int64_t)bh * N + own_row) * D;
+                float* dst = (o == 0 ? p.out1 : p.out2) + ((int64_t)bh * N + own_row) * D + half * OC;
                 const float mul = (kKeySide && o == 0) ? 1.f : p.scale;  // dV is not scaled
 #pragma unroll
-                for (int ch = 0; ch < D / 32; ++ch) {
+                for (int ch = 0; ch < OC / 32; ++ch) {
                     uint32_t a[32];
-                    if (n_steps > 0) {
-                        tmem_ld32(tAcc + o * D + ch * 32, a);
-                        tc_wait_ld();
-                    } else {
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) a[i] = 0u;
-                    }
+                    tmem_ld32(tAcc + o * D + half * OC + ch * 32, a);
+                    tc_wait_ld();
                     if (own_row < N) {
 #pragma unroll
                         for (int i = 0; i < 32; i += 4)
@@ -379,7 +382,7 @@ bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x1, const __grid_const
 
     tc_fence_before();
     __syncthreads();
-    if (warp == 5) {
+    if (warp == 9) {
         tc_fence_after();
         tmem_dealloc(tmem_base, 512);
     }
@@ -391,7 +394,7 @@ cudaError_t launch_side(const CUtensorMap& x1, const CUtensorMap& x2, const CUte
     cudaError_t e = set_max_dynamic_smem_once<bwd_tcgen05_kernel<D, kKeySide>>(BwdCfg<D>::SMEM_BYTES);
     if (e != cudaSuccess) return e;
     dim3 grid((unsigned)((p.seq + 127) / 128), (unsigned)bh);
-    bwd_tcgen05_kernel<D, kKeySide><<<grid, 192, BwdCfg<D>::SMEM_BYTES, stream>>>(x1, x2, y1, y2, p);
+    bwd_tcgen05_kernel<D, kKeySide><<<grid, 320, BwdCfg<D>::SMEM_BYTES, stream>>>(x1, x2, y1, y2, p);
     return cudaGetLastError();
 }
 
