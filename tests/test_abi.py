@@ -121,3 +121,36 @@ def test_product_does_not_import_the_oracle():
             if f.endswith((".py", ".cu", ".cuh", ".h")):
                 text = open(os.path.join(dirpath, f)).read()
                 assert "oracle" not in text.lower(), f"{f} mentions the oracle"
+
+
+def _split_args(text):
+    """Top-level comma split of an argument list (no nested parentheses in these signatures)."""
+    text = text.strip()
+    return [a for a in (x.strip() for x in text.split(",")) if a] if text and text != "void" else []
+
+
+def test_rust_binding_matches_the_header():
+    """rust/attn_ffi.rs (the extern "C" block a maintainer drops into crates/rustorch-cuda/src/) declares exactly
+    the functions of include/rustorch_attn.h with the same number of arguments, and rust/build.rs compiles exactly
+    the translation units the in-tree build compiles."""
+    import re
+    from rustorch_b200 import _lib as L
+    from rustorch_b200 import build
+    rs = open(os.path.join(ROOT, "rust", "attn_ffi.rs")).read()
+    rust = {m.group(1): len(_split_args(m.group(2)))
+            for m in re.finditer(r"pub fn (\w+)\(([^)]*)\)\s*(?:->\s*[^;]+)?;", rs, re.S)}
+    hdr = open(os.path.join(ROOT, "include", "rustorch_attn.h")).read()
+    hdr = re.sub(r"/\*.*?\*/", "", hdr, flags=re.S)
+    c = {m.group(1): len(_split_args(m.group(2)))
+         for m in re.finditer(r"\b(rt_\w+)\s*\(([^)]*)\)\s*;", hdr, re.S)}
+    assert set(rust) == set(c), (sorted(set(c) - set(rust)), sorted(set(rust) - set(c)))
+    for name, n in c.items():
+        assert rust[name] == n, f"{name}: {rust[name]} arguments in rust/attn_ffi.rs, {n} in the header"
+        assert len(L.PROTOTYPES[name][1]) == n, f"{name}: ctypes prototype has {len(L.PROTOTYPES[name][1])} arguments"
+    b = open(os.path.join(ROOT, "rust", "build.rs")).read()
+    listed = re.search(r"const SOURCES: &\[&str\] = &\[(.*?)\];", b, re.S).group(1)
+    assert [s.strip().strip('"') for s in listed.split(",") if s.strip()] == build.SOURCES
+    # the wrappers call only declared symbols
+    wrappers = open(os.path.join(ROOT, "rust", "attention.rs")).read()
+    for name in set(re.findall(r"\b(rt_\w+)\(", wrappers)):
+        assert name in rust, name

@@ -147,7 +147,7 @@ def test_decode_validation_errors():
 
 
 def test_decode_cfg4_shape_slice(oracle):
-    """BASELINE config 4 geometry (Hq=32, Hkv=8, D=128, max_seq 8192, lens ~ U[1024,8192]) on 8 of its
+    """The batched-decode workload's geometry (Hq=32, Hkv=8, D=128, max_seq 8192, lens ~ U[1024,8192]) on 8 of its
     64 sequences, full check against the oracle; plus split-invariance at the full batch."""
     import torch
     import rustorch_b200 as rt
@@ -161,7 +161,7 @@ def test_decode_cfg4_shape_slice(oracle):
 
 
 def test_decode_cfg4_full_size_split_invariance():
-    """Full config 4 (B=64): the result must not depend on how the KV range is sharded."""
+    """The full batched-decode workload (B=64): the result must not depend on how the KV range is sharded."""
     import torch
     import rustorch_b200 as rt
     B, Hq, Hkv, D, S = 64, 32, 8, 128, 8192

@@ -115,7 +115,7 @@ def test_prefill_tc_padding_keep_mask(oracle, shared):
 
 
 def test_prefill_tc_cfg1_shape(oracle):
-    """Config 1: B=1 H=8 N=2048 D=64 causal; the CPU-runnable reference case."""
+    """B=1 H=8 N=2048 D=64 causal: the small case the reference itself can run on a CPU."""
     q, k, v = _qkv(oracle, (1, 8, 2048, 64))
     out, lse = _run_tc(q, k, v, causal=True)
     _, ref, ref_lse = oracle.flash_forward_ext(q, k, v, causal=True)

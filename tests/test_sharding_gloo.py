@@ -73,7 +73,7 @@ def test_shard_units_cover_exactly_once():
 def test_kv_shard_alignment_and_config5_sizes():
     from rustorch_b200 import sharding
     spans = [sharding.kv_shard(1_048_576, 8, r, align=16) for r in range(8)]
-    assert all(e - b == 131_072 for b, e in spans)  # BASELINE config 5: 131072 positions per GPU
+    assert all(e - b == 131_072 for b, e in spans)  # the long-context workload: 131072 positions per GPU
     spans = [sharding.kv_shard(1000, 3, r, align=64) for r in range(3)]
     assert spans[0][0] == 0 and spans[-1][1] == 1000 and all(b % 64 == 0 for b, _ in spans)
 
