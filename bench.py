@@ -491,7 +491,10 @@ def main():
                                "flop_convention": "10*D*unmasked (q,k) pairs",
                                "l2": "Q,K,V,O,dO bf16 + dQ,dK,dV f32 = 1 GiB per step, larger than the 126 MB L2"},
                     "roofline": {"bound": "tensor", "achieved": btf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-                                 "frac": btf / peaks["bf16_tflops"], "peak_source": peaks["source"]},
+                                 "frac": btf / peaks["bf16_tflops"], "peak_source": peaks["source"],
+                                 "executed_frac": 1.4 * btf / peaks["bf16_tflops"],
+                                 "note": "tcgen05 kernel, two deterministic passes: 14*D flops executed per pair (scores "
+                                         "and dP are recomputed on the key side) for the 10*D counted"},
                     "gpu_launches": 3 * bsteps}
         del dob
     del q, k, v, o, lse
@@ -575,11 +578,13 @@ def main():
     dms = None
     if "decode" in legs:
         c = CFG4
-        g = torch.Generator(device="cuda").manual_seed(SEED_LEN + rank)
+        # the same lengths on every rank (weak scaling: every GPU streams the same number of bytes), own values
+        gl = torch.Generator(device="cuda").manual_seed(SEED_LEN)
+        lens = torch.randint(c["lo"], c["hi"] + 1, (c["B"],), device="cuda", generator=gl, dtype=torch.int32)
+        g = torch.Generator(device="cuda").manual_seed(SEED_LEN + 1 + rank)
         qd = torch.randn((c["B"], c["Hq"], c["D"]), device="cuda", generator=g).to(torch.bfloat16)
         kc = torch.randn((c["B"], c["Hkv"], c["S"], c["D"]), device="cuda", generator=g).to(torch.bfloat16)
         vc = torch.randn((c["B"], c["Hkv"], c["S"], c["D"]), device="cuda", generator=g).to(torch.bfloat16)
-        lens = torch.randint(c["lo"], c["hi"] + 1, (c["B"],), device="cuda", generator=g, dtype=torch.int32)
         kv_bytes = 2.0 * c["Hkv"] * c["D"] * 2 * float(lens.sum().item())
         od = torch.empty_like(qd)
         ld = torch.empty((c["B"], c["Hq"]), dtype=torch.float32, device="cuda")
@@ -609,9 +614,9 @@ def main():
             # every rank streams its own 1.2 GB; ms_per_step is the slowest rank's average over the timed region
             decode["per_rank_ms"] = rank_spread(dranks)
             decode["per_rank_gbs_fastest"] = kv_bytes / (min(dranks) * 1e-3) / 1e9
-            decode["per_rank_note"] = ("lengths differ per rank (seeded by rank), so ranks stream different byte counts "
-                                       "in slightly different times; value divides every rank's bytes by the slowest "
-                                       "rank's time")
+            decode["per_rank_note"] = ("every rank streams the same byte count (same lengths, own values); value divides "
+                                       "all ranks' bytes by the slowest rank's time, so the spread below is the spread "
+                                       "of the GPUs' own HBM rates")
             t = torch.tensor([kv_bytes], dtype=torch.float64, device="cuda")
             allb = [torch.zeros_like(t) for _ in range(world)]
             dist.all_gather(allb, t)
