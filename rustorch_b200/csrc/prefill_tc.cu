@@ -52,7 +52,7 @@ struct TcCfg {
     static constexpr int SUB_BYTES = 128 * 64 * 2;      // one 64-column (128-byte) swizzled sub-tile
     static constexpr int HALF_BYTES = 64 * 128;         // 64 rows inside a sub-tile
     static constexpr int NSUB = D / 64;
-    static constexpr int NBARS = 2 + 2 + 3 * KS + 3 * VS + 4 + 4 + 2 + 2 + 2 + 2 + 1;
+    static constexpr int NBARS = 2 + 2 + 3 * KS + 3 * VS + 4 + 4 + 2 + 2 + 2 + 2 + 1 + 1;
     // (batch, query block) pairs the length-sorted schedule can hold (two uint16 per pair); what is left of
     // the 227 KB of shared memory at D = 128 bounds it there
     static constexpr int SCHED_CAP = (D == 128) ? 384 : 2048;
@@ -77,13 +77,14 @@ struct TcParams {
     int n_qb;          // 256-row blocks per head
     int slots_per_head, n_slots, paired;  // static schedule, see tc_item
     int sorted;        // length-sorted schedule (launches with per-batch kv_lens), see tc_item
-    int single_tile;   // items are 128-row blocks handled by Q tile 1 alone (small launches, see tc_item)
+    int stagger_clocks;  // single-tile items: head start of tile 0 over tile 1, in SM clocks
+    int single_tile;   // items are 128-row blocks whose 64-key steps alternate between the two tiles (small launches, see tc_item)
 };
 
 
 // Timeout codes written to the device status word (100 + site).
 enum { kToQ = 101, kToKFull, kToKEmpty, kToVFull, kToVEmpty, kToSFull, kToPFull, kToOFull, kToDone, kToDrain,
-       kToQEmpty, kToOFree, kToStage };
+       kToQEmpty, kToOFree, kToStage, kToMerge };
 
 // 2^x for a pair of arguments on the FMA and integer pipes (x <= ~100): round to the nearest
 // integer n with the 1.5*2^23 trick, a cubic for 2^r on r = x - n in [-0.5, 0.5] (relative error
@@ -111,28 +112,36 @@ __device__ __forceinline__ float2 exp2_poly2(float2 x) {
 // than that costs more issue slots on the FMA pipe than it frees on the MUFU pipe).
 __host__ __device__ constexpr bool poly_pair(int q) { return (q & 3) == 3; }
 
+__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // One work item of a CTA's static list.
 struct TcItem {
     int bh, b, h, h_kv, q0, kv_hi, q_off;  // bh = b * heads + h indexes LSE; h_kv is the KV head h reads
-    int U0, U1;    // 64-key steps of each Q tile (U0 <= U1); scalars, so nothing is indexed dynamically
+    int U0, U1;    // 64-key steps of each Q tile; scalars, so nothing is indexed dynamically
     int n_tiles;   // 128-key K/V tiles to load
     bool end;      // the list is exhausted
     bool valid;    // false: this position of the list holds no item
     __device__ __forceinline__ int steps(int w) const { return w ? U1 : U0; }
+    // first query row of tile w: the tiles are stacked (q0, q0 + 128), or both sit on the item's one block
+    __device__ __forceinline__ int qrow(int w, bool single) const { return q0 + ((w || single) ? 128 : 0); }
 };
 
 // Static schedule.  The (batch, head)-major slot list is dealt round-robin to the CTAs, so the
 // CTAs running at one time work on a few neighbouring heads and share their K/V in L2.  In
 // paired mode a slot holds the 256-row blocks r and n_qb-1-r of one head, heavy one first: under
 // a causal mask every slot then costs the same, and the CTAs finish together.  A launch with fewer
-// 256-row blocks than 3/4 of the SMs uses 128-row items instead (single_tile): twice the CTAs, each with
-// one Q tile, which shortens the critical path of a small problem.
+// 256-row blocks than 3/4 of the SMs uses 128-row items instead (single_tile): twice the CTAs, and inside
+// a CTA the item's 64-key steps alternate between the two tiles (tile 0 takes the even steps = the first
+// half of every 128-key K/V tile, tile 1 the odd ones), each with its own running max, sum and accumulator;
+// the epilogue merges the two partial results straight out of TMEM.  Both softmax warpgroups and both MMA
+// issuers then work on the one block, which nearly halves the critical path of a small problem.
 // Sorted mode (per-batch kv_lens, where an item's cost is only known on the device): every CTA ranks the
 // (batch, query block) pairs by their step count at start-up (the same deterministic sort in every CTA, so
 // no queue, no atomics and no scratch memory are needed), the item list is that order with all heads of a
 // pair side by side, and it is dealt to the CTAs boustrophedon (0..G-1, G-1..0, ...), heaviest first: the
 // persistent kernel's overlap of one item's set-up with the previous item's tail, and a balanced finish.
-template <bool kCausal>
+template <bool kCausal, bool kSingle>
 __device__ __forceinline__ void tc_steps(const TcParams& p, int b, int q0, int& kv_hi, int& q_off, int& U0, int& U1) {
     kv_hi = p.seq_kv;
     if (p.kv_lens) {
@@ -142,11 +151,15 @@ __device__ __forceinline__ void tc_steps(const TcParams& p, int b, int q0, int& 
     q_off = p.q_offsets ? p.q_offsets[b] : 0;   // query row i sits at key position i + q_off
     const int n_steps = (kv_hi + 63) / 64;      // 64-key steps that hold a visible key
     const int last0 = q0 + 127 + q_off, last1 = last0 + 128;  // last key each tile's last row may see
-    U0 = p.single_tile ? 0 : (!kCausal ? n_steps : (last0 < 0 ? 0 : min(n_steps, last0 / 64 + 1)));
+    U0 = !kCausal ? n_steps : (last0 < 0 ? 0 : min(n_steps, last0 / 64 + 1));
     U1 = !kCausal ? n_steps : (last1 < 0 ? 0 : min(n_steps, last1 / 64 + 1));
+    if (kSingle) {  // the block's U1 steps are dealt alternately: even ones to tile 0, odd ones to tile 1
+        U0 = (U1 + 1) >> 1;
+        U1 = U1 >> 1;
+    }
 }
 
-template <bool kCausal>
+template <bool kCausal, bool kSingle>
 __device__ __forceinline__ TcItem tc_item(int j, const TcParams& p, const uint16_t* sched) {
     TcItem it;
     it.valid = false;
@@ -178,11 +191,11 @@ __device__ __forceinline__ TcItem tc_item(int j, const TcParams& p, const uint16
     }
     it.valid = true;
     it.h_kv = it.h / (p.heads / p.heads_kv);
-    // Single-tile items: block qb covers rows [128 qb, 128 qb + 128) and is given to Q tile 1, so the
-    // item's origin lies 128 rows earlier and Q tile 0 takes no part (its rows belong to another item).
-    it.q0 = p.single_tile ? qb * 128 - 128 : qb * 256;
-    tc_steps<kCausal>(p, it.b, it.q0, it.kv_hi, it.q_off, it.U0, it.U1);
-    it.n_tiles = (it.U1 + 1) / 2;
+    // Single-tile items: block qb covers rows [128 qb, 128 qb + 128); the item's origin is kept 128 rows
+    // earlier so that the block sits where tile 1 sits in a two-tile item (TcItem::qrow).
+    it.q0 = kSingle ? qb * 128 - 128 : qb * 256;
+    tc_steps<kCausal, kSingle>(p, it.b, it.q0, it.kv_hi, it.q_off, it.U0, it.U1);
+    it.n_tiles = kSingle ? it.U0 : (it.U1 + 1) / 2;
     return it;
 }
 
@@ -196,7 +209,7 @@ __device__ __forceinline__ TcItem tc_item(int j, const TcParams& p, const uint16
 // (o_free: the next item's first PV may overwrite it), stages it in the Q buffer (stage_full),
 // one thread stores it (q_empty: the next item's Q may land).  A tile that sees no key in an
 // item takes no part in these (its rows are written as NaN directly).
-template <int D, bool kCausal, bool kKeep>
+template <int D, bool kCausal, bool kKeep, bool kSingle>
 __global__ void __launch_bounds__(384, 1)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                   const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
@@ -223,7 +236,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     uint64_t* o_free = o_done + 2;        // [2]  one phase per item: the epilogue has read O out of TMEM
     uint64_t* stage_full = o_free + 2;    // [2]  one phase per item: the O tile is staged in shared memory
     uint64_t* done_bar = stage_full + 2;  // [1]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done_bar + 1);
+    uint64_t* merge_bar = done_bar + 1;   // [1]  single-tile items: both tiles have published their (max, sum)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(merge_bar + 1);
     uint16_t* sched = reinterpret_cast<uint16_t*>(tmem_slot + 4);  // [SCHED_CAP] pair order, then [SCHED_CAP] step counts
 
     // Broadcasting the warp index makes it provably warp-uniform, so role dispatch and the MMA
@@ -233,14 +247,19 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     const int Nkv = p.seq_kv;
 
     // ------------------------------------------------------------------ setup
+    // Launched with programmatic stream serialization, the CTA may start while the previous kernel of
+    // the stream is still running: barrier set-up and the TMEM allocation then overlap that kernel's tail.
+    // grid_dep_wait returns once the previous kernel has completed and its writes are visible (at once under
+    // a normal launch); every global access of this kernel comes after one.
     if (p.sorted) {
+        grid_dep_wait();  // kv_lens may be the previous kernel's output
         // Rank sort of the (batch, query block) pairs by their step count, descending, ties by index:
         // every CTA computes the same table.
         uint16_t* cost = sched + C::SCHED_CAP;
         const int n_pairs = p.n_slots / p.heads;
         for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
             int kv_hi, q_off, U0, U1;
-            tc_steps<kCausal>(p, i / p.n_qb, (i % p.n_qb) * 256, kv_hi, q_off, U0, U1);
+            tc_steps<kCausal, kSingle>(p, i / p.n_qb, (i % p.n_qb) * 256, kv_hi, q_off, U0, U1);
             cost[i] = (uint16_t)min(U0 + U1, 65535);
         }
         __syncthreads();
@@ -267,7 +286,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             mbar_init(&o_full[i], 1);
             mbar_init(&o_done[i], 1);
             mbar_init(&o_free[i], 128);
-            mbar_init(&stage_full[i], 128);
+            mbar_init(&stage_full[i], kSingle ? 256 : 128);  // both warpgroups stage a single-tile item's rows
         }
         for (int i = 0; i < 4; ++i) {
             mbar_init(&s_full[i], 1);
@@ -284,19 +303,32 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             mbar_init(&v_empty[VS + i], 1);
         }
         mbar_init(done_bar, 2);
+        mbar_init(merge_bar, 256);
         fence_barrier_init();
         fence_proxy_async();
+        grid_dep_wait();
         // Q and the first K tile of the first item are requested right away, so their latency
         // overlaps the TMEM allocation and the CTA-wide barrier below.
-        const TcItem it = tc_item<kCausal>(0, p, sched);
-        if (!it.end && it.valid && it.U1 > 0) {
+        const TcItem it = tc_item<kCausal, kSingle>(0, p, sched);
+        if (!it.end && it.valid && it.n_tiles > 0) {
             first_preloaded = true;
-            for (int w = 0; w < 2; ++w) {
-                if (w == 0 && it.U0 == 0) continue;
+            if constexpr (kSingle) {
+                // one Q tile serves both issuers (buffer 1, which also stages the output); K tile 0 follows
+                mbar_arrive_expect_tx(&q_full[1], TILE);
+#pragma unroll
+                for (int s = 0; s < C::NSUB; ++s)
+                    tma_load_4d(sQ + TILE + s * SUB, &tm_q, &q_full[1], s * 64, it.qrow(1, true), it.h, it.b);
+                mbar_arrive_expect_tx(&k_full[0], TILE);
+#pragma unroll
+                for (int s = 0; s < C::NSUB; ++s)
+                    tma_load_4d(sK + s * SUB, &tm_k, &k_full[0], s * 64, 0, it.h_kv, it.b);
+            }
+            for (int w = 0; w < 2 && !kSingle; ++w) {
+                if (it.steps(w) == 0) continue;
                 mbar_arrive_expect_tx(&q_full[w], TILE);
 #pragma unroll
                 for (int s = 0; s < C::NSUB; ++s)
-                    tma_load_4d(sQ + w * TILE + s * SUB, &tm_q, &q_full[w], s * 64, it.q0 + w * 128, it.h, it.b);
+                    tma_load_4d(sQ + w * TILE + s * SUB, &tm_q, &q_full[w], s * 64, it.qrow(w, kSingle), it.h, it.b);
                 if (w == 0 || it.U0 == 0) {
                     mbar_arrive_expect_tx(&k_full[0], TILE);
 #pragma unroll
@@ -314,6 +346,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    grid_dep_wait();
+    // The next kernel of the stream may be scheduled as SMs fall free (it waits as above before it reads or
+    // writes anything): its launch latency and set-up hide behind the tail of this grid.
+    grid_dep_launch();
 
     // The register hand-over sits inside each role's own branch: the compiler budgets the code
     // that follows a setmaxnreg only when no path with a different budget merges into it.
@@ -321,21 +357,63 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
       if (warp == 8) {
         // ============================================================== TMA producer
-        if (lane == 0) {
+        if (lane == 0 && kSingle) {
+            // A single-tile item is its CTA's only item; Q and K tile 0 were requested during setup.  Each
+            // issuer reads every tile once and asks for K tile u + 2 right after the PV of step u, so K runs
+            // two tiles ahead of V in the request order: K1 | K2 V0 | K3 V1 | ...
+            const TcItem it = tc_item<kCausal, kSingle>(0, p, sched);
+            if (first_preloaded) {
+                bool ok = true;
+                int kg = 1, vg = 0;
+                auto load_k = [&](int t) {
+                    const int ks = t % KS;
+                    const uint32_t par = ((uint32_t)(t / KS) & 1u) ^ 1u;
+                    if (!mbar_wait(&k_empty[ks], par, p.status, kToKEmpty) ||
+                        !mbar_wait(&k_empty[KS + ks], par, p.status, kToKEmpty))
+                        return false;
+                    mbar_arrive_expect_tx(&k_full[ks], TILE);
+#pragma unroll
+                    for (int s = 0; s < C::NSUB; ++s)
+                        tma_load_4d(sK + ks * TILE + s * SUB, &tm_k, &k_full[ks], s * 64, t * 128, it.h_kv, it.b);
+                    ++kg;
+                    return true;
+                };
+                if (it.n_tiles > 1) ok = load_k(1);
+                for (int t = 0; t < it.n_tiles && ok; ++t) {
+                    if (t + 2 < it.n_tiles && !load_k(t + 2)) break;
+                    const int vs = t % VS;
+                    const uint32_t par = ((uint32_t)(t / VS) & 1u) ^ 1u;
+                    if (!mbar_wait(&v_empty[vs], par, p.status, kToVEmpty) ||
+                        !mbar_wait(&v_empty[VS + vs], par, p.status, kToVEmpty))
+                        break;
+                    mbar_arrive_expect_tx(&v_full[vs], TILE);
+#pragma unroll
+                    for (int s = 0; s < C::NSUB; ++s)
+                        tma_load_4d(sV + vs * TILE + s * SUB, &tm_v, &v_full[vs], s * 64, t * 128, it.h_kv, it.b);
+                    ++vg;
+                }
+                // Drain: every copy this thread issued must have landed before the CTA may exit.
+                mbar_wait(&q_full[1], 0u, p.status, kToDrain);
+                for (int t = max(0, kg - KS); t < kg; ++t)
+                    mbar_wait(&k_full[t % KS], (uint32_t)(t / KS) & 1u, p.status, kToDrain);
+                for (int t = max(0, vg - VS); t < vg; ++t)
+                    mbar_wait(&v_full[t % VS], (uint32_t)(t / VS) & 1u, p.status, kToDrain);
+            }
+        } else if (lane == 0) {
             int kg = 0, vg = 0;    // K / V tiles requested so far (ring position and phase)
             int na0 = 0, na1 = 0;  // items so far in which tile w took part (phase of its per-item barriers)
             bool ok = true;
             for (int j = 0; ok; ++j) {
-                const TcItem it = tc_item<kCausal>(j, p, sched);
+                const TcItem it = tc_item<kCausal, kSingle>(j, p, sched);
                 if (it.end) break;
-                if (!it.valid || it.U1 == 0) continue;  // nothing to load
+                if (!it.valid || it.n_tiles == 0) continue;  // nothing to load
                 auto load_q = [&](int w, int na) {
                     // the previous item's O tile must have left the buffer
                     if (!mbar_wait(&q_empty[w], ((uint32_t)na & 1u) ^ 1u, p.status, kToQEmpty)) return false;
                     mbar_arrive_expect_tx(&q_full[w], TILE);
 #pragma unroll
                     for (int s = 0; s < C::NSUB; ++s)
-                        tma_load_4d(sQ + w * TILE + s * SUB, &tm_q, &q_full[w], s * 64, it.q0 + w * 128, it.h, it.b);
+                        tma_load_4d(sQ + w * TILE + s * SUB, &tm_q, &q_full[w], s * 64, it.qrow(w, kSingle), it.h, it.b);
                     return true;
                 };
                 const bool pre = first_preloaded && j == 0;  // Q and K tile 0 were requested during setup
@@ -359,7 +437,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                             tma_load_4d(sK + ks * TILE + s * SUB, &tm_k, &k_full[ks], s * 64, t * 128, it.h_kv, it.b);
                     }
                     ++kg;
-                    if (t == 0) {  // tile 1 usually still works on the previous item: its Q comes second
+                    if (t == 0 && it.U1 > 0) {  // tile 1 usually still works on the previous item: its Q comes second
                         if (!pre && !load_q(1, na1)) {
                             ok = false;
                             break;
@@ -398,7 +476,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             constexpr uint32_t idesc_o = make_idesc_bf16(128, D, 0, 1);
             // Descriptors are built once; each MMA only adds an offset (in 16-byte units) to the
             // start-address field, so the issuing thread keeps ahead of the tensor pipe.
-            const uint64_t dq = make_smem_desc_sw128(smem_u32(sQ + w * TILE), 16, 1024);
+            const uint64_t dq = make_smem_desc_sw128(smem_u32(sQ + (kSingle ? 1 : w) * TILE), 16, 1024);
             const uint64_t dk = make_smem_desc_sw128(smem_u32(sK), 16, 1024);
             const uint64_t dv = make_smem_desc_sw128(smem_u32(sV), SUB, 1024);
             const uint32_t tS = tmem_base + C::COL_S + w * 128, tO = tmem_base + C::COL_O + w * D;
@@ -415,13 +493,17 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             };
             bool ok = true;
             for (int j = 0; ok; ++j) {
-                const TcItem it = tc_item<kCausal>(j, p, sched);
+                const TcItem it = tc_item<kCausal, kSingle>(j, p, sched);
                 if (it.end) break;
-                if (!it.valid || it.U1 == 0) continue;
+                if (!it.valid || it.n_tiles == 0) continue;
                 const int n_u = it.steps(w);
-                // S_w(u): keys [64u, 64u+64) = rows (u&1)*64.. of the item's K tile u/2
+                // Step u of this tile reads half half_of(u) (64 rows) of the item's K/V tile tile_of(u): the
+                // tile's own steps are consecutive 64-key steps, or (single-tile items) every second one.
+                constexpr bool il = kSingle;
+                auto tile_of = [&](int u) { return il ? u : (u >> 1); };
+                auto half_of = [&](int u) { return il ? w : (u & 1); };
                 auto issue_S = [&](int u) {
-                    const uint64_t bk = dk + (uint64_t)((((kg + (u >> 1)) % KS) * TILE + (u & 1) * HALF) >> 4);
+                    const uint64_t bk = dk + (uint64_t)((((kg + tile_of(u)) % KS) * TILE + half_of(u) * HALF) >> 4);
                     const uint32_t d = tS + (u & 1) * 64;
 #pragma unroll
                     for (int kk = 0; kk < D / 16; ++kk) {
@@ -431,7 +513,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 };
                 // O_w += P V(u): P (bf16) sits in the first 32 columns of S[w][u&1]
                 auto issue_PV = [&](int u) {
-                    const uint64_t bv = dv + (uint64_t)((((vg + (u >> 1)) % VS) * TILE + (u & 1) * HALF) >> 4);
+                    const uint64_t bv = dv + (uint64_t)((((vg + tile_of(u)) % VS) * TILE + half_of(u) * HALF) >> 4);
                     const uint32_t a = tS + (u & 1) * 64;
                     const uint32_t acc0 = u > 0 ? 1u : 0u;
 #pragma unroll
@@ -439,23 +521,30 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                         if (leader)
                             mma_ts(tO, a + kk * 8, bv + (uint64_t)((kk * 2048) >> 4), idesc_o, kk > 0 ? 1u : acc0);
                 };
-                auto last_use = [&](int u) { return (u & 1) || u == n_u - 1; };  // of a 128-key tile, by this Q tile
+                auto last_use = [&](int u) { return il || (u & 1) || u == n_u - 1; };  // of a 128-key tile, by this Q tile
 
                 if (n_u > 0) {
                     ok = wait(&k_full[kg % KS], (uint32_t)(kg / KS) & 1u, kToKFull) &&
-                         wait(&q_full[w], (uint32_t)na & 1u, kToQ);
+                         wait(&q_full[il ? 1 : w], (uint32_t)na & 1u, kToQ);
                     if (!ok) break;
                     tc_fence_after();
                     issue_S(0);
                     commit(&s_full[w * 2]);
+                    int k_waited = 0, v_waited = -1;  // item-local tile indices already waited for
+                    if (il) commit(&ke[kg % KS]);
                     if (n_u > 1) {
+                        if (il) {  // the second step reads the next K tile
+                            if (!wait(&k_full[(kg + 1) % KS], (uint32_t)((kg + 1) / KS) & 1u, kToKFull)) { ok = false; break; }
+                            k_waited = 1;
+                            tc_fence_after();
+                        }
                         issue_S(1);
                         commit(&s_full[w * 2 + 1]);
+                        if (il) commit(&ke[(kg + 1) % KS]);
                     }
-                    commit(&ke[kg % KS]);
-                    int k_waited = 0, v_waited = -1;  // item-local tile indices already waited for
+                    if (!il) commit(&ke[kg % KS]);
                     for (int u = 0; u < n_u && ok; ++u) {
-                        const int vt = u >> 1;
+                        const int vt = tile_of(u);
                         if (vt > v_waited) {
                             if (!wait(&v_full[(vg + vt) % VS], (uint32_t)((vg + vt) / VS) & 1u, kToVFull)) { ok = false; break; }
                             v_waited = vt;
@@ -469,7 +558,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                         if (u == n_u - 1) commit(&o_done[w]);
                         if (last_use(u)) commit(&ve[(vg + vt) % VS]);
                         if (u + 2 < n_u) {
-                            const int kt = (u + 2) >> 1;
+                            const int kt = tile_of(u + 2);
                             if (kt > k_waited) {
                                 if (!wait(&k_full[(kg + kt) % KS], (uint32_t)((kg + kt) / KS) & 1u, kToKFull)) { ok = false; break; }
                                 k_waited = kt;
@@ -486,7 +575,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 }
                 // Tiles this Q tile does not read (it sees fewer keys than the other one) are passed on
                 // once they have landed, which keeps this issuer inside the ring window.
-                for (int t = (n_u + 1) / 2; t < it.n_tiles && ok; ++t) {
+                for (int t = il ? n_u : (n_u + 1) / 2; t < it.n_tiles && ok; ++t) {
                     ok = wait(&k_full[(kg + t) % KS], (uint32_t)((kg + t) / KS) & 1u, kToKFull);
                     if (ok) commit(&ke[(kg + t) % KS]);
                     ok = ok && wait(&v_full[(vg + t) % VS], (uint32_t)((vg + t) / VS) & 1u, kToVFull);
@@ -515,16 +604,19 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         bool ok = true;
 
         for (int j = 0; ok; ++j) {
-            const TcItem it = tc_item<kCausal>(j, p, sched);
+            const TcItem it = tc_item<kCausal, kSingle>(j, p, sched);
             if (it.end) break;
             if (!it.valid) continue;
             const int n_iter = it.steps(w);
+            constexpr bool il = kSingle;  // this tile's steps are every second 64-key step of the block
             const int bh = it.bh, kv_hi = it.kv_hi, q_off = it.q_off;
-            const int row = it.q0 + w * 128 + row_in_tile;  // query index within the sequence
+            const int row = it.qrow(w, il) + row_in_tile;  // query index within the sequence
             const uint8_t* keep = kKeep ? p.key_keep + (int64_t)it.b * p.keep_batch_stride : nullptr;
 
-            if (n_iter == 0) {  // the tile sees no key: NaN rows, LSE = -inf (cpu_forward.rs:411-420)
-                if (row < N && !(p.single_tile && w == 0)) {
+            // The tile sees no key: NaN rows, LSE = -inf (cpu_forward.rs:411-420).  A single-tile item whose
+            // other tile has a step still goes through the merge below with an empty partial result.
+            if (n_iter == 0 && !(il && it.n_tiles > 0)) {
+                if (row < N && !(il && w == 0)) {
                     uint4* dst = reinterpret_cast<uint4*>(p.out + it.b * p.o_stride_b + it.h * p.o_stride_h +
                                                           (int64_t)row * p.o_stride_row);
 #pragma unroll
@@ -545,6 +637,14 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                     break;
                 }
                 tc_fence_after();
+                if (il && w == 1 && u == 0 && p.stagger_clocks > 0) {
+                    // The two tiles of a single-tile item start together and would stay in step: both
+                    // warps of a scheduler would then wait for TMEM at the same moments.  Half a step of
+                    // offset lets one tile's loads and stores hide behind the other's arithmetic
+                    // (measured: 0.5-1 us of 21 on B=1 H=8 N=2048 D=64; RT_ATTN_PREFILL_STAGGER sets the clocks).
+                    const long long t0 = clock64();
+                    while (clock64() - t0 < p.stagger_clocks) {}
+                }
 
                 uint32_t s[64];
                 {
@@ -556,7 +656,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 }
 
                 // ---- masks: keys beyond kv_hi, causal diagonal, keep flags
-                const int col0 = u * 64;
+                const int col0 = (il ? 2 * u + w : u) * 64;
                 int lim = kv_hi - 1 - col0;                       // last visible column in this step
                 if (kCausal) lim = min(lim, row + q_off - col0);
                 if (lim < 63) {
@@ -639,7 +739,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                     tmem_st16(tS + buf * 64 + ch * 16, pk);
                 }
                 l += (sum_a.x + sum_a.y) + (sum_b.x + sum_b.y);
-                tc_wait_st();
+                tc_wait_st();  // warp-wide: every lane's part of the store has completed
                 tc_fence_before();
                 mbar_arrive(&p_full[w * 2 + buf]);
             }
@@ -648,12 +748,81 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             // ---- epilogue: O / l -> bf16 into the (now idle) shared-memory tile of Q_w in the swizzled
             // layout of the output tensor map, then one TMA store per 64-column half: 16-byte shared
             // stores instead of row-strided global stores, and rows past N are clipped by the hardware.
-            if (!__all_sync(kFullMask, mbar_wait(&o_done[w], (uint32_t)na & 1u, p.status, kToOFull))) {
+            if (n_iter > 0 && !__all_sync(kFullMask, mbar_wait(&o_done[w], (uint32_t)na & 1u, p.status, kToOFull))) {
                 ok = false;
                 break;
             }
             tc_fence_after();
-            {
+            if (il) {
+                // ---- single-tile item: the two tiles hold partial results of the same 128 rows (even and odd
+                // 64-key steps).  Each thread publishes its (max, sum, seen) in the first columns of its tile's
+                // idle score buffer, TMEM being readable by the other warpgroup's warp of the same lane
+                // quarter; after the barrier every thread knows both partials of its row.  The merged row is
+                //   O = (f0 O_0 + f1 O_1) / (f0 l_0 + f1 l_1),  f_w = 2^((m_w - max(m_0, m_1)) c),
+                // and warpgroup w produces columns [w D/2, (w+1) D/2) of it from both accumulators.
+                {
+                    uint32_t ex[16];
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) ex[i] = 0u;
+                    ex[0] = __float_as_uint(m_ref);
+                    ex[1] = __float_as_uint(l);
+                    ex[2] = seen ? 1u : 0u;
+                    tmem_st16(tS, ex);
+                    tc_wait_st();
+                    tc_fence_before();
+                    mbar_arrive(merge_bar);
+                }
+                if (!__all_sync(kFullMask, mbar_wait(merge_bar, (uint32_t)na & 1u, p.status, kToMerge))) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t tS_other = tmem_base + lane_sel + C::COL_S + (1 - w) * 128;
+                const uint32_t tO_other = tmem_base + lane_sel + C::COL_O + (1 - w) * D;
+                uint32_t exo[16];
+                tmem_ld16(tS_other, exo);
+                tc_wait_ld();
+                const float m_o = __uint_as_float(exo[0]), l_o = __uint_as_float(exo[1]);
+                const bool seen_any = seen || (exo[2] != 0u);
+                const float m_all = fmaxf(m_ref, m_o);
+                const float f_own = (m_ref == -INFINITY) ? 0.f : fast_exp2((m_ref - m_all) * c);
+                const float f_oth = (m_o == -INFINITY) ? 0.f : fast_exp2((m_o - m_all) * c);
+                const float l_all = f_own * l + f_oth * l_o;
+                const bool valid = seen_any && (l_all > 0.f);
+                const float inv = valid ? 1.f / l_all : 0.f;
+                const float a_own = f_own * inv, a_oth = f_oth * inv;
+                const bool has_own = n_iter > 0, has_oth = it.steps(1 - w) > 0;  // an idle tile's accumulator was never written
+                uint8_t* stage = sQ + TILE + row_in_tile * 128;  // tile 1's Q buffer: every score MMA of the item has retired
+#pragma unroll
+                for (int cq = 0; cq < D / 64; ++cq) {
+                    const int ch = w * (D / 64) + cq;
+                    uint32_t oa[32], ob[32];
+                    if (has_own) tmem_ld32(tO + ch * 32, oa);
+                    if (has_oth) tmem_ld32(tO_other + ch * 32, ob);
+                    tc_wait_ld();
+#pragma unroll
+                    for (int v4 = 0; v4 < 4; ++v4) {
+                        uint4 pack;
+                        uint32_t* pw = reinterpret_cast<uint32_t*>(&pack);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const int e = v4 * 8 + 2 * i;
+                            const float x0 = (has_own ? __uint_as_float(oa[e]) * a_own : 0.f) +
+                                             (has_oth ? __uint_as_float(ob[e]) * a_oth : 0.f);
+                            const float x1 = (has_own ? __uint_as_float(oa[e + 1]) * a_own : 0.f) +
+                                             (has_oth ? __uint_as_float(ob[e + 1]) * a_oth : 0.f);
+                            pw[i] = valid ? float2_to_bf16x2(x0, x1) : 0x7fc07fc0u;
+                        }
+                        const int cc = ch * 4 + v4;
+                        *reinterpret_cast<uint4*>(stage + (cc / 8) * SUB + (((cc % 8) ^ (row_in_tile & 7)) << 4)) = pack;
+                    }
+                }
+                if (w == 1 && p.lse && row < N)
+                    p.lse[(int64_t)bh * N + row] =
+                        valid ? (m_all * c + fast_log2(l_all)) * kLn2 : (seen_any ? NAN : -INFINITY);
+                fence_proxy_async();
+                mbar_arrive(&stage_full[1]);
+            } else {
                 // A masked score costs the polynomial path 2^-125 instead of 0, so a row counts as
                 // empty when it never saw a visible score, not when its sum is exactly 0.
                 const bool valid = seen && (l > 0.f);
@@ -688,13 +857,13 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 fence_proxy_async();  // generic-proxy writes above -> visible to the TMA (async proxy) read
                 mbar_arrive(&stage_full[w]);
             }
-            if (row_in_tile == 0) {
+            if (row_in_tile == 0 && !(il && w == 0)) {
                 if (!mbar_wait(&stage_full[w], (uint32_t)na & 1u, p.status, kToStage)) {
                     ok = false;
                 } else {
 #pragma unroll
                     for (int s = 0; s < C::NSUB; ++s)
-                        tma_store_4d(&tm_o, sQ + w * TILE + s * SUB, s * 64, it.q0 + w * 128, it.h, it.b);
+                        tma_store_4d(&tm_o, sQ + w * TILE + s * SUB, s * 64, it.qrow(w, il), it.h, it.b);
                     tma_store_commit_and_wait_read();  // the staged tile has been read: the next Q may land
                     mbar_arrive(&q_empty[w]);
                 }
@@ -807,14 +976,40 @@ bool make_tensor_map_bf16_3d(CUtensorMap* map, const void* base, int64_t bh, int
     return encode_bf16_map_cached(map, 3, base, dims, strides, box);
 }
 
+template <int D, bool kCausal, bool kKeep, bool kSingle>
+static cudaError_t launch_tc_s(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mo,
+                             const TcParams& p, int64_t n_ctas, cudaStream_t stream) {
+    auto kern = prefill_tc_kernel<D, kCausal, kKeep, kSingle>;
+    cudaError_t e = set_max_dynamic_smem_once<prefill_tc_kernel<D, kCausal, kKeep, kSingle>>(TcCfg<D>::SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    // RT_ATTN_PREFILL_PDL=0|1 forces programmatic stream serialization off or on.
+    static const int env_pdl = [] {
+        const char* s = getenv("RT_ATTN_PREFILL_PDL");
+        return s ? (s[0] == '0' ? 0 : 1) : -1;
+    }();
+    // Measured: the overlap pays for short single-tile launches (up to 1 us of 9-16 us); for long ones the
+    // dependency wait costs as much as the launch gap it hides.
+    const bool pdl = env_pdl >= 0 ? env_pdl == 1 : (kSingle && p.seq_kv <= 1024);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)n_ctas);
+    cfg.blockDim = dim3(384);
+    cfg.dynamicSmemBytes = TcCfg<D>::SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    if (pdl) {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+    }
+    return cudaLaunchKernelEx(&cfg, kern, mq, mk, mv, mo, p);
+}
+
 template <int D, bool kCausal, bool kKeep>
 static cudaError_t launch_tc(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mo,
                              const TcParams& p, int64_t n_ctas, cudaStream_t stream) {
-    auto kern = prefill_tc_kernel<D, kCausal, kKeep>;
-    cudaError_t e = set_max_dynamic_smem_once<prefill_tc_kernel<D, kCausal, kKeep>>(TcCfg<D>::SMEM_BYTES);
-    if (e != cudaSuccess) return e;
-    kern<<<(unsigned)n_ctas, 384, TcCfg<D>::SMEM_BYTES, stream>>>(mq, mk, mv, mo, p);
-    return cudaGetLastError();
+    return p.single_tile ? launch_tc_s<D, kCausal, kKeep, true>(mq, mk, mv, mo, p, n_ctas, stream)
+                         : launch_tc_s<D, kCausal, kKeep, false>(mq, mk, mv, mo, p, n_ctas, stream);
 }
 
 cudaError_t launch_prefill_tc(const void* q, const void* k, const void* v, void* out, float* lse, int64_t batch,
@@ -869,6 +1064,11 @@ cudaError_t launch_prefill_tc(const void* q, const void* k, const void* v, void*
         return (s && !strcmp(s, "persistent")) ? 1 : (s && !strcmp(s, "percta")) ? 2 : 0;
     }();
     p.single_tile = (seq > 128 && bh * ((seq + 255) / 256) * 4 < 3 * (int64_t)n_sm) ? 1 : 0;
+    static const int env_stagger = [] {
+        const char* s = getenv("RT_ATTN_PREFILL_STAGGER");
+        return s ? atoi(s) : 900;
+    }();
+    p.stagger_clocks = env_stagger;
     if (env_tiles == 1) p.single_tile = 1;
     if (env_tiles == 2) p.single_tile = 0;
     const int64_t n_qb = p.single_tile ? (seq + 127) / 128 : (seq + 255) / 256;
@@ -876,7 +1076,7 @@ cudaError_t launch_prefill_tc(const void* q, const void* k, const void* v, void*
     if (n_items > 0x3fffffff) return cudaErrorInvalidValue;
     p.n_qb = (int)n_qb;
     bool persistent = causal && kv_lens == nullptr && n_items >= 2 * (int64_t)n_sm && !p.single_tile;
-    if (env_sched == 1) persistent = true;
+    if (env_sched == 1 && !p.single_tile) persistent = true;  // a single-tile item is its CTA's only item (the merge reuses barriers)
     if (env_sched == 2) persistent = false;
     p.paired = (persistent && n_items >= 2 * (int64_t)n_sm) ? 1 : 0;
     // Per-batch lengths: the length-sorted persistent schedule, if its table fits (tc_item).
