@@ -80,22 +80,49 @@ struct BwdTcParams {
     float scale, scale_log2;
 };
 
-// delta_i = dO_i . O_i from the bf16 forward output, one warp per row.
+// delta_i = dO_i . O_i from the bf16 forward output.  Each thread takes 16 bytes (8 elements) of both
+// tensors, so D / 8 neighbouring lanes cover a row, a warp covers 32 / (D / 8) rows per pass and runs two
+// passes with all four loads in flight: the kernel is a pure HBM stream (4 D bytes per row).
+template <int D>
 __global__ void __launch_bounds__(256) bwd_delta_bf16_kernel(const __nv_bfloat16* __restrict__ out,
                                                              const __nv_bfloat16* __restrict__ d_out,
-                                                             float* __restrict__ delta, int64_t rows, int dim) {
-    const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
-    const int lane = threadIdx.x & 31;
-    if (row >= rows) return;
-    float acc = 0.f;
-    for (int d = lane * 2; d < dim; d += 64) {
-        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(out + row * dim + d));
-        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(d_out + row * dim + d));
-        acc = fmaf(a.x, b.x, fmaf(a.y, b.y, acc));
+                                                             float* __restrict__ delta, int64_t rows) {
+    constexpr int LPR = D / 8;        // lanes per row
+    constexpr int RPW = 32 / LPR;     // rows per warp and pass
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int sub = lane / LPR, col = (lane % LPR) * 8;
+    const int64_t row0 = ((int64_t)blockIdx.x * 8 + warp) * (2 * RPW) + sub;
+    float acc[2];
+    uint4 a[2], b[2];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+        const int64_t row = row0 + u * RPW;
+        if (row < rows) {
+            a[u] = __ldg(reinterpret_cast<const uint4*>(out + row * D + col));
+            b[u] = __ldg(reinterpret_cast<const uint4*>(d_out + row * D + col));
+        } else {
+            a[u] = b[u] = make_uint4(0u, 0u, 0u, 0u);
+        }
     }
 #pragma unroll
-    for (int off = 16; off; off >>= 1) acc += __shfl_xor_sync(kFullMask, acc, off);
-    if (lane == 0) delta[row] = acc;
+    for (int u = 0; u < 2; ++u) {
+        const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&a[u]);
+        const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&b[u]);
+        float s = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 x = __bfloat1622float2(pa[i]), y = __bfloat1622float2(pb[i]);
+            s = fmaf(x.x, y.x, fmaf(x.y, y.y, s));
+        }
+#pragma unroll
+        for (int off = LPR / 2; off; off >>= 1) s += __shfl_xor_sync(kFullMask, s, off);
+        acc[u] = s;
+    }
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+        const int64_t row = row0 + u * RPW;
+        if (col == 0 && row < rows) delta[row] = acc[u];
+    }
 }
 
 template <int D, bool kKeySide>
@@ -292,8 +319,17 @@ cudaError_t launch_backward_bf16(const void* q, const void* k, const void* v, co
     if (bh == 0 || seq == 0) return cudaSuccess;
     if (bh > 65535) return cudaErrorInvalidValue;
     const int64_t rows = bh * seq;
-    bwd_delta_bf16_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, stream>>>((const __nv_bfloat16*)out,
-                                                                          (const __nv_bfloat16*)d_out, delta_ws, rows, dim);
+    if (dim != 64 && dim != 128) return cudaErrorInvalidValue;
+    {
+        const int rows_per_cta = 8 * 2 * (32 / (dim / 8));
+        const unsigned grid = (unsigned)((rows + rows_per_cta - 1) / rows_per_cta);
+        if (dim == 128)
+            bwd_delta_bf16_kernel<128><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)out, (const __nv_bfloat16*)d_out,
+                                                                 delta_ws, rows);
+        else
+            bwd_delta_bf16_kernel<64><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)out, (const __nv_bfloat16*)d_out,
+                                                                delta_ws, rows);
+    }
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     // The tcgen05 / TMEM / TMA kernel (backward_tcgen05.cu) is the path; RT_ATTN_BACKWARD_IMPL=mma_sync keeps
