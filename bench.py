@@ -448,7 +448,13 @@ def main():
         e2e = {"value": n_gpus * flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                "h2d_bytes_per_step": int(3 * q.numel() * 2), "d2h_bytes_per_step": int(o.numel() * 2 + lse.numel() * 4),
                "steps": e2e_steps, "api": "rt_attn_prefill_bf16_host (pinned host buffers, copies inside the timed region)"}
-        assert torch.equal(ho.cuda(), o), "host entry and device entry disagree"
+        # The host entry runs the same kernel on (batch element, head range) chunks; small chunks take the
+        # small-launch schedule, whose summation order differs, so the results agree to a bf16 ulp, not bit for bit.
+        hd, od = ho.cuda().float(), o.float()
+        host_dev_diff = float(((hd - od).abs() / od.abs().clamp(min=1.0)).max())
+        assert host_dev_diff <= 2.0 ** -7, f"host entry and device entry disagree: {host_dev_diff}"
+        e2e["max_rel_diff_vs_device_entry"] = host_dev_diff
+        del hd, od
         del hq, hk, hv, ho, hl
         # The reference's own signature: flash_forward_masked(&AttentionShape, &[f32] q, k, v, &Mask, &mut [f32] out)
         # (cpu_forward.rs:193-200) -> rt_flash_forward_f32_host, f32 host slices in and out, bf16 tensor-core math.

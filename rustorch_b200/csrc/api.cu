@@ -215,10 +215,49 @@ int rt_attn_prefill_f32(const float* q, const float* k, const float* v, float* o
     return RT_OK;
 }
 
+// How a host call is cut into (batch element, head range) chunks for the three-stream pipeline.  The
+// upload is the long pole (three tensors in, one out) and the last chunk's kernel and download cannot hide
+// behind an upload, so the list starts with a few large chunks (few copies, each near the PCIe rate) and
+// ends by halving: ..., n/2, n/4, ... down to ~8 MB of upload (0.15 ms; below that the per-chunk launches cost more).  Each download stays shorter than the next
+// chunk's upload, and the exposed tail shrinks from a quarter of the call to a few tens of microseconds.
+struct HostChunk {
+    int64_t b0, nb, h0, h1;  // batch elements [b0, b0 + nb), heads [h0, h1)
+};
+constexpr int kMaxHostChunks = 32;
+static int plan_host_chunks(int64_t batch, int64_t heads, size_t unit_upload_bytes, HostChunk* out) {
+    constexpr int kTail = 8;  // entries kept for the halving tail
+    int64_t per_batch = (4 + batch - 1) / batch;
+    if (per_batch > heads) per_batch = heads;
+    int64_t batch_step = 1;  // batch elements per chunk
+    if (batch * per_batch > kMaxHostChunks - kTail) {
+        per_batch = 1;
+        batch_step = (batch + (kMaxHostChunks - kTail) - 1) / (kMaxHostChunks - kTail);
+    }
+    int n = 0;
+    for (int64_t b0 = 0; b0 < batch; b0 += batch_step) {
+        const int64_t nb = (b0 + batch_step <= batch) ? batch_step : batch - b0;
+        for (int64_t part = 0; part < per_batch; ++part)
+            out[n++] = HostChunk{b0, nb, heads * part / per_batch, heads * (part + 1) / per_batch};
+    }
+    HostChunk last = out[n - 1];
+    if (last.nb == 1) {
+        --n;
+        while (last.h1 - last.h0 > 1 && n < kMaxHostChunks - 1 &&
+               (size_t)(last.h1 - last.h0) * unit_upload_bytes > (size_t(8) << 20)) {
+            const int64_t take = (last.h1 - last.h0 + 1) / 2;
+            out[n++] = HostChunk{last.b0, 1, last.h0, last.h0 + take};
+            last.h0 += take;
+        }
+        out[n++] = last;
+    }
+    return n;
+}
+
+
 // Streams and events of the pipelined host entry, created once per device.
 namespace {
 struct HostPipeline {
-    static constexpr int kMaxChunks = 32;
+    static constexpr int kMaxChunks = kMaxHostChunks;
     cudaStream_t in[64] = {}, comp[64] = {}, out[64] = {};
     cudaEvent_t ev_in[64][kMaxChunks] = {}, ev_comp[64][kMaxChunks] = {};
     bool ready[64] = {};
@@ -288,21 +327,13 @@ int rt_flash_forward_f32_host(const float* q, size_t q_len, const float* k, size
         keep_dev = dkeep.as<uint8_t>();
     }
     const int flags = (mask_kind == RT_MASKKIND_CAUSAL) ? RT_MASK_CAUSAL : RT_MASK_NONE;
-    // chunking: (batch element, head range) pieces, at least 4 when the shape allows, at most kMaxChunks
-    int64_t per_batch = (4 + batch - 1) / batch;
-    if (per_batch > heads) per_batch = heads;
-    int64_t batch_step = 1;  // batch elements per chunk
-    if (batch * per_batch > HostPipeline::kMaxChunks) {
-        per_batch = 1;
-        batch_step = (batch + HostPipeline::kMaxChunks - 1) / HostPipeline::kMaxChunks;
-    }
     const size_t slab = (size_t)seq * (size_t)dim;  // elements of one (b,h)
-    int c = 0;
-    for (int64_t b0 = 0; b0 < batch; b0 += batch_step) {
-        const int64_t nb = (b0 + batch_step <= batch) ? batch_step : batch - b0;
-        for (int64_t part = 0; part < per_batch; ++part, ++c) {
-            const int64_t h0 = heads * part / per_batch, h1 = heads * (part + 1) / per_batch;
-            // with batch_step > 1 a chunk holds whole batch elements (per_batch == 1, h0 = 0, h1 = heads)
+    HostChunk plan[kMaxHostChunks];
+    const int n_chunks = plan_host_chunks(batch, heads, 3 * slab * sizeof(float), plan);
+    for (int c = 0; c < n_chunks; ++c) {
+        {
+            const int64_t b0 = plan[c].b0, nb = plan[c].nb, h0 = plan[c].h0, h1 = plan[c].h1;
+            // a chunk of several batch elements holds all their heads (h0 = 0, h1 = heads)
             const size_t off = ((size_t)b0 * heads + h0) * slab, cnt = (size_t)nb * (size_t)(h1 - h0) * slab;
             RT_CUDA(cudaMemcpyAsync(dq.as<float>() + off, q + off, cnt * 4, cudaMemcpyHostToDevice, s_in));
             RT_CUDA(cudaMemcpyAsync(dk.as<float>() + off, k + off, cnt * 4, cudaMemcpyHostToDevice, s_in));
@@ -369,16 +400,11 @@ int rt_attn_prefill_bf16_host(const void* q, const void* k, const void* v, void*
         RT_CUDA(dlens.alloc((size_t)batch * 4));
         RT_CUDA(cudaMemcpyAsync(dlens.p, kv_lens, (size_t)batch * 4, cudaMemcpyHostToDevice, s_in));
     }
-    // chunking: whole batch elements, each split into head ranges so that there are >= 4 chunks
-    int64_t per_batch = (4 + batch - 1) / batch;
-    if (per_batch > heads) per_batch = heads;
-    if (batch * per_batch > HostPipeline::kMaxChunks) per_batch = 1;
-    if (batch > HostPipeline::kMaxChunks) {  // very large batch: one chunk per group of batch elements is not
-        per_batch = 0;                       // expressible with per-batch kv_lens offsets; run unpipelined
-    }
     const size_t slab = (size_t)seq * dim;  // elements of one (b,h)
-    int c = 0;
-    if (per_batch == 0) {
+    HostChunk plan[kMaxHostChunks];
+    // per-batch kv_lens are passed by offset, so a chunk must stay inside one batch element
+    const int n_chunks = batch <= kMaxHostChunks - 8 ? plan_host_chunks(batch, heads, 3 * slab * 2, plan) : 0;
+    if (n_chunks == 0 || plan[0].nb != 1) {  // very large batch: run unpipelined
         RT_CUDA(cudaMemcpyAsync(dq.p, q, n * 2, cudaMemcpyHostToDevice, s_in));
         RT_CUDA(cudaMemcpyAsync(dk.p, k, n * 2, cudaMemcpyHostToDevice, s_in));
         RT_CUDA(cudaMemcpyAsync(dv.p, v, n * 2, cudaMemcpyHostToDevice, s_in));
@@ -390,9 +416,9 @@ int rt_attn_prefill_bf16_host(const void* q, const void* k, const void* v, void*
         RT_CUDA(cudaStreamSynchronize(s_in));
         return RT_OK;
     }
-    for (int64_t b = 0; b < batch; ++b) {
-        for (int64_t part = 0; part < per_batch; ++part, ++c) {
-            const int64_t h0 = heads * part / per_batch, h1 = heads * (part + 1) / per_batch;
+    for (int c = 0; c < n_chunks; ++c) {
+        {
+            const int64_t b = plan[c].b0, h0 = plan[c].h0, h1 = plan[c].h1;
             const size_t off = ((size_t)b * heads + h0) * slab, cnt = (size_t)(h1 - h0) * slab;
             const size_t roff = ((size_t)b * heads + h0) * seq, rcnt = (size_t)(h1 - h0) * seq;
             const char* hq = (const char*)q + off * 2;
