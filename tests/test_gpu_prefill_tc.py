@@ -348,59 +348,32 @@ def test_prefill_strided_validation():
     assert e.value.code == _lib.RT_ERR_ALIGNMENT
 
 
-@pytest.mark.parametrize("sched", ["persistent", "percta"])
-@pytest.mark.parametrize("case", ["odd_blocks_causal", "gqa_chunk_offsets", "varlen", "no_mask"])
-def test_prefill_schedules_agree(oracle, monkeypatch, sched, case):
-    """Both launch schedules of the kernel (one CTA per SM walking a paired list of 256-row blocks, or one CTA per
-    block) on shapes that stress the list: an odd number of blocks per head (the middle block has no partner),
-    grouped KV heads with per-batch causal offsets, per-batch lengths, and no mask at all."""
-    monkeypatch.setenv("RT_ATTN_PREFILL_SCHED", sched)
-    if case == "odd_blocks_causal":
-        B, Hq, Hkv, Nq, Nkv, D = 40, 8, 8, 1280, 1280, 128    # 320 heads x 5 blocks: more slots than SMs
-        kw, okw = dict(causal=True), dict(causal=True)
-    elif case == "gqa_chunk_offsets":
-        B, Hq, Hkv, Nq, Nkv, D = 3, 8, 2, 700, 2048, 64
-        lens = np.array([2048, 700, 1500], dtype=np.int32)
-        offs = (lens - Nq).astype(np.int32)
-        kw = dict(causal=True, kv_lens=util.to_cuda(lens), q_offsets=util.to_cuda(offs))
-        okw = dict(causal=True, kv_lens=lens, q_offsets=offs)
-    elif case == "varlen":
-        B, Hq, Hkv, Nq, Nkv, D = 6, 4, 4, 900, 900, 64
-        lens = np.array([900, 1, 257, 640, 0, 333], dtype=np.int32)
-        kw, okw = dict(causal=True, kv_lens=util.to_cuda(lens)), dict(causal=True, kv_lens=lens)
-    else:
-        B, Hq, Hkv, Nq, Nkv, D = 2, 5, 5, 777, 777, 128
-        kw, okw = dict(), dict()
-    if case == "odd_blocks_causal":   # the oracle is O(N^2) per head: check 6 of the 320 heads
-        q = util.normal_bf16(oracle, (B, Hq, Nq, D), util.SEED_Q)
-        k = util.normal_bf16(oracle, (B, Hkv, Nkv, D), util.SEED_K)
-        v = util.normal_bf16(oracle, (B, Hkv, Nkv, D), util.SEED_V)
-        out, lse = _run_tc(q, k, v, **kw)
-        for b, h in ((0, 0), (0, 7), (17, 3), (39, 0), (39, 7), (20, 5)):
-            _, ref, ref_lse = oracle.attention_general(q[b:b + 1, h:h + 1], k[b:b + 1, h:h + 1], v[b:b + 1, h:h + 1], **okw)
-            util.check_output(out[b:b + 1, h:h + 1], ref, label=f"{case} {sched} b{b} h{h}")
-            util.check_lse(lse[b:b + 1, h:h + 1], ref_lse)
-        return
-    q = util.normal_bf16(oracle, (B, Hq, Nq, D), util.SEED_Q)
-    k = util.normal_bf16(oracle, (B, Hkv, Nkv, D), util.SEED_K)
-    v = util.normal_bf16(oracle, (B, Hkv, Nkv, D), util.SEED_V)
-    out, lse = _run_tc(q, k, v, **kw)
-    _, ref, ref_lse = oracle.attention_general(q, k, v, **okw)
-    util.check_output(out, ref, label=f"{case} {sched}")
-    util.check_lse(lse, ref_lse)
+@pytest.mark.parametrize("var,value", [("RT_ATTN_PREFILL_SCHED", "persistent"), ("RT_ATTN_PREFILL_SCHED", "percta"),
+                                       ("RT_ATTN_PREFILL_TILES", "1"), ("RT_ATTN_PREFILL_TILES", "2")])
+def test_prefill_launch_overrides_agree_with_the_oracle(var, value):
+    """Both launch schedules (one CTA per SM walking a list of 256-row blocks, or one CTA per block) and both item
+    sizes (256-row items, or 128-row items whose 64-key steps alternate between the two tiles) against the oracle
+    on shapes that stress them.  The library reads the override once per process, so each one gets a child pytest
+    process running tests/prefill_override_cases.py."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ)
+    env[var] = value
+    r = subprocess.run([sys.executable, "-m", "pytest", "-q", "-x", "-m", "gpu", "-p", "no:cacheprovider",
+                        os.path.join("tests", "prefill_override_cases.py")],
+                       cwd=root, env=env, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, f"{var}={value}\n{r.stdout[-3000:]}\n{r.stderr[-1000:]}"
 
 
-@pytest.mark.parametrize("tiles", ["1", "2"])
-@pytest.mark.parametrize("D,N,causal", [(64, 2048, True), (128, 300, False), (128, 129, True)])
-def test_prefill_single_and_double_tile_items(oracle, monkeypatch, tiles, D, N, causal):
-    """Small launches hand each CTA one 128-row Q tile instead of two (more CTAs for the same rows); both item
-    sizes give the same numbers."""
-    monkeypatch.setenv("RT_ATTN_PREFILL_TILES", tiles)
-    q, k, v = _qkv(oracle, (1, 3, N, D))
-    out, lse = _run_tc(q, k, v, causal=causal)
-    _, ref, ref_lse = oracle.flash_forward_ext(q, k, v, causal=causal)
-    util.check_output(out, ref, label=f"tiles={tiles} N{N} D{D}")
-    util.check_lse(lse, ref_lse)
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("causal", [False, True])
+def test_prefill_key_split_edges(oracle, D, causal):
+    """The default launch of a small shape (128-row items, even / odd 64-key steps on the two tiles) on lengths
+    around the 64- and 128-key boundaries; the same case also runs under the overrides above."""
+    from tests.prefill_override_cases import test_key_split_edges
+    test_key_split_edges(oracle, D, causal)
 
 
 def test_prefill_is_deterministic_across_launches():
