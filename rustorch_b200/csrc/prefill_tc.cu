@@ -275,35 +275,27 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         __syncthreads();
     }
     bool first_preloaded = false;  // meaningful in the producer thread only
+    if (warp == 8) {
+        // The barriers are initialised by the 32 lanes side by side (one thread doing all of them costs
+        // ~0.4 us at the head of every CTA's critical path); all counts are 1 except the ones named here.
+        for (int i = lane; i < C::NBARS; i += 32) {
+            uint64_t* bar = bars + i;
+            uint32_t count = 1;
+            if (bar >= p_full && bar < p_full + 4) count = 128;
+            else if (bar >= o_free && bar < o_free + 2) count = 128;
+            else if (bar >= stage_full && bar < stage_full + 2) count = kSingle ? 256 : 128;  // both warpgroups stage a single-tile item's rows
+            else if (bar == done_bar) count = 2;
+            else if (bar == merge_bar) count = 256;
+            mbar_init(bar, count);
+        }
+        fence_barrier_init();
+        __syncwarp();
+    }
     if (warp == 8 && lane == 0) {
         prefetch_tensormap(&tm_q);
         prefetch_tensormap(&tm_k);
         prefetch_tensormap(&tm_v);
         prefetch_tensormap(&tm_o);
-        for (int i = 0; i < 2; ++i) {
-            mbar_init(&q_full[i], 1);
-            mbar_init(&q_empty[i], 1);
-            mbar_init(&o_full[i], 1);
-            mbar_init(&o_done[i], 1);
-            mbar_init(&o_free[i], 128);
-            mbar_init(&stage_full[i], kSingle ? 256 : 128);  // both warpgroups stage a single-tile item's rows
-        }
-        for (int i = 0; i < 4; ++i) {
-            mbar_init(&s_full[i], 1);
-            mbar_init(&p_full[i], 128);
-        }
-        for (int i = 0; i < KS; ++i) {
-            mbar_init(&k_full[i], 1);
-            mbar_init(&k_empty[i], 1);
-            mbar_init(&k_empty[KS + i], 1);
-        }
-        for (int i = 0; i < VS; ++i) {
-            mbar_init(&v_full[i], 1);
-            mbar_init(&v_empty[i], 1);
-            mbar_init(&v_empty[VS + i], 1);
-        }
-        mbar_init(done_bar, 2);
-        mbar_init(merge_bar, 256);
         fence_barrier_init();
         fence_proxy_async();
         grid_dep_wait();
