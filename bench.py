@@ -548,7 +548,7 @@ def main():
         of32, lf32 = rt.prefill_f32(qf, kf, vf, causal=True)
         ms_f32 = timed(lambda: rt.prefill_f32(qf, kf, vf, causal=True), max(args.steps, 20), 3, dist, torch)
         f32_row = {"ms": ms_f32, "tflops": fl1 / (ms_f32 * 1e-3) / 1e12,
-                   "kernel": "prefill_f32_kernel (CUDA cores, f32 in / f32 accumulate / f32 out, rt_attn_prefill_f32)"}
+                   "kernel": "prefill_f32_tiled_kernel (CUDA cores, f32 in / f32 accumulate / f32 out, rt_attn_prefill_f32)"}
         if check:
             qh, kh, vh = (orc_gen.fill_normal((c["B"], c["H"], c["N"], c["D"]), s) for s in (SEED_Q, SEED_K, SEED_V))
             rc32, ref32, ref_lse32 = orc.flash_forward_ext(qh, kh, vh, causal=True)
