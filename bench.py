@@ -478,6 +478,13 @@ def main():
                 fl = prefill_flops(cfg["B"], cfg["H"], cfg["N"], cfg["D"])
                 sig[name] = {"ms_per_step": w, "tflops": fl / (w * 1e-3) / 1e12, "h2d_bytes_per_step": 3 * n_el * 4,
                              "d2h_bytes_per_step": n_el * 4}
+                if name == "cfg1":  # the same call with the reference's default precision: exact f32 arithmetic
+                    def step_sig_f32():
+                        rt.flash_forward_masked(shp, arrs[0], arrs[1], arrs[2], rt.Mask.causal(), out_np, precision="f32")
+
+                    w32 = wall(step_sig_f32, 10)
+                    sig["cfg1_f32_precision"] = {"ms_per_step": w32, "tflops": fl / (w32 * 1e-3) / 1e12,
+                                                 "h2d_bytes_per_step": 3 * n_el * 4, "d2h_bytes_per_step": n_el * 4}
                 del bufs, outb, arrs, out_np
             e2e["reference_signature"] = sig
 

@@ -226,6 +226,12 @@ struct HostChunk {
 constexpr int kMaxHostChunks = 32;
 static int plan_host_chunks(int64_t batch, int64_t heads, size_t unit_upload_bytes, HostChunk* out) {
     constexpr int kTail = 8;  // entries kept for the halving tail
+    // A small call (under 32 MB of upload, ~0.6 ms) runs as one chunk: its kernels would not fill the GPU
+    // chunk by chunk, and four sets of copies and launches cost more than the overlap returns.
+    if ((size_t)batch * (size_t)heads * unit_upload_bytes < (size_t(32) << 20)) {
+        out[0] = HostChunk{0, batch, 0, heads};
+        return 1;
+    }
     int64_t per_batch = (4 + batch - 1) / batch;
     if (per_batch > heads) per_batch = heads;
     int64_t batch_step = 1;  // batch elements per chunk
