@@ -323,13 +323,15 @@ cudaError_t launch_prefill_f32(const float* q, const float* k, const float* v, f
     if (batch == 0 || heads_q == 0 || seq_q == 0) return cudaSuccess;
     SimtParams p{q, k, v, out, lse, heads_q, heads_kv, seq_q, seq_kv, dim, causal, kv_lens, q_offsets, key_keep,
                  keep_batch_stride, scale};
-    // The register-tiled kernel is the path (RT_ATTN_PREFILL_F32_IMPL=rows keeps the warp-per-row kernel for
-    // comparisons); its row scale is applied to Q once, the other kernel scales every score.
+    // The register-tiled kernel is the path for 16 query rows and more; a decode-shaped call (a few rows against
+    // a long cache) would waste most of its 64-row tile and keeps the warp-per-row kernel, which
+    // RT_ATTN_PREFILL_F32_IMPL=rows selects for every shape (comparisons).  The tiled kernel applies the scale
+    // to Q once, the other one to every score.
     static const bool rows_impl = [] {
         const char* e = getenv("RT_ATTN_PREFILL_F32_IMPL");
         return e && e[0] == 'r';
     }();
-    if (!rows_impl && dim <= 256) {
+    if (!rows_impl && dim <= 256 && seq_q >= 16) {
         if (dim <= 64) return launch_tiled<1>(p, batch, stream);
         if (dim <= 128) return launch_tiled<2>(p, batch, stream);
         return launch_tiled<4>(p, batch, stream);
