@@ -274,6 +274,40 @@ def timed(fn, steps, warmup, dist_mod, torch, per_rank=False):
     return (ms, ranks) if per_rank else ms
 
 
+def timed_graph(fn, steps, warmup, dist_mod, torch):
+    """The same K steps captured once into a CUDA graph and replayed once (each instantiated graph is replayed a
+    single time: the exchange epochs baked into its launches must not repeat).  Removes the host from the timed
+    region: with eight processes per box the Python enqueue of a 0.1 ms step is no longer negligible.
+    Returns the max over ranks of the average ms per step."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    if dist_mod is not None:
+        dist_mod.barrier()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for _ in range(steps):
+            fn()
+    torch.cuda.synchronize()
+    if dist_mod is not None:
+        dist_mod.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    if dist_mod is not None:
+        dist_mod.barrier()
+    ms = e0.elapsed_time(e1) / steps
+    if dist_mod is not None:
+        t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+        dist_mod.all_reduce(t, op=dist_mod.ReduceOp.MAX)
+        ms = float(t.item())
+    del g
+    return ms
+
+
 def rank_spread(ranks):
     s = sorted(ranks)
     return {"min": s[0], "median": s[len(s) // 2], "max": s[-1]}
@@ -766,7 +800,7 @@ def main():
         # The same exchange over peer memory: the record is decoded straight into this rank's slot, pushed
         # to every peer with NVLink stores + a flag, and the merge kernel waits (bounded) for all flags.
         exchange, exchange_note = None, ("peer stores over NVLink (symmetric memory) + flags, the merge waits in-kernel; "
-                                         "value = the fastest of the three forms timed below")
+                                         "value = the fastest of the forms timed below")
         try:
             exchange = sharding.PeerRecordExchange.create(Hq, Dd)
         except Exception as exc:  # symmetric memory not available: keep the NCCL form, and say so
@@ -785,6 +819,10 @@ def main():
             # decode kernel, then ONE kernel: chunk merge, row delivery, per-row wait, cross-rank merge
             return exchange.decode_exchange(q1, k1, v1, kv_len=T, workspace=ws)
 
+        def step_splitkv_ll():
+            # the same, every element as an 8-byte {value, epoch} word: no fence, no flag store, the reader spins on the words
+            return exchange.decode_exchange(q1, k1, v1, kv_len=T, workspace=ws, ll=True)
+
         # Verification over real peer memory, before anything is timed: every rank holds the SAME small cache
         # (4096 positions per rank), decodes only its own KV range, exchanges, and compares the merged result
         # with its own single-GPU decode of the whole range.
@@ -797,15 +835,15 @@ def main():
             whole, whole_lse = rt.gqa_decode(q1, kv_, vv_, kv_len=Tv, out_dtype=torch.float32)
             b0, b1 = sharding.kv_shard(Tv, world, rank, align=16)
             errs = []
-            for form in ("copy", "fused", "rows"):
+            for form in ("copy", "fused", "rows", "ll"):
                 if form == "copy":
                     rt.gqa_decode_record(q1, kv_, vv_, kv_len=Tv, kv_begin=b0, kv_end=b1, record=exchange.next_epoch())
                     exchange.push()
                 elif form == "fused":
                     exchange.decode_push(q1, kv_, vv_, kv_len=Tv, kv_begin=b0, kv_end=b1)
-                if form == "rows":
+                if form in ("rows", "ll"):
                     got, got_lse = exchange.decode_exchange(q1, kv_, vv_, kv_len=Tv, kv_begin=b0, kv_end=b1,
-                                                            out_dtype=torch.float32)
+                                                            out_dtype=torch.float32, ll=(form == "ll"))
                 else:
                     got, got_lse = exchange.merge(out_dtype=torch.float32)
                 torch.cuda.synchronize()
@@ -819,7 +857,7 @@ def main():
 
         nccl_ms = timed(step_splitkv_nccl, args.steps, args.warmup, dist, torch)
         sms = nccl_ms
-        sms_copy = sms_fused = sms_rows = None
+        sms_copy = sms_fused = sms_rows = sms_rows_graph = sms_copy_graph = sms_ll = sms_ll_graph = None
         if exchange is not None:
             a, b = step_splitkv_nccl(), step_splitkv_p2p()
             torch.cuda.synchronize()
@@ -835,7 +873,16 @@ def main():
             assert (a[0].float() - dd[0].float()).abs().max().item() <= 2e-2 and (a[1] - dd[1]).abs().max().item() <= 1e-5, \
                 "row exchange and NCCL exchange disagree"
             sms_rows = timed(step_splitkv_rows, args.steps, args.warmup, dist, torch)
-            sms = min(sms_copy, sms_fused, sms_rows)
+            # the two best forms again with the steps replayed from one CUDA graph per rank (no host in the loop)
+            sms_rows_graph = timed_graph(step_splitkv_rows, args.steps, args.warmup, dist, torch)
+            sms_copy_graph = timed_graph(step_splitkv_p2p, args.steps, args.warmup, dist, torch)
+            ee = step_splitkv_ll()
+            torch.cuda.synchronize()
+            assert (a[0].float() - ee[0].float()).abs().max().item() <= 2e-2 and (a[1] - ee[1]).abs().max().item() <= 1e-5, \
+                "word exchange and NCCL exchange disagree"
+            sms_ll = timed(step_splitkv_ll, args.steps, args.warmup, dist, torch)
+            sms_ll_graph = timed_graph(step_splitkv_ll, args.steps, args.warmup, dist, torch)
+            sms = min(sms_copy, sms_fused, sms_rows, sms_rows_graph, sms_copy_graph, sms_ll, sms_ll_graph)
             assert _lib.device_status() == 0, "a bounded wait of the peer exchange expired"
         total_bytes = shard_bytes * world
         splitkv = {"metric": "kv_read_gbs", "value": total_bytes / (sms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": sms,
@@ -846,9 +893,16 @@ def main():
                    "frac_of_hbm_per_gpu": total_bytes / world / (sms * 1e-3) / 1e9 / peaks["hbm_gbs"],
                    "nccl_all_gather_ms_per_step": nccl_ms, "peer_copy_kernel_ms_per_step": sms_copy,
                    "peer_fused_in_merge_ms_per_step": sms_fused, "peer_row_exchange_one_kernel_ms_per_step": sms_rows,
+                   "peer_row_exchange_graph_replay_ms_per_step": sms_rows_graph,
+                   "peer_copy_kernel_graph_replay_ms_per_step": sms_copy_graph,
+                   "peer_word_exchange_one_kernel_ms_per_step": sms_ll,
+                   "peer_word_exchange_graph_replay_ms_per_step": sms_ll_graph,
+                   "timing_note": "graph_replay rows: the K steps of a rank captured once into a CUDA graph and replayed "
+                                  "once, CUDA events around the replay, max over ranks; the others are enqueued step by "
+                                  "step from Python (3 to 1 ctypes calls per step on each of the N processes)",
                    "splitkv_verified": verified, "splitkv_verify_max_err": verify_err,
                    "splitkv_verify": "every rank decodes its range of a shared 4096*N-position cache, exchanges over real "
-                                     "peer memory (both forms) and compares with its own single-GPU decode (max |diff| "
+                                     "peer memory (every form) and compares with its own single-GPU decode (max |diff| "
                                      "of O and LSE over ranks, f32)"}
     del q1, k1, v1, ws
     torch.cuda.empty_cache()

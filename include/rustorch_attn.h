@@ -417,6 +417,30 @@ int rt_attn_merge_records_after_rows(const float* records, const uint32_t* row_f
                                      void* out_bf16, float* out_f32, float* lse, void* stream);
 
 /*
+ * rt_gqa_decode_exchange_bf16 with the flag inside the data (no reference counterpart).  Every element of a
+ * row travels as one 8-byte word {f32 bits, epoch}; an aligned 8-byte store is one access, so a reader that
+ * finds the epoch in a word has the value that came with it.  There is no system-scope fence between data and
+ * flag and no flag store: one NVLink round trip less per step.  The reader spins (bounded by wait_clocks, as
+ * above; expiry: device status 401) on the words themselves.
+ *   peer_words[r]  : on rank r, the [rows][D+1] u64 words r keeps for THIS rank (8-byte aligned; r == rank: local)
+ *   local_words    : this rank's words for all ranks, [world][rows][D+1] u64, zero before the first epoch
+ *   scratch_record : [rows, D+1] f32 of local memory (the decode writes the record here when the shard is one chunk)
+ *   epoch          : >= 1, increasing by one per exchange; two word sets are used alternately by the caller
+ *   do_wait = 0    : stop after the delivery; rt_attn_merge_ll_rows finishes the step (several ranks on ONE GPU)
+ */
+int rt_gqa_decode_exchange_ll_bf16(const void* q, const void* k_cache, const void* v_cache, void* out_bf16,
+                                   float* out_f32, float* lse, void* const* peer_words,
+                                   const void* local_words, float* scratch_record, int world, int rank,
+                                   uint32_t epoch, int64_t wait_clocks, int do_wait, int64_t batch,
+                                   int64_t n_heads, int64_t n_kv_heads, int head_dim, int64_t max_seq,
+                                   const int32_t* kv_lens, int64_t kv_len_uniform, int64_t kv_begin,
+                                   int64_t kv_end, float scale, void* workspace, size_t workspace_bytes,
+                                   void* stream);
+/* The second half of rt_gqa_decode_exchange_ll_bf16(do_wait = 0): bounded wait for every rank's words, then the merge. */
+int rt_attn_merge_ll_rows(const void* local_words, uint32_t epoch, int64_t wait_clocks, int world,
+                          int64_t rows, int dim, void* out_bf16, float* out_f32, float* lse, void* stream);
+
+/*
  * Host-slice mirror of
  *   gqa_forward_f32(q,k,v,out, batch,n_heads,n_kv_heads,seq_q,seq_kv,head_dim) -> Result<(),GQAError>
  * (gqa.rs:94-105), f32 arithmetic.  seq_q == seq_kv runs the unmasked prefill without

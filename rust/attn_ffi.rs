@@ -95,6 +95,14 @@ extern "C" {
     pub fn rt_attn_merge_records_after_rows(records: *const f32, row_flags: *const u32, epoch: u32, wait_clocks: i64,
         n_parts: i64, rows: i64, dim: c_int, out_bf16: *mut c_void, out_f32: *mut f32, lse: *mut f32,
         stream: *mut c_void) -> c_int;
+    pub fn rt_gqa_decode_exchange_ll_bf16(q: *const c_void, k_cache: *const c_void, v_cache: *const c_void,
+        out_bf16: *mut c_void, out_f32: *mut f32, lse: *mut f32, peer_words: *const *mut c_void,
+        local_words: *const c_void, scratch_record: *mut f32, world: c_int, rank: c_int, epoch: u32, wait_clocks: i64,
+        do_wait: c_int, batch: i64, n_heads: i64, n_kv_heads: i64, head_dim: c_int, max_seq: i64,
+        kv_lens: *const i32, kv_len_uniform: i64, kv_begin: i64, kv_end: i64, scale: f32, workspace: *mut c_void,
+        workspace_bytes: usize, stream: *mut c_void) -> c_int;
+    pub fn rt_attn_merge_ll_rows(local_words: *const c_void, epoch: u32, wait_clocks: i64, world: c_int, rows: i64,
+        dim: c_int, out_bf16: *mut c_void, out_f32: *mut f32, lse: *mut f32, stream: *mut c_void) -> c_int;
     pub fn rt_convert_f32_to_bf16(src: *const f32, dst: *mut c_void, n: i64, stream: *mut c_void) -> c_int;
     pub fn rt_convert_bf16_to_f32(src: *const c_void, dst: *mut f32, n: i64, stream: *mut c_void) -> c_int;
     pub fn rt_debug_tc_selftest(a: *const c_void, b: *const c_void, v: *const c_void, s_out: *mut f32,

@@ -87,6 +87,12 @@ PROTOTYPES = {
                                             c_void_p, c_size_t, c_void_p]),
     "rt_attn_merge_records_after_rows": (c_int, [c_void_p, c_void_p, ctypes.c_uint32, c_int64, c_int64, c_int64, c_int,
                                                  c_void_p, c_void_p, c_void_p, c_void_p]),
+    "rt_gqa_decode_exchange_ll_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                               c_void_p, c_int, c_int, ctypes.c_uint32, c_int64, c_int, c_int64, c_int64,
+                                               c_int64, c_int, c_int64, c_void_p, c_int64, c_int64, c_int64, c_float,
+                                               c_void_p, c_size_t, c_void_p]),
+    "rt_attn_merge_ll_rows": (c_int, [c_void_p, ctypes.c_uint32, c_int64, c_int, c_int64, c_int, c_void_p, c_void_p,
+                                      c_void_p, c_void_p]),
     "rt_attn_merge_records": (c_int, [c_void_p, c_int64, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
     "rt_gqa_decode_online_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                           c_void_p, c_size_t, c_void_p]),

@@ -733,6 +733,52 @@ int rt_gqa_decode_exchange_bf16(const void* q, const void* k_cache, const void* 
     return RT_OK;
 }
 
+int rt_gqa_decode_exchange_ll_bf16(const void* q, const void* k_cache, const void* v_cache, void* out_bf16,
+                                   float* out_f32, float* lse, void* const* peer_words, const void* local_words,
+                                   float* scratch_record, int world, int rank, uint32_t epoch, int64_t wait_clocks,
+                                   int do_wait, int64_t batch, int64_t n_heads, int64_t n_kv_heads, int head_dim,
+                                   int64_t max_seq, const int32_t* kv_lens, int64_t kv_len_uniform, int64_t kv_begin,
+                                   int64_t kv_end, float scale, void* workspace, size_t workspace_bytes, void* stream) {
+    if (world <= 0 || rank < 0 || rank >= world) return RT_ERR_BAD_LENGTH;
+    if (world > rt::kMaxPeers) return RT_ERR_UNSUPPORTED;
+    if (epoch == 0) return RT_ERR_BAD_LENGTH;  // zeroed words carry epoch 0
+    if (!peer_words || !local_words || !scratch_record) return RT_ERR_NULL_POINTER;
+    for (int r = 0; r < world; ++r) {
+        if (!peer_words[r]) return RT_ERR_NULL_POINTER;
+        if (reinterpret_cast<uintptr_t>(peer_words[r]) & 7) return RT_ERR_ALIGNMENT;
+    }
+    if (reinterpret_cast<uintptr_t>(local_words) & 7) return RT_ERR_ALIGNMENT;
+    if (do_wait && !out_bf16 && !out_f32) return RT_ERR_NULL_POINTER;
+    // The decode writes chunk partials, or with a single chunk the f32 record itself into scratch_record;
+    // the row-exchange kernel merges, delivers the words, waits for every rank's words and merges again.
+    rt::DecodeTail tail{0, nullptr, nullptr};
+    const int rc = decode_common(q, k_cache, v_cache, nullptr, scratch_record, scratch_record + head_dim, head_dim + 1,
+                                 head_dim + 1, batch, n_heads, n_kv_heads, head_dim, max_seq, kv_lens, kv_len_uniform,
+                                 kv_begin, kv_end, scale, workspace, workspace_bytes, stream, nullptr, nullptr, &tail);
+    if (rc != RT_OK || batch == 0) return rc;
+    const int64_t rows = batch * n_heads;
+    const bool direct = tail.n_chunks <= 1;
+    RT_CUDA(rt::launch_row_exchange_ll(direct ? scratch_record : tail.part_o,
+                                       direct ? scratch_record + head_dim : tail.part_lse, direct ? 1 : tail.n_chunks,
+                                       rows, head_dim, direct ? head_dim + 1 : head_dim, direct ? head_dim + 1 : 1,
+                                       out_bf16, out_f32, lse, peer_words, local_words, world, epoch,
+                                       (long long)wait_clocks, do_wait, as_stream(stream)));
+    return RT_OK;
+}
+
+int rt_attn_merge_ll_rows(const void* local_words, uint32_t epoch, int64_t wait_clocks, int world, int64_t rows,
+                          int dim, void* out_bf16, float* out_f32, float* lse, void* stream) {
+    if (dim == 0) return RT_ERR_ZERO_DIM;
+    if (world <= 0 || rows < 0 || dim < 0 || epoch == 0) return RT_ERR_BAD_LENGTH;
+    if (dim > 255 || world > rt::kMaxPeers) return RT_ERR_UNSUPPORTED;
+    if (rows == 0) return RT_OK;
+    if (!local_words || (!out_bf16 && !out_f32)) return RT_ERR_NULL_POINTER;
+    if (reinterpret_cast<uintptr_t>(local_words) & 7) return RT_ERR_ALIGNMENT;
+    RT_CUDA(rt::launch_ll_merge(local_words, world, rows, dim, epoch, (long long)wait_clocks, out_bf16, out_f32, lse,
+                                as_stream(stream)));
+    return RT_OK;
+}
+
 int rt_attn_merge_records_after_rows(const float* records, const uint32_t* row_flags, uint32_t epoch,
                                      int64_t wait_clocks, int64_t n_parts, int64_t rows, int dim, void* out_bf16,
                                      float* out_f32, float* lse, void* stream) {

@@ -503,6 +503,131 @@ __global__ void __launch_bounds__(kMergeWarps * 32) splitkv_row_exchange_kernel(
     if (tid == 0 && lse_out) lse_out[row] = lse;
 }
 
+// ---------------------------------------------------------------------------------------------
+// The same row exchange with the flag inside the data ("low-latency" words, as NCCL's LL protocol): every
+// element of a row travels as one 8-byte word {value bits, epoch}.  An aligned 8-byte store is a single
+// access, so a reader that sees the epoch in a word also sees the value that came with it: no system-scope
+// fence between data and flag, no flag store, and the reader needs no acquire - one NVLink round trip less
+// on the critical path of every step.  Slots are [rows][dim + 1] words; the two slot sets still alternate
+// with the epoch, and a stale word (epoch - 2 or older) simply does not match.
+struct LlExchange {
+    unsigned long long* words[kMaxPeers];   // on rank p: the [rows][dim + 1] words p keeps for this rank
+    const unsigned long long* local_words;  // this rank's words for all ranks: [world][rows][dim + 1]
+    int world;
+    uint32_t epoch;
+    long long max_clocks;
+    int* status;
+    int do_wait;
+};
+
+__device__ __forceinline__ void st_relaxed_sys_u64(unsigned long long* p, unsigned long long v) {
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long ld_relaxed_sys_u64(const unsigned long long* p) {
+    unsigned long long v;
+    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// Waits (bounded) until element tid of row `row` has arrived from every rank, then merges the rows by their
+// LSEs: o is the merged element tid (tid < dim), lse the merged LSE.  All threads of the CTA call it.
+__device__ __forceinline__ bool ll_wait_merge(const unsigned long long* local_words, int world, int64_t rows, int dim,
+                                              int64_t row, uint32_t epoch, long long max_clocks, int* status, float& o,
+                                              float& lse) {
+    __shared__ float s_lse[kMaxPeers];
+    __shared__ int s_fail;
+    const int tid = threadIdx.x;
+    if (tid == 0) s_fail = 0;
+    __syncthreads();
+    float v[kMaxPeers];
+#pragma unroll
+    for (int r = 0; r < kMaxPeers; ++r) v[r] = 0.f;
+    if (tid <= dim) {
+        const long long t0 = clock64();
+        bool alive = true;
+#pragma unroll
+        for (int r = 0; r < kMaxPeers; ++r) {
+            if (r >= world || !alive) continue;
+            const unsigned long long* p = local_words + ((int64_t)r * rows + row) * (dim + 1) + tid;
+            unsigned long long w = ld_relaxed_sys_u64(p);
+            while ((uint32_t)(w >> 32) != epoch) {
+                if (clock64() - t0 > max_clocks) {
+                    report_timeout(status, kToPeerFlag);
+                    s_fail = 1;
+                    alive = false;
+                    break;
+                }
+                w = ld_relaxed_sys_u64(p);
+            }
+            v[r] = __uint_as_float((uint32_t)w);
+            if (tid == dim) s_lse[r] = v[r];
+        }
+    }
+    __syncthreads();
+    if (s_fail) return false;
+    float m = -INFINITY;
+#pragma unroll
+    for (int r = 0; r < kMaxPeers; ++r)
+        if (r < world) m = fmaxf(m, s_lse[r]);
+    float l = 0.f, acc = 0.f;
+    if (m > -INFINITY) {
+#pragma unroll
+        for (int r = 0; r < kMaxPeers; ++r) {
+            if (r >= world) continue;
+            const float w = (s_lse[r] == -INFINITY) ? 0.f : expf(s_lse[r] - m);
+            l += w;
+            acc = fmaf(w, v[r], acc);
+        }
+    }
+    o = (l > 0.f) ? acc / l : 0.f;
+    lse = (l > 0.f) ? m + logf(l) : -INFINITY;
+    return true;
+}
+
+__global__ void __launch_bounds__(kMergeWarps * 32) splitkv_row_exchange_ll_kernel(
+    const float* __restrict__ o_parts, const float* __restrict__ lse_parts, int n_parts, int64_t rows, int dim,
+    int64_t in_row_stride, int64_t in_lse_stride, __nv_bfloat16* out_bf16, float* out_f32, float* lse_out,
+    LlExchange x) {
+    const int64_t row = blockIdx.x;
+    const int tid = threadIdx.x;
+    __shared__ float red[kMergeWarps];
+    __shared__ float s_ml[2];
+    extern __shared__ float merge_sm[];
+    asm volatile("griddepcontrol.wait;" ::: "memory");  // see splitkv_row_exchange_kernel
+    float lse;
+    const float o = merge_row(o_parts + row * in_row_stride, lse_parts + row * in_lse_stride, n_parts,
+                              rows * in_row_stride, rows * in_lse_stride, dim, merge_sm, red, s_ml, lse);
+    const int64_t rec = row * (dim + 1);
+    const unsigned long long tag = (unsigned long long)x.epoch << 32;
+    for (int r = 0; r < x.world; ++r) {
+        if (tid < dim) st_relaxed_sys_u64(x.words[r] + rec + tid, tag | __float_as_uint(o));
+        if (tid == 0) st_relaxed_sys_u64(x.words[r] + rec + dim, tag | __float_as_uint(lse));
+    }
+    if (!x.do_wait) return;
+    float o2, lse2;
+    if (!ll_wait_merge(x.local_words, x.world, rows, dim, row, x.epoch, x.max_clocks, x.status, o2, lse2)) return;
+    if (tid < dim) {
+        if (out_bf16) out_bf16[row * dim + tid] = __float2bfloat16(o2);
+        if (out_f32) out_f32[row * dim + tid] = o2;
+    }
+    if (tid == 0 && lse_out) lse_out[row] = lse2;
+}
+
+// Second half alone (after a delivery with do_wait = 0: several ranks emulated on one GPU).
+__global__ void __launch_bounds__(kMergeWarps * 32) splitkv_ll_merge_kernel(
+    const unsigned long long* __restrict__ local_words, int world, int64_t rows, int dim, uint32_t epoch,
+    long long max_clocks, int* status, __nv_bfloat16* out_bf16, float* out_f32, float* lse_out) {
+    const int64_t row = blockIdx.x;
+    const int tid = threadIdx.x;
+    float o, lse;
+    if (!ll_wait_merge(local_words, world, rows, dim, row, epoch, max_clocks, status, o, lse)) return;
+    if (tid < dim) {
+        if (out_bf16) out_bf16[row * dim + tid] = __float2bfloat16(o);
+        if (out_f32) out_f32[row * dim + tid] = o;
+    }
+    if (tid == 0 && lse_out) lse_out[row] = lse;
+}
+
 static size_t merge_smem_bytes(int64_t n_parts, int dim) {
     return sizeof(float) * ((size_t)kMergeWarps * dim + (size_t)n_parts);
 }
@@ -791,6 +916,48 @@ cudaError_t launch_row_exchange(const float* o_parts, const float* lse_parts, in
     }
     return cudaLaunchKernelEx(&cfg, splitkv_row_exchange_kernel, o_parts, lse_parts, (int)n_parts, rows, dim, in_row_stride,
                               in_lse_stride, (__nv_bfloat16*)out_bf16, out_f32, lse, x);
+}
+
+cudaError_t launch_row_exchange_ll(const float* o_parts, const float* lse_parts, int64_t n_parts, int64_t rows, int dim,
+                                   int64_t in_row_stride, int64_t in_lse_stride, void* out_bf16, float* out_f32,
+                                   float* lse, void* const* peer_words, const void* local_words, int world,
+                                   uint32_t epoch, long long wait_clocks, int do_wait, cudaStream_t stream) {
+    if (rows == 0) return cudaSuccess;
+    if (world <= 0 || world > kMaxPeers || dim + 1 > kMergeWarps * 32 || !merge_fits(n_parts, dim))
+        return cudaErrorInvalidValue;
+    LlExchange x;
+    for (int r = 0; r < kMaxPeers; ++r) x.words[r] = r < world ? static_cast<unsigned long long*>(peer_words[r]) : nullptr;
+    x.local_words = static_cast<const unsigned long long*>(local_words);
+    x.world = world;
+    x.epoch = epoch;
+    x.max_clocks = wait_clocks > 0 ? wait_clocks : (1ll << 31);
+    x.status = device_status_ptr();
+    x.do_wait = do_wait;
+    if (!x.status) return cudaErrorInvalidSymbol;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)rows);
+    cfg.blockDim = dim3(kMergeWarps * 32);
+    cfg.dynamicSmemBytes = merge_smem_bytes(n_parts, dim);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // as launch_row_exchange
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, splitkv_row_exchange_ll_kernel, o_parts, lse_parts, (int)n_parts, rows, dim,
+                              in_row_stride, in_lse_stride, (__nv_bfloat16*)out_bf16, out_f32, lse, x);
+}
+
+cudaError_t launch_ll_merge(const void* local_words, int world, int64_t rows, int dim, uint32_t epoch,
+                            long long wait_clocks, void* out_bf16, float* out_f32, float* lse, cudaStream_t stream) {
+    if (rows == 0) return cudaSuccess;
+    if (world <= 0 || world > kMaxPeers || dim + 1 > kMergeWarps * 32) return cudaErrorInvalidValue;
+    int* status = device_status_ptr();
+    if (!status) return cudaErrorInvalidSymbol;
+    splitkv_ll_merge_kernel<<<(unsigned)rows, kMergeWarps * 32, 0, stream>>>(
+        static_cast<const unsigned long long*>(local_words), world, rows, dim, epoch,
+        wait_clocks > 0 ? wait_clocks : (1ll << 31), status, (__nv_bfloat16*)out_bf16, out_f32, lse);
+    return cudaGetLastError();
 }
 
 // Copies this rank's packed (O | LSE) record into the slot every peer keeps for it and raises the

@@ -64,6 +64,13 @@ cudaError_t launch_row_exchange(const float* o_parts, const float* lse_parts, in
                                 void* const* peer_slots, void* const* peer_flags, const float* local_slots,
                                 const uint32_t* local_flags, int world, uint32_t epoch, long long wait_clocks,
                                 int do_wait, cudaStream_t stream);
+// The row exchange with the flag inside every 8-byte word (no fence, no flag store): see decode.cu.
+cudaError_t launch_row_exchange_ll(const float* o_parts, const float* lse_parts, int64_t n_parts, int64_t rows, int dim,
+                                   int64_t in_row_stride, int64_t in_lse_stride, void* out_bf16, float* out_f32,
+                                   float* lse, void* const* peer_words, const void* local_words, int world,
+                                   uint32_t epoch, long long wait_clocks, int do_wait, cudaStream_t stream);
+cudaError_t launch_ll_merge(const void* local_words, int world, int64_t rows, int dim, uint32_t epoch,
+                            long long wait_clocks, void* out_bf16, float* out_f32, float* lse, cudaStream_t stream);
 cudaError_t launch_push_records(const float* record, void* const* peer_slots, void* const* peer_flags, int world,
                                 int64_t record_floats, uint32_t epoch, cudaStream_t stream);
 cudaError_t launch_kv_append(void* k_cache, void* v_cache, const void* k_in, const void* v_in, int64_t batch,

@@ -99,6 +99,8 @@ class PeerRecordExchange:
         self._done = None  # device int32, zero between calls (used by decode_push)
         self.row_flags = None      # local int32 [2, world, rows]: one flag per (rank, row), for decode_exchange
         self.row_flag_ptrs = None  # base address of every rank's `row_flags'
+        self.ll_words = None       # local int64 [2, world, rows, dim + 1]: {f32 bits, epoch} words, for decode_exchange(ll=True)
+        self.ll_word_ptrs = None   # base address of every rank's `ll_words`
         if (rows * (dim + 1)) % 4:
             raise ValueError("rows * (dim + 1) must be a multiple of 4 (16-byte copies)")
 
@@ -123,9 +125,15 @@ class PeerRecordExchange:
         h_rows = symm.rendezvous(row_flags, group.group_name)
         torch.cuda.synchronize()
         dist.barrier(group)
+        ll_words = symm.empty((2, world, rows, dim + 1), dtype=torch.int64, device=device)
+        ll_words.zero_()
+        h_ll = symm.rendezvous(ll_words, group.group_name)
+        torch.cuda.synchronize()
+        dist.barrier(group)
         ex = cls(rank, world, rows, dim, records, flags, h_rec.buffer_ptrs, h_flag.buffer_ptrs)
         ex.row_flags, ex.row_flag_ptrs = row_flags, list(h_rows.buffer_ptrs)
-        ex._handles = (h_rec, h_flag, h_rows)  # keep the mappings alive
+        ex.ll_words, ex.ll_word_ptrs = ll_words, list(h_ll.buffer_ptrs)
+        ex._handles = (h_rec, h_flag, h_rows, h_ll)  # keep the mappings alive
         return ex
 
     @classmethod
@@ -137,8 +145,10 @@ class PeerRecordExchange:
         rowf = [torch.zeros((2, world, rows), dtype=torch.int32, device=device) for _ in range(world)]
         out = [cls(r, world, rows, dim, recs[r], flgs[r], [t.data_ptr() for t in recs], [t.data_ptr() for t in flgs])
                for r in range(world)]
+        llw = [torch.zeros((2, world, rows, dim + 1), dtype=torch.int64, device=device) for _ in range(world)]
         for r, ex in enumerate(out):
             ex.row_flags, ex.row_flag_ptrs = rowf[r], [t.data_ptr() for t in rowf]
+            ex.ll_words, ex.ll_word_ptrs = llw[r], [t.data_ptr() for t in llw]
         return out
 
     def next_epoch(self):
@@ -184,12 +194,16 @@ class PeerRecordExchange:
         return record
 
     def decode_exchange(self, q, k_cache, v_cache, kv_lens=None, kv_len=None, kv_begin: int = 0, kv_end: int = -1,
-                        scale=None, workspace=None, out_dtype=None, wait: bool = True, wait_clocks: int = 0):
+                        scale=None, workspace=None, out_dtype=None, wait: bool = True, wait_clocks: int = 0,
+                        ll: bool = False):
         """One exchange in two launches (``rt_gqa_decode_exchange_bf16``): the decode kernel over this rank's KV
         shard, then ONE kernel that merges its chunk partials row by row, delivers each row to every rank, waits
         for the same row from every rank and merges them.  Returns (out [rows, D], lse [rows]).  With
         ``wait=False`` the second kernel stops after the delivery and ``merge_rows()`` finishes the step (for
-        several ranks emulated on one GPU, where no kernel may wait for a later launch of the same GPU)."""
+        several ranks emulated on one GPU, where no kernel may wait for a later launch of the same GPU).
+        ``ll=True`` sends every element as an 8-byte {value, epoch} word (``rt_gqa_decode_exchange_ll_bf16``): no
+        fence and no flag store between data and flag, the reader spins on the words; ``merge_rows(ll=True)``
+        is its second half."""
         import ctypes
         import torch
         from . import _lib
@@ -210,6 +224,20 @@ class PeerRecordExchange:
         out_dtype = out_dtype or torch.bfloat16
         out = torch.empty((self.rows, self.dim), dtype=out_dtype, device=q.device)
         lse = torch.empty((self.rows,), dtype=torch.float32, device=q.device)
+        if ll:
+            word_off = (par * self.world + self.rank) * self.rows * (self.dim + 1) * 8
+            words = (ctypes.c_void_p * self.world)(*[p + word_off for p in self.ll_word_ptrs])
+            rc = _lib.lib().rt_gqa_decode_exchange_ll_bf16(
+                q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+                out.data_ptr() if out_dtype == torch.bfloat16 else None,
+                out.data_ptr() if out_dtype == torch.float32 else None, lse.data_ptr(), words,
+                self.ll_words[par].data_ptr(), self.records[par, self.rank].data_ptr(), self.world, self.rank, self.epoch,
+                wait_clocks, 1 if wait else 0, B, Hq, Hkv, D, max_seq,
+                kv_lens.data_ptr() if kv_lens is not None else None, 0 if kv_len is None else int(kv_len), kv_begin,
+                kv_end, -1.0 if scale is None else float(scale), workspace.data_ptr() if workspace is not None else None,
+                workspace.numel() if workspace is not None else 0, _stream_ptr())
+            _lib.check(rc, "rt_gqa_decode_exchange_ll_bf16")
+            return out, lse
         rc = _lib.lib().rt_gqa_decode_exchange_bf16(
             q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
             out.data_ptr() if out_dtype == torch.bfloat16 else None, out.data_ptr() if out_dtype == torch.float32 else None,
@@ -221,7 +249,7 @@ class PeerRecordExchange:
         _lib.check(rc, "rt_gqa_decode_exchange_bf16")
         return out, lse
 
-    def merge_rows(self, out_dtype=None, wait_clocks: int = 0):
+    def merge_rows(self, out_dtype=None, wait_clocks: int = 0, ll: bool = False):
         """Second half of ``decode_exchange(wait=False)``: waits per row for every rank's row, then merges."""
         import torch
         from . import _lib
@@ -230,6 +258,13 @@ class PeerRecordExchange:
         out_dtype = out_dtype or torch.bfloat16
         out = torch.empty((self.rows, self.dim), dtype=out_dtype, device=self.records.device)
         lse = torch.empty((self.rows,), dtype=torch.float32, device=self.records.device)
+        if ll:
+            rc = _lib.lib().rt_attn_merge_ll_rows(
+                self.ll_words[par].data_ptr(), self.epoch, wait_clocks, self.world, self.rows, self.dim,
+                out.data_ptr() if out_dtype == torch.bfloat16 else None,
+                out.data_ptr() if out_dtype == torch.float32 else None, lse.data_ptr(), _stream_ptr())
+            _lib.check(rc, "rt_attn_merge_ll_rows")
+            return out, lse
         rc = _lib.lib().rt_attn_merge_records_after_rows(
             self.records[par].data_ptr(), self.row_flags[par].data_ptr(), self.epoch, wait_clocks, self.world, self.rows,
             self.dim, out.data_ptr() if out_dtype == torch.bfloat16 else None,

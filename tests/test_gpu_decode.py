@@ -384,12 +384,15 @@ def test_decode_long_context_shard_at_full_size(oracle):
     assert _lib.device_status() == 0
 
 
+@pytest.mark.parametrize("ll", [False, True])
 @pytest.mark.parametrize("kv_total,S", [(2900, 3000), (40000, 40960), (100, 128)])
-def test_row_exchange_on_one_device(oracle, kv_total, S):
+def test_row_exchange_on_one_device(oracle, kv_total, S, ll):
     """rt_gqa_decode_exchange_bf16 with the ranks emulated on one device: every rank's exchange kernel merges its
     chunk partials row by row and delivers the rows (wait = 0), then rt_attn_merge_records_after_rows waits per
     row and merges.  Every rank must end with the merge of the ranks' records (many chunks, few chunks, and a
-    single chunk whose record comes straight from the decode kernel), two epochs so both slot sets are used."""
+    single chunk whose record comes straight from the decode kernel), three epochs so both slot sets are used
+    and one is used again.  ll: the same through rt_gqa_decode_exchange_ll_bf16 / rt_attn_merge_ll_rows, where
+    every element travels as an 8-byte {value, epoch} word and the reader spins on the words."""
     import torch
     import rustorch_b200 as rt
     from rustorch_b200 import _lib, sharding
@@ -398,20 +401,25 @@ def test_row_exchange_on_one_device(oracle, kv_total, S):
     k = torch.randn((B, Hkv, S, D), device="cuda", generator=g).to(torch.bfloat16)
     v = torch.randn((B, Hkv, S, D), device="cuda", generator=g).to(torch.bfloat16)
     ranks = sharding.PeerRecordExchange.local_pair(world, B * Hq, D)
-    for step in range(2):
+    for step in range(3):
         q = torch.randn((B, Hq, D), device="cuda", generator=g).to(torch.bfloat16)
         recs = []
         for r, ex in enumerate(ranks):
             b0, b1 = sharding.kv_shard(kv_total, world, r, align=16)
             recs.append(rt.gqa_decode_record(q, k, v, kv_len=kv_total, kv_begin=b0, kv_end=b1))
-            ex.decode_exchange(q, k, v, kv_len=kv_total, kv_begin=b0, kv_end=b1, wait=False)
+            ex.decode_exchange(q, k, v, kv_len=kv_total, kv_begin=b0, kv_end=b1, wait=False, ll=ll)
         want, want_lse = rt.merge_records(torch.stack(recs), out_dtype=torch.float32)
         for ex in ranks:
-            out, lse = ex.merge_rows(out_dtype=torch.float32)
+            out, lse = ex.merge_rows(out_dtype=torch.float32, ll=ll)
             assert (out - want).abs().max().item() < 1e-5 and (lse - want_lse).abs().max().item() < 1e-5
-            # the slots hold exactly the records the ranks produced
             par = ex.epoch & 1
-            assert (ex.records[par] - torch.stack(recs)).abs().max().item() < 1e-5
+            if ll:  # every word carries the epoch in its upper half and the record's bits in the lower
+                words = ex.ll_words[par]
+                assert bool(((words >> 32) == ex.epoch).all())
+                vals = (words & 0xFFFFFFFF).to(torch.int32).view(torch.float32)
+                assert (vals - torch.stack(recs)).abs().max().item() < 1e-5
+            else:   # the slots hold exactly the records the ranks produced
+                assert (ex.records[par] - torch.stack(recs)).abs().max().item() < 1e-5
         torch.cuda.synchronize()
         assert _lib.device_status() == 0
     full, full_lse = rt.gqa_decode(q, k, v, kv_len=kv_total, out_dtype=torch.float32)
@@ -422,14 +430,15 @@ def test_row_exchange_on_one_device(oracle, kv_total, S):
         util.check_lse(util.to_np(want_lse).reshape(B, Hq), ref_lse)
 
 
-def test_row_exchange_wait_runs_out_and_reports():
+@pytest.mark.parametrize("ll", [False, True])
+def test_row_exchange_wait_runs_out_and_reports(ll):
     """A row that never arrives: the per-row wait (here ~10 ms) expires, nothing is written, status 401."""
     import torch
     from rustorch_b200 import _lib, sharding
     ranks = sharding.PeerRecordExchange.local_pair(2, 32, 128)
     for ex in ranks:
         ex.epoch = 1  # nobody delivered anything for epoch 1
-    out, lse = ranks[0].merge_rows(out_dtype=torch.float32, wait_clocks=20_000_000)
+    out, lse = ranks[0].merge_rows(out_dtype=torch.float32, wait_clocks=20_000_000, ll=ll)
     torch.cuda.synchronize()
     assert _lib.device_status() == 401
     assert _lib.device_status() == 0

@@ -56,6 +56,11 @@ def _worker(rank, world, port, tmpdir):
             torch.cuda.synchronize()
             assert _lib.device_status() == 0
             assert (got3 - want).abs().max().item() < 1e-5 and (got3_lse - want_lse).abs().max().item() < 1e-5
+            # and the same tail with the flag inside every 8-byte word (no fence, no flag store)
+            got4, got4_lse = ex.decode_exchange(q, k, v, kv_len=T, kv_begin=lo, kv_end=hi, out_dtype=torch.float32, ll=True)
+            torch.cuda.synchronize()
+            assert _lib.device_status() == 0
+            assert (got4 - want).abs().max().item() < 1e-5 and (got4_lse - want_lse).abs().max().item() < 1e-5
             assert (got - full.reshape(Hq, D)).abs().max().item() < 1e-3
             assert (got_lse - full_lse.reshape(Hq)).abs().max().item() < 1e-4
         dist.barrier()
