@@ -799,7 +799,7 @@ def main():
 
         # The same exchange over peer memory: the record is decoded straight into this rank's slot, pushed
         # to every peer with NVLink stores + a flag, and the merge kernel waits (bounded) for all flags.
-        exchange, exchange_note = None, ("peer stores over NVLink (symmetric memory) + flags, the merge waits in-kernel; "
+        exchange, exchange_note = None, ("peer stores over NVLink (symmetric memory), flags or flag-in-word rows, the merge waits in-kernel; "
                                          "value = the fastest of the forms timed below")
         try:
             exchange = sharding.PeerRecordExchange.create(Hq, Dd)
