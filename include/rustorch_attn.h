@@ -427,6 +427,7 @@ int rt_attn_merge_records_after_rows(const float* records, const uint32_t* row_f
  *   scratch_record : [rows, D+1] f32 of local memory (the decode writes the record here when the shard is one chunk)
  *   epoch          : >= 1, increasing by one per exchange; two word sets are used alternately by the caller
  *   do_wait = 0    : stop after the delivery; rt_attn_merge_ll_rows finishes the step (several ranks on ONE GPU)
+ * head_dim 64 or 128 (one thread per word of a row: D + 1 <= 256; 256 returns RT_ERR_UNSUPPORTED before any launch).
  */
 int rt_gqa_decode_exchange_ll_bf16(const void* q, const void* k_cache, const void* v_cache, void* out_bf16,
                                    float* out_f32, float* lse, void* const* peer_words,

@@ -742,6 +742,7 @@ int rt_gqa_decode_exchange_ll_bf16(const void* q, const void* k_cache, const voi
     if (world <= 0 || rank < 0 || rank >= world) return RT_ERR_BAD_LENGTH;
     if (world > rt::kMaxPeers) return RT_ERR_UNSUPPORTED;
     if (epoch == 0) return RT_ERR_BAD_LENGTH;  // zeroed words carry epoch 0
+    if (head_dim > 255) return RT_ERR_UNSUPPORTED;  // one thread per word of a row (D + 1 <= 256); checked before any launch
     if (!peer_words || !local_words || !scratch_record) return RT_ERR_NULL_POINTER;
     for (int r = 0; r < world; ++r) {
         if (!peer_words[r]) return RT_ERR_NULL_POINTER;
