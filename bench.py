@@ -963,6 +963,39 @@ def main():
                     row["reference_cuda_us"] = None if rus is None else rus * 1e3
                     row["reference_cuda_max_abs_diff"] = float((ro.float() - od1[0].float()).abs().max().item())
                 rows.append(row)
+        # One layer's attention step of the reference's decode loop (cuda_backend.rs:917-987): rope on q and on the new
+        # K row, append of K and V, attention.  Four launches there, two here (rope + append fused; the decode is
+        # scheduled while the append still runs and waits for it on the device).
+        hq, hkv, dd, kv = 32, 8, 128, 4096
+        qd1 = torch.randn((1, hq, dd), device="cuda", generator=g).to(torch.bfloat16)
+        kc1 = torch.randn((1, hkv, 8192, dd), device="cuda", generator=g).to(torch.bfloat16)
+        vc1 = torch.randn((1, hkv, 8192, dd), device="cuda", generator=g).to(torch.bfloat16)
+        kn1 = torch.randn((1, hkv, dd), device="cuda", generator=g).to(torch.bfloat16)
+        vn1 = torch.randn((1, hkv, dd), device="cuda", generator=g).to(torch.bfloat16)
+        od1 = torch.empty_like(qd1)
+        inv = rt.rope_inv_freq(dd, 10000.0)
+
+        def layer_step():
+            rt.rope_kv_append(qd1, kn1, vn1, kc1, vc1, inv, pos=kv - 1, style="adjacent")
+            rt.gqa_decode(qd1, kc1, vc1, kv_len=kv, out=od1, return_lse=False)
+
+        row = {"shape": f"decode step of one layer (rope q, rope k, append, attention) Hq{hq} Hkv{hkv} D{dd} kv{kv} batch 1",
+               "ref_hw": "not published", "us": timed(layer_step, 50, 5, dist, torch) * 1e3, "launches": 2}
+        gl = graph_ms(layer_step)
+        row["graph_us"] = None if gl is None else gl * 1e3
+        if ref_cuda is not None:
+            ro = torch.empty_like(qd1[0])
+
+            def ref_layer_step():
+                ref_cuda.rope_half_split_bf16(qd1[0], inv, kv - 1)
+                ref_cuda.rope_half_split_bf16(kn1[0], inv, kv - 1)
+                ref_cuda.kv_append_bf16(kc1[0], vc1[0], kn1[0], vn1[0], kv - 1)
+                ref_cuda.gqa_decode_online_bf16(qd1[0], kc1[0], vc1[0], kv, out=ro)
+
+            rus = graph_ms(ref_layer_step, iters=10)
+            row["reference_cuda_us"] = None if rus is None else rus * 1e3
+            row["reference_launches"] = 4
+        rows.append(row)
         published = {"rows": rows, "note": "ms/us = one call per step from Python (includes the ctypes enqueue); graph_* = "
                                            "the same call replayed from a CUDA graph; reference_cuda_us = the reference's "
                                            "own gqa_decode_online_bf16 CUDA kernel (llm_kernels.rs:376-458) on this GPU, "

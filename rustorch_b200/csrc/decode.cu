@@ -420,6 +420,8 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_partials_kernel(const 
         // its writes are visible (at once under a normal launch).
         asm volatile("griddepcontrol.wait;" ::: "memory");
     }
+    // what follows in the stream (the next step's decode) may be scheduled; it waits before it reads anything
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (wait.flags) {
         // Part r of this merge is written into local memory by rank r (on that GPU), which then raises
         // flags[r] (or, with per-row flags, flags[r * rows + row]) to the epoch with a system-scope release.
@@ -646,6 +648,8 @@ bool merge_fits(int64_t n_parts, int dim) {
 __global__ void kv_append_kernel(__nv_bfloat16* k_cache, __nv_bfloat16* v_cache,
                                  const __nv_bfloat16* k_in, const __nv_bfloat16* v_in, int n_kv,
                                  int head_dim, int64_t max_seq, int64_t pos, const int32_t* positions) {
+    // the decode that follows may be scheduled at once; it waits for this kernel's completion before it reads
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int kvh = blockIdx.x, b = blockIdx.y;
     const int64_t at = positions ? (int64_t)positions[b] : pos;
     if (at < 0 || at >= max_seq) return;
@@ -668,6 +672,8 @@ __global__ void rope_kv_append_kernel(__nv_bfloat16* q, const __nv_bfloat16* k_i
                                       __nv_bfloat16* k_cache, __nv_bfloat16* v_cache, const float* inv_freq,
                                       const int32_t* positions, int64_t pos_uniform, int n_heads, int n_kv,
                                       int head_dim, int64_t max_seq, int style) {
+    // the decode that follows may be scheduled at once; it waits for this kernel's completion before it reads
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int b = blockIdx.y, hrow = blockIdx.x, half = head_dim / 2;
     const int64_t pos = positions ? (int64_t)positions[b] : pos_uniform;
     if (pos < 0 || pos >= max_seq) return;

@@ -258,6 +258,12 @@ gqa_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
     const int64_t row0 = (int64_t)b * p.n_heads + (int64_t)kvh * G;
     const bool direct = (p.n_chunks == 1);
 
+    // Launched with programmatic stream serialisation, the CTA may be resident before the kernel ahead of it in
+    // the stream has finished (the append of this token's K and V rows, the previous step's merge): this
+    // returns once that kernel has completed and its writes are visible (at once under a normal launch).
+    // Nothing is read from global memory before it.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+
     int64_t len = p.kv_lens ? (int64_t)p.kv_lens[b] : p.kv_len_uniform;
     if (len > p.max_seq) len = p.max_seq;
     const int64_t hi = (p.kv_end >= 0 && p.kv_end < len) ? p.kv_end : len;
@@ -505,9 +511,24 @@ static cudaError_t launch_dg(const CUtensorMap& mk, const CUtensorMap& mv, const
     auto kern = gqa_decode_tc_kernel<D, G>;
     cudaError_t e = set_max_dynamic_smem_once<gqa_decode_tc_kernel<D, G>>(DecodeTcCfg<D>::SMEM_BYTES);
     if (e != cudaSuccess) return e;
-    dim3 grid(p.n_chunks, p.n_kv, (unsigned)batch);
-    kern<<<grid, 128, DecodeTcCfg<D>::SMEM_BYTES, stream>>>(mk, mv, p);
-    return cudaGetLastError();
+    // RT_ATTN_DECODE_PDL=0 launches without programmatic stream serialisation.
+    static const bool pdl = [] {
+        const char* e = getenv("RT_ATTN_DECODE_PDL");
+        return !(e && e[0] == '0');
+    }();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(p.n_chunks, p.n_kv, (unsigned)batch);
+    cfg.blockDim = dim3(128);
+    cfg.dynamicSmemBytes = DecodeTcCfg<D>::SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    if (pdl) {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+    }
+    return cudaLaunchKernelEx(&cfg, kern, mk, mv, p);
 }
 
 template <int D>

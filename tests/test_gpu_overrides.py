@@ -9,6 +9,7 @@ set.  What runs under each override:
   RT_ATTN_DECODE_PUSH_IN_KERNEL=1    record delivery from inside the decode kernel       (csrc/decode_tc.cu)
   RT_ATTN_EXCHANGE_PDL=0             the row-exchange kernel under a plain launch        (csrc/decode.cu)
   RT_ATTN_MERGE_PDL=0                the chunk-merge kernel under a plain launch         (csrc/decode.cu)
+  RT_ATTN_DECODE_PDL=0               the decode kernel under a plain launch              (csrc/decode_tc.cu)
   RT_ATTN_BACKWARD_IMPL=mma_sync     the mma.sync backward kernel                        (csrc/backward_tc.cu)
   RT_ATTN_PREFILL_F32_IMPL=rows      the warp-per-row exact f32 forward                  (csrc/prefill_simt.cu)
 """
@@ -40,6 +41,7 @@ def run_tests_with(var, value, target, select=None, timeout=900):
     ("RT_ATTN_DECODE_PUSH_IN_KERNEL", "1", "test_gpu_decode.py", "exchange or push or peer or record"),
     ("RT_ATTN_EXCHANGE_PDL", "0", "test_gpu_decode.py", "exchange"),
     ("RT_ATTN_MERGE_PDL", "0", "test_gpu_decode.py", None),
+    ("RT_ATTN_DECODE_PDL", "0", "test_gpu_decode.py", None),
     ("RT_ATTN_BACKWARD_IMPL", "mma_sync", "test_gpu_backward.py", None),
     ("RT_ATTN_PREFILL_F32_IMPL", "rows", "test_gpu_prefill_f32.py", None),
 ])
