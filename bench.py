@@ -874,15 +874,26 @@ def main():
                 "row exchange and NCCL exchange disagree"
             sms_rows = timed(step_splitkv_rows, args.steps, args.warmup, dist, torch)
             # the two best forms again with the steps replayed from one CUDA graph per rank (no host in the loop)
-            sms_rows_graph = timed_graph(step_splitkv_rows, args.steps, args.warmup, dist, torch)
-            sms_copy_graph = timed_graph(step_splitkv_p2p, args.steps, args.warmup, dist, torch)
+            def graph_or_none(step):
+                # a refused capture must not cost the line: the step-by-step timing of the same form stands.  Every
+                # rank takes the same branch (the capture fails on all or none: same code, same library).
+                try:
+                    return timed_graph(step, args.steps, args.warmup, dist, torch)
+                except Exception as exc:
+                    sys.stderr.write(f"[bench] graph replay of {step.__name__} not timed: {type(exc).__name__}: {exc}\n")
+                    torch.cuda.synchronize()
+                    return None
+
+            sms_rows_graph = graph_or_none(step_splitkv_rows)
+            sms_copy_graph = graph_or_none(step_splitkv_p2p)
             ee = step_splitkv_ll()
             torch.cuda.synchronize()
             assert (a[0].float() - ee[0].float()).abs().max().item() <= 2e-2 and (a[1] - ee[1]).abs().max().item() <= 1e-5, \
                 "word exchange and NCCL exchange disagree"
             sms_ll = timed(step_splitkv_ll, args.steps, args.warmup, dist, torch)
-            sms_ll_graph = timed_graph(step_splitkv_ll, args.steps, args.warmup, dist, torch)
-            sms = min(sms_copy, sms_fused, sms_rows, sms_rows_graph, sms_copy_graph, sms_ll, sms_ll_graph)
+            sms_ll_graph = graph_or_none(step_splitkv_ll)
+            sms = min(x for x in (sms_copy, sms_fused, sms_rows, sms_rows_graph, sms_copy_graph, sms_ll, sms_ll_graph)
+                      if x is not None)
             assert _lib.device_status() == 0, "a bounded wait of the peer exchange expired"
         total_bytes = shard_bytes * world
         splitkv = {"metric": "kv_read_gbs", "value": total_bytes / (sms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": sms,
