@@ -170,3 +170,32 @@ def test_random_shapes_property_replay_on_gpu(oracle):
         _, ref = oracle.naive_forward_masked(q, k, v, mask_kind=kind, keep=keep)
         assert np.abs(out - ref).max() < 1e-3, (shape, kind)
         assert np.all(np.isfinite(out))
+
+
+@pytest.mark.parametrize("precision,kind", [("f32", 1), ("bf16", 1), ("f32", 2)])
+def test_flash_forward_host_entry_on_a_chunked_shape(oracle, precision, kind):
+    """A call large enough (50 MB of upload) to be cut into (batch element, head range) chunks with a halving
+    tail and pipelined over three streams: causal in both precisions and a padding mask in f32, three heads
+    (first, one at a chunk boundary, last) against the oracle."""
+    import rustorch_b200 as rt
+    shape = (2, 16, 1024, 128)
+    n = int(np.prod(shape))
+    q, k, v = (oracle.fill_normal(shape, 700 + j).astype(np.float32) for j in range(3))
+    keep = None
+    if kind == 2:
+        keep = (np.random.default_rng(9).random(shape[2]) > 0.3)
+        keep[5] = True
+    mask = rt.Mask.causal() if kind == 1 else rt.Mask.padding(keep)
+    out = np.zeros(shape, dtype=np.float32)
+    rt.flash_forward_masked(rt.AttentionShape.new(*shape), q.reshape(-1), k.reshape(-1), v.reshape(-1), mask,
+                            out.reshape(-1), precision=precision)
+    for b, h in ((0, 0), (1, 8), (1, 15)):
+        qs, ks, vs = (t[b:b + 1, h:h + 1] for t in (q, k, v))
+        if precision == "bf16":  # the entry rounds its inputs to bf16; the oracle gets the same rounded inputs
+            qs, ks, vs = (oracle.round_to_bf16(t) for t in (qs, ks, vs))
+        _, ref, _ = oracle.flash_forward_ext(qs, ks, vs, causal=(kind == 1), keep=keep.astype(np.uint8) if keep is not None else None)
+        got = out[b:b + 1, h:h + 1]
+        if precision == "f32":
+            assert np.abs(got - ref).max() < 1e-4, (b, h)
+        else:
+            util.check_output(got, ref, label=f"chunked host entry b{b} h{h}")

@@ -258,14 +258,16 @@ def test_prefill_f32_chunk_against_cache(oracle):
     util.check_lse(util.to_np(lse), ref_lse)
 
 
-@pytest.mark.parametrize("B,H", [(3, 5), (1, 7), (40, 1)])
-def test_prefill_bf16_host_entry_matches_device_entry(oracle, B, H):
-    """rt_attn_prefill_bf16_host (pinned host buffers, chunks pipelined over three streams) returns exactly
-    what the device entry returns, for chunkings that split heads unevenly and for the unpipelined path."""
+@pytest.mark.parametrize("B,H,N,D", [(3, 5, 300, 64), (1, 7, 300, 64), (40, 1, 300, 64),
+                                     (2, 16, 2048, 128), (1, 23, 2048, 128), (3, 10, 2048, 128)])
+def test_prefill_bf16_host_entry_matches_device_entry(oracle, B, H, N, D):
+    """rt_attn_prefill_bf16_host (pinned host buffers, three streams) against the device entry.  The small calls
+    run as one chunk and must match bit for bit; the large ones (more than 32 MB of upload) are cut into (batch
+    element, head range) chunks — even head ranges, uneven ones, and a halving tail — whose launches may take the
+    small-launch schedule with another summation order, so they match to one bf16 ulp and 1e-4 in the LSE."""
     import torch
     import rustorch_b200 as rt
     from rustorch_b200 import _lib
-    N, D = 300, 64
     g = torch.Generator().manual_seed(5)
     hq, hk, hv = (torch.randn((B, H, N, D), generator=g).to(torch.bfloat16).pin_memory() for _ in range(3))
     lens = torch.randint(1, N + 1, (B,), generator=g, dtype=torch.int32)
@@ -276,7 +278,18 @@ def test_prefill_bf16_host_entry_matches_device_entry(oracle, B, H):
     assert rc == 0
     out, lse = rt.prefill_bf16(hq.cuda(), hk.cuda(), hv.cuda(), causal=True, kv_lens=lens.cuda())
     torch.cuda.synchronize()
-    assert torch.equal(ho, out.cpu()) and torch.equal(hl, lse.cpu())
+    if 3 * hq.numel() * 2 < (32 << 20):
+        assert torch.equal(ho, out.cpu()) and torch.equal(hl, lse.cpu())
+    else:
+        a, b = ho.float(), out.cpu().float()
+        assert float(((a - b).abs() / b.abs().clamp(min=1.0)).max()) <= 2.0 ** -7
+        assert float((hl - lse.cpu()).abs().max()) <= 1e-4
+        # and one chunk-boundary head against the oracle
+        h = H // 2
+        _, ref, ref_lse = oracle.flash_forward_ext(util.to_np(hq[:1, h:h + 1]), util.to_np(hk[:1, h:h + 1]),
+                                                   util.to_np(hv[:1, h:h + 1]), causal=True, kv_lens=lens[:1].numpy())
+        util.check_output(util.to_np(ho[:1, h:h + 1]), ref, label=f"host entry B{B} H{H}")
+        util.check_lse(util.to_np(hl[:1, h:h + 1]), ref_lse)
     _clean_status()
 
 
