@@ -259,11 +259,12 @@ def test_prefill_f32_chunk_against_cache(oracle):
 
 
 @pytest.mark.parametrize("B,H,N,D", [(3, 5, 300, 64), (1, 7, 300, 64), (40, 1, 300, 64),
-                                     (2, 16, 2048, 128), (1, 23, 2048, 128), (3, 10, 2048, 128)])
+                                     (2, 16, 2048, 128), (1, 23, 2048, 128), (3, 10, 2048, 128), (40, 1, 2048, 128)])
 def test_prefill_bf16_host_entry_matches_device_entry(oracle, B, H, N, D):
     """rt_attn_prefill_bf16_host (pinned host buffers, three streams) against the device entry.  The small calls
     run as one chunk and must match bit for bit; the large ones (more than 32 MB of upload) are cut into (batch
-    element, head range) chunks — even head ranges, uneven ones, and a halving tail — whose launches may take the
+    element, head range) chunks — even head ranges, uneven ones, a halving tail, and a batch too large to chunk by
+    element, which runs unpipelined — whose launches may take the
     small-launch schedule with another summation order, so they match to one bf16 ulp and 1e-4 in the LSE."""
     import torch
     import rustorch_b200 as rt
