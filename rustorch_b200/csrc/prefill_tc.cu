@@ -134,8 +134,9 @@ struct TcItem {
 // 256-row blocks than 3/4 of the SMs uses 128-row items instead (single_tile): twice the CTAs, and inside
 // a CTA the item's 64-key steps alternate between the two tiles (tile 0 takes the even steps = the first
 // half of every 128-key K/V tile, tile 1 the odd ones), each with its own running max, sum and accumulator;
-// the epilogue merges the two partial results straight out of TMEM.  Both softmax warpgroups and both MMA
-// issuers then work on the one block, which nearly halves the critical path of a small problem.
+// the epilogue merges the two partial results straight out of TMEM and stores the rows directly (no staged
+// tile: such a CTA has no further item).  Both softmax warpgroups and both MMA issuers then work on the one
+// block, which nearly halves the critical path of a small problem.
 // Sorted mode (per-batch kv_lens, where an item's cost is only known on the device): every CTA ranks the
 // (batch, query block) pairs by their step count at start-up (the same deterministic sort in every CTA, so
 // no queue, no atomics and no scratch memory are needed), the item list is that order with all heads of a
@@ -283,7 +284,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             uint32_t count = 1;
             if (bar >= p_full && bar < p_full + 4) count = 128;
             else if (bar >= o_free && bar < o_free + 2) count = 128;
-            else if (bar >= stage_full && bar < stage_full + 2) count = kSingle ? 256 : 128;  // both warpgroups stage a single-tile item's rows
+            else if (bar >= stage_full && bar < stage_full + 2) count = 128;
             else if (bar == done_bar) count = 2;
             else if (bar == merge_bar) count = 256;
             mbar_init(bar, count);
@@ -784,7 +785,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 const float inv = valid ? 1.f / l_all : 0.f;
                 const float a_own = f_own * inv, a_oth = f_oth * inv;
                 const bool has_own = n_iter > 0, has_oth = it.steps(1 - w) > 0;  // an idle tile's accumulator was never written
-                uint8_t* stage = sQ + TILE + row_in_tile * 128;  // tile 1's Q buffer: every score MMA of the item has retired
+                // The merged half rows go straight to global memory (64 or 128 contiguous bytes per thread): the CTA
+                // has no further item, and a staged tile, its barrier and a TMA store would only lengthen the
+                // tail of a launch whose time is its longest CTA.
+                __nv_bfloat16* dst = p.out + it.b * p.o_stride_b + it.h * p.o_stride_h + (int64_t)row * p.o_stride_row;
 #pragma unroll
                 for (int cq = 0; cq < D / 64; ++cq) {
                     const int ch = w * (D / 64) + cq;
@@ -805,15 +809,12 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                                              (has_oth ? __uint_as_float(ob[e + 1]) * a_oth : 0.f);
                             pw[i] = valid ? float2_to_bf16x2(x0, x1) : 0x7fc07fc0u;
                         }
-                        const int cc = ch * 4 + v4;
-                        *reinterpret_cast<uint4*>(stage + (cc / 8) * SUB + (((cc % 8) ^ (row_in_tile & 7)) << 4)) = pack;
+                        if (row < N) *reinterpret_cast<uint4*>(dst + ch * 32 + v4 * 8) = pack;
                     }
                 }
                 if (w == 1 && p.lse && row < N)
                     p.lse[(int64_t)bh * N + row] =
                         valid ? (m_all * c + fast_log2(l_all)) * kLn2 : (seen_any ? NAN : -INFINITY);
-                fence_proxy_async();
-                mbar_arrive(&stage_full[1]);
             } else {
                 // A masked score costs the polynomial path 2^-125 instead of 0, so a row counts as
                 // empty when it never saw a visible score, not when its sum is exactly 0.
@@ -849,7 +850,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 fence_proxy_async();  // generic-proxy writes above -> visible to the TMA (async proxy) read
                 mbar_arrive(&stage_full[w]);
             }
-            if (row_in_tile == 0 && !(il && w == 0)) {
+            if (row_in_tile == 0 && !il) {
                 if (!mbar_wait(&stage_full[w], (uint32_t)na & 1u, p.status, kToStage)) {
                     ok = false;
                 } else {
