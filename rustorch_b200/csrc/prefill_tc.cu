@@ -78,6 +78,7 @@ struct TcParams {
     int slots_per_head, n_slots, paired;  // static schedule, see tc_item
     int sorted;        // length-sorted schedule (launches with per-batch kv_lens), see tc_item
     int stagger_clocks;  // single-tile items: head start of tile 0 over tile 1, in SM clocks
+    int direct_out;    // one item per CTA: the epilogue stores its rows straight from registers (no staged tile, no TMA store)
     int single_tile;   // items are 128-row blocks whose 64-key steps alternate between the two tiles (small launches, see tc_item)
 };
 
@@ -821,6 +822,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 const bool valid = seen && (l > 0.f);
                 const float inv = valid ? 1.f / l : 0.f;
                 uint8_t* stage = sQ + w * TILE + row_in_tile * 128;  // every score MMA that read Q_w has retired
+                __nv_bfloat16* dst = p.out + it.b * p.o_stride_b + it.h * p.o_stride_h + (int64_t)row * p.o_stride_row;
 #pragma unroll
                 for (int ch = 0; ch < D / 32; ++ch) {
                     uint32_t o[32];
@@ -841,16 +843,22 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                             pw[i] = valid ? float2_to_bf16x2(a, bb) : 0x7fc07fc0u;
                         }
                         const int cc = ch * 4 + v4;  // 16-byte chunk of the row: sub-tile cc/8, chunk cc%8
-                        *reinterpret_cast<uint4*>(stage + (cc / 8) * SUB + (((cc % 8) ^ (row_in_tile & 7)) << 4)) = pack;
+                        if (p.direct_out) {  // the CTA's only item: no overlap to win, the staged store would just add to the tail
+                            if (row < N) *reinterpret_cast<uint4*>(dst + cc * 8) = pack;
+                        } else {
+                            *reinterpret_cast<uint4*>(stage + (cc / 8) * SUB + (((cc % 8) ^ (row_in_tile & 7)) << 4)) = pack;
+                        }
                     }
                 }
                 if (p.lse && row < N)
                     p.lse[(int64_t)bh * N + row] =
                         valid ? (m_ref * c + fast_log2(l)) * kLn2 : (seen ? NAN : -INFINITY);
-                fence_proxy_async();  // generic-proxy writes above -> visible to the TMA (async proxy) read
-                mbar_arrive(&stage_full[w]);
+                if (!p.direct_out) {
+                    fence_proxy_async();  // generic-proxy writes above -> visible to the TMA (async proxy) read
+                    mbar_arrive(&stage_full[w]);
+                }
             }
-            if (row_in_tile == 0 && !il) {
+            if (row_in_tile == 0 && !il && !p.direct_out) {
                 if (!mbar_wait(&stage_full[w], (uint32_t)na & 1u, p.status, kToStage)) {
                     ok = false;
                 } else {
@@ -1083,6 +1091,7 @@ cudaError_t launch_prefill_tc(const void* q, const void* k, const void* v, void*
     p.slots_per_head = p.paired ? (int)((n_qb + 1) / 2) : (int)n_qb;
     p.n_slots = (int)(bh * p.slots_per_head);
     const int64_t n_ctas = (persistent && p.n_slots > n_sm) ? n_sm : p.n_slots;
+    p.direct_out = (n_ctas == p.n_slots && !p.paired && !p.sorted) ? 1 : 0;  // every CTA has exactly one item
     const bool keep = key_keep != nullptr;
 #define RT_TC_DISPATCH(DD)                                                                         \
     if (causal) {                                                                                  \
