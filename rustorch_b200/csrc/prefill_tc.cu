@@ -1064,7 +1064,14 @@ cudaError_t launch_prefill_tc(const void* q, const void* k, const void* v, void*
         const char* s = getenv("RT_ATTN_PREFILL_SCHED");
         return (s && !strcmp(s, "persistent")) ? 1 : (s && !strcmp(s, "percta")) ? 2 : 0;
     }();
-    p.single_tile = (seq > 128 && bh * ((seq + 255) / 256) * 4 < 3 * (int64_t)n_sm) ? 1 : 0;
+    // 128-row items (key split inside the CTA) for launches of fewer 256-row blocks than 3/4 of the SMs, and for
+    // long sequences up to the point where the persistent schedule takes over: with 64 and more key steps per
+    // block the finer items pack the causal imbalance better than they lose per step (measured on B=1 H=8 / 16,
+    // N=4096, D=128: 58.6 / 93.7 us against 62.4 / 98.4; at N=2048 the two are level or 256-row items win).
+    const int64_t n_blocks256 = bh * ((seq + 255) / 256);
+    p.single_tile = (seq > 128 && (n_blocks256 * 4 < 3 * (int64_t)n_sm ||
+                                   (n_blocks256 < 2 * (int64_t)n_sm && seq_kv >= 4096 && causal && kv_lens == nullptr)))
+                        ? 1 : 0;
     static const int env_stagger = [] {
         const char* s = getenv("RT_ATTN_PREFILL_STAGGER");
         return s ? atoi(s) : 900;
